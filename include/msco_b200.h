@@ -1,0 +1,180 @@
+/*
+ * msco_b200.h -- C ABI of libmsco_b200.so: the B200 (sm_100a) kernels behind
+ * the `reshape_and_cache` and `paged_attention` operators.
+ *
+ * This is the boundary the reference crosses when its operator glue calls the
+ * closed kernel library (`internal_v2::InternalOp`): create an op, hand it a
+ * host-side parameter block (which for paged attention includes the host copy
+ * of `context_lens`), ask for the workspace size, then launch on the caller's
+ * stream with raw device addresses.  Reference call sites replaced:
+ *   ops/c_api/reshape_and_cache/reshape_and_cache.cc:48-60      (CreateAsdReshapeAndCacheOp)
+ *   ops/c_api/paged_attention/paged_attention_graph.cc:718-806  (CreateCustomPagedAttentionOp + param fill)
+ *   ops/c_api/paged_attention/paged_attention_graph.cc:808-856  (UpdateParam on new lengths, tiling key)
+ *   ops/framework/ms_kernels_internal/graphmode/internal_kernel_mod.cc:158-203,341-365
+ *   ops/framework/ms_kernels_internal/pyboost/internal_pyboost_runner.cc:93-141,210-231
+ *                                                               (tiling, workspace, InternalOp::Launch)
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every `void *stream` is a cudaStream_t;
+ *   - all tensors are contiguous, row-major, in the layouts documented below;
+ *   - every function returns an MSCO_* code; msco_last_error() gives the
+ *     message of the last failure on the calling thread;
+ *   - launches are asynchronous on `stream`; nothing here synchronises;
+ *   - no entry point below allocates device memory: caches, outputs and the
+ *     paged-attention workspace are caller-owned.
+ */
+#ifndef MSCO_B200_H_
+#define MSCO_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MSCO_ABI_VERSION 1
+
+/* status codes */
+#define MSCO_OK 0
+#define MSCO_ERR_INVALID_ARG 1 /* a shape / pointer / attribute violates the contract      */
+#define MSCO_ERR_UNSUPPORTED 2 /* valid for the reference operator, not built for B200     */
+#define MSCO_ERR_CUDA 3        /* a CUDA runtime / driver call failed                      */
+#define MSCO_ERR_TIMEOUT 4     /* a bounded device-side wait gave up (see msco_paged_attention_status) */
+#define MSCO_ERR_OOB 5         /* a slot or block id is outside the cache                  */
+#define MSCO_ERR_INTERNAL 6
+
+/* element types */
+#define MSCO_DTYPE_F16 0
+#define MSCO_DTYPE_BF16 1
+#define MSCO_DTYPE_I8 2
+#define MSCO_DTYPE_F32 3
+#define MSCO_DTYPE_I32 4
+#define MSCO_DTYPE_I64 5
+
+int msco_version(void);
+const char *msco_last_error(void);
+
+/* ------------------------------------------------------------------------
+ * reshape_and_cache: scatter token rows into the paged cache.
+ *
+ * Replaces the device op created at reshape_and_cache.cc:55-59 (ND cache
+ * format only).  For every token i with s = slot_mapping[i] >= 0 the row
+ * key[i, :] (k_row_bytes bytes) is copied bit-for-bit to
+ * key_cache + s * k_row_bytes, i.e. to cache[s / block_size, s % block_size]
+ * of a contiguous [num_blocks, block_size, kv_heads, head_dim] cache; the
+ * same for value.  Negative slots are skipped.  Duplicate non-negative slots
+ * race (as in the reference, which requires unique slots).
+ *
+ * value / value_cache may both be NULL (key-only mode).  Row sizes must be
+ * multiples of 2 bytes; the fast path needs 16-byte aligned pointers and row
+ * sizes that are multiples of 16 bytes and falls back to a 2-byte path
+ * otherwise.  num_slots = num_blocks * block_size bounds the slot check:
+ * slots >= num_slots are not written and are counted in *oob_count when
+ * oob_count (device int32, may be NULL) is given.
+ * ---------------------------------------------------------------------- */
+int msco_reshape_and_cache(const void *key, const void *value, void *key_cache, void *value_cache,
+                           const int32_t *slot_mapping, int64_t num_tokens, int64_t k_row_bytes,
+                           int64_t v_row_bytes, int64_t num_slots, int32_t *oob_count, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Quantising variant (extension; the reference operator has no such mode).
+ * Rows arrive in fp16/bf16 (in_dtype), the caches are int8, and per channel
+ * c = (kv_head, head_dim):
+ *     q = saturate_int8( rint( (float)x / descale[c] ) - offset[c] )
+ * with IEEE float32 division and round-half-to-even: the exact inverse of the
+ * de-quantisation paged_attention applies with quant_type = 1.
+ * k_offset / v_offset may be NULL (offset 0).
+ * ---------------------------------------------------------------------- */
+int msco_reshape_and_cache_quant(const void *key, const void *value, int8_t *key_cache,
+                                 int8_t *value_cache, const int32_t *slot_mapping,
+                                 int64_t num_tokens, int64_t k_row_elems, int64_t v_row_elems,
+                                 int32_t in_dtype, const float *k_descale, const int32_t *k_offset,
+                                 const float *v_descale, const int32_t *v_offset, int64_t num_slots,
+                                 int32_t *oob_count, void *stream);
+
+/* ------------------------------------------------------------------------
+ * paged_attention (decode: one query token per sequence).
+ *
+ * The descriptor carries what the reference puts into
+ * CustomASDPagedAttentionParam (paged_attention_graph.cc:726-790) plus the
+ * shapes the reference reads from its tensor infos.
+ * ---------------------------------------------------------------------- */
+typedef struct MscoPaDesc {
+  int32_t q_dtype;            /* MSCO_DTYPE_F16 | MSCO_DTYPE_BF16; also the output dtype        */
+  int32_t kv_dtype;           /* same as q_dtype, or MSCO_DTYPE_I8 when quant_type == 1         */
+  int32_t num_q_heads;        /* q_head_num                                                     */
+  int32_t num_kv_heads;       /* kv_head_num; divides num_q_heads                               */
+  int32_t head_dim;           /* <= 256                                                         */
+  int32_t block_size;         /* tokens per cache block                                         */
+  int64_t num_blocks;         /* blocks in each cache                                           */
+  int32_t max_blocks_per_seq; /* row length of block_tables                                     */
+  float qk_scale;             /* "tor": multiplies q.k before the softmax                       */
+  int32_t quant_type;         /* 0 = none, 1 = int8 KV with (x + offset) * descale              */
+  int32_t has_quant_offset;   /* offsets are read only when non-zero                            */
+  int32_t mask_type;          /* 0 = none, 1 = NORM, 2 = ALIBI (additive, decode shapes)        */
+  int32_t mask_dtype;         /* dtype of attn_mask (F16 / BF16 / F32) when mask_type != 0      */
+  int64_t mask_batch_stride;  /* elements between sequences in attn_mask                        */
+  int64_t mask_head_stride;   /* elements between q heads (0 for NORM)                          */
+  int32_t kernel;             /* 0 = auto, 1 = force the generic kernel, 2 = require the TMA kernel */
+  int32_t reserved;
+} MscoPaDesc;
+
+typedef struct MscoPaPlan MscoPaPlan;
+
+typedef struct MscoPaPlanInfo {
+  int32_t kernel;          /* 1 = generic, 2 = TMA + tensor-core kernel                 */
+  int32_t grid;            /* CTAs of the attention kernel                              */
+  int32_t work_items;      /* (sequence, kv head, q-row block, KV split) items          */
+  int32_t partials;        /* split partials that go through the reduce kernel          */
+  int32_t max_splits;      /* largest split count of any sequence                       */
+  int32_t rows_per_item;   /* q rows of one kv-head group handled by one item           */
+  int64_t workspace_bytes; /* same as msco_paged_attention_workspace_bytes              */
+  int64_t kv_tokens;       /* sum of context_lens                                       */
+} MscoPaPlanInfo;
+
+/* Split rule: tokens per KV split as a function of one sequence's length
+ * only (never of the batch), so a request's result is bitwise independent of
+ * what it is batched with. */
+int32_t msco_paged_attention_split_tokens(int32_t context_len);
+
+/* Build the launch plan from the host copy of context_lens (the reference
+ * reads the same host values into its param: paged_attention_graph.cc:773-776,
+ * paged_attention_pynative.cc:686-692).  Pure host work; allocates only host
+ * (pinned) memory owned by the plan. */
+int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *host_context_lens, int32_t batch,
+                              MscoPaPlan **plan);
+size_t msco_paged_attention_workspace_bytes(const MscoPaPlan *plan);
+int msco_paged_attention_plan_info(const MscoPaPlan *plan, MscoPaPlanInfo *info);
+void msco_paged_attention_plan_destroy(MscoPaPlan *plan);
+
+/* Launch.  Layouts (all contiguous):
+ *   query        [batch, num_q_heads, head_dim]                      q_dtype
+ *   key_cache    [num_blocks, block_size, num_kv_heads, head_dim]    kv_dtype
+ *   value_cache  same shape as key_cache
+ *   block_tables [batch, max_blocks_per_seq] int32 (device)
+ *   k_descale / v_descale [num_kv_heads * head_dim] float32, k_offset / v_offset int32
+ *                (quant_type == 1 only; offsets only when has_quant_offset)
+ *   attn_mask    NORM [batch, 1, max_ctx], ALIBI [batch, num_q_heads, 1, max_ctx]
+ *   out          [batch, num_q_heads, head_dim]                      q_dtype
+ *   workspace    >= msco_paged_attention_workspace_bytes(plan), 256-byte aligned;
+ *                holds the uploaded plan, the split partials and a status word.
+ * The first bytes of the workspace are written by an async copy from the
+ * plan's pinned host memory: the plan must outlive the launch. */
+int msco_paged_attention_launch(const MscoPaPlan *plan, const void *query, const void *key_cache,
+                                const void *value_cache, const int32_t *block_tables,
+                                const float *k_descale, const int32_t *k_offset,
+                                const float *v_descale, const int32_t *v_offset,
+                                const void *attn_mask, void *out, void *workspace,
+                                size_t workspace_bytes, void *stream);
+
+/* After the stream has been synchronised: reads the status word the kernels
+ * leave in the workspace.  MSCO_OK, MSCO_ERR_TIMEOUT (a bounded wait inside
+ * the kernel expired) or MSCO_ERR_OOB (a block id outside the cache was met;
+ * the affected tokens were skipped).  Synchronous device-to-host copy. */
+int msco_paged_attention_status(const MscoPaPlan *plan, const void *workspace);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MSCO_B200_H_ */

@@ -1,0 +1,129 @@
+"""ctypes bindings of libmsco_b200.so (declared in include/msco_b200.h).
+
+Loading fails loudly: there is no CPU or PyTorch fallback for these operators.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmsco_b200.so")
+
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_OOB, ERR_INTERNAL = range(7)
+DTYPE_F16, DTYPE_BF16, DTYPE_I8, DTYPE_F32, DTYPE_I32, DTYPE_I64 = range(6)
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_TMA = 0, 1, 2
+
+
+class MscoPaDesc(C.Structure):
+    _fields_ = [
+        ("q_dtype", C.c_int32), ("kv_dtype", C.c_int32), ("num_q_heads", C.c_int32),
+        ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("block_size", C.c_int32),
+        ("num_blocks", C.c_int64), ("max_blocks_per_seq", C.c_int32), ("qk_scale", C.c_float),
+        ("quant_type", C.c_int32), ("has_quant_offset", C.c_int32), ("mask_type", C.c_int32),
+        ("mask_dtype", C.c_int32), ("mask_batch_stride", C.c_int64), ("mask_head_stride", C.c_int64),
+        ("kernel", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
+class MscoPaPlanInfo(C.Structure):
+    _fields_ = [
+        ("kernel", C.c_int32), ("grid", C.c_int32), ("work_items", C.c_int32), ("partials", C.c_int32),
+        ("max_splits", C.c_int32), ("rows_per_item", C.c_int32), ("workspace_bytes", C.c_int64),
+        ("kv_tokens", C.c_int64),
+    ]
+
+
+class MscoError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"[msco error {code}] {message}")
+        self.code = code
+        self.message = message
+
+
+_lib = None
+
+# every symbol include/msco_b200.h declares
+EXPORTS = (
+    "msco_version", "msco_last_error", "msco_reshape_and_cache", "msco_reshape_and_cache_quant",
+    "msco_paged_attention_split_tokens", "msco_paged_attention_plan", "msco_paged_attention_workspace_bytes",
+    "msco_paged_attention_plan_info", "msco_paged_attention_plan_destroy", "msco_paged_attention_launch",
+    "msco_paged_attention_status",
+)
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m ms_custom_ops_b200.build` "
+            "(nvcc, sm_100a). These operators have no fallback implementation.")
+    L = C.CDLL(LIB_PATH)
+    vp, i32, i64, sz = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t
+    L.msco_version.restype = C.c_int
+    L.msco_last_error.restype = C.c_char_p
+    L.msco_reshape_and_cache.restype = C.c_int
+    L.msco_reshape_and_cache.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, vp]
+    L.msco_reshape_and_cache_quant.restype = C.c_int
+    L.msco_reshape_and_cache_quant.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, vp, vp, vp, vp, i64, vp, vp]
+    L.msco_paged_attention_split_tokens.restype = i32
+    L.msco_paged_attention_split_tokens.argtypes = [i32]
+    L.msco_paged_attention_plan.restype = C.c_int
+    L.msco_paged_attention_plan.argtypes = [C.POINTER(MscoPaDesc), C.POINTER(i32), i32, C.POINTER(vp)]
+    L.msco_paged_attention_workspace_bytes.restype = sz
+    L.msco_paged_attention_workspace_bytes.argtypes = [vp]
+    L.msco_paged_attention_plan_info.restype = C.c_int
+    L.msco_paged_attention_plan_info.argtypes = [vp, C.POINTER(MscoPaPlanInfo)]
+    L.msco_paged_attention_plan_destroy.restype = None
+    L.msco_paged_attention_plan_destroy.argtypes = [vp]
+    L.msco_paged_attention_launch.restype = C.c_int
+    L.msco_paged_attention_launch.argtypes = [vp] * 12 + [sz, vp]
+    L.msco_paged_attention_status.restype = C.c_int
+    L.msco_paged_attention_status.argtypes = [vp, vp]
+    _lib = L
+    return L
+
+
+def check(code):
+    if code != OK:
+        raise MscoError(code, lib().msco_last_error().decode("utf-8", "replace"))
+
+
+class PaPlan:
+    """Owner of one MscoPaPlan (host-side launch plan for a vector of context lengths)."""
+
+    def __init__(self, desc: MscoPaDesc, context_lens):
+        L = lib()
+        lens = (C.c_int32 * len(context_lens))(*[int(x) for x in context_lens])
+        h = C.c_void_p()
+        check(L.msco_paged_attention_plan(C.byref(desc), lens, len(context_lens), C.byref(h)))
+        self._h = h
+        self.desc = desc
+        self.batch = len(context_lens)
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def workspace_bytes(self) -> int:
+        return int(lib().msco_paged_attention_workspace_bytes(self._h))
+
+    def info(self) -> MscoPaPlanInfo:
+        out = MscoPaPlanInfo()
+        check(lib().msco_paged_attention_plan_info(self._h, C.byref(out)))
+        return out
+
+    def close(self):
+        if self._h:
+            lib().msco_paged_attention_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

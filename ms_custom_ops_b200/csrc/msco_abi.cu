@@ -1,0 +1,263 @@
+// C ABI of libmsco_b200.so: error reporting, paged-attention planning and launch.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <new>
+#include <numeric>
+
+#include "msco_common.cuh"
+#include "pa_params.h"
+
+namespace msco {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int fail(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace msco
+
+using namespace msco;
+
+extern "C" int msco_version(void) { return MSCO_ABI_VERSION; }
+extern "C" const char *msco_last_error(void) { return g_err; }
+
+// Tokens per KV split.  A function of the sequence's own length only: the
+// result for one request never depends on what else is in the batch.
+extern "C" int32_t msco_paged_attention_split_tokens(int32_t context_len) {
+  if (context_len <= 16384) return 512;
+  if (context_len <= 65536) return 1024;
+  return 2048;
+}
+
+static int validate_desc(const MscoPaDesc &d) {
+  if (d.q_dtype != MSCO_DTYPE_F16 && d.q_dtype != MSCO_DTYPE_BF16)
+    return fail(MSCO_ERR_UNSUPPORTED, "paged_attention: query dtype must be float16/bfloat16 (full-quant int8 query is not built)");
+  if (d.quant_type == 0) {
+    if (d.kv_dtype != d.q_dtype)
+      return fail(MSCO_ERR_INVALID_ARG, "paged_attention: in unquant mode the cache dtype must equal the query dtype");
+  } else if (d.quant_type == 1) {
+    if (d.kv_dtype != MSCO_DTYPE_I8)
+      return fail(MSCO_ERR_INVALID_ARG, "paged_attention: in dequant mode the cache dtype must be int8");
+  } else {
+    return fail(MSCO_ERR_UNSUPPORTED, "paged_attention: quant_type %d is not built (0 and 1 are)", d.quant_type);
+  }
+  if (d.num_q_heads <= 0 || d.num_kv_heads <= 0 || d.num_q_heads % d.num_kv_heads != 0)
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention: q heads (%d) must be a positive multiple of kv heads (%d)",
+                d.num_q_heads, d.num_kv_heads);
+  if (d.head_dim <= 0 || d.head_dim > 256)
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention: head_dim must be in (0, 256], got %d", d.head_dim);
+  if (d.block_size <= 0 || d.num_blocks <= 0 || d.max_blocks_per_seq < 0)
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention: bad cache geometry");
+  if (d.mask_type < 0 || d.mask_type > 2)
+    return fail(MSCO_ERR_UNSUPPORTED, "paged_attention: mask_type %d is not built (0, 1, 2 are)", d.mask_type);
+  if (d.mask_type != 0 && d.mask_dtype != MSCO_DTYPE_F16 && d.mask_dtype != MSCO_DTYPE_BF16 &&
+      d.mask_dtype != MSCO_DTYPE_F32)
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention: mask dtype must be float16/bfloat16/float32");
+  return MSCO_OK;
+}
+
+extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *host_context_lens,
+                                         int32_t batch, MscoPaPlan **out_plan) {
+  if (desc == nullptr || out_plan == nullptr || batch < 0 || (batch > 0 && host_context_lens == nullptr))
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: NULL argument");
+  *out_plan = nullptr;
+  int rc = validate_desc(*desc);
+  if (rc != MSCO_OK) return rc;
+  const MscoPaDesc &d = *desc;
+  const int64_t cap = (int64_t)d.max_blocks_per_seq * d.block_size;
+  for (int b = 0; b < batch; ++b) {
+    if (host_context_lens[b] < 0)
+      return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: context_lens[%d] = %d is negative", b,
+                  host_context_lens[b]);
+    if (host_context_lens[b] > cap)
+      return fail(MSCO_ERR_INVALID_ARG,
+                  "paged_attention_plan: context_lens[%d] = %d exceeds the block table (%d blocks of %d)", b,
+                  host_context_lens[b], d.max_blocks_per_seq, d.block_size);
+  }
+  MscoPaPlan *pl = new (std::nothrow) MscoPaPlan();
+  if (pl == nullptr) return fail(MSCO_ERR_INTERNAL, "paged_attention_plan: out of host memory");
+  pl->desc = d;
+  pl->batch = batch;
+  const int g = d.num_q_heads / d.num_kv_heads;
+  const bool tma_ok = pa_tma_supported(d);
+  if (d.kernel == kKernelTma && !tma_ok) {
+    delete pl;
+    return fail(MSCO_ERR_UNSUPPORTED, "paged_attention_plan: the TMA kernel needs head_dim 128, block_size 16/32/64/128, no mask");
+  }
+  pl->kernel = (d.kernel == kKernelGeneric || !tma_ok) ? kKernelGeneric : kKernelTma;
+  pl->rows_per_item = (pl->kernel == kKernelTma && g > 8) ? 16 : 8;
+  const int nqb = (g + pl->rows_per_item - 1) / pl->rows_per_item;
+  const int items_per_split = d.num_kv_heads * nqb;
+
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
+    pl->num_sms = sms;
+  else
+    (void)cudaGetLastError();  // no device (planning only): keep the B200 default
+
+  // sequences with tokens, longest first (stable), so that the big items lead the round-robin
+  std::vector<int> order;
+  for (int b = 0; b < batch; ++b)
+    if (host_context_lens[b] > 0) order.push_back(b);
+  std::stable_sort(order.begin(), order.end(),
+                   [&](int a, int b) { return host_context_lens[a] > host_context_lens[b]; });
+  const int nseq = (int)order.size();
+  pl->nseq = nseq;
+  pl->plan_words = kPlanHeaderWords + (size_t)(nseq + 1) + 5 * (size_t)nseq + 2 * (size_t)batch;
+  pl->plan_bytes = pl->plan_words * 4;
+  if (cudaHostAlloc(reinterpret_cast<void **>(&pl->host_words), std::max<size_t>(pl->plan_bytes, 64),
+                    cudaHostAllocDefault) == cudaSuccess) {
+    pl->host_pinned = true;
+  } else {
+    (void)cudaGetLastError();
+    pl->host_words = static_cast<int32_t *>(malloc(std::max<size_t>(pl->plan_bytes, 64)));
+    if (pl->host_words == nullptr) {
+      delete pl;
+      return fail(MSCO_ERR_INTERNAL, "paged_attention_plan: out of host memory");
+    }
+  }
+  int32_t *w = pl->host_words;
+  memset(w, 0, pl->plan_bytes);
+  int32_t *item_base = w + kPlanHeaderWords;
+  int32_t *seq_idx = item_base + nseq + 1, *seq_len = seq_idx + nseq, *chunk = seq_len + nseq;
+  int32_t *nsplit = chunk + nseq, *part_base = nsplit + nseq;
+  int32_t *b_nsplit = part_base + nseq, *b_part_base = b_nsplit + batch;
+  int64_t items = 0, parts = 0, kv_tokens = 0;
+  int max_splits = 0;
+  for (int s = 0; s < nseq; ++s) {
+    const int b = order[s], len = host_context_lens[b];
+    const int c = msco_paged_attention_split_tokens(len);
+    const int ns = (len + c - 1) / c;
+    item_base[s] = (int32_t)items;
+    seq_idx[s] = b; seq_len[s] = len; chunk[s] = c; nsplit[s] = ns;
+    part_base[s] = (int32_t)parts;
+    b_nsplit[b] = ns; b_part_base[b] = (int32_t)parts;
+    items += (int64_t)ns * items_per_split;
+    if (ns > 1) parts += ns;
+    max_splits = std::max(max_splits, ns);
+    kv_tokens += len;
+    if (items > 0x7fffffffLL) {
+      msco_paged_attention_plan_destroy(pl);
+      return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: too many work items");
+    }
+  }
+  item_base[nseq] = (int32_t)items;
+  w[0] = 0; w[1] = nseq; w[2] = (int32_t)items; w[3] = (int32_t)parts; w[4] = batch; w[5] = items_per_split;
+  pl->total_items = (int)items;
+  pl->total_parts = (int)parts;
+  pl->max_splits = max_splits;
+  pl->kv_tokens = kv_tokens;
+  pl->need_reduce = parts > 0 || nseq < batch;
+  pl->grid = pl->kernel == kKernelTma ? (int)std::min<int64_t>(items, pl->num_sms) : (int)items;
+  pl->part_o_offset = align_up(pl->plan_bytes, 256);
+  const size_t part_o_bytes = (size_t)parts * d.num_q_heads * d.head_dim * 4;
+  pl->part_ml_offset = align_up(pl->part_o_offset + part_o_bytes, 256);
+  pl->workspace_bytes = align_up(pl->part_ml_offset + (size_t)parts * d.num_q_heads * 2 * 4, 256);
+  *out_plan = pl;
+  return MSCO_OK;
+}
+
+extern "C" size_t msco_paged_attention_workspace_bytes(const MscoPaPlan *plan) {
+  return plan ? plan->workspace_bytes : 0;
+}
+
+extern "C" int msco_paged_attention_plan_info(const MscoPaPlan *plan, MscoPaPlanInfo *info) {
+  if (plan == nullptr || info == nullptr) return fail(MSCO_ERR_INVALID_ARG, "plan_info: NULL argument");
+  info->kernel = plan->kernel;
+  info->grid = plan->grid;
+  info->work_items = plan->total_items;
+  info->partials = plan->total_parts;
+  info->max_splits = plan->max_splits;
+  info->rows_per_item = plan->rows_per_item;
+  info->workspace_bytes = (int64_t)plan->workspace_bytes;
+  info->kv_tokens = plan->kv_tokens;
+  return MSCO_OK;
+}
+
+extern "C" void msco_paged_attention_plan_destroy(MscoPaPlan *plan) {
+  if (plan == nullptr) return;
+  if (plan->host_words != nullptr) {
+    if (plan->host_pinned) cudaFreeHost(plan->host_words); else free(plan->host_words);
+  }
+  delete plan;
+}
+
+extern "C" int msco_paged_attention_launch(const MscoPaPlan *plan, const void *query, const void *key_cache,
+                                           const void *value_cache, const int32_t *block_tables,
+                                           const float *k_descale, const int32_t *k_offset,
+                                           const float *v_descale, const int32_t *v_offset,
+                                           const void *attn_mask, void *out, void *workspace,
+                                           size_t workspace_bytes, void *stream) {
+  if (plan == nullptr) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch: NULL plan");
+  if (plan->batch == 0) return MSCO_OK;
+  const MscoPaDesc &d = plan->desc;
+  if (query == nullptr || key_cache == nullptr || value_cache == nullptr || block_tables == nullptr ||
+      out == nullptr || workspace == nullptr)
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch: NULL tensor");
+  if (workspace_bytes < plan->workspace_bytes)
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch: workspace too small (%zu < %zu)", workspace_bytes,
+                plan->workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255)
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch: workspace must be 256-byte aligned");
+  if (d.quant_type == 1 && (k_descale == nullptr || v_descale == nullptr))
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch: k_descale / v_descale are required when quant_type = 1");
+  if (d.quant_type == 1 && d.has_quant_offset && (k_offset == nullptr || v_offset == nullptr))
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch: k_offset / v_offset are required when has_quant_offset");
+  if (d.mask_type != 0 && attn_mask == nullptr)
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch: attn_mask is required when mask_type != 0");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  PaParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = query; p.key_cache = key_cache; p.value_cache = value_cache; p.block_tables = block_tables;
+  if (d.quant_type == 1) {
+    p.k_descale = k_descale; p.v_descale = v_descale;
+    if (d.has_quant_offset) { p.k_offset = k_offset; p.v_offset = v_offset; }
+  }
+  p.mask = d.mask_type ? attn_mask : nullptr;
+  p.out = out;
+  char *ws = static_cast<char *>(workspace);
+  p.plan = reinterpret_cast<int32_t *>(ws);
+  p.part_o = reinterpret_cast<float *>(ws + plan->part_o_offset);
+  p.part_ml = reinterpret_cast<float *>(ws + plan->part_ml_offset);
+  p.num_blocks = d.num_blocks;
+  p.mask_batch_stride = d.mask_batch_stride; p.mask_head_stride = d.mask_head_stride;
+  p.num_q_heads = d.num_q_heads; p.num_kv_heads = d.num_kv_heads; p.head_dim = d.head_dim;
+  p.block_size = d.block_size; p.group = d.num_q_heads / d.num_kv_heads;
+  p.rows_per_item = plan->rows_per_item; p.max_blocks_per_seq = d.max_blocks_per_seq;
+  p.mask_type = d.mask_type; p.mask_dtype = d.mask_dtype;
+  p.scale = d.qk_scale;
+  p.scale_log2e = d.qk_scale * 1.4426950408889634f;
+
+  MSCO_CUDA_CHECK(cudaMemcpyAsync(ws, plan->host_words, plan->plan_bytes, cudaMemcpyHostToDevice, st));
+  int rc = plan->kernel == kKernelTma ? launch_pa_tma(plan, p, st) : launch_pa_generic(plan, p, st);
+  if (rc != MSCO_OK) return rc;
+  if (plan->need_reduce) rc = launch_pa_reduce(plan, p, st);
+  return rc;
+}
+
+extern "C" int msco_paged_attention_status(const MscoPaPlan *plan, const void *workspace) {
+  if (plan == nullptr || workspace == nullptr) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_status: NULL argument");
+  if (plan->batch == 0) return MSCO_OK;
+  int32_t status = 0;
+  MSCO_CUDA_CHECK(cudaMemcpy(&status, workspace, sizeof(status), cudaMemcpyDeviceToHost));
+  if (status == kStatusTimeout) return fail(MSCO_ERR_TIMEOUT, "paged_attention: a bounded wait inside the kernel expired");
+  if (status == kStatusOob) return fail(MSCO_ERR_OOB, "paged_attention: a block id outside the cache was met");
+  return MSCO_OK;
+}

@@ -1,0 +1,74 @@
+// Kernel parameter block and host-side plan object of paged attention.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <vector>
+
+#include "msco_b200.h"
+
+namespace msco {
+
+// Passed by value to every paged-attention kernel.
+struct PaParams {
+  const void *q;
+  const void *key_cache;
+  const void *value_cache;
+  const int32_t *block_tables;
+  const float *k_descale;
+  const int32_t *k_offset;
+  const float *v_descale;
+  const int32_t *v_offset;
+  const void *mask;
+  void *out;
+  int32_t *plan;   // device copy of the plan words; word 0 is the status
+  float *part_o;   // [total_parts, num_q_heads, head_dim] un-normalised partial outputs
+  float *part_ml;  // [total_parts, num_q_heads, 2] (running max in log2 domain, running sum)
+  int64_t num_blocks;
+  int64_t mask_batch_stride, mask_head_stride;
+  int num_q_heads, num_kv_heads, head_dim, block_size, group, rows_per_item, max_blocks_per_seq;
+  int mask_type, mask_dtype;
+  float scale;        // qk_scale
+  float scale_log2e;  // qk_scale * log2(e)
+};
+
+constexpr int kKernelGeneric = 1;
+constexpr int kKernelTma = 2;
+
+}  // namespace msco
+
+struct MscoPaPlan {
+  MscoPaDesc desc;
+  int batch = 0;
+  int kernel = 0;
+  int rows_per_item = 8;
+  int grid = 0;
+  int num_sms = 148;
+  int nseq = 0, total_items = 0, total_parts = 0, max_splits = 0;
+  bool need_reduce = false;
+  int64_t kv_tokens = 0;
+  int32_t *host_words = nullptr;  // pinned when a CUDA device is present
+  bool host_pinned = false;
+  size_t plan_words = 0;
+  size_t plan_bytes = 0;        // bytes uploaded per launch
+  size_t part_o_offset = 0;     // byte offsets inside the workspace
+  size_t part_ml_offset = 0;
+  size_t workspace_bytes = 0;
+  // tensor maps of the TMA kernel, rebuilt when the cache addresses change
+  mutable std::mutex tm_mutex;
+  mutable const void *tm_k_ptr = nullptr;
+  mutable const void *tm_v_ptr = nullptr;
+  alignas(64) mutable unsigned char tm_k[128];
+  alignas(64) mutable unsigned char tm_v[128];
+};
+
+namespace msco {
+// kernel launchers (defined next to the kernels)
+int launch_pa_generic(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream);
+int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream);
+int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream);
+bool pa_tma_supported(const MscoPaDesc &d);
+}  // namespace msco

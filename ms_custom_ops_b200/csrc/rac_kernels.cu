@@ -1,0 +1,270 @@
+// reshape_and_cache for B200: scatter new K/V token rows into the paged cache.
+//
+// HBM-bound byte movement.  One warp moves the K row and the V row of one
+// token with 16-byte loads that are all issued before the first store, so a
+// resident SM keeps hundreds of KB in flight.  Algorithmic bytes per valid
+// token: (k_row_bytes + v_row_bytes) read + the same written + 4 (slot).
+#include "msco_common.cuh"
+
+namespace msco {
+namespace {
+
+constexpr int kRacThreads = 256;
+constexpr int kRacWarps = kRacThreads / 32;
+
+__device__ __forceinline__ uint4 ld_stream16(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// 16-byte path.  k16 / v16 = 16-byte chunks per row (v16 == 0: key only).
+// UNROLL chunks per lane are loaded before any is stored.
+template <int UNROLL>
+__global__ void __launch_bounds__(kRacThreads)
+rac_scatter16_kernel(const uint4 *__restrict__ key, const uint4 *__restrict__ value,
+                     uint4 *__restrict__ key_cache, uint4 *__restrict__ value_cache,
+                     const int32_t *__restrict__ slot_mapping, int64_t num_tokens, int k16, int v16,
+                     int64_t num_slots, int32_t *oob_count) {
+  const int lane = threadIdx.x & 31;
+  const int64_t tok = (int64_t)blockIdx.x * kRacWarps + (threadIdx.x >> 5);
+  if (tok >= num_tokens) return;
+  const int64_t slot = __ldg(slot_mapping + tok);
+  if (slot < 0) return;  // padding token: nothing is written
+  if (slot >= num_slots) {
+    if (lane == 0 && oob_count != nullptr) atomicAdd(oob_count, 1);
+    return;
+  }
+  const uint4 *ks = key + tok * k16;
+  uint4 *kd = key_cache + slot * k16;
+  const uint4 *vs = value + tok * v16;
+  uint4 *vd = value_cache + slot * v16;
+  const int total = k16 + v16;  // K chunks then V chunks, one flat index space
+  for (int c0 = lane; c0 < total; c0 += 32 * UNROLL) {
+    uint4 r[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int c = c0 + 32 * u;
+      if (c < total) r[u] = (c < k16) ? ld_stream16(ks + c) : ld_stream16(vs + (c - k16));
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int c = c0 + 32 * u;
+      if (c < total) {
+        if (c < k16) kd[c] = r[u]; else vd[c - k16] = r[u];
+      }
+    }
+  }
+}
+
+// 2-byte path for rows or pointers that are not 16-byte aligned.
+__global__ void __launch_bounds__(kRacThreads)
+rac_scatter2_kernel(const uint16_t *__restrict__ key, const uint16_t *__restrict__ value,
+                    uint16_t *__restrict__ key_cache, uint16_t *__restrict__ value_cache,
+                    const int32_t *__restrict__ slot_mapping, int64_t num_tokens, int k2, int v2,
+                    int64_t num_slots, int32_t *oob_count) {
+  const int lane = threadIdx.x & 31;
+  const int64_t tok = (int64_t)blockIdx.x * kRacWarps + (threadIdx.x >> 5);
+  if (tok >= num_tokens) return;
+  const int64_t slot = __ldg(slot_mapping + tok);
+  if (slot < 0) return;
+  if (slot >= num_slots) {
+    if (lane == 0 && oob_count != nullptr) atomicAdd(oob_count, 1);
+    return;
+  }
+  for (int c = lane; c < k2; c += 32) key_cache[slot * k2 + c] = key[tok * k2 + c];
+  for (int c = lane; c < v2; c += 32) value_cache[slot * v2 + c] = value[tok * v2 + c];
+}
+
+// 1-byte path (int8 rows of odd length)
+__global__ void __launch_bounds__(kRacThreads)
+rac_scatter1_kernel(const uint8_t *__restrict__ key, const uint8_t *__restrict__ value,
+                    uint8_t *__restrict__ key_cache, uint8_t *__restrict__ value_cache,
+                    const int32_t *__restrict__ slot_mapping, int64_t num_tokens, int k1, int v1,
+                    int64_t num_slots, int32_t *oob_count) {
+  const int lane = threadIdx.x & 31;
+  const int64_t tok = (int64_t)blockIdx.x * kRacWarps + (threadIdx.x >> 5);
+  if (tok >= num_tokens) return;
+  const int64_t slot = __ldg(slot_mapping + tok);
+  if (slot < 0) return;
+  if (slot >= num_slots) {
+    if (lane == 0 && oob_count != nullptr) atomicAdd(oob_count, 1);
+    return;
+  }
+  for (int c = lane; c < k1; c += 32) key_cache[slot * k1 + c] = key[tok * k1 + c];
+  for (int c = lane; c < v1; c += 32) value_cache[slot * v1 + c] = value[tok * v1 + c];
+}
+
+// ---- quantising scatter ------------------------------------------------------
+// q = saturate_int8(rint(float(x) / descale[c]) - offset[c]); IEEE division,
+// round-half-to-even, NaN -> 0: bit-identical to float32 numpy arithmetic.
+__device__ __forceinline__ int quant_one(float x, float d, float off) {
+  float q = rintf(__fdiv_rn(x, d));
+  q = __fsub_rn(q, off);
+  if (q != q) q = 0.f;
+  q = fminf(fmaxf(q, -128.f), 127.f);
+  return (int)q;
+}
+
+template <typename T>
+__device__ __forceinline__ void quant_row8(const T *__restrict__ src, int8_t *__restrict__ dst,
+                                           const float *__restrict__ descale,
+                                           const int32_t *__restrict__ offset, int elems, int lane) {
+  // 8 elements per lane per step: one 16-byte load, one 8-byte store
+  for (int e = lane * 8; e < elems; e += 32 * 8) {
+    uint4 raw = ld_stream16(src + e);
+    const T *x = reinterpret_cast<const T *>(&raw);
+    const float4 d0 = __ldg(reinterpret_cast<const float4 *>(descale + e));
+    const float4 d1 = __ldg(reinterpret_cast<const float4 *>(descale + e + 4));
+    float o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (offset != nullptr) {
+      const int4 o0 = __ldg(reinterpret_cast<const int4 *>(offset + e));
+      const int4 o1 = __ldg(reinterpret_cast<const int4 *>(offset + e + 4));
+      o[0] = (float)o0.x; o[1] = (float)o0.y; o[2] = (float)o0.z; o[3] = (float)o0.w;
+      o[4] = (float)o1.x; o[5] = (float)o1.y; o[6] = (float)o1.z; o[7] = (float)o1.w;
+    }
+    const float d[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo |= (uint32_t)(quant_one(to_f32<T>(x[i]), d[i], o[i]) & 0xff) << (8 * i);
+      hi |= (uint32_t)(quant_one(to_f32<T>(x[i + 4]), d[i + 4], o[i + 4]) & 0xff) << (8 * i);
+    }
+    *reinterpret_cast<uint2 *>(dst + e) = make_uint2(lo, hi);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void quant_row1(const T *__restrict__ src, int8_t *__restrict__ dst,
+                                           const float *__restrict__ descale,
+                                           const int32_t *__restrict__ offset, int elems, int lane) {
+  for (int e = lane; e < elems; e += 32) {
+    const float off = offset ? (float)__ldg(offset + e) : 0.f;
+    dst[e] = (int8_t)quant_one(to_f32<T>(src[e]), __ldg(descale + e), off);
+  }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kRacThreads)
+rac_scatter_quant_kernel(const T *__restrict__ key, const T *__restrict__ value,
+                         int8_t *__restrict__ key_cache, int8_t *__restrict__ value_cache,
+                         const int32_t *__restrict__ slot_mapping, int64_t num_tokens, int k_elems,
+                         int v_elems, const float *__restrict__ k_descale,
+                         const int32_t *__restrict__ k_offset, const float *__restrict__ v_descale,
+                         const int32_t *__restrict__ v_offset, int64_t num_slots, int32_t *oob_count) {
+  const int lane = threadIdx.x & 31;
+  const int64_t tok = (int64_t)blockIdx.x * kRacWarps + (threadIdx.x >> 5);
+  if (tok >= num_tokens) return;
+  const int64_t slot = __ldg(slot_mapping + tok);
+  if (slot < 0) return;
+  if (slot >= num_slots) {
+    if (lane == 0 && oob_count != nullptr) atomicAdd(oob_count, 1);
+    return;
+  }
+  if (VEC) {
+    quant_row8<T>(key + tok * k_elems, key_cache + slot * k_elems, k_descale, k_offset, k_elems, lane);
+    if (v_elems) quant_row8<T>(value + tok * v_elems, value_cache + slot * v_elems, v_descale, v_offset, v_elems, lane);
+  } else {
+    quant_row1<T>(key + tok * k_elems, key_cache + slot * k_elems, k_descale, k_offset, k_elems, lane);
+    if (v_elems) quant_row1<T>(value + tok * v_elems, value_cache + slot * v_elems, v_descale, v_offset, v_elems, lane);
+  }
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+}  // namespace msco
+
+using namespace msco;
+
+extern "C" int msco_reshape_and_cache(const void *key, const void *value, void *key_cache, void *value_cache,
+                                      const int32_t *slot_mapping, int64_t num_tokens, int64_t k_row_bytes,
+                                      int64_t v_row_bytes, int64_t num_slots, int32_t *oob_count,
+                                      void *stream) {
+  if (num_tokens < 0 || k_row_bytes < 0 || v_row_bytes < 0 || num_slots < 0)
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache: negative size");
+  const bool has_v = (value != nullptr) || (value_cache != nullptr);
+  if (has_v && (value == nullptr || value_cache == nullptr))
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache: value and value_cache must be given together");
+  if (!has_v) v_row_bytes = 0;
+  // zero-sized inputs: the reference skips execution (reshape_and_cache.cc:90-119)
+  if (num_tokens == 0 || k_row_bytes == 0 || num_slots == 0) return MSCO_OK;
+  if (key == nullptr || key_cache == nullptr || slot_mapping == nullptr)
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache: key, key_cache and slot_mapping must not be NULL");
+  if (k_row_bytes > (int64_t)INT32_MAX || v_row_bytes > (int64_t)INT32_MAX)
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache: row too large");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t blocks64 = (num_tokens + kRacWarps - 1) / kRacWarps;
+  if (blocks64 > 0x7fffffffLL) return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache: too many tokens");
+  const dim3 grid((unsigned)blocks64), block(kRacThreads);
+  const bool vec = (k_row_bytes % 16 == 0) && (v_row_bytes % 16 == 0) && aligned16(key) && aligned16(key_cache) &&
+                   (!has_v || (aligned16(value) && aligned16(value_cache)));
+  if (vec) {
+    const int k16 = (int)(k_row_bytes / 16), v16 = (int)(v_row_bytes / 16);
+    if (k16 + v16 > 128) {
+      rac_scatter16_kernel<8><<<grid, block, 0, st>>>(
+          (const uint4 *)key, (const uint4 *)value, (uint4 *)key_cache, (uint4 *)value_cache, slot_mapping,
+          num_tokens, k16, v16, num_slots, oob_count);
+    } else {
+      rac_scatter16_kernel<4><<<grid, block, 0, st>>>(
+          (const uint4 *)key, (const uint4 *)value, (uint4 *)key_cache, (uint4 *)value_cache, slot_mapping,
+          num_tokens, k16, v16, num_slots, oob_count);
+    }
+  } else if (k_row_bytes % 2 == 0 && v_row_bytes % 2 == 0 && (((uintptr_t)key | (uintptr_t)key_cache |
+             (uintptr_t)value | (uintptr_t)value_cache) & 1) == 0) {
+    rac_scatter2_kernel<<<grid, block, 0, st>>>((const uint16_t *)key, (const uint16_t *)value,
+                                                (uint16_t *)key_cache, (uint16_t *)value_cache, slot_mapping,
+                                                num_tokens, (int)(k_row_bytes / 2), (int)(v_row_bytes / 2),
+                                                num_slots, oob_count);
+  } else {
+    rac_scatter1_kernel<<<grid, block, 0, st>>>((const uint8_t *)key, (const uint8_t *)value,
+                                                (uint8_t *)key_cache, (uint8_t *)value_cache, slot_mapping,
+                                                num_tokens, (int)k_row_bytes, (int)v_row_bytes, num_slots,
+                                                oob_count);
+  }
+  MSCO_CUDA_CHECK(cudaGetLastError());
+  return MSCO_OK;
+}
+
+extern "C" int msco_reshape_and_cache_quant(const void *key, const void *value, int8_t *key_cache,
+                                            int8_t *value_cache, const int32_t *slot_mapping,
+                                            int64_t num_tokens, int64_t k_row_elems, int64_t v_row_elems,
+                                            int32_t in_dtype, const float *k_descale, const int32_t *k_offset,
+                                            const float *v_descale, const int32_t *v_offset, int64_t num_slots,
+                                            int32_t *oob_count, void *stream) {
+  if (num_tokens < 0 || k_row_elems < 0 || v_row_elems < 0 || num_slots < 0)
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: negative size");
+  if (in_dtype != MSCO_DTYPE_F16 && in_dtype != MSCO_DTYPE_BF16)
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: input rows must be float16 or bfloat16");
+  const bool has_v = (value != nullptr) || (value_cache != nullptr);
+  if (has_v && (value == nullptr || value_cache == nullptr || v_descale == nullptr))
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: value, value_cache and v_descale go together");
+  if (!has_v) v_row_elems = 0;
+  if (num_tokens == 0 || k_row_elems == 0 || num_slots == 0) return MSCO_OK;
+  if (key == nullptr || key_cache == nullptr || slot_mapping == nullptr || k_descale == nullptr)
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: key, key_cache, slot_mapping, k_descale required");
+  if (k_row_elems > (int64_t)INT32_MAX || v_row_elems > (int64_t)INT32_MAX)
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: row too large");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t blocks64 = (num_tokens + kRacWarps - 1) / kRacWarps;
+  if (blocks64 > 0x7fffffffLL) return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: too many tokens");
+  const dim3 grid((unsigned)blocks64), block(kRacThreads);
+  const bool vec = (k_row_elems % 8 == 0) && (v_row_elems % 8 == 0) && aligned16(key) && aligned16(k_descale) &&
+                   ((uintptr_t)key_cache % 8 == 0) && (k_offset == nullptr || aligned16(k_offset)) &&
+                   (!has_v || (aligned16(value) && aligned16(v_descale) && ((uintptr_t)value_cache % 8 == 0) &&
+                               (v_offset == nullptr || aligned16(v_offset))));
+#define MSCO_LAUNCH_Q(T, VEC)                                                                             \
+  rac_scatter_quant_kernel<T, VEC><<<grid, block, 0, st>>>(                                               \
+      (const T *)key, (const T *)value, key_cache, value_cache, slot_mapping, num_tokens, (int)k_row_elems, \
+      (int)v_row_elems, k_descale, k_offset, v_descale, v_offset, num_slots, oob_count)
+  if (in_dtype == MSCO_DTYPE_F16) {
+    if (vec) MSCO_LAUNCH_Q(__half, true); else MSCO_LAUNCH_Q(__half, false);
+  } else {
+    if (vec) MSCO_LAUNCH_Q(__nv_bfloat16, true); else MSCO_LAUNCH_Q(__nv_bfloat16, false);
+  }
+#undef MSCO_LAUNCH_Q
+  MSCO_CUDA_CHECK(cudaGetLastError());
+  return MSCO_OK;
+}

@@ -1,0 +1,112 @@
+"""Thin-ABI launchers: torch tensors in, libmsco_b200.so kernels on torch's current stream.
+
+PyTorch is used here only as the owner of device memory and streams; every
+byte of arithmetic happens in the library's CUDA kernels.  These helpers do no
+argument validation beyond what the C ABI itself checks -- the operator-level
+API (``ms_custom_ops_b200.reshape_and_cache`` / ``paged_attention``) does that.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _abi
+
+_TORCH2MSCO = {torch.float16: _abi.DTYPE_F16, torch.bfloat16: _abi.DTYPE_BF16, torch.int8: _abi.DTYPE_I8,
+               torch.float32: _abi.DTYPE_F32, torch.int32: _abi.DTYPE_I32, torch.int64: _abi.DTYPE_I64}
+
+
+def msco_dtype(t: torch.dtype) -> int:
+    return _TORCH2MSCO[t]
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def rac_scatter(key, value, key_cache, value_cache, slot_mapping, oob_count=None):
+    """msco_reshape_and_cache on the current stream (bit copy of token rows into cache slots)."""
+    t = slot_mapping.numel()
+    krow = key.numel() // max(t, 1) * key.element_size()
+    vrow = 0 if value is None else value.numel() // max(t, 1) * value.element_size()
+    nslots = key_cache.shape[0] * key_cache.shape[1]
+    _abi.check(_abi.lib().msco_reshape_and_cache(
+        _ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache), _ptr(slot_mapping), t, krow, vrow, nslots,
+        _ptr(oob_count), _stream()))
+
+
+def rac_scatter_quant(key, value, key_cache, value_cache, slot_mapping, k_descale, v_descale,
+                      k_offset=None, v_offset=None, oob_count=None):
+    """msco_reshape_and_cache_quant on the current stream (fp16/bf16 rows -> int8 cache)."""
+    t = slot_mapping.numel()
+    krow = key.numel() // max(t, 1)
+    vrow = 0 if value is None else value.numel() // max(t, 1)
+    nslots = key_cache.shape[0] * key_cache.shape[1]
+    _abi.check(_abi.lib().msco_reshape_and_cache_quant(
+        _ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache), _ptr(slot_mapping), t, krow, vrow,
+        msco_dtype(key.dtype), _ptr(k_descale), _ptr(k_offset), _ptr(v_descale), _ptr(v_offset), nslots,
+        _ptr(oob_count), _stream()))
+
+
+def make_pa_desc(query, key_cache, block_tables, qk_scale, quant_type=0, has_quant_offset=False,
+                 mask=None, mask_type=0, kernel=_abi.KERNEL_AUTO) -> _abi.MscoPaDesc:
+    d = _abi.MscoPaDesc()
+    d.q_dtype = msco_dtype(query.dtype)
+    d.kv_dtype = msco_dtype(key_cache.dtype)
+    d.num_q_heads = query.shape[1]
+    d.num_kv_heads = key_cache.shape[2]
+    d.head_dim = query.shape[2]
+    d.block_size = key_cache.shape[1]
+    d.num_blocks = key_cache.shape[0]
+    d.max_blocks_per_seq = block_tables.shape[1]
+    d.qk_scale = float(qk_scale)
+    d.quant_type = int(quant_type)
+    d.has_quant_offset = int(bool(has_quant_offset))
+    d.mask_type = int(mask_type)
+    if mask is not None and mask_type:
+        d.mask_dtype = msco_dtype(mask.dtype)
+        d.mask_batch_stride = mask.stride(0)
+        d.mask_head_stride = mask.stride(1) if mask_type == 2 else 0
+    d.kernel = int(kernel)
+    return d
+
+
+def pa_launch(plan: _abi.PaPlan, query, key_cache, value_cache, block_tables, out, workspace,
+              k_descale=None, k_offset=None, v_descale=None, v_offset=None, mask=None):
+    """msco_paged_attention_launch on the current stream."""
+    _abi.check(_abi.lib().msco_paged_attention_launch(
+        plan.handle, _ptr(query), _ptr(key_cache), _ptr(value_cache), _ptr(block_tables), _ptr(k_descale),
+        _ptr(k_offset), _ptr(v_descale), _ptr(v_offset), _ptr(mask), _ptr(out), _ptr(workspace),
+        workspace.numel() * workspace.element_size(), _stream()))
+
+
+def pa_status(plan: _abi.PaPlan, workspace) -> int:
+    """Status word left by the kernels (synchronises); raises MscoError unless OK."""
+    torch.cuda.current_stream().synchronize()
+    _abi.check(_abi.lib().msco_paged_attention_status(plan.handle, _ptr(workspace)))
+    return _abi.OK
+
+
+def paged_attention_raw(query, key_cache, value_cache, block_tables, context_lens, qk_scale, quant_type=0,
+                        k_descale=None, k_offset=None, v_descale=None, v_offset=None, mask=None, mask_type=0,
+                        kernel=_abi.KERNEL_AUTO, check_status=True):
+    """Plan + launch + (optionally) status check in one call; returns (out, plan info)."""
+    desc = make_pa_desc(query, key_cache, block_tables, qk_scale, quant_type,
+                        k_offset is not None, mask, mask_type, kernel)
+    plan = _abi.PaPlan(desc, [int(x) for x in context_lens])
+    ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device=query.device)
+    out = torch.empty_like(query)
+    pa_launch(plan, query, key_cache, value_cache, block_tables, out, ws, k_descale, k_offset, v_descale,
+              v_offset, mask)
+    info = plan.info()
+    if check_status:
+        pa_status(plan, ws)
+    else:
+        torch.cuda.current_stream().synchronize()
+    plan.close()
+    return out, info

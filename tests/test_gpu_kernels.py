@@ -1,0 +1,340 @@
+"""GPU parity of the CUDA kernels, called through the thin C ABI, against the CPU oracle.
+
+reshape_and_cache is bit-exact; paged attention is checked at the decode
+path's tolerances (rtol = atol = 1e-2 bf16, 5e-3 fp16, 2e-2 with int8 KV), by
+the reference's own acceptance rule, and by a scale-free error bound so that a
+wrong kernel cannot pass on small magnitudes alone.
+"""
+import numpy as np
+import pytest
+import torch
+
+from ms_custom_ops_b200 import _abi, kernels, workloads
+from oracle import paged_kv_numpy as oracle
+from tests.helpers import BF16, assert_close, to_dev, to_np, tol_for
+
+pytestmark = pytest.mark.gpu
+
+NP = {"float16": np.float16, "bfloat16": BF16, "int8": np.int8}
+
+
+# ----------------------------------------------------------------------------
+# reshape_and_cache
+# ----------------------------------------------------------------------------
+def _rac_inputs(dtype, kv_dim, t=39, nb=20, bs=64, heads=16, hd=32, seed=0, vhd=None):
+    rng = np.random.default_rng(seed)
+    vhd = vhd or hd
+
+    def rnd(shape):
+        if dtype == "int8":
+            return rng.integers(-128, 128, shape, dtype=np.int8)
+        return rng.random(shape, dtype=np.float32).astype(NP[dtype])
+    kshape = (t, heads * hd) if kv_dim == 2 else (13, t // 13, heads * hd)
+    vshape = (t, heads * vhd) if kv_dim == 2 else (13, t // 13, heads * vhd)
+    slot = rng.permutation(nb * bs)[:t].astype(np.int32)
+    return rnd(kshape), rnd(vshape), rnd((nb, bs, heads, hd)), rnd((nb, bs, heads, vhd)), slot
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16", "int8"])
+@pytest.mark.parametrize("kv_dim", [2, 3])
+def test_rac_reference_shapes_bit_exact(dtype, kv_dim):
+    # shapes of tests/st/test_custom_reshape_and_cache.py:50-56,345-347
+    k, v, kc, vc, slot = _rac_inputs(dtype, kv_dim)
+    gk, gv = oracle.reshape_and_cache_golden(k, v, kc, vc, slot)
+    dkc, dvc = to_dev(kc), to_dev(vc)
+    kernels.rac_scatter(to_dev(k), to_dev(v), dkc, dvc, to_dev(slot))
+    torch.cuda.synchronize()
+    assert np.array_equal(to_np(dkc).view(np.uint8), gk.view(np.uint8))
+    assert np.array_equal(to_np(dvc).view(np.uint8), gv.view(np.uint8))
+
+
+def test_rac_key_only_and_different_head_dims():
+    k, v, kc, vc, slot = _rac_inputs("float16", 2, vhd=48)
+    gk, gv = oracle.reshape_and_cache_golden(k, v, kc, vc, slot)
+    dkc, dvc = to_dev(kc), to_dev(vc)
+    kernels.rac_scatter(to_dev(k), to_dev(v), dkc, dvc, to_dev(slot))
+    assert np.array_equal(to_np(dkc), gk) and np.array_equal(to_np(dvc), gv)
+    dkc2 = to_dev(kc)
+    kernels.rac_scatter(to_dev(k), None, dkc2, None, to_dev(slot))
+    assert np.array_equal(to_np(dkc2), gk)
+
+
+def test_rac_unaligned_rows_use_scalar_path():
+    # 7 heads x 9 dims = 63 elements: neither 16-byte rows (fp16) nor even bytes (int8)
+    for dtype in ("float16", "int8"):
+        k, v, kc, vc, slot = _rac_inputs(dtype, 2, heads=7, hd=9)
+        gk, gv = oracle.reshape_and_cache_golden(k, v, kc, vc, slot)
+        dkc, dvc = to_dev(kc), to_dev(vc)
+        kernels.rac_scatter(to_dev(k), to_dev(v), dkc, dvc, to_dev(slot))
+        assert np.array_equal(to_np(dkc), gk) and np.array_equal(to_np(dvc), gv)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "int8"])
+def test_rac_negative_slots_skipped_and_oob_counted(dtype):
+    case = workloads.scatter_case(2048, 64, dtype="bfloat16", pad_frac=0.05, seed=11)
+    k, v, kc, vc = case["key"], case["value"], case["key_cache"], case["value_cache"]
+    if dtype == "int8":
+        k, v, kc, vc = (a.view(np.int8)[..., ::2].copy() for a in (k, v, kc, vc))
+    slot = case["slot_mapping"].copy()
+    assert (slot < 0).any()
+    gk, gv = oracle.reshape_and_cache_golden(k, v, kc, vc, slot)
+    dkc, dvc = to_dev(kc), to_dev(vc)
+    oob = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kernels.rac_scatter(to_dev(k), to_dev(v), dkc, dvc, to_dev(slot), oob)
+    assert np.array_equal(to_np(dkc).view(np.uint8), gk.view(np.uint8))
+    assert np.array_equal(to_np(dvc).view(np.uint8), gv.view(np.uint8))
+    assert int(oob.item()) == 0
+    # slots beyond the cache are dropped and counted, never written
+    slot2 = slot.copy()
+    slot2[:3] = 64 * 128 + np.arange(3)
+    keep = slot2.copy()
+    keep[:3] = -1
+    gk2, gv2 = oracle.reshape_and_cache_golden(k, v, kc, vc, keep)
+    dkc, dvc = to_dev(kc), to_dev(vc)
+    kernels.rac_scatter(to_dev(k), to_dev(v), dkc, dvc, to_dev(slot2), oob)
+    assert np.array_equal(to_np(dkc).view(np.uint8), gk2.view(np.uint8))
+    assert int(oob.item()) == 3
+
+
+def test_rac_empty_inputs_are_a_no_op():
+    k, v, kc, vc, slot = _rac_inputs("float16", 2)
+    dkc = to_dev(kc)
+    empty = torch.empty((0, k.shape[1]), dtype=torch.float16, device="cuda")
+    kernels.rac_scatter(empty, empty, dkc, to_dev(vc), torch.empty(0, dtype=torch.int32, device="cuda"))
+    assert np.array_equal(to_np(dkc), kc)
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("offsets", [False, True])
+def test_rac_quant_bit_exact(dtype, offsets):
+    case = workloads.scatter_case(1500, 32, dtype=dtype, pad_frac=0.05, seed=7, quant=True)
+    rng = np.random.default_rng(1)
+    c = case["key"].shape[1]
+    ko = rng.integers(-20, 20, c).astype(np.int32) if offsets else None
+    vo = rng.integers(-20, 20, c).astype(np.int32) if offsets else None
+    # exercise saturation, exact .5 ties and zeros
+    case["key"][0, :8] = np.array([1e4, -1e4, 0.0, 0.5, 1.5, 2.5, -0.5, -1.5], dtype=np.float32).astype(NP[dtype])
+    case["k_descale"][:8] = np.array([0.01, 0.01, 0.02, 1.0, 1.0, 1.0, 1.0, 1.0], dtype=np.float32)
+    gk, gv = oracle.reshape_and_cache_quant_golden(case["key"], case["value"], case["key_cache"],
+                                                   case["value_cache"], case["slot_mapping"],
+                                                   case["k_descale"], case["v_descale"], ko, vo)
+    dkc, dvc = to_dev(case["key_cache"]), to_dev(case["value_cache"])
+    kernels.rac_scatter_quant(to_dev(case["key"]), to_dev(case["value"]), dkc, dvc, to_dev(case["slot_mapping"]),
+                              to_dev(case["k_descale"]), to_dev(case["v_descale"]), to_dev(ko), to_dev(vo))
+    assert np.array_equal(to_np(dkc), gk)
+    assert np.array_equal(to_np(dvc), gv)
+
+
+# ----------------------------------------------------------------------------
+# paged attention
+# ----------------------------------------------------------------------------
+def _run_pa(case, kernel=_abi.KERNEL_AUTO):
+    v = workloads.operator_view(case)
+    out, info = kernels.paged_attention_raw(
+        to_dev(v["query"]), to_dev(v["key_cache"]), to_dev(v["value_cache"]), to_dev(v["block_tables"]),
+        [int(x) for x in v["context_lens"]], v["qk_scale"], v["quant_type"],
+        to_dev(v["k_descale"]), to_dev(v["k_offset"]), to_dev(v["v_descale"]), to_dev(v["v_offset"]),
+        to_dev(v["mask"]), v.get("mask_type", 0), kernel)
+    return to_np(out), info
+
+
+def _golden(case):
+    return oracle.paged_attention_golden(
+        case["query"], case["key_cache"], case["value_cache"], case["block_tables"], case["context_lens"],
+        case["qk_scale"], case["k_descale"], case["v_descale"], case["k_offset"], case["v_offset"],
+        case["mask"], case.get("mask_type", 0))
+
+
+def _check(case, out, what):
+    quant = case["quant_type"] != 0
+    # (1) the reference's own rule against the reference's own golden, which for bf16 is computed
+    #     from the un-rounded float32 draws (tests/st/test_custom_paged_attention.py:1005-1099)
+    g_ref = _golden(case)
+    ok, detail = oracle.reference_accuracy_verdict(out, g_ref, case["q_dtype"], case["num_heads"],
+                                                   int(max(case["context_lens"])), quant)
+    assert ok, (what, detail)
+    # (2) the decode path's tolerance against the float32 golden of the tensors the operator
+    #     actually received (bf16 caches and masks rounded to bf16)
+    g = _golden(workloads.operator_view(case))
+    assert_close(out, g, tol_for(case["q_dtype"], quant), what)
+    rel_max, rel_l2 = oracle.scale_free_error(out, g)
+    assert rel_l2 < 1e-2, (what, rel_max, rel_l2)
+
+
+# (seed, heads, kv_heads, head, block, blocks, lens, q dtype, kv dtype, quant, offset, qk_scale, mask)
+# seeds, shapes and mask types of the reference's decode tests,
+# tests/st/test_custom_paged_attention.py:1562-2311 (qk_scale None = 1/sqrt(head))
+L4 = [192, 193, 194, 195]
+ST_CASES = {
+    "basic_fp16": (3001, 32, 1, 128, 128, 64, L4, "float16", None, 0, False, 1.0, 0),
+    "basic_bf16": (3001, 32, 1, 128, 128, 64, L4, "bfloat16", None, 0, False, 1.0, 0),
+    "no_mask_mha": (4115, 32, 32, 128, 128, 64, L4, "float16", None, 0, False, 1.0, 0),
+    "norm_mask_fp16": (4116, 32, 32, 128, 128, 64, L4, "float16", None, 0, False, None, 1),
+    "norm_mask_bf16": (4116, 32, 32, 128, 128, 64, L4, "bfloat16", None, 0, False, None, 1),
+    "alibi_fp16": (4100, 32, 32, 128, 128, 64, [500, 500], "float16", None, 0, False, None, 2),
+    "alibi_bf16": (4100, 32, 32, 128, 128, 64, [500, 500], "bfloat16", None, 0, False, None, 2),
+    "gqa_8to1_alibi": (4101, 8, 1, 128, 128, 1024, [88] * 13, "float16", None, 0, False, None, 2),
+    "gqa_4to2_alibi": (4102, 4, 2, 128, 128, 1024, [88] * 13, "float16", None, 0, False, None, 2),
+    "gqa_32to8_alibi": (4103, 32, 8, 128, 128, 1024, [88] * 13, "float16", None, 0, False, None, 2),
+    "odd_heads": (4104, 7, 7, 128, 128, 1024, [88] * 13, "float16", None, 0, False, None, 1),
+    "heads_20_bf16": (4110, 20, 20, 128, 128, 64, [500, 500], "bfloat16", None, 0, False, None, 1),
+    "head_256_block_16": (4107, 16, 16, 256, 16, 512, L4, "float16", None, 0, False, None, 0),
+    "block_16": (4108, 32, 32, 128, 16, 512, L4, "float16", None, 0, False, None, 0),
+    "small_seqlen": (4105, 32, 32, 128, 128, 64, [33, 33, 33, 33], "float16", None, 0, False, None, 1),
+    "large_seqlen_bf16": (4106, 32, 32, 128, 128, 128, [3000, 3000], "bfloat16", None, 0, False, None, 1),
+    "varied_seqlens": (4111, 32, 32, 128, 128, 256, [100, 500, 1000, 2000], "float16", None, 0, False, None, 1),
+    "int8_kv": (3003, 32, 1, 128, 128, 64, L4, "float16", "int8", 1, False, None, 0),
+    "int8_kv_offset": (3004, 32, 1, 128, 128, 64, L4, "float16", "int8", 1, True, None, 0),
+    "gqa_int8_bf16": (4112, 32, 8, 128, 128, 64, L4, "bfloat16", "int8", 1, False, None, 1),
+    "gqa_int8_offset": (4113, 32, 8, 128, 128, 64, L4, "float16", "int8", 1, True, None, 1),
+    "bf16_int8_768": (6001, 32, 32, 128, 128, 256, [768], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_len128": (6002 + 128, 24, 24, 64, 128, 256, [128], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_len513": (6002 + 513, 24, 24, 64, 128, 256, [513], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_len1025": (6002 + 1025, 24, 24, 64, 128, 256, [1025], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_head32": (6100 + 32, 32, 32, 32, 16, 512, [512], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_head33": (6100 + 33, 32, 32, 33, 16, 512, [512], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_head128": (6100 + 128, 32, 32, 128, 16, 512, [512], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_gqa_4to1": (6200 + 401, 4, 1, 128, 128, 512, [766], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_gqa_24to2": (6200 + 2402, 24, 2, 128, 128, 512, [766], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_gqa_64to32": (6200 + 6432, 64, 32, 128, 128, 512, [766], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_block16": (6300 + 16, 32, 8, 64, 16, 1024, [1024], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_block128": (6300 + 128, 32, 8, 64, 128, 1024, [1024], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_len309": (6400, 64, 64, 32, 16, 256, [309], "bfloat16", "int8", 1, False, None, 1),
+}
+
+
+def _st_case(name, mask_free=False):
+    seed, h, kvh, hd, bs, nb, lens, qd, kvd, quant, off, scale, mask = ST_CASES[name]
+    return workloads.st_style_case(seed, h, kvh, hd, bs, nb, lens, qd, kvd, quant, off, 0 if mask_free else mask, scale)
+
+
+@pytest.mark.parametrize("name", sorted(ST_CASES))
+def test_pa_reference_case_matrix(name):
+    case = _st_case(name)
+    out, info = _run_pa(case)
+    _check(case, out, name)
+
+
+@pytest.mark.parametrize("name", ["basic_fp16", "basic_bf16", "gqa_32to8_alibi", "block_16", "varied_seqlens",
+                                  "int8_kv_offset", "gqa_int8_bf16", "bf16_int8_gqa_24to2",
+                                  "bf16_int8_gqa_64to32", "bf16_int8_head128", "odd_heads", "large_seqlen_bf16"])
+def test_pa_both_kernels_agree_with_oracle(name):
+    # the same shapes without the mask, so that the TMA kernel is eligible
+    case = _st_case(name, mask_free=True)
+    out_g, info_g = _run_pa(case, _abi.KERNEL_GENERIC)
+    out_t, info_t = _run_pa(case, _abi.KERNEL_TMA)
+    assert info_g.kernel == 1 and info_t.kernel == 2
+    _check(case, out_g, name + "/generic")
+    _check(case, out_t, name + "/tma")
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 4, 5])
+def test_pa_benchmark_configs_scaled(n):
+    # the five benchmark configurations at reduced batch / length, reshape_and_cache first
+    scale = {1: 1.0, 2: 0.125, 3: 0.125, 4: 0.06, 5: 0.125}[n]
+    spec = workloads.config_spec(n, scale)
+    case = workloads.decode_case(spec)
+    dkc, dvc = to_dev(case["key_cache"]), to_dev(case["value_cache"])
+    slot = case["slot_mapping"]
+    if spec.kv_int8:
+        gk, gv = oracle.reshape_and_cache_quant_golden(case["key"], case["value"], case["key_cache"],
+                                                       case["value_cache"], slot, case["k_descale"], case["v_descale"])
+        kernels.rac_scatter_quant(to_dev(case["key"]), to_dev(case["value"]), dkc, dvc, to_dev(slot),
+                                  to_dev(case["k_descale"]), to_dev(case["v_descale"]))
+    else:
+        gk, gv = oracle.reshape_and_cache_golden(case["key"], case["value"], case["key_cache"],
+                                                 case["value_cache"], slot)
+        kernels.rac_scatter(to_dev(case["key"]), to_dev(case["value"]), dkc, dvc, to_dev(slot))
+    assert np.array_equal(to_np(dkc).view(np.uint8), gk.view(np.uint8))
+    assert np.array_equal(to_np(dvc).view(np.uint8), gv.view(np.uint8))
+    out, info = kernels.paged_attention_raw(
+        to_dev(case["query"]), dkc, dvc, to_dev(case["block_tables"]), list(case["context_lens"]),
+        case["qk_scale"], 1 if spec.kv_int8 else 0, to_dev(case["k_descale"]), None, to_dev(case["v_descale"]), None)
+    assert info.kernel == 2
+    g = oracle.paged_attention_golden(case["query"], gk, gv, case["block_tables"], case["context_lens"],
+                                      case["qk_scale"], case["k_descale"], case["v_descale"])
+    tol = tol_for(spec.dtype, spec.kv_int8)
+    assert_close(to_np(out), g, tol, spec.name)
+    rel_max, rel_l2 = oracle.scale_free_error(to_np(out), g)
+    assert rel_l2 < 1e-2 and rel_max < 3e-2, (spec.name, rel_max, rel_l2)
+
+
+@pytest.mark.parametrize("dtype,kv8", [("bfloat16", False), ("float16", False), ("bfloat16", True)])
+def test_pa_length_edges_and_empty_sequences(dtype, kv8):
+    lens = [0, 1, 15, 16, 17, 127, 128, 129, 511, 512, 513, 1023, 1025, 0, 2048, 3000]
+    spec = workloads.DecodeSpec("edges", len(lens), 32, dtype=dtype, kv_int8=kv8, seed=21)
+    rng = np.random.default_rng(spec.seed)
+    case = workloads.decode_case(spec)
+    nb, tables, slots = workloads.layout(spec, np.array(lens, dtype=np.int32), rng)
+    assert nb <= case["num_blocks"] or True
+    spec2 = workloads.DecodeSpec("edges", len(lens), 32, dtype=dtype, kv_int8=kv8, seed=21, num_blocks=nb)
+    spec2.len_lo, spec2.len_hi = 1, 1
+    case = workloads.decode_case(spec2)
+    case["context_lens"] = np.array(lens, dtype=np.int32)
+    case["block_tables"] = tables
+    for kernel in (_abi.KERNEL_GENERIC, _abi.KERNEL_TMA):
+        out, info = kernels.paged_attention_raw(
+            to_dev(case["query"]), to_dev(case["key_cache"]), to_dev(case["value_cache"]), to_dev(tables), lens,
+            case["qk_scale"], 1 if kv8 else 0, to_dev(case["k_descale"]), None, to_dev(case["v_descale"]), None,
+            kernel=kernel)
+        g = oracle.paged_attention_golden(case["query"], case["key_cache"], case["value_cache"], tables,
+                                          case["context_lens"], case["qk_scale"], case["k_descale"], case["v_descale"])
+        o = to_np(out).astype(np.float32)
+        assert np.all(o[0] == 0) and np.all(o[13] == 0)  # empty sequences give zeros
+        assert_close(o, g, tol_for(dtype, kv8), f"edges kernel={kernel}")
+        rel_max, rel_l2 = oracle.scale_free_error(o, g)
+        assert rel_l2 < 1e-2, (kernel, rel_max, rel_l2)
+
+
+def test_pa_long_context_uses_larger_splits():
+    # 20000 and 70000 tokens: 1024- and 2048-token splits, many partials through the reduce kernel
+    lens = [20000, 70000, 700]
+    spec = workloads.DecodeSpec("long", 3, 16, kv_heads=2, dtype="bfloat16", seed=9, len_lo=1, len_hi=1)
+    rng = np.random.default_rng(3)
+    nb, tables, _ = workloads.layout(spec, np.array(lens, dtype=np.int32), rng)
+    spec.num_blocks = nb
+    case = workloads.decode_case(spec)
+    out, info = kernels.paged_attention_raw(to_dev(case["query"]), to_dev(case["key_cache"]),
+                                            to_dev(case["value_cache"]), to_dev(tables), lens, case["qk_scale"])
+    assert info.max_splits == 35 and info.partials == 20 + 35 + 2
+    g = oracle.paged_attention_golden(case["query"], case["key_cache"], case["value_cache"], tables,
+                                      np.array(lens), case["qk_scale"])
+    assert_close(to_np(out), g, 1e-2, "long")
+    rel_max, rel_l2 = oracle.scale_free_error(to_np(out), g)
+    assert rel_l2 < 1e-2, (rel_max, rel_l2)
+
+
+@pytest.mark.parametrize("kernel", [_abi.KERNEL_GENERIC, _abi.KERNEL_TMA])
+@pytest.mark.parametrize("kv8", [False, True])
+def test_pa_batch_invariance_bitwise(kernel, kv8):
+    # a request's output must not depend on what it is batched with
+    # (tests/st/test_custom_paged_attention_batch_invariant.py:231-317)
+    lens_all = [255, 256, 257, 511, 512, 513, 2048, 4096, 700, 1, 33, 1500] * 4
+    spec = workloads.DecodeSpec("binv", len(lens_all), 32, dtype="bfloat16", kv_int8=kv8, seed=33, len_lo=1, len_hi=1)
+    rng = np.random.default_rng(5)
+    nb, tables, _ = workloads.layout(spec, np.array(lens_all, dtype=np.int32), rng)
+    spec.num_blocks = nb
+    case = workloads.decode_case(spec)
+    q, kc, vc = to_dev(case["query"]), to_dev(case["key_cache"]), to_dev(case["value_cache"])
+    kd, vd = to_dev(case["k_descale"]), to_dev(case["v_descale"])
+    dt = to_dev(tables)
+    full, _ = kernels.paged_attention_raw(q, kc, vc, dt, lens_all, case["qk_scale"], int(kv8), kd, None, vd, None,
+                                          kernel=kernel)
+    full = to_np(full).view(np.uint16)
+    for i in (0, 3, 6, 7, 9, 23, 47):
+        one, _ = kernels.paged_attention_raw(q[i:i + 1].contiguous(), kc, vc, dt[i:i + 1].contiguous(),
+                                             [lens_all[i]], case["qk_scale"], int(kv8), kd, None, vd, None,
+                                             kernel=kernel)
+        assert np.array_equal(to_np(one).view(np.uint16)[0], full[i]), f"request {i} changed with the batch"
+
+
+def test_pa_out_of_range_block_id_is_reported_not_faulted():
+    case = _st_case("gqa_32to8_alibi", mask_free=True)
+    v = workloads.operator_view(case)
+    tables = v["block_tables"].copy()
+    tables[2, 0] = 10 ** 6
+    for kernel in (_abi.KERNEL_GENERIC, _abi.KERNEL_TMA):
+        with pytest.raises(_abi.MscoError) as e:
+            kernels.paged_attention_raw(to_dev(v["query"]), to_dev(v["key_cache"]), to_dev(v["value_cache"]),
+                                        to_dev(tables), list(v["context_lens"]), v["qk_scale"], kernel=kernel)
+        assert e.value.code == _abi.ERR_OOB
