@@ -185,12 +185,12 @@ extern "C" int msco_reshape_and_cache(const void *key, const void *value, void *
                                       void *stream) {
   if (num_tokens < 0 || k_row_bytes < 0 || v_row_bytes < 0 || num_slots < 0)
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache: negative size");
+  // zero-sized inputs: the reference skips execution (reshape_and_cache.cc:90-119)
+  if (num_tokens == 0 || k_row_bytes == 0 || num_slots == 0) return MSCO_OK;
   const bool has_v = (value != nullptr) || (value_cache != nullptr);
   if (has_v && (value == nullptr || value_cache == nullptr))
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache: value and value_cache must be given together");
   if (!has_v) v_row_bytes = 0;
-  // zero-sized inputs: the reference skips execution (reshape_and_cache.cc:90-119)
-  if (num_tokens == 0 || k_row_bytes == 0 || num_slots == 0) return MSCO_OK;
   if (key == nullptr || key_cache == nullptr || slot_mapping == nullptr)
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache: key, key_cache and slot_mapping must not be NULL");
   if (k_row_bytes > (int64_t)INT32_MAX || v_row_bytes > (int64_t)INT32_MAX)
@@ -238,11 +238,11 @@ extern "C" int msco_reshape_and_cache_quant(const void *key, const void *value, 
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: negative size");
   if (in_dtype != MSCO_DTYPE_F16 && in_dtype != MSCO_DTYPE_BF16)
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: input rows must be float16 or bfloat16");
+  if (num_tokens == 0 || k_row_elems == 0 || num_slots == 0) return MSCO_OK;
   const bool has_v = (value != nullptr) || (value_cache != nullptr);
   if (has_v && (value == nullptr || value_cache == nullptr || v_descale == nullptr))
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: value, value_cache and v_descale go together");
   if (!has_v) v_row_elems = 0;
-  if (num_tokens == 0 || k_row_elems == 0 || num_slots == 0) return MSCO_OK;
   if (key == nullptr || key_cache == nullptr || slot_mapping == nullptr || k_descale == nullptr)
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: key, key_cache, slot_mapping, k_descale required");
   if (k_row_elems > (int64_t)INT32_MAX || v_row_elems > (int64_t)INT32_MAX)
