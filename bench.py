@@ -1,0 +1,427 @@
+"""Benchmark of the paged-KV decode hot path: reshape_and_cache -> paged_attention.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
+
+One step = one decode step over one batch of synthetic sequences: the newest
+token's K/V rows are scattered into the paged cache (reshape_and_cache), then
+paged attention runs over every sequence's context.  The metric is decode
+tokens per second (= sequences per step / step time), whole job.
+
+Printed JSON line (rank 0):
+  value      device-timed throughput with every input resident in HBM
+  e2e        the same step through the operator API with the step's inputs in pinned host memory:
+             host->device copies of query / new rows / slots / block tables and the device->host
+             read of the attention output are inside the timed region
+  roofline   the attention kernel alone: algorithmic bytes / its CUDA-event duration, against the
+             measured HBM copy bandwidth (MEASURED_PEAKS.json, else the stated fallback)
+  cpu_baseline  the CPU restatement of the reference golden (oracle/, all host cores), timed on
+             the same workload; its output doubles as a full-size parity check of the GPU result
+
+With N > 1 (torchrun) the KV cache is partitioned by kv head: each rank owns
+num_kv_heads / N heads of every block and the matching q heads, and the
+per-head outputs are all-gathered over NCCL.  Total work is fixed: "strong".
+
+`--impl reference` times the CPU implementation of the same path (the oracle
+port of the reference's numpy golden, all host threads) on a bounded sample
+of the workload and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from ms_custom_ops_b200 import workloads  # noqa: E402
+
+METRIC = "paged-attn decode tokens/s"
+UNIT = "tokens/s"
+FALLBACK_HBM_GBS = 6650.0
+L2_BYTES = 126 << 20
+
+
+def workload_spec(name):
+    n = int(name.lower().lstrip("c"))
+    return workloads.config_spec(n)
+
+
+def workload_config(spec, lens, extra=None):
+    cfg = {"workload": f"{spec.name}: batch {spec.batch}, {spec.num_heads} q heads / {spec.kv_heads} kv heads, "
+                       f"head_dim {spec.head_size}, block_size {spec.block_size}, "
+                       f"{'int8 KV + ' if spec.kv_int8 else ''}{spec.dtype}, context_lens {spec.len_dist} "
+                       f"[{spec.len_lo},{spec.len_hi}], one new token per sequence via reshape_and_cache",
+           "batch": spec.batch, "kv_tokens": int(np.asarray(lens, dtype=np.int64).sum()),
+           "seed": spec.seed}
+    if extra:
+        cfg.update(extra)
+    return cfg
+
+
+# ----------------------------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, gpu_uuid=None):
+        self.path = tempfile.mktemp(prefix="clocks_", suffix=".csv")
+        cmd = ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"]
+        if gpu_uuid:
+            cmd.insert(1, f"--id={gpu_uuid}")
+        try:
+            self.proc = subprocess.Popen(cmd, stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx.append(float(parts[1]))
+                except ValueError:
+                    continue
+                for name, val in zip(self.NAMES, parts[3:7]):
+                    if val.lower() == "active":
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def measured_hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ----------------------------------------------------------------------------------------------
+# reference arm: CPU implementation of the path on the host cores
+# ----------------------------------------------------------------------------------------------
+def cpu_step(c_oracle, case, threads=0):
+    """One decode step on the CPU: scatter the new rows into the caches in place, then attention.
+    Returns the output."""
+    if case["k_descale"] is not None:
+        gk, gv = c_oracle.reshape_and_cache_quant(case["key"], case["value"], case["key_cache"], case["value_cache"],
+                                                  case["slot_mapping"], case["k_descale"], case["v_descale"],
+                                                  threads=threads, inplace=True)
+    else:
+        gk, gv = c_oracle.reshape_and_cache(case["key"], case["value"], case["key_cache"], case["value_cache"],
+                                            case["slot_mapping"], threads=threads, inplace=True)
+    return c_oracle.paged_attention(case["query"], gk, gv, case["block_tables"], case["context_lens"],
+                                    case["qk_scale"], case["k_descale"], case["v_descale"], threads=threads)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return  # one CPU run per job; the other ranks have nothing to do
+    from oracle import c_oracle
+    spec = workload_spec(args.workload)
+    full_batch = spec.batch
+    # bounded sample: the first `sample` sequences' worth of the same length distribution
+    sample = min(full_batch, args.cpu_sample)
+    sspec = workloads.DecodeSpec(**{**spec.__dict__, "batch": sample})
+    case = workloads.decode_case(sspec)
+    cores = c_oracle.max_threads()
+    for _ in range(args.warmup):
+        cpu_step(c_oracle, case)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(c_oracle, case)
+    dt = (time.perf_counter() - t0) / max(args.steps, 1)
+    value = sample / dt
+    what = (f"{sample} of {full_batch} sequences per step ({int(case['context_lens'].sum())} context tokens), "
+            f"C restatement of the reference numpy golden, OpenMP over (sequence, kv head)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(spec, case["context_lens"], {"sample": what}),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": what},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    import ms_custom_ops_b200 as ops
+    from ms_custom_ops_b200 import _abi, kernels
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    spec = workload_spec(args.workload)
+    if spec.kv_heads % world != 0:
+        raise SystemExit(f"{spec.kv_heads} kv heads cannot be split over {world} GPUs")
+    hpr = spec.kv_heads // world                      # kv heads per rank
+    h0, h1 = rank * hpr, (rank + 1) * hpr
+    g = spec.num_heads // spec.kv_heads
+    case = workloads.decode_case_device(spec, dev, (h0, h1))
+    lens = [int(x) for x in case["context_lens"]]
+    quant = 1 if spec.kv_int8 else 0
+    q, key, val = case["query"], case["key"], case["value"]
+    kc, vc, bt, slot = case["key_cache"], case["value_cache"], case["block_tables"], case["slot_mapping"]
+    kd, vd = case["k_descale"], case["v_descale"]
+    hq_local = hpr * g
+
+    desc = kernels.make_pa_desc(q, kc, bt, case["qk_scale"], quant)
+    plan = _abi.PaPlan(desc, lens)
+    info = plan.info()
+    ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device=dev)
+    out_local = torch.empty_like(q)
+    # gathered layout: [rank, batch, q heads per rank, head_dim]; rank r's slice holds q heads
+    # r*hq_local .. (r+1)*hq_local-1, i.e. out[b, h] = gathered[h // hq_local, b, h % hq_local]
+    gathered = torch.empty((world,) + tuple(q.shape), dtype=q.dtype, device=dev) if world > 1 else None
+
+    def step():
+        if spec.kv_int8:
+            kernels.rac_scatter_quant(key, val, kc, vc, slot, kd, vd)
+        else:
+            kernels.rac_scatter(key, val, kc, vc, slot)
+        kernels.pa_launch(plan, q, kc, vc, bt, out_local, ws, kd, None, vd, None)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out_local)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timed region ------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step()
+    kernels.pa_status(plan, ws)
+    graph = None
+    if args.graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(2):
+            graph.replay()
+    else:
+        plan.profile_enable(True)
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)) if rank == 0 else None
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    kernel_ms = [] if graph is not None else plan.profile_read()
+    if graph is not None:  # kernel durations from an eager pass of the same steps, events around the kernel
+        plan.profile_enable(True)
+        for _ in range(min(args.steps, 64)):
+            step()
+        torch.cuda.synchronize()
+        kernel_ms = plan.profile_read()
+    plan.profile_enable(False)
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+
+    # ---- end-to-end through the operator API, inputs in pinned host memory ----------------
+    pin = lambda x: x.detach().cpu().pin_memory()
+    h_q, h_key, h_val, h_slot, h_bt = pin(q), pin(key), pin(val), pin(slot), pin(bt)
+    h_lens = torch.tensor(lens, dtype=torch.int32)
+    out_shape = (world,) + tuple(q.shape) if world > 1 else tuple(q.shape)
+    h_out = torch.empty(out_shape, dtype=q.dtype).pin_memory()
+    d_q, d_key, d_val, d_slot, d_bt = (torch.empty_like(x) for x in (q, key, val, slot, bt))
+    pa_kw = dict(q_head_num=hq_local, kv_head_num=hpr, qk_scale=case["qk_scale"])
+    if spec.kv_int8:
+        pa_kw.update(quant_type=1, k_descale=kd, v_descale=vd)
+
+    def e2e_step():
+        for d, h in ((d_q, h_q), (d_key, h_key), (d_val, h_val), (d_slot, h_slot), (d_bt, h_bt)):
+            d.copy_(h, non_blocking=True)
+        if spec.kv_int8:
+            ops.reshape_and_cache_quant(d_key, d_val, kc, vc, d_slot, kd, vd)
+        else:
+            ops.reshape_and_cache(d_key, d_val, kc, vc, d_slot, 0, 0)
+        o = ops.paged_attention(d_q, kc, vc, d_bt, h_lens, **pa_kw)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, o)
+            o = gathered
+        h_out.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the step's result is read on the host
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / args.steps
+    clocks = sampler.stop() if sampler else None
+    ops.paged_attention_check_status(dev)
+    h2d = sum(x.numel() * x.element_size() for x in (h_q, h_key, h_val, h_slot, h_bt))
+    d2h = h_out.numel() * h_out.element_size()
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the attention kernel --------------------------------------------------
+    kvb = 1 if spec.kv_int8 else 2
+    alg_bytes = workloads.algorithmic_bytes_attention(lens, hq_local, hpr, spec.head_size, kvb, quant=spec.kv_int8)
+    peak, peak_src = measured_hbm_peak()
+    roofline = {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None,
+                "kernel": "pa_tma_kernel" if info.kernel == 2 else "pa_generic_kernel",
+                "peak_source": peak_src, "algorithmic_bytes": alg_bytes}
+    if kernel_ms:
+        kms = statistics.mean(kernel_ms)
+        roofline.update(achieved=alg_bytes / kms / 1e6, frac=alg_bytes / kms / 1e6 / peak, kernel_ms=kms,
+                        frac_of_8tbs=alg_bytes / kms / 1e6 / 8000.0, launches_timed=len(kernel_ms))
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        try:
+            tr = json.load(open(traffic_file)).get(args.workload.lower())
+            if tr:  # DRAM bytes per context token from an ncu capture, scaled to this launch
+                roofline["traffic"] = tr["dram_bytes_per_kv_token_per_head"] * sum(lens) * hpr
+        except Exception:
+            pass
+
+    # ---- CPU baseline on the same workload (also the full-size parity check) ---------------
+    cpu = None
+    checked = None
+    if not args.no_cpu:
+        from oracle import c_oracle
+        nseq = min(spec.batch, args.cpu_sample)
+        # pre-scatter state is gone (the steps wrote the rows); the scatter is idempotent, so the
+        # current cache is the post-scatter cache and the CPU step reproduces the same result
+        host = {"query": _to_np(q[:nseq]), "key": _to_np(key[:nseq]), "value": _to_np(val[:nseq]),
+                "key_cache": _to_np(kc), "value_cache": _to_np(vc),
+                "block_tables": bt[:nseq].cpu().numpy(), "slot_mapping": slot[:nseq].cpu().numpy(),
+                "context_lens": np.array(lens[:nseq], dtype=np.int32), "qk_scale": case["qk_scale"],
+                "k_descale": None if kd is None else kd.cpu().numpy(),
+                "v_descale": None if vd is None else vd.cpu().numpy()}
+        ref = cpu_step(c_oracle, host)  # warm-up + reference output
+        reps, t_best = 0, float("inf")
+        t_begin = time.perf_counter()
+        while reps < 3 and time.perf_counter() - t_begin < 20.0:
+            t0 = time.perf_counter()
+            cpu_step(c_oracle, host)
+            t_best = min(t_best, time.perf_counter() - t0)
+            reps += 1
+        sample = (f"{nseq} of {spec.batch} sequences ({int(sum(lens[:nseq]))} context tokens), kv heads {h0}..{h1 - 1}, "
+                  f"best of {reps}; C restatement of the reference numpy golden, OpenMP")
+        cpu = {"value": nseq / t_best, "unit": UNIT, "cores": c_oracle.max_threads(), "kind": "port",
+               "sample": sample}
+        got = out_local[:nseq].float().cpu().numpy()
+        err = np.abs(got - ref)
+        tol = 2e-2 if spec.kv_int8 else 1e-2
+        checked = {"sequences": nseq, "max_abs_err": float(err.max()), "max_abs_golden": float(np.abs(ref).max()),
+                   "rel_l2": float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30)),
+                   "within_tolerance": bool(np.all(err <= tol + tol * np.abs(ref))), "tolerance": tol}
+
+    kernels_per_step = 2 + (1 if info.partials > 0 or min(lens) == 0 else 0)
+    line = {
+        "metric": METRIC, "value": spec.batch / ms_step * 1e3, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16" if spec.dtype == "bfloat16" else "f16", "data": "synthetic",
+        "config": workload_config(spec, lens, {
+            "parallelism": f"kv-head sharding x{world}" + (" + NCCL all-gather of outputs" if world > 1 else ""),
+            "l2": f"inputs larger than L2: {alg_bytes / 1e6:.0f} MB of KV per GPU per step vs {L2_BYTES >> 20} MB",
+            "launch": "CUDA graph replay" if graph is not None else "eager launches on one stream",
+            "work_items": info.work_items, "split_partials": info.partials, "grid": info.grid}),
+        "e2e": {"value": spec.batch / e2e_ms * 1e3, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+        "gpu_launches": kernels_per_step * args.steps,
+        "roofline": roofline, "cpu_baseline": cpu, "parity_check": checked, "clocks": clocks,
+        "achieved_gbs_step": alg_bytes / ms_step / 1e6,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _to_np(t):
+    import torch
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.uint16).numpy().view(workloads.bfloat16)
+    return t.numpy()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2", help="c1..c5: benchmark configuration (default c2)")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays of the step")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity check")
+    ap.add_argument("--cpu-sample", type=int, default=64, help="sequences in the CPU sample")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

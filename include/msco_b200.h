@@ -171,8 +171,18 @@ int msco_paged_attention_launch(const MscoPaPlan *plan, const void *query, const
 /* After the stream has been synchronised: reads the status word the kernels
  * leave in the workspace.  MSCO_OK, MSCO_ERR_TIMEOUT (a bounded wait inside
  * the kernel expired) or MSCO_ERR_OOB (a block id outside the cache was met;
- * the affected tokens were skipped).  Synchronous device-to-host copy. */
+ * the affected tokens were skipped).  Synchronous device-to-host copy.  `plan`
+ * may be NULL (the status word is the first word of the workspace). */
 int msco_paged_attention_status(const MscoPaPlan *plan, const void *workspace);
+
+/* Kernel timing for benchmarks.  After msco_paged_attention_profile_enable(plan, 1) every launch
+ * of this plan records a pair of CUDA events directly around the attention kernel (not around the
+ * plan upload or the reduce kernel) into a ring of 64 pairs owned by the plan.
+ * msco_paged_attention_profile_read synchronises on the recorded pairs and returns the kernel
+ * durations of the most recent launches, oldest first (at most `max_count`, at most 64), then
+ * clears the ring.  Off by default; enabling it makes the plan unsuitable for stream capture. */
+int msco_paged_attention_profile_enable(MscoPaPlan *plan, int32_t enable);
+int msco_paged_attention_profile_read(MscoPaPlan *plan, float *kernel_ms, int32_t max_count, int32_t *count);
 
 #ifdef __cplusplus
 }

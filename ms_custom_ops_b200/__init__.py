@@ -1,13 +1,255 @@
-"""B200-native paged-KV decode operators: reshape_and_cache and paged_attention.
+"""B200-native paged-KV decode operators: ``reshape_and_cache`` and ``paged_attention``.
 
-Drop-in for the two operators of the same names in `ms_custom_ops`
-(python/ms_custom_ops/__init__.py:76 re-exports them from the plugin module):
-same argument names, order, defaults, layouts, dtypes and attribute values.
-Underneath: hand-written CUDA kernels for sm_100a behind a thin C ABI
-(libmsco_b200.so).  There is no CPU or PyTorch fallback; importing the
-operators without the built library raises.
+Drop-in for the two operators of the same names in ``ms_custom_ops``
+(python/ms_custom_ops/__init__.py:76 re-exports them from the plugin module;
+pybind definitions at ops/c_api/reshape_and_cache/reshape_and_cache.cc:212-217
+and ops/c_api/paged_attention/paged_attention_pynative.cc:763-777): the same
+argument names, order, defaults, layouts, dtypes and attribute values.
+
+Call path: this module -> libms_custom_ops_host.so (C++ operator layer:
+validation, plan cache) -> libmsco_b200.so (hand-written sm_100a kernels).
+Tensors are torch CUDA tensors, used purely as handles to device memory; the
+launch goes to torch's current stream.  ``context_lens`` must live on the host
+(a CPU int32 tensor, a numpy array or a list), exactly as the reference
+requires.  There is no CPU or PyTorch fallback: without the built libraries
+the operators raise ImportError.
 """
-from . import _abi  # noqa: F401
-from ._abi import MscoError  # noqa: F401
+from __future__ import annotations
 
-__all__ = ["MscoError"]
+import ctypes as C
+import math
+
+import numpy as np
+
+from . import _abi, _host
+from ._abi import MscoError  # noqa: F401
+from ._host import UnsupportedOnB200, plan_cache_clear, plan_cache_stats, registered_ops  # noqa: F401
+
+__all__ = ["reshape_and_cache", "reshape_and_cache_quant", "paged_attention", "paged_attention_infer",
+           "paged_attention_workspace_size", "paged_attention_check_status", "TensorSpec", "MscoError",
+           "UnsupportedOnB200", "registered_ops", "plan_cache_stats", "plan_cache_clear"]
+
+_DT = {"float16": _abi.DTYPE_F16, "bfloat16": _abi.DTYPE_BF16, "int8": _abi.DTYPE_I8,
+       "float32": _abi.DTYPE_F32, "int32": _abi.DTYPE_I32, "int64": _abi.DTYPE_I64}
+_DT_NAMES = {v: k for k, v in _DT.items()}
+
+
+class TensorSpec:
+    """Shape / dtype of a tensor without data: enough for shape inference and workspace sizing."""
+
+    def __init__(self, shape, dtype, on_host=False, data=0):
+        self.shape = tuple(int(s) for s in shape)
+        self.dtype = dtype if isinstance(dtype, str) else str(dtype).replace("torch.", "")
+        self.on_host = on_host
+        self.data = data
+
+
+def _dtype_code(dt) -> int:
+    name = dt if isinstance(dt, str) else str(dt).replace("torch.", "")
+    if name not in _DT:
+        raise TypeError(f"unsupported dtype {dt}")
+    return _DT[name]
+
+
+def _contig_strides(shape):
+    st, acc = [], 1
+    for s in reversed(shape):
+        st.append(acc)
+        acc *= max(int(s), 1)
+    return list(reversed(st))
+
+
+class _Descs:
+    """Builds MsTensorDesc structs and keeps the Python objects behind them alive."""
+
+    def __init__(self):
+        self.keep = []
+
+    def __call__(self, t, host_ok=False):
+        if t is None:
+            return None
+        d = _host.MsTensorDesc()
+        if isinstance(t, TensorSpec):
+            shape, strides = t.shape, _contig_strides(t.shape)
+            d.data, d.dtype, d.on_host = t.data, _dtype_code(t.dtype), int(t.on_host)
+        elif isinstance(t, (list, tuple, np.ndarray)):
+            if not host_ok:
+                raise TypeError("device tensors must be torch CUDA tensors")
+            a = np.ascontiguousarray(np.asarray(t))
+            if a.dtype == np.int64 and isinstance(t, (list, tuple)):
+                a = a.astype(np.int32)
+            self.keep.append(a)
+            shape, strides = a.shape, [s // max(a.itemsize, 1) for s in a.strides]
+            d.data, d.dtype, d.on_host = a.ctypes.data, _dtype_code(str(a.dtype)), 1
+        else:  # torch tensor
+            shape, strides = tuple(t.shape), list(t.stride())
+            d.data, d.dtype, d.on_host = t.data_ptr(), _dtype_code(t.dtype), 0 if t.is_cuda else 1
+            self.keep.append(t)
+        if len(shape) > _host.MS_MAX_DIMS:
+            raise ValueError("tensors of more than 8 dimensions are not supported")
+        d.ndim = len(shape)
+        for i, (s, st) in enumerate(zip(shape, strides)):
+            d.shape[i], d.strides[i] = int(s), int(st)
+        self.keep.append(d)
+        return C.pointer(d)
+
+
+def _stream():
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+# --------------------------------------------------------------------------
+# reshape_and_cache
+# --------------------------------------------------------------------------
+def reshape_and_cache(key, value=None, key_cache=None, value_cache=None, slot_mapping=None, cache_mode=0,
+                      head_num=0):
+    """Scatter the token rows of `key` / `value` into the paged caches, in place.
+
+    key / value   [tokens, kv_heads * head_dim] or [batch, seq, kv_heads * head_dim]; fp16 / bf16 / int8
+    key_cache / value_cache  [num_blocks, block_size, kv_heads, head_dim], same dtype as key / value
+    slot_mapping  int32 [tokens]; token i goes to block slot // block_size, offset slot % block_size;
+                  negative slots are skipped
+    cache_mode    0 = ND (1 = FRACTAL_NZ is Ascend-only and raises UnsupportedOnB200)
+    head_num      only used by the NZ layout
+
+    Returns None (the reference returns a placeholder tensor that carries no data).
+    """
+    D = _Descs()
+    _host.check(_host.lib().ms_custom_ops_reshape_and_cache(
+        D(key), D(value), D(key_cache), D(value_cache), D(slot_mapping), int(cache_mode), int(head_num), _stream()))
+    return None
+
+
+def reshape_and_cache_quant(key, value, key_cache, value_cache, slot_mapping, k_descale, v_descale,
+                            k_offset=None, v_offset=None):
+    """Extension: quantise fp16 / bf16 rows to the int8 caches while scattering them.
+
+    Per channel c = (kv_head, head_dim): ``q = saturate_int8(rint(float32(x) / descale[c]) - offset[c])``
+    with IEEE division and round-half-to-even -- the inverse of the ``(q + offset) * descale``
+    de-quantisation of ``paged_attention(quant_type=1)``.  The reference operator has no such mode.
+    """
+    D = _Descs()
+    _host.check(_host.lib().ms_custom_ops_reshape_and_cache_quant(
+        D(key), D(value), D(key_cache), D(value_cache), D(slot_mapping), D(k_descale), D(v_descale),
+        D(k_offset), D(v_offset), _stream()))
+    return None
+
+
+# --------------------------------------------------------------------------
+# paged_attention
+# --------------------------------------------------------------------------
+def _pa_args(D, query, key_cache, value_cache, block_tables, context_lens, attn_mask, batch_run_status,
+             k_descale, k_offset, v_descale, v_offset, razor_offset, p_scale, log_n, q_seq_lens, q_head_num,
+             qk_scale, kv_head_num, mask_type, batch_run_status_enable, quant_type, out_data_type,
+             has_quant_offset, compress_type, calc_type, scale_type, input_layout, mla_v_dim, input_format):
+    a = _host.MsPagedAttentionArgs()
+    a.query, a.key_cache, a.value_cache, a.block_tables = D(query), D(key_cache), D(value_cache), D(block_tables)
+    a.context_lens = D(context_lens, host_ok=True)
+    a.attn_mask = D(attn_mask)
+    a.batch_run_status = D(batch_run_status, host_ok=True)
+    a.k_descale, a.k_offset, a.v_descale, a.v_offset = D(k_descale), D(k_offset), D(v_descale), D(v_offset)
+    a.razor_offset, a.p_scale, a.log_n = D(razor_offset), D(p_scale), D(log_n)
+    a.q_seq_lens = D(q_seq_lens, host_ok=True)
+    a.q_head_num, a.qk_scale, a.kv_head_num = int(q_head_num), float(qk_scale), int(kv_head_num)
+    a.mask_type, a.batch_run_status_enable = int(mask_type), int(bool(batch_run_status_enable))
+    a.quant_type, a.out_data_type, a.has_quant_offset = int(quant_type), int(out_data_type), int(bool(has_quant_offset))
+    a.compress_type, a.calc_type, a.scale_type = int(compress_type), int(calc_type), int(scale_type)
+    a.input_layout, a.mla_v_dim, a.input_format = int(input_layout), int(mla_v_dim), int(input_format)
+    return a
+
+
+_workspaces = {}  # (device index, stream handle) -> grow-only uint8 buffer
+
+
+def _workspace(device, nbytes):
+    import torch
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(int(nbytes * 1.25), 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def paged_attention(query, key_cache, value_cache, block_tables, context_lens, attn_mask=None,
+                    batch_run_status=None, k_descale=None, k_offset=None, v_descale=None, v_offset=None,
+                    razor_offset=None, p_scale=None, log_n=None, q_seq_lens=None, q_head_num=0, qk_scale=1.0,
+                    kv_head_num=0, mask_type=0, batch_run_status_enable=False, quant_type=0, out_data_type=-1,
+                    has_quant_offset=False, compress_type=0, calc_type=0, scale_type=0, input_layout=0,
+                    mla_v_dim=0, input_format=0):
+    """Decode attention over the paged KV cache; returns ``attention_out`` shaped like `query`.
+
+    query        [batch, q_head_num, head_dim] fp16 / bf16 (one token per sequence)
+    key_cache / value_cache  [num_blocks, block_size, kv_heads, head_dim]; query's dtype, or int8
+                 with quant_type = 1
+    block_tables int32 [batch, max_blocks]; context_lens int32 [batch] on the HOST
+    attn_mask    additive: mask_type 1 (NORM) [batch, 1, max_ctx], 2 (ALIBI) [batch, heads, 1, max_ctx]
+    k_descale / v_descale float32, k_offset / v_offset int32, [kv_heads * head_dim] (quant_type = 1):
+                 K = (int8 + offset) * descale per channel
+    Attribute values are the reference's (mask_type, quant_type, ... enums).  Combinations that the
+    reference accepts but this build does not implement raise UnsupportedOnB200; invalid
+    combinations raise ValueError as in the reference.
+    """
+    import torch
+    D = _Descs()
+    a = _pa_args(D, query, key_cache, value_cache, block_tables, context_lens, attn_mask, batch_run_status,
+                 k_descale, k_offset, v_descale, v_offset, razor_offset, p_scale, log_n, q_seq_lens, q_head_num,
+                 qk_scale, kv_head_num, mask_type, batch_run_status_enable, quant_type, out_data_type,
+                 has_quant_offset, compress_type, calc_type, scale_type, input_layout, mla_v_dim, input_format)
+    L = _host.lib()
+    nbytes = C.c_size_t()
+    _host.check(L.ms_custom_ops_paged_attention_workspace_size(C.byref(a), C.byref(nbytes)))
+    out = torch.empty_like(query)
+    ws = _workspace(query.device, nbytes.value)
+    _host.check(L.ms_custom_ops_paged_attention(C.byref(a), D(out), C.c_void_p(ws.data_ptr()), ws.numel(), _stream()))
+    return out
+
+
+def paged_attention_infer(query, key_cache, value_cache, block_tables, context_lens, **kw):
+    """Shape / dtype inference (and full argument validation) without touching a GPU.
+
+    Accepts TensorSpec or real tensors; returns (shape tuple, dtype name).
+    """
+    D = _Descs()
+    a = _pa_args(D, query, key_cache, value_cache, block_tables, context_lens, *_kw_to_positional(kw))
+    dt, nd = C.c_int32(), C.c_int32()
+    shp = (C.c_int64 * _host.MS_MAX_DIMS)()
+    _host.check(_host.lib().ms_custom_ops_paged_attention_infer(C.byref(a), C.byref(dt), C.byref(nd), shp))
+    return tuple(shp[i] for i in range(nd.value)), _DT_NAMES[dt.value]
+
+
+def paged_attention_workspace_size(query, key_cache, value_cache, block_tables, context_lens, **kw) -> int:
+    """Bytes of device workspace a launch with these arguments needs (planning only, no GPU work)."""
+    D = _Descs()
+    a = _pa_args(D, query, key_cache, value_cache, block_tables, context_lens, *_kw_to_positional(kw))
+    n = C.c_size_t()
+    _host.check(_host.lib().ms_custom_ops_paged_attention_workspace_size(C.byref(a), C.byref(n)))
+    return int(n.value)
+
+
+_PA_OPTIONAL = ("attn_mask", "batch_run_status", "k_descale", "k_offset", "v_descale", "v_offset", "razor_offset",
+                "p_scale", "log_n", "q_seq_lens")
+_PA_ATTRS = (("q_head_num", 0), ("qk_scale", 1.0), ("kv_head_num", 0), ("mask_type", 0),
+             ("batch_run_status_enable", False), ("quant_type", 0), ("out_data_type", -1),
+             ("has_quant_offset", False), ("compress_type", 0), ("calc_type", 0), ("scale_type", 0),
+             ("input_layout", 0), ("mla_v_dim", 0), ("input_format", 0))
+
+
+def _kw_to_positional(kw):
+    unknown = set(kw) - set(_PA_OPTIONAL) - {n for n, _ in _PA_ATTRS}
+    if unknown:
+        raise TypeError(f"paged_attention got unexpected arguments {sorted(unknown)}")
+    return [kw.get(n) for n in _PA_OPTIONAL] + [kw.get(n, d) for n, d in _PA_ATTRS]
+
+
+def paged_attention_check_status(device=None):
+    """Synchronise the current stream and raise if the last paged_attention launch on it reported
+    an expired bounded wait (MSCO_ERR_TIMEOUT) or a block id outside the cache (MSCO_ERR_OOB)."""
+    import torch
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    stream = torch.cuda.current_stream(device)
+    ws = _workspaces.get((device.index, stream.cuda_stream))
+    stream.synchronize()
+    if ws is not None:
+        _host.check(_host.lib().ms_custom_ops_paged_attention_status(C.c_void_p(ws.data_ptr())))

@@ -48,7 +48,7 @@ EXPORTS = (
     "msco_version", "msco_last_error", "msco_reshape_and_cache", "msco_reshape_and_cache_quant",
     "msco_paged_attention_split_tokens", "msco_paged_attention_plan", "msco_paged_attention_workspace_bytes",
     "msco_paged_attention_plan_info", "msco_paged_attention_plan_destroy", "msco_paged_attention_launch",
-    "msco_paged_attention_status",
+    "msco_paged_attention_status", "msco_paged_attention_profile_enable", "msco_paged_attention_profile_read",
 )
 
 
@@ -83,6 +83,10 @@ def lib():
     L.msco_paged_attention_launch.argtypes = [vp] * 12 + [sz, vp]
     L.msco_paged_attention_status.restype = C.c_int
     L.msco_paged_attention_status.argtypes = [vp, vp]
+    L.msco_paged_attention_profile_enable.restype = C.c_int
+    L.msco_paged_attention_profile_enable.argtypes = [vp, i32]
+    L.msco_paged_attention_profile_read.restype = C.c_int
+    L.msco_paged_attention_profile_read.argtypes = [vp, C.POINTER(C.c_float), i32, C.POINTER(i32)]
     _lib = L
     return L
 
@@ -116,6 +120,16 @@ class PaPlan:
         out = MscoPaPlanInfo()
         check(lib().msco_paged_attention_plan_info(self._h, C.byref(out)))
         return out
+
+    def profile_enable(self, enable=True):
+        check(lib().msco_paged_attention_profile_enable(self._h, int(enable)))
+
+    def profile_read(self):
+        """Attention-kernel durations (ms) of the launches since the last read (at most 64)."""
+        buf = (C.c_float * 64)()
+        n = C.c_int32()
+        check(lib().msco_paged_attention_profile_read(self._h, buf, 64, C.byref(n)))
+        return [float(buf[i]) for i in range(n.value)]
 
     def close(self):
         if self._h:

@@ -190,8 +190,38 @@ extern "C" int msco_paged_attention_plan_info(const MscoPaPlan *plan, MscoPaPlan
   return MSCO_OK;
 }
 
+extern "C" int msco_paged_attention_profile_enable(MscoPaPlan *plan, int32_t enable) {
+  if (plan == nullptr) return fail(MSCO_ERR_INVALID_ARG, "profile_enable: NULL plan");
+  if (enable && plan->prof_ev[0][0] == nullptr) {
+    for (int i = 0; i < MscoPaPlan::kProfRing; ++i)
+      for (int j = 0; j < 2; ++j) MSCO_CUDA_CHECK(cudaEventCreate(&plan->prof_ev[i][j]));
+  }
+  plan->profile = enable != 0;
+  plan->prof_count = 0;
+  return MSCO_OK;
+}
+
+extern "C" int msco_paged_attention_profile_read(MscoPaPlan *plan, float *kernel_ms, int32_t max_count,
+                                                 int32_t *count) {
+  if (plan == nullptr || kernel_ms == nullptr || count == nullptr)
+    return fail(MSCO_ERR_INVALID_ARG, "profile_read: NULL argument");
+  const int64_t have = std::min<int64_t>(plan->prof_count, MscoPaPlan::kProfRing);
+  const int64_t n = std::min<int64_t>(have, max_count);
+  for (int64_t i = 0; i < n; ++i) {
+    const int64_t idx = (plan->prof_count - n + i) % MscoPaPlan::kProfRing;
+    MSCO_CUDA_CHECK(cudaEventSynchronize(plan->prof_ev[idx][1]));
+    MSCO_CUDA_CHECK(cudaEventElapsedTime(&kernel_ms[i], plan->prof_ev[idx][0], plan->prof_ev[idx][1]));
+  }
+  *count = (int32_t)n;
+  plan->prof_count = 0;
+  return MSCO_OK;
+}
+
 extern "C" void msco_paged_attention_plan_destroy(MscoPaPlan *plan) {
   if (plan == nullptr) return;
+  if (plan->prof_ev[0][0] != nullptr)
+    for (int i = 0; i < MscoPaPlan::kProfRing; ++i)
+      for (int j = 0; j < 2; ++j) cudaEventDestroy(plan->prof_ev[i][j]);
   if (plan->host_words != nullptr) {
     if (plan->host_pinned) cudaFreeHost(plan->host_words); else free(plan->host_words);
   }
@@ -246,15 +276,25 @@ extern "C" int msco_paged_attention_launch(const MscoPaPlan *plan, const void *q
   p.scale_log2e = d.qk_scale * 1.4426950408889634f;
 
   MSCO_CUDA_CHECK(cudaMemcpyAsync(ws, plan->host_words, plan->plan_bytes, cudaMemcpyHostToDevice, st));
+  cudaEvent_t *pe = nullptr;
+  if (plan->profile && plan->total_items > 0) {
+    pe = plan->prof_ev[plan->prof_count % MscoPaPlan::kProfRing];
+    MSCO_CUDA_CHECK(cudaEventRecord(pe[0], st));
+  }
   int rc = plan->kernel == kKernelTma ? launch_pa_tma(plan, p, st) : launch_pa_generic(plan, p, st);
   if (rc != MSCO_OK) return rc;
+  if (pe != nullptr) {
+    MSCO_CUDA_CHECK(cudaEventRecord(pe[1], st));
+    ++plan->prof_count;
+  }
   if (plan->need_reduce) rc = launch_pa_reduce(plan, p, st);
   return rc;
 }
 
 extern "C" int msco_paged_attention_status(const MscoPaPlan *plan, const void *workspace) {
-  if (plan == nullptr || workspace == nullptr) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_status: NULL argument");
-  if (plan->batch == 0) return MSCO_OK;
+  // plan may be NULL: the status word is always the first word of the workspace
+  if (workspace == nullptr) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_status: NULL workspace");
+  if (plan != nullptr && plan->batch == 0) return MSCO_OK;
   int32_t status = 0;
   MSCO_CUDA_CHECK(cudaMemcpy(&status, workspace, sizeof(status), cudaMemcpyDeviceToHost));
   if (status == kStatusTimeout) return fail(MSCO_ERR_TIMEOUT, "paged_attention: a bounded wait inside the kernel expired");

@@ -63,6 +63,11 @@ struct MscoPaPlan {
   mutable const void *tm_v_ptr = nullptr;
   alignas(64) mutable unsigned char tm_k[128];
   alignas(64) mutable unsigned char tm_v[128];
+  // optional kernel timing (benchmarks): ring of event pairs recorded around the attention kernel
+  static constexpr int kProfRing = 64;
+  bool profile = false;
+  mutable cudaEvent_t prof_ev[kProfRing][2] = {};
+  mutable int64_t prof_count = 0;
 };
 
 namespace msco {

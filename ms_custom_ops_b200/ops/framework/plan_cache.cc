@@ -1,0 +1,173 @@
+#include "ops/framework/plan_cache.h"
+
+#include <cstdlib>
+#include <cstring>
+
+#include "ops/framework/tensor.h"
+
+namespace ms_custom_ops {
+
+uint64_t HashBytes(const void *data, size_t len, uint64_t seed) {
+  const unsigned char *p = static_cast<const unsigned char *>(data);
+  uint64_t h = seed ^ (len * 0x9e3779b97f4a7c15ull);
+  auto mix = [](uint64_t x) {
+    x ^= x >> 30; x *= 0xbf58476d1ce4e5b9ull;
+    x ^= x >> 27; x *= 0x94d049bb133111ebull;
+    x ^= x >> 31;
+    return x;
+  };
+  while (len >= 8) {
+    uint64_t w;
+    memcpy(&w, p, 8);
+    h = mix(h ^ w) + 0x9e3779b97f4a7c15ull;
+    p += 8;
+    len -= 8;
+  }
+  if (len) {
+    uint64_t w = 0;
+    memcpy(&w, p, len);
+    h = mix(h ^ w) + 0x9e3779b97f4a7c15ull;
+  }
+  return mix(h);
+}
+
+PlanKey MakePlanKey(const MscoPaDesc &desc, const std::vector<int32_t> &lens) {
+  // field by field: the struct has padding bytes that must not enter the key
+  const int64_t f[] = {desc.q_dtype, desc.kv_dtype, desc.num_q_heads, desc.num_kv_heads, desc.head_dim,
+                       desc.block_size, desc.num_blocks, desc.max_blocks_per_seq, desc.quant_type,
+                       desc.has_quant_offset, desc.mask_type, desc.mask_dtype, desc.mask_batch_stride,
+                       desc.mask_head_stride, desc.kernel, static_cast<int64_t>(lens.size())};
+  uint32_t scale_bits;
+  memcpy(&scale_bits, &desc.qk_scale, 4);
+  PlanKey k;
+  k.h1 = HashBytes(f, sizeof(f), 0x243f6a8885a308d3ull ^ scale_bits);
+  k.h2 = HashBytes(f, sizeof(f), 0x13198a2e03707344ull + scale_bits);
+  k.h1 = HashBytes(lens.data(), lens.size() * sizeof(int32_t), k.h1);
+  k.h2 = HashBytes(lens.data(), lens.size() * sizeof(int32_t), k.h2);
+  return k;
+}
+
+PlanRef &PlanRef::operator=(PlanRef &&o) noexcept {
+  if (this != &o) {
+    if (cache_ && entry_) cache_->Release(entry_);
+    cache_ = o.cache_; entry_ = o.entry_; plan_ = o.plan_;
+    o.cache_ = nullptr; o.entry_ = nullptr; o.plan_ = nullptr;
+  }
+  return *this;
+}
+PlanRef::~PlanRef() {
+  if (cache_ && entry_) cache_->Release(entry_);
+}
+
+PlanCache &PlanCache::Instance() {
+  static PlanCache *inst = new PlanCache();  // intentionally leaked: no CUDA calls at process exit
+  return *inst;
+}
+
+PlanCache::PlanCache() {
+  if (const char *e = getenv("MSCO_PLAN_CACHE_CAPACITY")) {
+    const long v = strtol(e, nullptr, 10);
+    if (v > 0) capacity_ = static_cast<size_t>(v);
+  }
+}
+PlanCache::~PlanCache() = default;
+
+PlanRef PlanCache::GetOrCreate(const MscoPaDesc &desc, const std::vector<int32_t> &lens) {
+  const PlanKey key = MakePlanKey(desc, lens);
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = map_.find(key);
+    if (it != map_.end()) {
+      Entry *e = it->second.get();
+      ++hits_;
+      ++e->refs;
+      lru_.erase(e->lru_it);
+      lru_.push_front(e);
+      e->lru_it = lru_.begin();
+      return PlanRef(this, e, e->plan);
+    }
+    ++misses_;
+  }
+  // plan outside the lock: pure host work, may take tens of microseconds
+  MscoPaPlan *plan = nullptr;
+  const int rc = msco_paged_attention_plan(&desc, lens.data(), static_cast<int32_t>(lens.size()), &plan);
+  if (rc != MSCO_OK) {
+    ErrorBuilder b(rc == MSCO_ERR_UNSUPPORTED ? MS_ERR_KIND_UNSUPPORTED
+                   : rc == MSCO_ERR_INVALID_ARG ? MS_ERR_KIND_VALUE : MS_ERR_KIND_RUNTIME, rc);
+    b << "For PagedAttention, planning failed: " << msco_last_error();
+    b.Throw();
+  }
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = map_.find(key);
+  if (it != map_.end()) {  // another thread planned the same key meanwhile
+    msco_paged_attention_plan_destroy(plan);
+    Entry *e = it->second.get();
+    ++e->refs;
+    return PlanRef(this, e, e->plan);
+  }
+  auto e = std::make_unique<Entry>();
+  e->key = key;
+  e->plan = plan;
+  e->refs = 1;
+  lru_.push_front(e.get());
+  e->lru_it = lru_.begin();
+  Entry *raw = e.get();
+  map_.emplace(key, std::move(e));
+  EvictLocked();
+  return PlanRef(this, raw, plan);
+}
+
+void PlanCache::Release(void *entry) {
+  std::lock_guard<std::mutex> g(mu_);
+  Entry *e = static_cast<Entry *>(entry);
+  if (e->refs > 0) --e->refs;
+}
+
+void PlanCache::RetireLocked(MscoPaPlan *plan) {
+  // keep the last few evicted plans alive: an asynchronous copy from a plan's pinned buffer may
+  // still be queued on a stream
+  retired_.push_back(plan);
+  while (retired_.size() > 32) {
+    msco_paged_attention_plan_destroy(retired_.front());
+    retired_.pop_front();
+  }
+}
+
+void PlanCache::EvictLocked() {
+  auto it = lru_.end();
+  while (map_.size() > capacity_ && it != lru_.begin()) {
+    --it;
+    Entry *e = *it;
+    if (e->refs == 0) {
+      RetireLocked(e->plan);
+      const PlanKey key = e->key;
+      it = lru_.erase(it);
+      map_.erase(key);
+    }
+  }
+}
+
+void PlanCache::Stats(int64_t *hits, int64_t *misses, int64_t *entries) {
+  std::lock_guard<std::mutex> g(mu_);
+  if (hits) *hits = hits_;
+  if (misses) *misses = misses_;
+  if (entries) *entries = static_cast<int64_t>(map_.size());
+}
+
+void PlanCache::Clear() {
+  std::lock_guard<std::mutex> g(mu_);
+  for (auto it = lru_.begin(); it != lru_.end();) {
+    Entry *e = *it;
+    if (e->refs == 0) {
+      RetireLocked(e->plan);
+      const PlanKey key = e->key;
+      it = lru_.erase(it);
+      map_.erase(key);
+    } else {
+      ++it;
+    }
+  }
+  hits_ = misses_ = 0;
+}
+
+}  // namespace ms_custom_ops

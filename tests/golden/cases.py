@@ -1,0 +1,91 @@
+"""Case tables shared by the fixture generator (make_golden.py) and the parity tests.
+
+ST_CASES: seeds, shapes and mask types of the reference's own decode tests
+(tests/st/test_custom_paged_attention.py:1562-2311).  Tuple layout:
+(seed, q heads, kv heads, head size, block size, num blocks, context lens,
+ q dtype, kv dtype or None (= q dtype), quant_type, has_quant_offset,
+ qk_scale or None (= 1/sqrt(head size)), mask_type)
+"""
+import hashlib
+
+import numpy as np
+
+L4 = [192, 193, 194, 195]
+ST_CASES = {
+    "basic_fp16": (3001, 32, 1, 128, 128, 64, L4, "float16", None, 0, False, 1.0, 0),
+    "basic_bf16": (3001, 32, 1, 128, 128, 64, L4, "bfloat16", None, 0, False, 1.0, 0),
+    "no_mask_mha": (4115, 32, 32, 128, 128, 64, L4, "float16", None, 0, False, 1.0, 0),
+    "norm_mask_fp16": (4116, 32, 32, 128, 128, 64, L4, "float16", None, 0, False, None, 1),
+    "norm_mask_bf16": (4116, 32, 32, 128, 128, 64, L4, "bfloat16", None, 0, False, None, 1),
+    "alibi_fp16": (4100, 32, 32, 128, 128, 64, [500, 500], "float16", None, 0, False, None, 2),
+    "alibi_bf16": (4100, 32, 32, 128, 128, 64, [500, 500], "bfloat16", None, 0, False, None, 2),
+    "gqa_8to1_alibi": (4101, 8, 1, 128, 128, 1024, [88] * 13, "float16", None, 0, False, None, 2),
+    "gqa_4to2_alibi": (4102, 4, 2, 128, 128, 1024, [88] * 13, "float16", None, 0, False, None, 2),
+    "gqa_32to8_alibi": (4103, 32, 8, 128, 128, 1024, [88] * 13, "float16", None, 0, False, None, 2),
+    "odd_heads": (4104, 7, 7, 128, 128, 1024, [88] * 13, "float16", None, 0, False, None, 1),
+    "heads_20_bf16": (4110, 20, 20, 128, 128, 64, [500, 500], "bfloat16", None, 0, False, None, 1),
+    "head_256_block_16": (4107, 16, 16, 256, 16, 512, L4, "float16", None, 0, False, None, 0),
+    "block_16": (4108, 32, 32, 128, 16, 512, L4, "float16", None, 0, False, None, 0),
+    "small_seqlen": (4105, 32, 32, 128, 128, 64, [33, 33, 33, 33], "float16", None, 0, False, None, 1),
+    "large_seqlen_bf16": (4106, 32, 32, 128, 128, 128, [3000, 3000], "bfloat16", None, 0, False, None, 1),
+    "varied_seqlens": (4111, 32, 32, 128, 128, 256, [100, 500, 1000, 2000], "float16", None, 0, False, None, 1),
+    "int8_kv": (3003, 32, 1, 128, 128, 64, L4, "float16", "int8", 1, False, None, 0),
+    "int8_kv_offset": (3004, 32, 1, 128, 128, 64, L4, "float16", "int8", 1, True, None, 0),
+    "gqa_int8_bf16": (4112, 32, 8, 128, 128, 64, L4, "bfloat16", "int8", 1, False, None, 1),
+    "gqa_int8_offset": (4113, 32, 8, 128, 128, 64, L4, "float16", "int8", 1, True, None, 1),
+    "bf16_int8_768": (6001, 32, 32, 128, 128, 256, [768], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_len128": (6002 + 128, 24, 24, 64, 128, 256, [128], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_len513": (6002 + 513, 24, 24, 64, 128, 256, [513], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_len1025": (6002 + 1025, 24, 24, 64, 128, 256, [1025], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_head32": (6100 + 32, 32, 32, 32, 16, 512, [512], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_head33": (6100 + 33, 32, 32, 33, 16, 512, [512], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_head128": (6100 + 128, 32, 32, 128, 16, 512, [512], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_gqa_4to1": (6200 + 401, 4, 1, 128, 128, 512, [766], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_gqa_24to2": (6200 + 2402, 24, 2, 128, 128, 512, [766], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_gqa_64to32": (6200 + 6432, 64, 32, 128, 128, 512, [766], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_block16": (6300 + 16, 32, 8, 64, 16, 1024, [1024], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_block128": (6300 + 128, 32, 8, 64, 128, 1024, [1024], "bfloat16", "int8", 1, False, None, 1),
+    "bf16_int8_len309": (6400, 64, 64, 32, 16, 256, [309], "bfloat16", "int8", 1, False, None, 1),
+}
+
+# reshape_and_cache cases: (dtype, key rank, key head dim, value head dim, seed); cache geometry of
+# tests/st/test_custom_reshape_and_cache.py:50-56 (20 blocks x 64 slots, 16 heads, 39 tokens)
+RAC_CASES = {
+    "fp16_rank3": ("float16", 3, 32, 32, 101),
+    "fp16_rank2": ("float16", 2, 32, 32, 102),
+    "bf16_rank3": ("bfloat16", 3, 32, 32, 103),
+    "int8_rank2": ("int8", 2, 32, 32, 104),
+    "fp16_kv_dims_differ": ("float16", 3, 32, 48, 105),
+}
+
+
+def st_case(name, mask_free=False):
+    from ms_custom_ops_b200 import workloads
+    seed, h, kvh, hd, bs, nb, lens, qd, kvd, quant, off, scale, mask = ST_CASES[name]
+    return workloads.st_style_case(seed, h, kvh, hd, bs, nb, lens, qd, kvd, quant, off, 0 if mask_free else mask,
+                                   scale)
+
+
+def rac_case(name):
+    """Seeded inputs in the reference test's shapes; slots are a permutation as in :207-210."""
+    import ml_dtypes
+    dtype, rank, khd, vhd, seed = RAC_CASES[name]
+    rng = np.random.default_rng(seed)
+    nb, bs, heads, batch, seq = 20, 64, 16, 13, 3
+    t = batch * seq
+    npdt = {"float16": np.float16, "bfloat16": ml_dtypes.bfloat16, "int8": np.int8}[dtype]
+
+    def rnd(shape):
+        if dtype == "int8":
+            return rng.integers(-128, 127, shape, dtype=np.int8)
+        return rng.random(shape, dtype=np.float32).astype(npdt)
+    kshape = (t, heads * khd) if rank == 2 else (batch, seq, heads * khd)
+    vshape = (t, heads * vhd) if rank == 2 else (batch, seq, heads * vhd)
+    return {"key": rnd(kshape), "value": rnd(vshape), "key_cache": rnd((nb, bs, heads, khd)),
+            "value_cache": rnd((nb, bs, heads, vhd)),
+            "slot_mapping": rng.permutation(t).astype(np.int32)}
+
+
+def digest(a) -> str:
+    a = np.ascontiguousarray(a)
+    return hashlib.sha256(a.view(np.uint8).tobytes()).hexdigest()

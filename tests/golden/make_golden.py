@@ -1,0 +1,91 @@
+"""Generate the golden fixtures from the reference's own numpy goldens.
+
+Run on a machine that has a checkout of the reference (it cannot travel with
+the test-suite):
+
+    python tests/golden/make_golden.py /path/to/reference
+
+For every case of tests/golden/cases.py the inputs come from this
+repository's seeded generators; the expected outputs come from the
+reference's `PagedAttentionDataGenerator.compute_golden_reference`
+(tests/st/test_custom_paged_attention.py:528-699) and
+`InferenceEngine.nd_inference` (tests/st/test_custom_reshape_and_cache.py:282-307),
+imported unchanged through a stub of the `mindspore` module.  For the
+reference-style attention cases the script also checks that our generator
+reproduces the reference generator's inputs bit for bit.
+
+Written files (tests/golden/):
+  pa_<case>.npz       golden output + sha256 of every input
+  rac_<case>.npz      sha256 of the golden caches (and of the inputs)
+  config1.npz         benchmark configuration 1: cache digests after the scatter + attention output
+"""
+import math
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from oracle import ms_stub  # noqa: E402
+from tests.golden import cases  # noqa: E402
+from ms_custom_ops_b200 import workloads  # noqa: E402
+
+
+def main(ref_root):
+    ms = ms_stub.install()
+    sys.path.insert(0, os.path.join(ref_root, "tests", "st"))
+    import test_custom_paged_attention as tpa
+    import test_custom_reshape_and_cache as trc
+    msd = {"float16": ms.float16, "bfloat16": ms.bfloat16, "int8": ms.int8}
+
+    for name, cfg in cases.ST_CASES.items():
+        seed, h, kvh, hd, bs, nb, lens, qd, kvd, quant, off, scale, mask = cfg
+        case = cases.st_case(name)
+        gen = tpa.PagedAttentionDataGenerator(seed)
+        ref_in = gen.generate_inputs(h, kvh, hd, bs, nb, [1] * len(lens), lens, msd[qd], msd[kvd or qd], mask,
+                                     quant, off)
+        for key in ("query", "key_cache", "value_cache", "block_tables", "k_descale", "v_descale", "k_offset",
+                    "v_offset", "mask"):
+            a, b = ref_in[key], case[key]
+            assert (a is None) == (b is None), (name, key)
+            if a is not None:
+                assert np.array_equal(np.asarray(a).astype(np.float32), np.asarray(b).astype(np.float32)), (name, key)
+        golden = gen.compute_golden_reference(
+            ref_in["query"], ref_in["key_cache"], ref_in["value_cache"], ref_in["block_tables"],
+            ref_in["q_seq_lens"], ref_in["kv_seq_lens"], case["qk_scale"], ref_in["mask"], mask,
+            ref_in["k_descale"], ref_in["v_descale"], ref_in["k_offset"], ref_in["v_offset"])
+        digests = {k: cases.digest(case[k]) for k in ("query", "key_cache", "value_cache", "block_tables")}
+        np.savez_compressed(os.path.join(HERE, f"pa_{name}.npz"), golden=np.asarray(golden),
+                            **{f"sha_{k}": np.array(v) for k, v in digests.items()})
+        print("pa", name, golden.dtype, golden.shape)
+
+    for name in cases.RAC_CASES:
+        c = cases.rac_case(name)
+        gk, gv = trc.InferenceEngine.nd_inference(c["key"], c["value"], c["key_cache"], c["value_cache"],
+                                                  c["slot_mapping"])
+        np.savez_compressed(os.path.join(HERE, f"rac_{name}.npz"), sha_key_cache=np.array(cases.digest(gk)),
+                            sha_value_cache=np.array(cases.digest(gv)),
+                            sha_in_key=np.array(cases.digest(c["key"])),
+                            sha_in_key_cache=np.array(cases.digest(c["key_cache"])))
+        print("rac", name)
+
+    # benchmark configuration 1, exactly: scatter of the newest token, then attention
+    spec = workloads.config_spec(1)
+    c = workloads.decode_case(spec)
+    gk, gv = trc.InferenceEngine.nd_inference(c["key"], c["value"], c["key_cache"], c["value_cache"],
+                                              c["slot_mapping"])
+    gen = tpa.PagedAttentionDataGenerator(0)
+    golden = gen.compute_golden_reference(c["query"], gk, gv, c["block_tables"], np.ones(spec.batch, np.int32),
+                                          c["context_lens"], 1.0 / math.sqrt(spec.head_size), None, 0)
+    np.savez_compressed(os.path.join(HERE, "config1.npz"), golden=np.asarray(golden),
+                        context_lens=c["context_lens"], sha_key_cache=np.array(cases.digest(gk)),
+                        sha_value_cache=np.array(cases.digest(gv)), sha_query=np.array(cases.digest(c["query"])),
+                        sha_in_key_cache=np.array(cases.digest(c["key_cache"])))
+    print("config1", golden.dtype, golden.shape, c["context_lens"])
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -5,12 +5,15 @@ path's tolerances (rtol = atol = 1e-2 bf16, 5e-3 fp16, 2e-2 with int8 KV), by
 the reference's own acceptance rule, and by a scale-free error bound so that a
 wrong kernel cannot pass on small magnitudes alone.
 """
+import os
+
 import numpy as np
 import pytest
 import torch
 
 from ms_custom_ops_b200 import _abi, kernels, workloads
 from oracle import paged_kv_numpy as oracle
+from tests.golden import cases
 from tests.helpers import BF16, assert_close, to_dev, to_np, tol_for
 
 pytestmark = pytest.mark.gpu
@@ -161,51 +164,13 @@ def _check(case, out, what):
     assert rel_l2 < 1e-2, (what, rel_max, rel_l2)
 
 
-# (seed, heads, kv_heads, head, block, blocks, lens, q dtype, kv dtype, quant, offset, qk_scale, mask)
-# seeds, shapes and mask types of the reference's decode tests,
-# tests/st/test_custom_paged_attention.py:1562-2311 (qk_scale None = 1/sqrt(head))
-L4 = [192, 193, 194, 195]
-ST_CASES = {
-    "basic_fp16": (3001, 32, 1, 128, 128, 64, L4, "float16", None, 0, False, 1.0, 0),
-    "basic_bf16": (3001, 32, 1, 128, 128, 64, L4, "bfloat16", None, 0, False, 1.0, 0),
-    "no_mask_mha": (4115, 32, 32, 128, 128, 64, L4, "float16", None, 0, False, 1.0, 0),
-    "norm_mask_fp16": (4116, 32, 32, 128, 128, 64, L4, "float16", None, 0, False, None, 1),
-    "norm_mask_bf16": (4116, 32, 32, 128, 128, 64, L4, "bfloat16", None, 0, False, None, 1),
-    "alibi_fp16": (4100, 32, 32, 128, 128, 64, [500, 500], "float16", None, 0, False, None, 2),
-    "alibi_bf16": (4100, 32, 32, 128, 128, 64, [500, 500], "bfloat16", None, 0, False, None, 2),
-    "gqa_8to1_alibi": (4101, 8, 1, 128, 128, 1024, [88] * 13, "float16", None, 0, False, None, 2),
-    "gqa_4to2_alibi": (4102, 4, 2, 128, 128, 1024, [88] * 13, "float16", None, 0, False, None, 2),
-    "gqa_32to8_alibi": (4103, 32, 8, 128, 128, 1024, [88] * 13, "float16", None, 0, False, None, 2),
-    "odd_heads": (4104, 7, 7, 128, 128, 1024, [88] * 13, "float16", None, 0, False, None, 1),
-    "heads_20_bf16": (4110, 20, 20, 128, 128, 64, [500, 500], "bfloat16", None, 0, False, None, 1),
-    "head_256_block_16": (4107, 16, 16, 256, 16, 512, L4, "float16", None, 0, False, None, 0),
-    "block_16": (4108, 32, 32, 128, 16, 512, L4, "float16", None, 0, False, None, 0),
-    "small_seqlen": (4105, 32, 32, 128, 128, 64, [33, 33, 33, 33], "float16", None, 0, False, None, 1),
-    "large_seqlen_bf16": (4106, 32, 32, 128, 128, 128, [3000, 3000], "bfloat16", None, 0, False, None, 1),
-    "varied_seqlens": (4111, 32, 32, 128, 128, 256, [100, 500, 1000, 2000], "float16", None, 0, False, None, 1),
-    "int8_kv": (3003, 32, 1, 128, 128, 64, L4, "float16", "int8", 1, False, None, 0),
-    "int8_kv_offset": (3004, 32, 1, 128, 128, 64, L4, "float16", "int8", 1, True, None, 0),
-    "gqa_int8_bf16": (4112, 32, 8, 128, 128, 64, L4, "bfloat16", "int8", 1, False, None, 1),
-    "gqa_int8_offset": (4113, 32, 8, 128, 128, 64, L4, "float16", "int8", 1, True, None, 1),
-    "bf16_int8_768": (6001, 32, 32, 128, 128, 256, [768], "bfloat16", "int8", 1, False, None, 1),
-    "bf16_int8_len128": (6002 + 128, 24, 24, 64, 128, 256, [128], "bfloat16", "int8", 1, False, None, 1),
-    "bf16_int8_len513": (6002 + 513, 24, 24, 64, 128, 256, [513], "bfloat16", "int8", 1, False, None, 1),
-    "bf16_int8_len1025": (6002 + 1025, 24, 24, 64, 128, 256, [1025], "bfloat16", "int8", 1, False, None, 1),
-    "bf16_int8_head32": (6100 + 32, 32, 32, 32, 16, 512, [512], "bfloat16", "int8", 1, False, None, 1),
-    "bf16_int8_head33": (6100 + 33, 32, 32, 33, 16, 512, [512], "bfloat16", "int8", 1, False, None, 1),
-    "bf16_int8_head128": (6100 + 128, 32, 32, 128, 16, 512, [512], "bfloat16", "int8", 1, False, None, 1),
-    "bf16_int8_gqa_4to1": (6200 + 401, 4, 1, 128, 128, 512, [766], "bfloat16", "int8", 1, False, None, 1),
-    "bf16_int8_gqa_24to2": (6200 + 2402, 24, 2, 128, 128, 512, [766], "bfloat16", "int8", 1, False, None, 1),
-    "bf16_int8_gqa_64to32": (6200 + 6432, 64, 32, 128, 128, 512, [766], "bfloat16", "int8", 1, False, None, 1),
-    "bf16_int8_block16": (6300 + 16, 32, 8, 64, 16, 1024, [1024], "bfloat16", "int8", 1, False, None, 1),
-    "bf16_int8_block128": (6300 + 128, 32, 8, 64, 128, 1024, [1024], "bfloat16", "int8", 1, False, None, 1),
-    "bf16_int8_len309": (6400, 64, 64, 32, 16, 256, [309], "bfloat16", "int8", 1, False, None, 1),
-}
+ST_CASES = cases.ST_CASES
+_st_case = cases.st_case
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
-def _st_case(name, mask_free=False):
-    seed, h, kvh, hd, bs, nb, lens, qd, kvd, quant, off, scale, mask = ST_CASES[name]
-    return workloads.st_style_case(seed, h, kvh, hd, bs, nb, lens, qd, kvd, quant, off, 0 if mask_free else mask, scale)
+def _fixture(name):
+    return np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
 
 
 @pytest.mark.parametrize("name", sorted(ST_CASES))
@@ -213,6 +178,13 @@ def test_pa_reference_case_matrix(name):
     case = _st_case(name)
     out, info = _run_pa(case)
     _check(case, out, name)
+    # and against the stored output of the reference's own golden function for these inputs
+    fx = _fixture("pa_" + name)
+    assert str(fx["sha_query"]) == cases.digest(case["query"])
+    quant = case["quant_type"] != 0
+    ok, detail = oracle.reference_accuracy_verdict(out, fx["golden"], case["q_dtype"], case["num_heads"],
+                                                   int(max(case["context_lens"])), quant)
+    assert ok, (name, detail)
 
 
 @pytest.mark.parametrize("name", ["basic_fp16", "basic_bf16", "gqa_32to8_alibi", "block_16", "varied_seqlens",

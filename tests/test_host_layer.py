@@ -1,0 +1,221 @@
+"""CPU: the C-ABI libraries load and export every declared symbol; the operator layer
+validates like the reference; planning is a pure function of each sequence's length."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import yaml
+
+import ms_custom_ops_b200 as ops
+from ms_custom_ops_b200 import TensorSpec as T
+from ms_custom_ops_b200 import _abi, _host
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared(header):
+    text = open(os.path.join(ROOT, "include", header)).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b((?:msco|ms_custom_ops)_[a-z0-9_]+)\s*\(", text)))
+
+
+@pytest.mark.parametrize("header,loader,listed", [("msco_b200.h", _abi.lib, _abi.EXPORTS),
+                                                  ("ms_custom_ops_c.h", _host.lib, _host.EXPORTS)])
+def test_library_exports_every_declared_symbol(header, loader, listed):
+    names = _declared(header)
+    assert sorted(listed) == names, "the Python binding list and the header disagree"
+    lib = loader()
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/{header} but not exported"
+    assert _abi.lib().msco_version() == 1
+
+
+def test_registered_signatures_match_the_yaml_definitions():
+    reg = ops.registered_ops()
+    for op, sub in (("reshape_and_cache", "reshape_and_cache"), ("paged_attention", "paged_attention")):
+        y = yaml.safe_load(open(os.path.join(ROOT, "ms_custom_ops_b200", "ops", "c_api", sub, op + "_op.yaml")))
+        parts = []
+        for name, spec in y[op]["args"].items():
+            parts.append(name if "default" not in spec else f"{name}={spec['default']}")
+        assert reg[op] == f"{op}({', '.join(parts)})"
+    # and the Python functions expose the same names, order and defaults
+    import inspect
+    for op in ("reshape_and_cache", "paged_attention"):
+        sig = inspect.signature(getattr(ops, op))
+        got = ", ".join(n if p.default is inspect._empty else f"{n}={p.default}" for n, p in sig.parameters.items())
+        assert reg[op] == f"{op}({got})"
+
+
+Q = T((4, 32, 128), "float16")
+KC = T((64, 128, 8, 128), "float16")
+KC8 = T((64, 128, 8, 128), "int8")
+BT = T((4, 8), "int32")
+LENS = [100, 200, 1024, 5]
+OKW = dict(q_head_num=32, kv_head_num=8, qk_scale=0.088)
+
+
+def test_infer_returns_query_shape_and_dtype():
+    assert ops.paged_attention_infer(Q, KC, KC, BT, LENS, **OKW) == ((4, 32, 128), "float16")
+    qb = T((4, 32, 128), "bfloat16")
+    sc, of = T((1024,), "float32"), T((1024,), "int32")
+    assert ops.paged_attention_infer(qb, KC8, KC8, BT, LENS, quant_type=1, k_descale=sc, v_descale=sc, k_offset=of,
+                                     v_offset=of, has_quant_offset=True, **OKW)[1] == "bfloat16"
+
+
+@pytest.mark.parametrize("kw,exc,frag", [
+    (dict(q_head_num=0), ValueError, "q_head_num should be greater than 0"),
+    (dict(q_head_num=32, kv_head_num=-1), ValueError, "kv_head_num should be greater than or equal to 0"),
+    (dict(q_head_num=32, kv_head_num=5), ValueError, "must be divisible by kv_head_num"),
+    (dict(q_head_num=32, kv_head_num=8, scale_type=2), ValueError, "scale_type is invalid"),
+    (dict(q_head_num=32, kv_head_num=8, scale_type=1, quant_type=1), ValueError, "scale type logn"),
+    (dict(q_head_num=32, kv_head_num=8, mla_v_dim=577), ValueError, "[0, 576]"),
+    (dict(q_head_num=32, kv_head_num=8, input_layout=2), ValueError, "input layout should be"),
+    (dict(q_head_num=32, kv_head_num=8, calc_type=2), ValueError, "calc_type should be"),
+    (dict(q_head_num=32, kv_head_num=8, calc_type=1, quant_type=1), ValueError, "MTP scene"),
+    (dict(q_head_num=32, kv_head_num=8, input_layout=1, scale_type=1), ValueError, "BNSD"),
+    (dict(q_head_num=32, kv_head_num=8, compress_type=3), ValueError, "compress type should not be 3"),
+    (dict(q_head_num=32, kv_head_num=8, compress_type=2), ValueError, "mask type should not be"),
+    (dict(q_head_num=32, kv_head_num=8, quant_type=2), ValueError, "out_data_type must be"),
+    (dict(q_head_num=32, kv_head_num=8, quant_type=3, out_data_type=1, has_quant_offset=True), ValueError,
+     "has_quant_offset must be false"),
+    (dict(q_head_num=32, kv_head_num=8, mla_v_dim=64), ValueError, "kv_head_num should be 1"),
+    (dict(q_head_num=32, kv_head_num=8, quant_type=1), ValueError, "key cache dtype must be int8"),
+    (dict(q_head_num=16, kv_head_num=8), ValueError, "must equal query's head dimension"),
+    (dict(q_head_num=32, kv_head_num=4), ValueError, "must equal the head_num of key_cache"),
+    (dict(q_head_num=32, kv_head_num=8, mask_type=4), ValueError, "MASK_FREE is only supported on 310P"),
+    (dict(q_head_num=32, kv_head_num=8, mask_type=1), ValueError, "attn_mask must be provided"),
+    # accepted by the reference, not built here
+    (dict(q_head_num=32, kv_head_num=8, calc_type=1), ops.UnsupportedOnB200, "calc_type=1"),
+    (dict(q_head_num=32, kv_head_num=8, mask_type=3), ops.UnsupportedOnB200, "mask_type=3"),
+    (dict(q_head_num=32, kv_head_num=8, scale_type=1), ops.UnsupportedOnB200, "LogN"),
+    (dict(q_head_num=32, kv_head_num=8, input_layout=1), ops.UnsupportedOnB200, "BNSD"),
+    (dict(q_head_num=32, kv_head_num=8, compress_type=1), ops.UnsupportedOnB200, "compress_type"),
+    (dict(q_head_num=32, kv_head_num=8, batch_run_status_enable=True), ops.UnsupportedOnB200, "batch_run_status"),
+])
+def test_parameter_rules_raise_like_the_reference(kw, exc, frag):
+    with pytest.raises(exc) as e:
+        ops.paged_attention_infer(Q, KC, KC, BT, LENS, **kw)
+    assert frag in str(e.value)
+
+
+def test_shape_and_type_rules():
+    bad_rank = T((4, 32 * 128), "float16")
+    with pytest.raises(ValueError, match="rank of query must be 3"):
+        ops.paged_attention_infer(bad_rank, KC, KC, BT, LENS, **OKW)
+    with pytest.raises(ValueError, match="rank of key_cache must be 4"):
+        ops.paged_attention_infer(Q, T((64, 128, 1024), "float16"), KC, BT, LENS, **OKW)
+    with pytest.raises(ValueError, match="rank of block table must be 2"):
+        ops.paged_attention_infer(Q, KC, KC, T((32,), "int32"), LENS, **OKW)
+    with pytest.raises(ValueError, match="num_blocks of key_cache and value_cache must be same"):
+        ops.paged_attention_infer(Q, KC, T((32, 128, 8, 128), "float16"), BT, LENS, **OKW)
+    with pytest.raises(ValueError, match="head_size of key_cache and query must be same"):
+        ops.paged_attention_infer(T((4, 32, 64), "float16"), KC, KC, BT, LENS, **OKW)
+    with pytest.raises(ValueError, match=r"block_size \* head_size must be <= 128 \* 128"):
+        big = T((64, 256, 8, 128), "float16")
+        ops.paged_attention_infer(Q, big, big, BT, LENS, **OKW)
+    with pytest.raises(ValueError, match="query dtype must be float16/bfloat16"):
+        ops.paged_attention_infer(T((4, 32, 128), "float32"), KC, KC, BT, LENS, **OKW)
+    with pytest.raises(ValueError, match="cache dtype must equal the query dtype"):
+        ops.paged_attention_infer(Q, T((64, 128, 8, 128), "bfloat16"), T((64, 128, 8, 128), "bfloat16"), BT, LENS, **OKW)
+    with pytest.raises(ValueError, match="context_lens has 3 entries"):
+        ops.paged_attention_infer(Q, KC, KC, BT, [1, 2, 3], **OKW)
+    with pytest.raises(ValueError, match="exceeds the block table"):
+        ops.paged_attention_workspace_size(Q, KC, KC, BT, [1, 2, 3, 1025], **OKW)
+    with pytest.raises(ops.UnsupportedOnB200, match="FRACTAL_NZ"):
+        ops.paged_attention_infer(T((4, 4096), "float16"), T((64, 128, 1024), "float16"),
+                                  T((64, 128, 1024), "float16"), BT, LENS, input_format=1, **OKW)
+    # context_lens must live on the host, as in the reference
+    with pytest.raises(ops.MscoError, match="must be a CPU tensor"):
+        ops.paged_attention_infer(Q, KC, KC, BT, T((4,), "int32", on_host=False), **OKW)
+    with pytest.raises(ops.MscoError, match="must be Int32"):
+        ops.paged_attention_infer(Q, KC, KC, BT, np.array([1, 2, 3, 4], dtype=np.int64), **OKW)
+
+
+def test_reshape_and_cache_validation_without_a_gpu():
+    L = _host.lib()
+    D = ops._Descs()
+    key, cache, slot = T((39, 512), "float16"), T((20, 64, 16, 32), "float16"), T((39,), "int32")
+
+    def call(*a, mode=0):
+        return L.ms_custom_ops_reshape_and_cache(*[D(x) for x in a], mode, 0, None)
+    with pytest.raises(ops.UnsupportedOnB200, match="FRACTAL_NZ"):
+        _host.check(call(key, None, cache, None, slot, mode=1))
+    with pytest.raises(ValueError, match="cache_mode must be 0"):
+        _host.check(call(key, None, cache, None, slot, mode=7))
+    with pytest.raises(TypeError, match="same dtype"):
+        _host.check(call(key, None, T((20, 64, 16, 32), "bfloat16"), None, slot))
+    with pytest.raises(ValueError, match="provided together"):
+        _host.check(call(key, key, cache, None, slot))
+    with pytest.raises(ValueError, match="slot_mapping has"):
+        _host.check(call(key, None, cache, None, T((40,), "int32")))
+    with pytest.raises(ValueError, match="hidden size"):
+        _host.check(call(T((39, 256), "float16"), None, cache, None, slot))
+    with pytest.raises(TypeError, match="slot_mapping must be Int32"):
+        _host.check(call(key, None, cache, None, T((39,), "int64")))
+    # zero-sized inputs are a successful no-op (no CUDA call is made)
+    assert call(T((0, 512), "float16"), None, cache, None, T((0,), "int32")) == 0
+
+
+def _plan(lens, hq=32, hkv=8, d=128, bs=128, kv="bfloat16", kernel=0, mask=0):
+    desc = _abi.MscoPaDesc()
+    desc.q_dtype = _abi.DTYPE_BF16
+    desc.kv_dtype = {"bfloat16": _abi.DTYPE_BF16, "int8": _abi.DTYPE_I8}[kv]
+    desc.quant_type = 1 if kv == "int8" else 0
+    desc.num_q_heads, desc.num_kv_heads, desc.head_dim, desc.block_size = hq, hkv, d, bs
+    desc.num_blocks = 1 << 20
+    desc.max_blocks_per_seq = (max(lens + [1]) + bs - 1) // bs
+    desc.qk_scale = 0.1
+    desc.kernel = kernel
+    desc.mask_type = mask
+    desc.mask_dtype = _abi.DTYPE_F32
+    return _abi.PaPlan(desc, lens)
+
+
+def test_split_rule_depends_on_the_sequence_only():
+    f = _abi.lib().msco_paged_attention_split_tokens
+    assert [f(n) for n in (1, 512, 513, 16384, 16385, 65536, 65537, 131072)] == [512] * 4 + [1024] * 2 + [2048] * 2
+    lens = [5000, 300, 0, 70000, 512, 513]
+    info = _plan(lens).info()
+    splits = [(n + f(n) - 1) // f(n) if n else 0 for n in lens]
+    assert info.max_splits == max(splits) == 35
+    assert info.partials == sum(s for s in splits if s > 1)
+    assert info.work_items == sum(splits) * 8
+    assert info.kv_tokens == sum(lens)
+    assert info.kernel == 2 and info.rows_per_item == 8 and info.grid == 148
+    # per-sequence split counts do not change with the batch they are planned in
+    alone = _plan([5000]).info()
+    assert alone.partials == splits[0] and alone.work_items == splits[0] * 8
+
+
+def test_kernel_selection_and_workspace():
+    assert _plan([100], hq=64, hkv=8).info().rows_per_item == 8
+    assert _plan([100], hq=128, hkv=8).info().rows_per_item == 16
+    wide = _plan([100], hq=24 * 8, hkv=8).info()      # 24 q rows per kv head -> two 16-row items
+    assert wide.rows_per_item == 16 and wide.work_items == 16
+    assert _plan([100], d=64).info().kernel == 1       # head_dim 64 -> general kernel
+    assert _plan([100], bs=48).info().kernel == 1
+    assert _plan([100], mask=1).info().kernel == 1
+    assert _plan([100], kv="int8").info().kernel == 2
+    with pytest.raises(_abi.MscoError):
+        _plan([100], d=64, kernel=2)
+    p = _plan([1000, 3000])
+    parts = 2 + 6
+    assert p.workspace_bytes >= parts * 32 * (128 + 2) * 4
+    assert p.workspace_bytes % 256 == 0
+    empty = _plan([0, 0])
+    assert empty.info().work_items == 0 and empty.workspace_bytes % 256 == 0
+    with pytest.raises(_abi.MscoError, match="negative"):
+        _plan([-1])
+
+
+def test_plan_cache_hits_on_repeated_lengths():
+    ops.plan_cache_clear()
+    for _ in range(3):
+        ops.paged_attention_workspace_size(Q, KC, KC, BT, LENS, **OKW)
+    ops.paged_attention_workspace_size(Q, KC, KC, BT, [100, 200, 1024, 6], **OKW)
+    st = ops.plan_cache_stats()
+    assert st["misses"] == 2 and st["hits"] == 2 and st["entries"] == 2
+    ops.plan_cache_clear()
+    assert ops.plan_cache_stats()["entries"] == 0
