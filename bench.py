@@ -31,9 +31,7 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
 import time
 
 import numpy as np
@@ -71,50 +69,54 @@ def workload_config(spec, lens, extra=None):
 # clocks
 # ----------------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
-    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+    """SM clock and throttle reasons sampled every few milliseconds between start() and stop().
 
-    def __init__(self, gpu_uuid=None):
-        self.path = tempfile.mktemp(prefix="clocks_", suffix=".csv")
-        cmd = ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"]
-        if gpu_uuid:
-            cmd.insert(1, f"--id={gpu_uuid}")
+    Reads NVML (the source nvidia-smi prints: clocks.sm, clocks.max.sm and the
+    clocks_event_reasons bits) from a background thread, because the timed regions last only
+    milliseconds and nvidia-smi's own loop cannot sample that fast.  Read-only: no setting of the
+    GPU is touched.
+    """
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, gpu_uuid, interval_s=0.004):
+        import threading
+        self.samples, self.bits, self.max_mhz = [], 0, None
+        self._stop = threading.Event()
+        self._thread = None
         try:
-            self.proc = subprocess.Popen(cmd, stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                h = pynvml.nvmlDeviceGetHandleByUUID(gpu_uuid)
+            except Exception:
+                h = pynvml.nvmlDeviceGetHandleByUUID(gpu_uuid.encode())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            return
+
+        def loop():
+            while not self._stop.is_set():
+                try:
+                    self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                    self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                except Exception:
+                    pass
+                self._stop.wait(interval_s)
+        self._thread = threading.Thread(target=loop, daemon=True)
+
+    def start(self):
+        if self._thread is not None:
+            self._thread.start()
+        return self
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        try:
-            for line in open(self.path):
-                parts = [p.strip() for p in line.split(",")]
-                if len(parts) < 7:
-                    continue
-                try:
-                    sm.append(float(parts[0]))
-                    mx.append(float(parts[1]))
-                except ValueError:
-                    continue
-                for name, val in zip(self.NAMES, parts[3:7]):
-                    if val.lower() == "active":
-                        reasons.add(name)
-            os.unlink(self.path)
-        except OSError:
-            pass
-        if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
-        return out
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+        reasons = sorted(name for bit, name in self.REASONS.items() if self.bits & bit)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.samples), "source": "nvml, 4 ms interval, under load"}
 
 
 def measured_hbm_peak():
@@ -250,7 +252,9 @@ def run_gpu(args):
             graph.replay()
     else:
         plan.profile_enable(True)
-    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)) if rank == 0 else None
+    # clocks are sampled from the start of the device-timed region to the end of the end-to-end
+    # region (the GPU is busy throughout)
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)).start() if rank == 0 else None
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()

@@ -108,7 +108,8 @@ def test_operator_errors_on_the_gpu_box():
     with pytest.raises(ops.MscoError, match="must be a CPU tensor"):
         ops.paged_attention(q, kc, vc, bt, to_dev(c["context_lens"]), q_head_num=32, kv_head_num=1)
     with pytest.raises(ops.MscoError, match="must be contiguous"):
-        ops.paged_attention(q.transpose(0, 1), kc, vc, bt, c["context_lens"], q_head_num=4, kv_head_num=1)
+        strided = torch.zeros((4, 32, 256), dtype=q.dtype, device=q.device)[:, :, :128]
+        ops.paged_attention(strided, kc, vc, bt, c["context_lens"], q_head_num=32, kv_head_num=1)
     with pytest.raises(ValueError, match="q_head_num should be greater than 0"):
         ops.paged_attention(q, kc, vc, bt, c["context_lens"])
     # a block id outside the cache is reported through the status word; the GPU stays usable
