@@ -133,10 +133,10 @@ typedef struct MscoPaPlanInfo {
   int64_t kv_tokens;       /* sum of context_lens                                       */
 } MscoPaPlanInfo;
 
-/* Split rule: tokens per KV split as a function of one sequence's length
- * only (never of the batch), so a request's result is bitwise independent of
- * what it is batched with. */
-int32_t msco_paged_attention_split_tokens(int32_t context_len);
+/* Split rule: tokens per KV split as a function of one sequence's length and
+ * the cache element type (MSCO_DTYPE_*) only -- never of the batch -- so a
+ * request's result is bitwise independent of what it is batched with. */
+int32_t msco_paged_attention_split_tokens(int32_t context_len, int32_t kv_dtype);
 
 /* Build the launch plan from the host copy of context_lens (the reference
  * reads the same host values into its param: paged_attention_graph.cc:773-776,

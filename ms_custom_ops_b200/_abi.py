@@ -70,7 +70,7 @@ def lib():
     L.msco_reshape_and_cache_quant.restype = C.c_int
     L.msco_reshape_and_cache_quant.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, vp, vp, vp, vp, i64, vp, vp]
     L.msco_paged_attention_split_tokens.restype = i32
-    L.msco_paged_attention_split_tokens.argtypes = [i32]
+    L.msco_paged_attention_split_tokens.argtypes = [i32, i32]
     L.msco_paged_attention_plan.restype = C.c_int
     L.msco_paged_attention_plan.argtypes = [C.POINTER(MscoPaDesc), C.POINTER(i32), i32, C.POINTER(vp)]
     L.msco_paged_attention_workspace_bytes.restype = sz

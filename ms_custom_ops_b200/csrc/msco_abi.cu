@@ -36,12 +36,14 @@ using namespace msco;
 extern "C" int msco_version(void) { return MSCO_ABI_VERSION; }
 extern "C" const char *msco_last_error(void) { return g_err; }
 
-// Tokens per KV split.  A function of the sequence's own length only: the
-// result for one request never depends on what else is in the batch.
-extern "C" int32_t msco_paged_attention_split_tokens(int32_t context_len) {
-  if (context_len <= 16384) return 512;
-  if (context_len <= 65536) return 1024;
-  return 2048;
+// Tokens per KV split.  A function of the sequence's own length (and of the
+// cache element type, fixed per call) only: the result for one request never
+// depends on what else is in the batch.  A split is sized to about 256 KB of
+// K/V per kv head at the short end, so that the per-split merge is amortised.
+extern "C" int32_t msco_paged_attention_split_tokens(int32_t context_len, int32_t kv_dtype) {
+  if (context_len > 65536) return 2048;
+  if (context_len > 16384) return 1024;
+  return kv_dtype == MSCO_DTYPE_I8 ? 1024 : 512;
 }
 
 static int validate_desc(const MscoPaDesc &d) {
@@ -142,7 +144,7 @@ extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *
   int max_splits = 0;
   for (int s = 0; s < nseq; ++s) {
     const int b = order[s], len = host_context_lens[b];
-    const int c = msco_paged_attention_split_tokens(len);
+    const int c = msco_paged_attention_split_tokens(len, d.kv_dtype);
     const int ns = (len + c - 1) / c;
     item_base[s] = (int32_t)items;
     seq_idx[s] = b; seq_len[s] = len; chunk[s] = c; nsplit[s] = ns;

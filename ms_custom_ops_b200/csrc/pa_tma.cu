@@ -2,21 +2,29 @@
 //
 // HBM-bound: every K/V byte of the context is read exactly once.  One
 // persistent CTA per SM walks a static round-robin list of work items
-// (sequence, kv head, q-row block, KV split).  A producer warp streams
-// 128-token K and V tiles of the paged cache into a ring of shared-memory
-// stages with tiled TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no
-// multicast) that complete on mbarriers; the stream runs ahead across item
-// boundaries, so the memory pipe never drains between items.  Eight consumer
-// warps each own 16 of the tile's 128 tokens and keep an independent online
-// softmax state (m, l, O) for the padded GQA group (M = 16 rows):
-//   S = Q K^T  and  O += P V  as mma.sync m16n8k16 micro-tiles, fp32 accumulate,
-//   K fragments by ldmatrix, V fragments by ldmatrix.trans,
-//   int8 KV: bytes -> fp16 in registers (xor 0x80, byte-permute into
-//   0x6400|u = 1024+u, subtract 1152), k_descale folded into Q once per item,
-//   v_descale / v_offset applied once to the output.
-// At the end of an item the eight states are merged through shared memory and
-// either written as the final output (one split) or as an fp32 partial
-// (m, l, O) for the reduce kernel.
+// (sequence, kv head, q-row block, KV split).  A producer warp streams K and V
+// tiles of the paged cache into a ring of shared-memory stages with tiled TMA
+// loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) that complete
+// on mbarriers; the stream runs ahead across item boundaries, so the memory
+// pipe never drains between items.  Each consumer warp owns 16 tokens of a
+// tile and keeps an independent online-softmax state (m, l, O) for the GQA
+// group of q rows.
+//
+// The micro-tiles put the TOKENS on the M side of mma.sync m16n8k16 and the q
+// rows on the N side (N = 8 per tile, one or two tiles), so a group of up to 8
+// q rows costs no padding work:
+//   S^T = K Q^T     A = K tile (ldmatrix),        B = Q^T (registers, loaded once per item)
+//   O^T += V^T P^T  A = V^T   (ldmatrix.trans),   B = P^T (movmatrix of the probabilities)
+// fp32 accumulation throughout.  int8 KV: bytes become fp16 in registers
+// (xor 0x80, byte-permute into 0x6400|u = 1024 + u); for K the constant 1152
+// is not removed because it shifts every score of a q row by the same amount,
+// which the softmax cancels; for V it stays in the accumulators and
+// 1152 * l is subtracted once per item.  The row sums l are accumulated by the
+// tensor cores from the same rounded probabilities (a tile of ones in place
+// of V^T).  k_descale is folded into Q once per item, v_descale / v_offset
+// are applied once to the output.  At the end of an item the warps' states are merged through shared
+// memory and written either as the final output (one split) or as an fp32
+// partial (m, l, O) for the reduce kernel.
 //
 // Algorithmic bytes per context token: 2 * head_dim * sizeof(kv) per kv head.
 #include <cuda.h>
@@ -30,49 +38,54 @@ namespace msco {
 namespace {
 
 constexpr int kD = 128;               // head_dim of this kernel
-constexpr int kTile = 128;            // tokens per tile
-constexpr int kConsumerWarps = 8;     // 16 tokens of the tile each
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kMergeStride = 136;     // floats per merged row (bank-conflict padding)
+constexpr int kMergeStride = 132;     // floats per merged row (bank-conflict padding)
 constexpr int kQSlotBytes = 16 * kD * 2;
 constexpr float kNeg = -1.0e30f;
 constexpr uint32_t kWaitLimit = 1u << 24;
 
-template <bool KV8, bool G16> struct Cfg {
+// NT = number of 8-row tiles of the q group (1: up to 8 rows, 2: up to 16).
+template <bool KV8, int NT> struct Cfg {
+  static constexpr int kWarps = (KV8 && NT == 1) ? 16 : 8;  // consumer warps, 16 tokens each
+  static constexpr int kTile = kWarps * 16;                 // tokens per tile
+  static constexpr int kThreads = (kWarps + 1) * 32;
+  static constexpr int kConsumerThreads = kWarps * 32;
   static constexpr int kRowBytes = KV8 ? kD : 2 * kD;       // one token row of one head
-  static constexpr int kStageBytes = kTile * kRowBytes;     // 16 KB (int8) / 32 KB (16-bit)
-  static constexpr int kStages = KV8 ? 8 : (G16 ? 4 : 5);
-  static constexpr int kRows = G16 ? 16 : 8;
-  static constexpr int kMergeBytes = kConsumerWarps * kRows * kMergeStride * 4;
+  static constexpr int kStageBytes = kTile * kRowBytes;     // 16 / 32 KB
+  static constexpr int kStages = KV8 ? (NT == 1 ? 4 : 8) : (NT == 1 ? 5 : 4);
+  static constexpr int kRows = 8 * NT;
+  static constexpr int kMergeBytes = kWarps * kRows * kMergeStride * 4;
   static constexpr int kOffQ = kStages * kStageBytes;
-  static constexpr int kOffMerge = kOffQ + 2 * kQSlotBytes;
-  static constexpr int kOffMl = kOffMerge + kMergeBytes;           // [warp][16][2] floats
-  static constexpr int kOffDesc = kOffMl + kConsumerWarps * 16 * 2 * 4;  // 2 x WorkItem (8 ints)
-  static constexpr int kOffBar = kOffDesc + 2 * 8 * 4;             // mbarriers
+  static constexpr int kOffQFrag = kOffQ + 2 * kQSlotBytes;         // int8 KV: scaled fp16 Q in fragment order
+  static constexpr int kQFragBytes = KV8 ? NT * 4 * 32 * 16 : 0;    // [row tile][k-step pair][lane] uint4
+  static constexpr int kOffMerge = kOffQFrag + kQFragBytes;
+  static constexpr int kOffMl = kOffMerge + kMergeBytes;            // [warp][16] float2
+  static constexpr int kOffDesc = kOffMl + kWarps * 16 * 2 * 4;     // 2 x 8 ints
+  static constexpr int kOffBar = kOffDesc + 2 * 8 * 4;              // mbarriers
   static constexpr int kNumBars = 2 * kStages + 4;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
-  static constexpr int kDynSmem = kSmemBytes + 1024;               // slack for 1024-byte alignment
+  static constexpr int kDynSmem = kSmemBytes + 1024;                // slack for 1024-byte alignment
 };
 
-// int8x4 (already xor-ed with 0x80808080) -> two fp16x2 registers holding the
-// signed values of byte pairs (sel picks which bytes).
-__device__ __forceinline__ uint32_t bytes_to_half2(uint32_t x, uint32_t sel) {
+// int8x4 (already xor-ed with 0x80808080) -> fp16x2 {1024 + u_a, 1024 + u_b}; sel picks bytes a, b.
+__device__ __forceinline__ uint32_t bytes_to_half2_biased(uint32_t x, uint32_t sel) {
   uint32_t h;
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(h) : "r"(x), "r"(0x64646464u), "r"(sel));
-  // h = {1024 + u_lo, 1024 + u_hi} as fp16x2; remove 1024 + 128
-  const uint32_t bias = 0x64806480u;  // fp16 1152.0 twice
-  uint32_t r;
-  asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(h), "r"(bias));
-  return r;
+  return h;
+}
+// transpose of an 8x8 matrix of 16-bit values held as one register per lane
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
 }
 
-template <typename T, bool KV8, bool G16>
-__global__ void __launch_bounds__(kThreads, 1)
+template <typename T, bool KV8, int NT>
+__global__ void __launch_bounds__(Cfg<KV8, NT>::kThreads, 1)
 pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, PaParams p) {
-  using C = Cfg<KV8, G16>;
-  // fp16 arithmetic for int8 KV (integers up to 255 are exact in fp16, not in bf16)
+  using C = Cfg<KV8, NT>;
+  // fp16 arithmetic for int8 KV (integers up to 1279 are exact in fp16, not in bf16)
   using MT = typename std::conditional<KV8, __half, T>::type;
+  constexpr int kTile = C::kTile;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + C::kOffBar);
@@ -84,11 +97,11 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::kStages; ++i) {
       mbar_init(&full[i], 1);
-      mbar_init(&empty[i], kConsumerWarps);
+      mbar_init(&empty[i], C::kWarps);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&qfull[i], 1);
-      mbar_init(&qempty[i], kConsumerWarps);
+      mbar_init(&qempty[i], C::kWarps);
     }
     fence_barrier_init();
   }
@@ -96,9 +109,8 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
   const PlanView pv = make_plan_view(p.plan);
   const int total = pv.total_items;
-  const int rpi = C::kRows;
 
-  if (warp == kConsumerWarps) {
+  if (warp == C::kWarps) {
     // ======================= producer warp =======================
     if (lane == 0) {
       prefetch_tmap(&tm_k);
@@ -106,10 +118,10 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
     uint32_t st = 0, ph = 0;
     const int bs = p.block_size;
-    const int bpt = kTile / bs;  // cache blocks per tile
+    const int bpt = kTile / bs;  // cache blocks per tile (divides 32)
     int qi = 0;
     for (int t = blockIdx.x; t < total; t += gridDim.x, ++qi) {
-      const WorkItem w = decode_item(pv, t, p.num_kv_heads, p.group, rpi);
+      const WorkItem w = decode_item(pv, t, p.num_kv_heads, p.group, C::kRows);
       const int qs = qi & 1;
       const uint32_t qph = (qi >> 1) & 1;
       if (!mbar_wait(&qempty[qs], qph ^ 1, kWaitLimit)) {
@@ -131,7 +143,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       const int32_t *trow = p.block_tables + (int64_t)w.b * p.max_blocks_per_seq + w.tok0 / bs;
       int tile = 0;
       for (int blk0 = 0; blk0 < nblk_item; blk0 += 32) {
-        // 32 block ids per batch, one per lane; a batch holds whole tiles (bpt divides 32)
+        // 32 block ids per batch, one per lane; a batch holds whole tiles
         int my_id = 0;
         if (blk0 + lane < nblk_item) {
           my_id = __ldg(trow + blk0 + lane);
@@ -157,12 +169,8 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
               if (lane == 0) {
                 const CUtensorMap *tm = op == 0 ? &tm_k : &tm_v;
                 const int z = id * bs;
-                if (KV8) {
-                  tma_load_3d(dst + j * bs * 128, tm, 0, w.kvh, z, &full[st]);
-                } else {
-                  tma_load_3d(dst + j * bs * 128, tm, 0, w.kvh, z, &full[st]);
-                  tma_load_3d(dst + kTile * 128 + j * bs * 128, tm, 64, w.kvh, z, &full[st]);
-                }
+                tma_load_3d(dst + j * bs * 128, tm, 0, w.kvh, z, &full[st]);
+                if (!KV8) tma_load_3d(dst + kTile * 128 + j * bs * 128, tm, 64, w.kvh, z, &full[st]);
               }
             }
             if (++st == C::kStages) { st = 0; ph ^= 1; }
@@ -175,14 +183,15 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
   // ======================= consumer warps =======================
   const int gid = lane >> 2, q4 = lane & 3;
-  const int t0 = warp * 16;                 // this warp's token rows inside a tile
-  const int mat = lane >> 3, mr = lane & 7; // ldmatrix: matrix id and row supplied by this lane
+  const int t0 = warp * 16;                  // this warp's token rows inside a tile
+  const int mat = lane >> 3, mr = lane & 7;  // ldmatrix: matrix id and row supplied by this lane
   const uint32_t stage0 = smem_u32(smem);
   float *mbuf = reinterpret_cast<float *>(smem + C::kOffMerge);
   float2 *mlbuf = reinterpret_cast<float2 *>(smem + C::kOffMl);
-  // per-lane byte offsets of the ldmatrix rows (swizzle: 16-byte chunk ^= row & 7)
-  const uint32_t k_row_off = (uint32_t)(t0 + (mat >> 1) * 8 + mr) * 128u;  // K: matrices 2,3 = tokens +8
-  const uint32_t v_row_off = (uint32_t)(t0 + (mat & 1) * 8 + mr) * 128u;   // V: matrices 1,3 = tokens +8
+  // byte offsets of the ldmatrix rows this lane supplies (swizzle: 16-byte chunk ^= row & 7)
+  //   K 16-bit, K int8, V int8: matrices 1,3 are the tokens +8;  V 16-bit: matrices 2,3
+  const uint32_t row_m1 = (uint32_t)(t0 + (mat & 1) * 8 + mr) * 128u;
+  const uint32_t row_m2 = (uint32_t)(t0 + (mat >> 1) * 8 + mr) * 128u;
   const int tid = threadIdx.x;
 
   uint32_t st = 0, ph = 0;
@@ -198,93 +207,116 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const int b = dsc[0], kvh = dsc[1], row0 = dsc[2], nrows = dsc[3];
     const int tok0 = dsc[4], tok1 = dsc[5], nsplit = dsc[6], part = dsc[7];
 
-    // ---- Q fragments (A operand, 16 x 128), rows >= nrows are zero ----
-    uint32_t qa[8][4];
+    // ---- Q^T fragments (B operand): lane holds q row 8nt + gid, rows >= nrows are zero ----
+    uint32_t qb[8][NT][2];
     {
       const T *qsm = reinterpret_cast<const T *>(smem + C::kOffQ + qs * kQSlotBytes);
-      const bool vlo = gid < nrows, vhi = G16 && (gid + 8 < nrows);
-      const T *qlo = qsm + gid * kD, *qhi = qsm + (gid + 8) * kD;
       if (!KV8) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const int c = 16 * ks + 2 * q4;
-          qa[ks][0] = vlo ? *reinterpret_cast<const uint32_t *>(qlo + c) : 0u;
-          qa[ks][1] = vhi ? *reinterpret_cast<const uint32_t *>(qhi + c) : 0u;
-          qa[ks][2] = vlo ? *reinterpret_cast<const uint32_t *>(qlo + c + 8) : 0u;
-          qa[ks][3] = vhi ? *reinterpret_cast<const uint32_t *>(qhi + c + 8) : 0u;
+        for (int nt = 0; nt < NT; ++nt) {
+          const bool valid = 8 * nt + gid < nrows;
+          const T *qr = qsm + (8 * nt + gid) * kD;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const int c = 16 * ks + 2 * q4;
+            qb[ks][nt][0] = valid ? *reinterpret_cast<const uint32_t *>(qr + c) : 0u;
+            qb[ks][nt][1] = valid ? *reinterpret_cast<const uint32_t *>(qr + c + 8) : 0u;
+          }
         }
       } else {
-        // int8 K: the contraction index inside each 16-wide group is permuted so that the four
-        // bytes a lane gets from ldmatrix (d = 16ks + 4q4 .. +3) are its two B registers; Q uses
-        // the same permutation.  k_descale is folded into Q here.
+        // int8 K: k_descale is folded into Q, and inside each 16-wide group of the head dimension
+        // the contraction index is permuted so that the four bytes a lane gets from ldmatrix
+        // (d = 16ks + 4q4 .. +3) are its two A registers.  The warps convert the rows together,
+        // once per item, into fragment order: word (row tile, k-step pair, lane, 2 (ks & 1) + j)
+        // holds the fp16 pair Q[8nt + gid][16ks + 4q4 + 2j, + 1] * k_descale.
+        uint32_t *qfrag = reinterpret_cast<uint32_t *>(smem + C::kOffQFrag);
         const float *ksc = p.k_descale + kvh * kD;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const int c = 16 * ks + 4 * q4;
-          const float4 sc = __ldg(reinterpret_cast<const float4 *>(ksc + c));
-          float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
-          if (vlo) {
-            lo[0] = to_f32<T>(qlo[c]) * sc.x; lo[1] = to_f32<T>(qlo[c + 1]) * sc.y;
-            lo[2] = to_f32<T>(qlo[c + 2]) * sc.z; lo[3] = to_f32<T>(qlo[c + 3]) * sc.w;
+        for (int u = tid; u < C::kRows * 64; u += C::kConsumerThreads) {
+          const int r = u >> 6, dp = u & 63;  // q row, index of the pair of head-dim columns
+          float e0 = 0.f, e1 = 0.f;
+          if (r < nrows) {
+            const float2 sc = __ldg(reinterpret_cast<const float2 *>(ksc + 2 * dp));
+            e0 = to_f32<T>(qsm[r * kD + 2 * dp]) * sc.x;
+            e1 = to_f32<T>(qsm[r * kD + 2 * dp + 1]) * sc.y;
           }
-          if (vhi) {
-            hi[0] = to_f32<T>(qhi[c]) * sc.x; hi[1] = to_f32<T>(qhi[c + 1]) * sc.y;
-            hi[2] = to_f32<T>(qhi[c + 2]) * sc.z; hi[3] = to_f32<T>(qhi[c + 3]) * sc.w;
-          }
-          qa[ks][0] = pack2<__half>(lo[0], lo[1]);
-          qa[ks][1] = pack2<__half>(hi[0], hi[1]);
-          qa[ks][2] = pack2<__half>(lo[2], lo[3]);
-          qa[ks][3] = pack2<__half>(hi[2], hi[3]);
+          const int ks = dp >> 3, qq = (dp >> 1) & 3, j = dp & 1;
+          qfrag[(((r >> 3) * 4 + (ks >> 1)) * 32 + (r & 7) * 4 + qq) * 4 + 2 * (ks & 1) + j] = pack2<__half>(e0, e1);
         }
+        named_bar_sync(1, C::kConsumerThreads);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int kp = 0; kp < 4; ++kp) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(qfrag + ((nt * 4 + kp) * 32 + lane) * 4);
+            qb[2 * kp][nt][0] = v.x; qb[2 * kp][nt][1] = v.y;
+            qb[2 * kp + 1][nt][0] = v.z; qb[2 * kp + 1][nt][1] = v.w;
+          }
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&qempty[qs]);
 
-    float m_lo = kNeg, m_hi = kNeg, l_lo = 0.f, l_hi = 0.f;  // l_*: this thread's share of the row sum
-    float o[16][4];
+    // running state of this lane's two q rows per row tile (rows 8nt + 2q4, + 1)
+    // The row sums l come from the tensor cores too: a tile of ones in place of V^T gives
+    // sum_tokens P (of exactly the rounded probabilities the output is built from) in ol[nt][0..1].
+    float m_run[NT][2];
+    float ol[NT][4];
+    float o[8][NT][4];  // O^T: [16-wide slice of head_dim][row tile]
 #pragma unroll
-    for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int nt = 0; nt < NT; ++nt) {
+      m_run[nt][0] = m_run[nt][1] = kNeg;
+      ol[nt][0] = ol[nt][1] = ol[nt][2] = ol[nt][3] = 0.f;
+    }
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) o[mt][nt][0] = o[mt][nt][1] = o[mt][nt][2] = o[mt][nt][3] = 0.f;
 
     const int ntiles = (tok1 - tok0 + kTile - 1) / kTile;
     for (int ti = 0; ti < ntiles; ++ti) {
       const int nv = min(kTile, tok1 - tok0 - ti * kTile);
       const bool active = t0 < nv;  // warp-uniform: any of this warp's 16 tokens valid
-      // ---------------- S = Q K^T ----------------
-      float s[2][4];
+      // ---------------- S^T = K Q^T ----------------
+      float s[NT][4];
 #pragma unroll
-      for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
       if (!mbar_wait(&full[st], ph, kWaitLimit)) {
         atomicExch(p.plan, kStatusTimeout);
         return;
       }
       if (active) {
-        const uint32_t kbase = stage0 + st * C::kStageBytes + k_row_off;
+        const uint32_t kbase = stage0 + st * C::kStageBytes + row_m1;
         if (!KV8) {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t cc = (uint32_t)(2 * (ks & 3) + (mat & 1));
+            const uint32_t cc = (uint32_t)(2 * (ks & 3) + (mat >> 1));
             const uint32_t addr = kbase + (uint32_t)(ks >> 2) * (kTile * 128) + ((cc ^ (uint32_t)mr) << 4);
-            uint32_t b0, b1, b2, b3;
-            ldmatrix_x4(addr, b0, b1, b2, b3);
-            mma16816<MT>(s[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
-            mma16816<MT>(s[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4(addr, a0, a1, a2, a3);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma16816<MT>(s[nt], a0, a1, a2, a3, qb[ks][nt][0], qb[ks][nt][1]);
           }
         } else {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const uint32_t cc = (uint32_t)(2 * i + (mat & 1));
-            uint32_t r0, r1, r2, r3;
+            const uint32_t cc = (uint32_t)(2 * i + (mat >> 1));
+            uint32_t r0, r1, r2, r3;  // (tokens lo, 2i) (tokens hi, 2i) (lo, 2i+1) (hi, 2i+1)
             ldmatrix_x4(kbase + ((cc ^ (uint32_t)mr) << 4), r0, r1, r2, r3);
             r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
-            mma16816<MT>(s[0], qa[2 * i][0], qa[2 * i][1], qa[2 * i][2], qa[2 * i][3],
-                         bytes_to_half2(r0, 0x5140u), bytes_to_half2(r0, 0x5342u));
-            mma16816<MT>(s[0], qa[2 * i + 1][0], qa[2 * i + 1][1], qa[2 * i + 1][2], qa[2 * i + 1][3],
-                         bytes_to_half2(r1, 0x5140u), bytes_to_half2(r1, 0x5342u));
-            mma16816<MT>(s[1], qa[2 * i][0], qa[2 * i][1], qa[2 * i][2], qa[2 * i][3],
-                         bytes_to_half2(r2, 0x5140u), bytes_to_half2(r2, 0x5342u));
-            mma16816<MT>(s[1], qa[2 * i + 1][0], qa[2 * i + 1][1], qa[2 * i + 1][2], qa[2 * i + 1][3],
-                         bytes_to_half2(r3, 0x5140u), bytes_to_half2(r3, 0x5342u));
+            {
+              const uint32_t a0 = bytes_to_half2_biased(r0, 0x5140u), a1 = bytes_to_half2_biased(r1, 0x5140u);
+              const uint32_t a2 = bytes_to_half2_biased(r0, 0x5342u), a3 = bytes_to_half2_biased(r1, 0x5342u);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt)
+                mma16816<MT>(s[nt], a0, a1, a2, a3, qb[2 * i][nt][0], qb[2 * i][nt][1]);
+            }
+            {
+              const uint32_t a0 = bytes_to_half2_biased(r2, 0x5140u), a1 = bytes_to_half2_biased(r3, 0x5140u);
+              const uint32_t a2 = bytes_to_half2_biased(r2, 0x5342u), a3 = bytes_to_half2_biased(r3, 0x5342u);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt)
+                mma16816<MT>(s[nt], a0, a1, a2, a3, qb[2 * i + 1][nt][0], qb[2 * i + 1][nt][1]);
+            }
           }
         }
       }
@@ -293,57 +325,42 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       if (++st == C::kStages) { st = 0; ph ^= 1; }
 
       // ---------------- online softmax ----------------
-      uint32_t pa[4] = {0u, 0u, 0u, 0u};
+      // s[nt]: [0] (token gid, row 2q4) [1] (token gid, row 2q4+1) [2] (token gid+8, row 2q4) [3] (gid+8, 2q4+1)
+      uint32_t pb[NT][2];
       if (active) {
         const float c = p.scale_log2e;
+        const bool dead_lo = t0 + gid >= nv, dead_hi = t0 + gid + 8 >= nv;  // past the end of the range
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int nt = 0; nt < NT; ++nt) {
+          float x0 = dead_lo ? kNeg : s[nt][0] * c, x1 = dead_lo ? kNeg : s[nt][1] * c;
+          float x2 = dead_hi ? kNeg : s[nt][2] * c, x3 = dead_hi ? kNeg : s[nt][3] * c;
+          float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) s[j][e] *= c;
-        if (nv < t0 + 16) {  // tail: mask tokens at or beyond the end of the range
-#pragma unroll
-          for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              if (t0 + 8 * j + 2 * q4 + (e & 1) >= nv) s[j][e] = kNeg;
-        }
-        {
-          float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-          const float mnew = fmaxf(m_lo, mx);
-          const float alpha = fast_exp2(m_lo - mnew);
-          m_lo = mnew;
-          const float p0 = fast_exp2(s[0][0] - mnew), p1 = fast_exp2(s[0][1] - mnew);
-          const float p2 = fast_exp2(s[1][0] - mnew), p3 = fast_exp2(s[1][1] - mnew);
-          l_lo = l_lo * alpha + (p0 + p1) + (p2 + p3);
-          pa[0] = pack2<MT>(p0, p1);
-          pa[2] = pack2<MT>(p2, p3);
-          if (alpha != 1.f) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) { o[i][0] *= alpha; o[i][1] *= alpha; }
+          for (int sh = 4; sh <= 16; sh <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
           }
-        }
-        if (G16) {
-          float mx = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-          const float mnew = fmaxf(m_hi, mx);
-          const float alpha = fast_exp2(m_hi - mnew);
-          m_hi = mnew;
-          const float p0 = fast_exp2(s[0][2] - mnew), p1 = fast_exp2(s[0][3] - mnew);
-          const float p2 = fast_exp2(s[1][2] - mnew), p3 = fast_exp2(s[1][3] - mnew);
-          l_hi = l_hi * alpha + (p0 + p1) + (p2 + p3);
-          pa[1] = pack2<MT>(p0, p1);
-          pa[3] = pack2<MT>(p2, p3);
-          if (alpha != 1.f) {
+          const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
+          const float al0 = fast_exp2(m_run[nt][0] - mn0), al1 = fast_exp2(m_run[nt][1] - mn1);
+          m_run[nt][0] = mn0;
+          m_run[nt][1] = mn1;
+          x0 = fast_exp2(x0 - mn0); x2 = fast_exp2(x2 - mn0);
+          x1 = fast_exp2(x1 - mn1); x3 = fast_exp2(x3 - mn1);
+          if (al0 != 1.f || al1 != 1.f) {
+            ol[nt][0] *= al0; ol[nt][1] *= al1;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) { o[i][2] *= alpha; o[i][3] *= alpha; }
+            for (int mt = 0; mt < 8; ++mt) {
+              o[mt][nt][0] *= al0; o[mt][nt][2] *= al0;
+              o[mt][nt][1] *= al1; o[mt][nt][3] *= al1;
+            }
           }
+          // probabilities (token-major) -> P^T fragments: (tokens 2q4, 2q4+1 | +8; row gid)
+          pb[nt][0] = movmatrix_trans(pack2<MT>(x0, x1));
+          pb[nt][1] = movmatrix_trans(pack2<MT>(x2, x3));
         }
       }
 
-      // ---------------- O += P V ----------------
+      // ---------------- O^T += V^T P^T ----------------
       if (!mbar_wait(&full[st], ph, kWaitLimit)) {
         atomicExch(p.plan, kStatusTimeout);
         return;
@@ -365,29 +382,43 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           fence_proxy_async();
           __syncwarp();
         }
-        const uint32_t vbase = stage0 + st * C::kStageBytes + v_row_off;
-        if (!KV8) {
+        {
+          const uint32_t ones = std::is_same<MT, __half>::value ? 0x3C003C00u : 0x3F803F80u;  // 1.0 twice
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint32_t c16 = (uint32_t)(2 * i + (mat >> 1));
-            const uint32_t addr = vbase + (c16 >> 3) * (kTile * 128) + (((c16 & 7) ^ (uint32_t)mr) << 4);
-            uint32_t v0, v1, v2, v3;
-            ldmatrix_x4_trans(addr, v0, v1, v2, v3);
-            mma16816<MT>(o[2 * i], pa[0], pa[1], pa[2], pa[3], v0, v1);
-            mma16816<MT>(o[2 * i + 1], pa[0], pa[1], pa[2], pa[3], v2, v3);
+          for (int nt = 0; nt < NT; ++nt) mma16816<MT>(ol[nt], ones, ones, ones, ones, pb[nt][0], pb[nt][1]);
+        }
+        if (!KV8) {
+          const uint32_t vbase = stage0 + st * C::kStageBytes + row_m2;
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) {
+            const uint32_t cc = (uint32_t)(2 * (mt & 3) + (mat & 1));
+            const uint32_t addr = vbase + (uint32_t)(mt >> 2) * (kTile * 128) + ((cc ^ (uint32_t)mr) << 4);
+            uint32_t a0, a1, a2, a3;  // (d lo, tok lo) (d hi, tok lo) (d lo, tok hi) (d hi, tok hi)
+            ldmatrix_x4_trans(addr, a0, a1, a2, a3);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma16816<MT>(o[mt][nt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
           }
         } else {
+          const uint32_t vbase = stage0 + st * C::kStageBytes + row_m1;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint32_t cc = (uint32_t)(2 * i + (mat >> 1));
-            uint32_t r0, r1, r2, r3;
+            uint32_t r0, r1, r2, r3;  // (tok lo, 2i) (tok hi, 2i) (tok lo, 2i+1) (tok hi, 2i+1)
             ldmatrix_x4_trans(vbase + ((cc ^ (uint32_t)mr) << 4), r0, r1, r2, r3);
             r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
-            // bytes 0,2 = even column of the 16-wide group, bytes 1,3 = odd column
-            mma16816<MT>(o[4 * i + 0], pa[0], pa[1], pa[2], pa[3], bytes_to_half2(r0, 0x5240u), bytes_to_half2(r1, 0x5240u));
-            mma16816<MT>(o[4 * i + 1], pa[0], pa[1], pa[2], pa[3], bytes_to_half2(r0, 0x5341u), bytes_to_half2(r1, 0x5341u));
-            mma16816<MT>(o[4 * i + 2], pa[0], pa[1], pa[2], pa[3], bytes_to_half2(r2, 0x5240u), bytes_to_half2(r3, 0x5240u));
-            mma16816<MT>(o[4 * i + 3], pa[0], pa[1], pa[2], pa[3], bytes_to_half2(r2, 0x5341u), bytes_to_half2(r3, 0x5341u));
+            // bytes 0,2: head-dim column 16c + 2 gid (tile rows 0..7); bytes 1,3: column + 1 (rows 8..15)
+            {
+              const uint32_t a0 = bytes_to_half2_biased(r0, 0x5240u), a1 = bytes_to_half2_biased(r0, 0x5341u);
+              const uint32_t a2 = bytes_to_half2_biased(r1, 0x5240u), a3 = bytes_to_half2_biased(r1, 0x5341u);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) mma16816<MT>(o[2 * i][nt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
+            }
+            {
+              const uint32_t a0 = bytes_to_half2_biased(r2, 0x5240u), a1 = bytes_to_half2_biased(r2, 0x5341u);
+              const uint32_t a2 = bytes_to_half2_biased(r3, 0x5240u), a3 = bytes_to_half2_biased(r3, 0x5341u);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) mma16816<MT>(o[2 * i + 1][nt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
+            }
           }
         }
       }
@@ -396,91 +427,75 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       if (++st == C::kStages) { st = 0; ph ^= 1; }
     }
 
-    // ---------------- merge the eight warps' states ----------------
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-    if (G16) {
-      l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
-      l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-    }
-    if (q4 == 0) {
-      mlbuf[warp * 16 + gid] = make_float2(m_lo, l_lo);
-      if (G16) mlbuf[warp * 16 + gid + 8] = make_float2(m_hi, l_hi);
-    }
-    named_bar_sync(1, kConsumerThreads);
-    {
-      float Mlo = kNeg, Mhi = kNeg;
+    // ---------------- merge the warps' states ----------------
+    // Every warp publishes (m, l) of its rows and its un-scaled O^T; after one barrier each
+    // output element is reduced over the warps with the weights 2^(m_w - M).
 #pragma unroll
-      for (int w2 = 0; w2 < kConsumerWarps; ++w2) {
-        Mlo = fmaxf(Mlo, mlbuf[w2 * 16 + gid].x);
-        if (G16) Mhi = fmaxf(Mhi, mlbuf[w2 * 16 + gid + 8].x);
+    for (int nt = 0; nt < NT; ++nt) {
+      const int r0 = 8 * nt + 2 * q4;
+      if (gid == 0) {
+        mlbuf[warp * 16 + r0] = make_float2(m_run[nt][0], ol[nt][0]);
+        mlbuf[warp * 16 + r0 + 1] = make_float2(m_run[nt][1], ol[nt][1]);
       }
-      const float flo = fast_exp2(m_lo - Mlo), fhi = G16 ? fast_exp2(m_hi - Mhi) : 0.f;
-      float *rlo = mbuf + (warp * C::kRows + gid) * kMergeStride;
-      float *rhi = mbuf + (warp * C::kRows + (G16 ? gid + 8 : 0)) * kMergeStride;
-      if (!KV8) {
+      float *w0 = mbuf + (warp * C::kRows + r0) * kMergeStride, *w1 = w0 + kMergeStride;
 #pragma unroll
-        for (int jn = 0; jn < 16; ++jn) {
-          const int d = 8 * jn + 2 * q4;
-          *reinterpret_cast<float2 *>(rlo + d) = make_float2(o[jn][0] * flo, o[jn][1] * flo);
-          if (G16) *reinterpret_cast<float2 *>(rhi + d) = make_float2(o[jn][2] * fhi, o[jn][3] * fhi);
-        }
-      } else {
-#pragma unroll
-        for (int cg = 0; cg < 8; ++cg) {
-          const int d = 16 * cg + 4 * q4;  // even tile -> d, d+2; odd tile -> d+1, d+3
-          *reinterpret_cast<float4 *>(rlo + d) =
-              make_float4(o[2 * cg][0] * flo, o[2 * cg + 1][0] * flo, o[2 * cg][1] * flo, o[2 * cg + 1][1] * flo);
-          if (G16)
-            *reinterpret_cast<float4 *>(rhi + d) =
-                make_float4(o[2 * cg][2] * fhi, o[2 * cg + 1][2] * fhi, o[2 * cg][3] * fhi, o[2 * cg + 1][3] * fhi);
-        }
+      for (int mt = 0; mt < 8; ++mt) {
+        // accumulator columns: 16-bit KV  d = 16mt + gid, + 8;  int8 KV  d = 16mt + 2 gid, + 1
+        const int da = KV8 ? 16 * mt + 2 * gid : 16 * mt + gid;
+        const int db = KV8 ? da + 1 : da + 8;
+        w0[da] = o[mt][nt][0]; w1[da] = o[mt][nt][1];
+        w0[db] = o[mt][nt][2]; w1[db] = o[mt][nt][3];
       }
     }
-    named_bar_sync(1, kConsumerThreads);
-    {
-      const int c4 = (tid & 31) * 4;  // four consecutive head-dim columns
+    named_bar_sync(1, C::kConsumerThreads);
+    for (int u = tid; u < C::kRows * 32; u += C::kConsumerThreads) {
+      const int row = u >> 5, c4 = (u & 31) * 4;  // four consecutive head-dim columns of one row
+      if (row < nrows) {
+        float2 ml[C::kWarps];
+        float M = kNeg;
 #pragma unroll
-      for (int rr = 0; rr < C::kRows / 8; ++rr) {
-        const int row = (tid >> 5) + 8 * rr;
-        if (row < nrows) {
-          float M = kNeg;
+        for (int w2 = 0; w2 < C::kWarps; ++w2) {
+          ml[w2] = mlbuf[w2 * 16 + row];
+          M = fmaxf(M, ml[w2].x);
+        }
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-          for (int w2 = 0; w2 < kConsumerWarps; ++w2) M = fmaxf(M, mlbuf[w2 * 16 + row].x);
-          float L = 0.f;
-          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-          for (int w2 = 0; w2 < kConsumerWarps; ++w2) {
-            const float2 ml = mlbuf[w2 * 16 + row];
-            L = fmaf(ml.y, fast_exp2(ml.x - M), L);
-            const float4 v = *reinterpret_cast<const float4 *>(mbuf + (w2 * C::kRows + row) * kMergeStride + c4);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-          }
-          const int hq = kvh * p.group + row0 + row;
-          if (nsplit == 1) {
-            const float inv = 1.f / L;
-            float r0 = acc.x * inv, r1 = acc.y * inv, r2 = acc.z * inv, r3 = acc.w * inv;
-            if (KV8) {
-              const float4 vs = __ldg(reinterpret_cast<const float4 *>(p.v_descale + kvh * kD + c4));
-              if (p.v_offset != nullptr) {
-                const int4 vo = __ldg(reinterpret_cast<const int4 *>(p.v_offset + kvh * kD + c4));
-                r0 += (float)vo.x; r1 += (float)vo.y; r2 += (float)vo.z; r3 += (float)vo.w;
-              }
-              r0 *= vs.x; r1 *= vs.y; r2 *= vs.z; r3 *= vs.w;
+        for (int w2 = 0; w2 < C::kWarps; ++w2) {
+          const float f = fast_exp2(ml[w2].x - M);
+          L = fmaf(ml[w2].y, f, L);
+          const float4 v = *reinterpret_cast<const float4 *>(mbuf + (w2 * C::kRows + row) * kMergeStride + c4);
+          acc.x = fmaf(v.x, f, acc.x); acc.y = fmaf(v.y, f, acc.y);
+          acc.z = fmaf(v.z, f, acc.z); acc.w = fmaf(v.w, f, acc.w);
+        }
+        if (KV8) {  // remove the bias the V bytes carried: sum_t p (v + 1152) = O + 1152 l
+          acc.x = fmaf(-1152.f, L, acc.x); acc.y = fmaf(-1152.f, L, acc.y);
+          acc.z = fmaf(-1152.f, L, acc.z); acc.w = fmaf(-1152.f, L, acc.w);
+        }
+        const int hq = kvh * p.group + row0 + row;
+        if (nsplit == 1) {
+          const float inv = 1.f / L;
+          float r0 = acc.x * inv, r1 = acc.y * inv, r2 = acc.z * inv, r3 = acc.w * inv;
+          if (KV8) {
+            const float4 vs = __ldg(reinterpret_cast<const float4 *>(p.v_descale + kvh * kD + c4));
+            if (p.v_offset != nullptr) {
+              const int4 vo = __ldg(reinterpret_cast<const int4 *>(p.v_offset + kvh * kD + c4));
+              r0 += (float)vo.x; r1 += (float)vo.y; r2 += (float)vo.z; r3 += (float)vo.w;
             }
-            uint2 pk;
-            pk.x = pack2<T>(r0, r1);
-            pk.y = pack2<T>(r2, r3);
-            *reinterpret_cast<uint2 *>(static_cast<T *>(p.out) + ((int64_t)b * p.num_q_heads + hq) * kD + c4) = pk;
-          } else {
-            const int64_t prow = (int64_t)part * p.num_q_heads + hq;
-            *reinterpret_cast<float4 *>(p.part_o + prow * kD + c4) = acc;
-            if ((tid & 31) == 0) *reinterpret_cast<float2 *>(p.part_ml + prow * 2) = make_float2(M, L);
+            r0 *= vs.x; r1 *= vs.y; r2 *= vs.z; r3 *= vs.w;
           }
+          uint2 pk;
+          pk.x = pack2<T>(r0, r1);
+          pk.y = pack2<T>(r2, r3);
+          *reinterpret_cast<uint2 *>(static_cast<T *>(p.out) + ((int64_t)b * p.num_q_heads + hq) * kD + c4) = pk;
+        } else {
+          const int64_t prow = (int64_t)part * p.num_q_heads + hq;
+          *reinterpret_cast<float4 *>(p.part_o + prow * kD + c4) = acc;
+          if ((u & 31) == 0) *reinterpret_cast<float2 *>(p.part_ml + prow * 2) = make_float2(M, L);
         }
       }
     }
-    named_bar_sync(1, kConsumerThreads);  // merge buffers are reused by the next item
+    named_bar_sync(1, C::kConsumerThreads);  // merge buffers are reused by the next item
   }
 }
 
@@ -512,7 +527,7 @@ int make_cache_tmap(CUtensorMap *tm, const void *cache, const MscoPaDesc &d) {
   const cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)d.num_kv_heads,
                               (cuuint64_t)d.num_blocks * (cuuint64_t)d.block_size};
   const cuuint64_t strides[2] = {(cuuint64_t)kD * es, (cuuint64_t)d.num_kv_heads * kD * es};
-  const cuuint32_t box[3] = {(cuuint32_t)(kv8 ? 128 : 64), 1u, (cuuint32_t)(d.block_size < kTile ? d.block_size : kTile)};
+  const cuuint32_t box[3] = {(cuuint32_t)(kv8 ? 128 : 64), 1u, (cuuint32_t)d.block_size};
   const cuuint32_t estr[3] = {1u, 1u, 1u};
   const CUtensorMapDataType dt = kv8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                      : (d.kv_dtype == MSCO_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
@@ -524,12 +539,12 @@ int make_cache_tmap(CUtensorMap *tm, const void *cache, const MscoPaDesc &d) {
   return MSCO_OK;
 }
 
-template <typename T, bool KV8, bool G16>
+template <typename T, bool KV8, int NT>
 int launch_one(const MscoPaPlan *plan, const PaParams &p, const CUtensorMap &tk, const CUtensorMap &tv,
                cudaStream_t stream) {
-  using C = Cfg<KV8, G16>;
+  using C = Cfg<KV8, NT>;
   static_assert(C::kDynSmem <= 232448, "shared memory budget of one SM exceeded");
-  auto kfn = pa_tma_kernel<T, KV8, G16>;
+  auto kfn = pa_tma_kernel<T, KV8, NT>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [&] {
@@ -537,7 +552,7 @@ int launch_one(const MscoPaPlan *plan, const PaParams &p, const CUtensorMap &tk,
   });
   if (attr_err != cudaSuccess)
     return fail(MSCO_ERR_CUDA, "paged_attention: cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
-  kfn<<<dim3(plan->grid), dim3(kThreads), C::kDynSmem, stream>>>(tk, tv, p);
+  kfn<<<dim3(plan->grid), dim3(C::kThreads), C::kDynSmem, stream>>>(tk, tv, p);
   MSCO_CUDA_CHECK(cudaGetLastError());
   return MSCO_OK;
 }
@@ -576,11 +591,11 @@ int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream
   const bool f16 = plan->desc.q_dtype == MSCO_DTYPE_F16;
 #define MSCO_GO(T, A, B) return launch_one<T, A, B>(plan, p, tk, tv, stream)
   if (f16) {
-    if (kv8) { if (g16) MSCO_GO(__half, true, true); else MSCO_GO(__half, true, false); }
-    else     { if (g16) MSCO_GO(__half, false, true); else MSCO_GO(__half, false, false); }
+    if (kv8) { if (g16) MSCO_GO(__half, true, 2); else MSCO_GO(__half, true, 1); }
+    else     { if (g16) MSCO_GO(__half, false, 2); else MSCO_GO(__half, false, 1); }
   } else {
-    if (kv8) { if (g16) MSCO_GO(__nv_bfloat16, true, true); else MSCO_GO(__nv_bfloat16, true, false); }
-    else     { if (g16) MSCO_GO(__nv_bfloat16, false, true); else MSCO_GO(__nv_bfloat16, false, false); }
+    if (kv8) { if (g16) MSCO_GO(__nv_bfloat16, true, 2); else MSCO_GO(__nv_bfloat16, true, 1); }
+    else     { if (g16) MSCO_GO(__nv_bfloat16, false, 2); else MSCO_GO(__nv_bfloat16, false, 1); }
   }
 #undef MSCO_GO
 }
