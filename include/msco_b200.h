@@ -175,6 +175,48 @@ int msco_paged_attention_launch(const MscoPaPlan *plan, const void *query, const
  * may be NULL (the status word is the first word of the workspace). */
 int msco_paged_attention_status(const MscoPaPlan *plan, const void *workspace);
 
+/* ------------------------------------------------------------------------
+ * Launch without any caller-provided scratch memory.
+ *
+ * Has no counterpart in the reference (there the framework always hands the
+ * kernel library a workspace it allocated).  It exists for callers that are
+ * not in a position to allocate device memory when they need to launch:
+ * code running inside a framework whose allocator they must not re-enter
+ * (custom-op callbacks that may only touch the tensors they were given), hosts
+ * that pre-allocate everything at start-up and forbid cudaMalloc afterwards
+ * (real-time serving loops, where an allocation can stall the whole device),
+ * and thin language bindings that have pointers to inputs and outputs but no
+ * allocator at all.  Those callers still pass every input and the output; what
+ * they cannot supply is the scratch area for the split-KV partials and the
+ * uploaded plan.
+ *
+ * Same arguments and same result as msco_paged_attention_launch, minus
+ * `workspace`: the scratch is a fixed MSCO_STATIC_SCRATCH_BYTES array that
+ * lives inside the library's device image, so every GPU that loads the library
+ * carries it until the process exits.  Plans whose workspace need is larger
+ * are rejected with MSCO_ERR_INVALID_ARG and a message stating both sizes (use
+ * msco_paged_attention_workspace_bytes(plan) to know beforehand) -- nothing is
+ * launched in that case.
+ *
+ * The first call on each device looks up the device address of the array
+ * (one cudaGetSymbolAddress, with that device current); make that first call
+ * outside any stream capture.  No call allocates or frees device memory.
+ * All calls on one device share the one array and it keeps whatever the last
+ * call left there; each launch rewrites everything it later reads (plan words,
+ * status word, partials), so nothing needs clearing by the caller -- but two
+ * launches that can overlap on the GPU (different streams, or graph branches)
+ * would write the same bytes at the same time: serialise them.
+ * msco_paged_attention_status_static reads the status word of the last launch
+ * on the current device (after synchronising the stream).
+ * ---------------------------------------------------------------------- */
+#define MSCO_STATIC_SCRATCH_BYTES (16u << 20)
+int msco_paged_attention_launch_static(const MscoPaPlan *plan, const void *query, const void *key_cache,
+                                       const void *value_cache, const int32_t *block_tables,
+                                       const float *k_descale, const int32_t *k_offset,
+                                       const float *v_descale, const int32_t *v_offset,
+                                       const void *attn_mask, void *out, void *stream);
+int msco_paged_attention_status_static(const MscoPaPlan *plan);
+
 /* Kernel timing for benchmarks.  After msco_paged_attention_profile_enable(plan, 1) every launch
  * of this plan records a pair of CUDA events directly around the attention kernel (not around the
  * plan upload or the reduce kernel) into a ring of 64 pairs owned by the plan.

@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(_HERE, "libmsco_b200.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_OOB, ERR_INTERNAL = range(7)
 DTYPE_F16, DTYPE_BF16, DTYPE_I8, DTYPE_F32, DTYPE_I32, DTYPE_I64 = range(6)
+STATIC_SCRATCH_BYTES = 16 << 20  # MSCO_STATIC_SCRATCH_BYTES
 KERNEL_AUTO, KERNEL_GENERIC, KERNEL_TMA = 0, 1, 2
 
 
@@ -49,6 +50,7 @@ EXPORTS = (
     "msco_paged_attention_split_tokens", "msco_paged_attention_plan", "msco_paged_attention_workspace_bytes",
     "msco_paged_attention_plan_info", "msco_paged_attention_plan_destroy", "msco_paged_attention_launch",
     "msco_paged_attention_status", "msco_paged_attention_profile_enable", "msco_paged_attention_profile_read",
+    "msco_paged_attention_launch_static", "msco_paged_attention_status_static",
 )
 
 
@@ -83,6 +85,10 @@ def lib():
     L.msco_paged_attention_launch.argtypes = [vp] * 12 + [sz, vp]
     L.msco_paged_attention_status.restype = C.c_int
     L.msco_paged_attention_status.argtypes = [vp, vp]
+    L.msco_paged_attention_launch_static.restype = C.c_int
+    L.msco_paged_attention_launch_static.argtypes = [vp] * 12
+    L.msco_paged_attention_status_static.restype = C.c_int
+    L.msco_paged_attention_status_static.argtypes = [vp]
     L.msco_paged_attention_profile_enable.restype = C.c_int
     L.msco_paged_attention_profile_enable.argtypes = [vp, i32]
     L.msco_paged_attention_profile_read.restype = C.c_int

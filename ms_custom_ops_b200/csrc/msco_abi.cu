@@ -303,3 +303,61 @@ extern "C" int msco_paged_attention_status(const MscoPaPlan *plan, const void *w
   if (status == kStatusOob) return fail(MSCO_ERR_OOB, "paged_attention: a block id outside the cache was met");
   return MSCO_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Launch without caller-provided scratch: the workspace is a fixed array in the device image.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+// Scratch of msco_paged_attention_launch_static.  In host code this name is only a handle for
+// cudaGetSymbolAddress -- it is NOT a device address and must never be passed to a kernel.
+static __device__ __align__(256) unsigned char g_static_scratch[MSCO_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void *g_static_ptr[kMaxDevices] = {};  // device address of g_static_scratch, per device ordinal
+
+// Device address of the scratch array on the current device; looked up once per device.
+int static_scratch(void **ptr) {
+  int dev = -1;
+  MSCO_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(MSCO_ERR_INTERNAL, "launch_static: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> g(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void *p = nullptr;
+    MSCO_CUDA_CHECK(cudaGetSymbolAddress(&p, g_static_scratch));
+    if (p == nullptr) return fail(MSCO_ERR_CUDA, "launch_static: cudaGetSymbolAddress returned a NULL address");
+    g_static_ptr[dev] = p;
+  }
+  *ptr = g_static_ptr[dev];
+  return MSCO_OK;
+}
+
+}  // namespace
+
+extern "C" int msco_paged_attention_launch_static(const MscoPaPlan *plan, const void *query,
+                                                  const void *key_cache, const void *value_cache,
+                                                  const int32_t *block_tables, const float *k_descale,
+                                                  const int32_t *k_offset, const float *v_descale,
+                                                  const int32_t *v_offset, const void *attn_mask, void *out,
+                                                  void *stream) {
+  if (plan == nullptr) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch_static: NULL plan");
+  if (plan->workspace_bytes > (size_t)MSCO_STATIC_SCRATCH_BYTES)
+    return fail(MSCO_ERR_INVALID_ARG,
+                "paged_attention_launch_static: this plan needs %zu bytes of scratch but the built-in scratch "
+                "holds %zu; use msco_paged_attention_launch with a caller-provided workspace",
+                plan->workspace_bytes, (size_t)MSCO_STATIC_SCRATCH_BYTES);
+  void *ws = nullptr;
+  const int rc = static_scratch(&ws);
+  if (rc != MSCO_OK) return rc;
+  return msco_paged_attention_launch(plan, query, key_cache, value_cache, block_tables, k_descale, k_offset,
+                                     v_descale, v_offset, attn_mask, out, ws, (size_t)MSCO_STATIC_SCRATCH_BYTES,
+                                     stream);
+}
+
+extern "C" int msco_paged_attention_status_static(const MscoPaPlan *plan) {
+  void *ws = nullptr;
+  const int rc = static_scratch(&ws);
+  if (rc != MSCO_OK) return rc;
+  return msco_paged_attention_status(plan, ws);
+}
