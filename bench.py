@@ -184,7 +184,7 @@ def run_gpu(args):
     import torch.distributed as dist
 
     import ms_custom_ops_b200 as ops
-    from ms_custom_ops_b200 import _abi, kernels
+    from ms_custom_ops_b200 import _abi, kernels, sharding
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -201,7 +201,7 @@ def run_gpu(args):
     if spec.kv_heads % world != 0:
         raise SystemExit(f"{spec.kv_heads} kv heads cannot be split over {world} GPUs")
     hpr = spec.kv_heads // world                      # kv heads per rank
-    h0, h1 = rank * hpr, (rank + 1) * hpr
+    h0, h1 = sharding.kv_head_range(rank, world, spec.kv_heads)
     g = spec.num_heads // spec.kv_heads
     case = workloads.decode_case_device(spec, dev, (h0, h1))
     lens = [int(x) for x in case["context_lens"]]
@@ -227,7 +227,7 @@ def run_gpu(args):
             kernels.rac_scatter(key, val, kc, vc, slot)
         kernels.pa_launch(plan, q, kc, vc, bt, out_local, ws, kd, None, vd, None)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out_local)
+            sharding.all_gather_outputs(out_local, gathered)
 
     def barrier():
         if world > 1:
@@ -299,7 +299,7 @@ def run_gpu(args):
             ops.reshape_and_cache(d_key, d_val, kc, vc, d_slot, 0, 0)
         o = ops.paged_attention(d_q, kc, vc, d_bt, h_lens, **pa_kw)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, o)
+            sharding.all_gather_outputs(o, gathered)
             o = gathered
         h_out.copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the step's result is read on the host
