@@ -130,6 +130,14 @@ def measured_hbm_peak():
 # ----------------------------------------------------------------------------------------------
 # reference arm: CPU implementation of the path on the host cores
 # ----------------------------------------------------------------------------------------------
+def host_threads():
+    """Host cores this process may use (torchrun exports OMP_NUM_THREADS=1; the CPU legs ignore it)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_step(c_oracle, case, threads=0):
     """One decode step on the CPU: scatter the new rows into the caches in place, then attention.
     Returns the output."""
@@ -155,12 +163,12 @@ def run_reference(args):
     sample = min(full_batch, args.cpu_sample)
     sspec = workloads.DecodeSpec(**{**spec.__dict__, "batch": sample})
     case = workloads.decode_case(sspec)
-    cores = c_oracle.max_threads()
+    cores = host_threads()
     for _ in range(args.warmup):
-        cpu_step(c_oracle, case)
+        cpu_step(c_oracle, case, cores)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_step(c_oracle, case)
+        cpu_step(c_oracle, case, cores)
     dt = (time.perf_counter() - t0) / max(args.steps, 1)
     value = sample / dt
     what = (f"{sample} of {full_batch} sequences per step ({int(case['context_lens'].sum())} context tokens), "
@@ -239,7 +247,10 @@ def run_gpu(args):
         step()
     kernels.pa_status(plan, ws)
     graph = None
-    if args.graph:
+    if args.graph and world > 1:
+        # capturing the NCCL all-gather hung both ranks on this pool; graphs are a 1-GPU option
+        print("--graph is ignored with more than one GPU", file=sys.stderr)
+    if args.graph and world == 1:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -361,17 +372,18 @@ def run_gpu(args):
                 "context_lens": np.array(lens[:nseq], dtype=np.int32), "qk_scale": case["qk_scale"],
                 "k_descale": None if kd is None else kd.cpu().numpy(),
                 "v_descale": None if vd is None else vd.cpu().numpy()}
-        ref = cpu_step(c_oracle, host)  # warm-up + reference output
+        cores = host_threads()
+        ref = cpu_step(c_oracle, host, cores)  # warm-up + reference output
         reps, t_best = 0, float("inf")
         t_begin = time.perf_counter()
         while reps < 3 and time.perf_counter() - t_begin < 20.0:
             t0 = time.perf_counter()
-            cpu_step(c_oracle, host)
+            cpu_step(c_oracle, host, cores)
             t_best = min(t_best, time.perf_counter() - t0)
             reps += 1
         sample = (f"{nseq} of {spec.batch} sequences ({int(sum(lens[:nseq]))} context tokens), kv heads {h0}..{h1 - 1}, "
                   f"best of {reps}; C restatement of the reference numpy golden, OpenMP")
-        cpu = {"value": nseq / t_best, "unit": UNIT, "cores": c_oracle.max_threads(), "kind": "port",
+        cpu = {"value": nseq / t_best, "unit": UNIT, "cores": cores, "kind": "port",
                "sample": sample}
         got = out_local[:nseq].float().cpu().numpy()
         err = np.abs(got - ref)
@@ -380,7 +392,7 @@ def run_gpu(args):
                    "rel_l2": float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30)),
                    "within_tolerance": bool(np.all(err <= tol + tol * np.abs(ref))), "tolerance": tol}
 
-    kernels_per_step = 2 + (1 if info.partials > 0 or min(lens) == 0 else 0)
+    kernels_per_step = 2 + (1 if info.partials > 0 or min(lens) == 0 else 0)  # scatter, attention, reduce
     line = {
         "metric": METRIC, "value": spec.batch / ms_step * 1e3, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",

@@ -206,6 +206,9 @@ __global__ void __launch_bounds__(kGenThreads) pa_generic_kernel(PaParams p) {
 // registers, and the partial rows are accumulated in split order with several loads in flight.
 template <typename TQ>
 __global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p) {
+  // launched with programmatic stream serialisation: wait here until the attention grid before us
+  // has completed and its partials are visible (a no-op for an ordinary launch)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const PlanView pv = make_plan_view(p.plan);
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -310,10 +313,18 @@ int launch_pa_generic(const MscoPaPlan *plan, const PaParams &p, cudaStream_t st
 int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream) {
   const int rows = plan->batch * plan->desc.num_q_heads;
   if (rows == 0) return MSCO_OK;
-  const dim3 grid((rows + 3) / 4), block(128);
-  if (plan->desc.q_dtype == MSCO_DTYPE_F16) pa_reduce_kernel<__half><<<grid, block, 0, stream>>>(p);
-  else pa_reduce_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(p);
-  MSCO_CUDA_CHECK(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((rows + 3) / 4);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (plan->desc.q_dtype == MSCO_DTYPE_F16) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__half>, p));
+  else MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__nv_bfloat16>, p));
   return MSCO_OK;
 }
 

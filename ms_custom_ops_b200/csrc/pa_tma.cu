@@ -94,6 +94,9 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   int *desc = reinterpret_cast<int *>(smem + C::kOffDesc);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // let the reduce kernel (launched with programmatic stream serialisation) become resident now;
+  // it blocks in griddepcontrol.wait until this grid has completed
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::kStages; ++i) {
       mbar_init(&full[i], 1);
