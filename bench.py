@@ -45,6 +45,9 @@ from ms_custom_ops_b200 import workloads  # noqa: E402
 METRIC = "paged-attn decode tokens/s"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
+# (dram__bytes_read.sum + dram__bytes_write.sum) / (context tokens * kv heads) from the ncu captures
+# in profiles/: config 2 (16-bit KV, 512 algorithmic bytes) and config 3 (int8 KV, 256 algorithmic)
+NCU_DRAM_BYTES_PER_TOKEN_HEAD = {"16bit": 523.4, "int8": 268.9}
 L2_BYTES = 126 << 20
 
 
@@ -349,14 +352,12 @@ def run_gpu(args):
         kms = statistics.mean(kernel_ms)
         roofline.update(achieved=alg_bytes / kms / 1e6, frac=alg_bytes / kms / 1e6 / peak, kernel_ms=kms,
                         frac_of_8tbs=alg_bytes / kms / 1e6 / 8000.0, launches_timed=len(kernel_ms))
-    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(traffic_file):
-        try:
-            tr = json.load(open(traffic_file)).get(args.workload.lower())
-            if tr:  # DRAM bytes per context token from an ncu capture, scaled to this launch
-                roofline["traffic"] = tr["dram_bytes_per_kv_token_per_head"] * sum(lens) * hpr
-        except Exception:
-            pass
+    # DRAM traffic of one launch: dram__bytes_read.sum + dram__bytes_write.sum of the ncu captures
+    # summarised in profiles/pa_tma_kernel_*.md, per context token per kv head, scaled to this
+    # launch (traffic grows in proportion to the tokens read)
+    if info.kernel == 2:
+        roofline["traffic"] = NCU_DRAM_BYTES_PER_TOKEN_HEAD["int8" if spec.kv_int8 else "16bit"] * sum(lens) * hpr
+        roofline["traffic_source"] = "ncu capture of config " + ("3" if spec.kv_int8 else "2") + ", scaled by tokens"
 
     # ---- CPU baseline on the same workload (also the full-size parity check) ---------------
     cpu = None
