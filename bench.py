@@ -294,19 +294,31 @@ def run_gpu(args):
     ms_step = float(t.item()) / args.steps
 
     # ---- end-to-end through the operator API, inputs in pinned host memory ----------------
-    pin = lambda x: x.detach().cpu().pin_memory()
-    h_q, h_key, h_val, h_slot, h_bt = pin(q), pin(key), pin(val), pin(slot), pin(bt)
+    # the step's inputs live in ONE pinned host staging buffer (query | new K rows | new V rows |
+    # slot_mapping | block_tables, each 256-byte aligned) and travel in one host->device copy; the
+    # operators read device views of the staging area
+    parts = [q, key, val, slot, bt]
+    offs, total = [], 0
+    for x in parts:
+        offs.append(total)
+        total += (x.numel() * x.element_size() + 255) // 256 * 256
+    h_stage = torch.empty(total, dtype=torch.uint8).pin_memory()
+    d_stage = torch.empty(total, dtype=torch.uint8, device=dev)
+
+    def view(buf, x, off):
+        return buf[off:off + x.numel() * x.element_size()].view(x.dtype).view(x.shape)
+    for x, off in zip(parts, offs):
+        view(h_stage, x, off).copy_(x.cpu())
+    d_q, d_key, d_val, d_slot, d_bt = (view(d_stage, x, off) for x, off in zip(parts, offs))
     h_lens = torch.tensor(lens, dtype=torch.int32)
     out_shape = (world,) + tuple(q.shape) if world > 1 else tuple(q.shape)
     h_out = torch.empty(out_shape, dtype=q.dtype).pin_memory()
-    d_q, d_key, d_val, d_slot, d_bt = (torch.empty_like(x) for x in (q, key, val, slot, bt))
     pa_kw = dict(q_head_num=hq_local, kv_head_num=hpr, qk_scale=case["qk_scale"])
     if spec.kv_int8:
         pa_kw.update(quant_type=1, k_descale=kd, v_descale=vd)
 
     def e2e_step():
-        for d, h in ((d_q, h_q), (d_key, h_key), (d_val, h_val), (d_slot, h_slot), (d_bt, h_bt)):
-            d.copy_(h, non_blocking=True)
+        d_stage.copy_(h_stage, non_blocking=True)
         if spec.kv_int8:
             ops.reshape_and_cache_quant(d_key, d_val, kc, vc, d_slot, kd, vd)
         else:
@@ -332,7 +344,7 @@ def run_gpu(args):
     e2e_ms = float(t.item()) / args.steps
     clocks = sampler.stop() if sampler else None
     ops.paged_attention_check_status(dev)
-    h2d = sum(x.numel() * x.element_size() for x in (h_q, h_key, h_val, h_slot, h_bt))
+    h2d = sum(x.numel() * x.element_size() for x in parts)
     d2h = h_out.numel() * h_out.element_size()
 
     if rank != 0:

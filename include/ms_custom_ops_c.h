@@ -119,6 +119,12 @@ int ms_custom_ops_paged_attention_workspace_size(const MsPagedAttentionArgs *arg
 int ms_custom_ops_paged_attention(const MsPagedAttentionArgs *args, const MsTensorDesc *attention_out,
                                   void *workspace, size_t workspace_bytes, void *stream);
 
+/* Workspace bytes the calling thread's last ms_custom_ops_paged_attention call needed.  A caller
+ * that keeps a grow-only workspace can skip the separate size query: launch with what it has and,
+ * if the call fails because the workspace is too small (nothing was launched), grow it to this
+ * size and call again. */
+size_t ms_custom_ops_paged_attention_last_workspace_need(void);
+
 /* After synchronising `stream`: MSCO_OK, MSCO_ERR_TIMEOUT or MSCO_ERR_OOB as
  * left in `workspace` by the last paged_attention launch that used it. */
 int ms_custom_ops_paged_attention_status(const void *workspace);

@@ -59,6 +59,9 @@ def _contig_strides(shape):
     return list(reversed(st))
 
 
+_desc_cache = {}  # (data_ptr, shape, strides, dtype, is_cuda) -> (MsTensorDesc, pointer): descriptors are immutable
+
+
 class _Descs:
     """Builds MsTensorDesc structs and keeps the Python objects behind them alive."""
 
@@ -82,9 +85,16 @@ class _Descs:
             shape, strides = a.shape, [s // max(a.itemsize, 1) for s in a.strides]
             d.data, d.dtype, d.on_host = a.ctypes.data, _dtype_code(str(a.dtype)), 1
         else:  # torch tensor
-            shape, strides = tuple(t.shape), list(t.stride())
-            d.data, d.dtype, d.on_host = t.data_ptr(), _dtype_code(t.dtype), 0 if t.is_cuda else 1
+            key = (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype, t.is_cuda)
+            hit = _desc_cache.get(key)
             self.keep.append(t)
+            if hit is not None:
+                return hit[1]
+            shape, strides = key[1], key[2]
+            d.data, d.dtype, d.on_host = key[0], _dtype_code(t.dtype), 0 if t.is_cuda else 1
+            if len(_desc_cache) > 4096:
+                _desc_cache.clear()
+            _desc_cache[key] = (d, C.pointer(d))
         if len(shape) > _host.MS_MAX_DIMS:
             raise ValueError("tensors of more than 8 dimensions are not supported")
         d.ndim = len(shape)
@@ -198,11 +208,18 @@ def paged_attention(query, key_cache, value_cache, block_tables, context_lens, a
                  qk_scale, kv_head_num, mask_type, batch_run_status_enable, quant_type, out_data_type,
                  has_quant_offset, compress_type, calc_type, scale_type, input_layout, mla_v_dim, input_format)
     L = _host.lib()
-    nbytes = C.c_size_t()
-    _host.check(L.ms_custom_ops_paged_attention_workspace_size(C.byref(a), C.byref(nbytes)))
     out = torch.empty_like(query)
-    ws = _workspace(query.device, nbytes.value)
-    _host.check(L.ms_custom_ops_paged_attention(C.byref(a), D(out), C.c_void_p(ws.data_ptr()), ws.numel(), _stream()))
+    # launch with the workspace at hand; if it is too small nothing was launched and the library
+    # tells how much is needed (one validation + plan lookup per call in the steady state)
+    ws = _workspace(query.device, 0)
+    rc = L.ms_custom_ops_paged_attention(C.byref(a), D(out), C.c_void_p(ws.data_ptr()), ws.numel(), _stream())
+    if rc != 0:
+        need = L.ms_custom_ops_paged_attention_last_workspace_need()
+        if need <= ws.numel():
+            _host.check(rc)
+        ws = _workspace(query.device, need)
+        _host.check(L.ms_custom_ops_paged_attention(C.byref(a), D(out), C.c_void_p(ws.data_ptr()), ws.numel(),
+                                                    _stream()))
     return out
 
 

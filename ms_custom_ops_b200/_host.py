@@ -36,7 +36,8 @@ class MsPagedAttentionArgs(C.Structure):
 EXPORTS = (
     "ms_custom_ops_reshape_and_cache", "ms_custom_ops_reshape_and_cache_quant",
     "ms_custom_ops_paged_attention_infer", "ms_custom_ops_paged_attention_workspace_size",
-    "ms_custom_ops_paged_attention", "ms_custom_ops_paged_attention_status", "ms_custom_ops_last_error",
+    "ms_custom_ops_paged_attention", "ms_custom_ops_paged_attention_last_workspace_need",
+    "ms_custom_ops_paged_attention_status", "ms_custom_ops_last_error",
     "ms_custom_ops_last_error_kind", "ms_custom_ops_num_ops", "ms_custom_ops_op_name",
     "ms_custom_ops_op_signature", "ms_custom_ops_plan_cache_stats", "ms_custom_ops_plan_cache_clear",
 )
@@ -69,6 +70,7 @@ def lib():
     L.ms_custom_ops_paged_attention_workspace_size.argtypes = [ap, C.POINTER(C.c_size_t)]
     L.ms_custom_ops_paged_attention.restype = C.c_int
     L.ms_custom_ops_paged_attention.argtypes = [ap, _TP, vp, C.c_size_t, vp]
+    L.ms_custom_ops_paged_attention_last_workspace_need.restype = C.c_size_t
     L.ms_custom_ops_paged_attention_status.restype = C.c_int
     L.ms_custom_ops_paged_attention_status.argtypes = [vp]
     L.ms_custom_ops_last_error.restype = C.c_char_p

@@ -99,7 +99,7 @@ extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *
   const bool tma_ok = pa_tma_supported(d);
   if (d.kernel == kKernelTma && !tma_ok) {
     delete pl;
-    return fail(MSCO_ERR_UNSUPPORTED, "paged_attention_plan: the TMA kernel needs head_dim 128, block_size 16/32/64/128, no mask");
+    return fail(MSCO_ERR_UNSUPPORTED, "paged_attention_plan: the TMA kernel needs head_dim 128 and block_size 16/32/64/128");
   }
   pl->kernel = (d.kernel == kKernelGeneric || !tma_ok) ? kKernelGeneric : kKernelTma;
   pl->rows_per_item = (pl->kernel == kKernelTma && g > 8) ? 16 : 8;

@@ -79,7 +79,14 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   return d;
 }
 
-template <typename T, bool KV8, int NT>
+// additive mask element (decode shapes): NORM [batch, 1, ctx] (head stride 0), ALIBI [batch, heads, 1, ctx]
+__device__ __forceinline__ float load_mask_elem(const void *mask, int dtype, int64_t idx) {
+  if (dtype == MSCO_DTYPE_F16) return __half2float(__ldg(static_cast<const __half *>(mask) + idx));
+  if (dtype == MSCO_DTYPE_BF16) return __bfloat162float(__ldg(static_cast<const __nv_bfloat16 *>(mask) + idx));
+  return __ldg(static_cast<const float *>(mask) + idx);
+}
+
+template <typename T, bool KV8, int NT, bool MASK>
 __global__ void __launch_bounds__(Cfg<KV8, NT>::kThreads, 1)
 pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, PaParams p) {
   using C = Cfg<KV8, NT>;
@@ -283,6 +290,28 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       float s[NT][4];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+      // additive mask of this lane's (token, row) pairs, fetched before the tile is waited for;
+      // same element order as s[nt][0..3]
+      float mk[NT][4];
+      if (MASK) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          mk[nt][0] = mk[nt][1] = mk[nt][2] = mk[nt][3] = 0.f;
+          if (active) {
+            const int tk = tok0 + ti * kTile + t0 + gid;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int r = 8 * nt + 2 * q4 + j;
+              if (r < nrows) {
+                const int64_t base = (int64_t)b * p.mask_batch_stride +
+                                     (int64_t)(kvh * p.group + row0 + r) * p.mask_head_stride;
+                if (t0 + gid < nv) mk[nt][j] = load_mask_elem(p.mask, p.mask_dtype, base + tk);
+                if (t0 + gid + 8 < nv) mk[nt][2 + j] = load_mask_elem(p.mask, p.mask_dtype, base + tk + 8);
+              }
+            }
+          }
+        }
+      }
       if (!mbar_wait(&full[st], ph, kWaitLimit)) {
         atomicExch(p.plan, kStatusTimeout);
         return;
@@ -335,8 +364,14 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         const bool dead_lo = t0 + gid >= nv, dead_hi = t0 + gid + 8 >= nv;  // past the end of the range
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          float x0 = dead_lo ? kNeg : s[nt][0] * c, x1 = dead_lo ? kNeg : s[nt][1] * c;
-          float x2 = dead_hi ? kNeg : s[nt][2] * c, x3 = dead_hi ? kNeg : s[nt][3] * c;
+          float x0 = s[nt][0] * c, x1 = s[nt][1] * c, x2 = s[nt][2] * c, x3 = s[nt][3] * c;
+          if (MASK) {
+            const float l2e = 1.4426950408889634f;
+            x0 = fmaf(mk[nt][0], l2e, x0); x1 = fmaf(mk[nt][1], l2e, x1);
+            x2 = fmaf(mk[nt][2], l2e, x2); x3 = fmaf(mk[nt][3], l2e, x3);
+          }
+          if (dead_lo) x0 = x1 = kNeg;
+          if (dead_hi) x2 = x3 = kNeg;
           float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
 #pragma unroll
           for (int sh = 4; sh <= 16; sh <<= 1) {
@@ -542,12 +577,12 @@ int make_cache_tmap(CUtensorMap *tm, const void *cache, const MscoPaDesc &d) {
   return MSCO_OK;
 }
 
-template <typename T, bool KV8, int NT>
+template <typename T, bool KV8, int NT, bool MASK>
 int launch_one(const MscoPaPlan *plan, const PaParams &p, const CUtensorMap &tk, const CUtensorMap &tv,
                cudaStream_t stream) {
   using C = Cfg<KV8, NT>;
   static_assert(C::kDynSmem <= 232448, "shared memory budget of one SM exceeded");
-  auto kfn = pa_tma_kernel<T, KV8, NT>;
+  auto kfn = pa_tma_kernel<T, KV8, NT, MASK>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [&] {
@@ -565,7 +600,7 @@ int launch_one(const MscoPaPlan *plan, const PaParams &p, const CUtensorMap &tk,
 bool pa_tma_supported(const MscoPaDesc &d) {
   const int bs = d.block_size;
   const bool bs_ok = bs == 16 || bs == 32 || bs == 64 || bs == 128;
-  return d.head_dim == kD && bs_ok && d.mask_type == 0 && d.num_blocks * (int64_t)bs < (1ll << 31);
+  return d.head_dim == kD && bs_ok && d.num_blocks * (int64_t)bs < (1ll << 31);
 }
 
 int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream) {
@@ -592,7 +627,12 @@ int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream
   const bool kv8 = plan->desc.kv_dtype == MSCO_DTYPE_I8;
   const bool g16 = plan->rows_per_item == 16;
   const bool f16 = plan->desc.q_dtype == MSCO_DTYPE_F16;
-#define MSCO_GO(T, A, B) return launch_one<T, A, B>(plan, p, tk, tv, stream)
+  const bool masked = plan->desc.mask_type != 0;
+#define MSCO_GO(T, A, B)                                                   \
+  do {                                                                     \
+    if (masked) return launch_one<T, A, B, true>(plan, p, tk, tv, stream); \
+    return launch_one<T, A, B, false>(plan, p, tk, tv, stream);            \
+  } while (0)
   if (f16) {
     if (kv8) { if (g16) MSCO_GO(__half, true, 2); else MSCO_GO(__half, true, 1); }
     else     { if (g16) MSCO_GO(__half, false, 2); else MSCO_GO(__half, false, 1); }

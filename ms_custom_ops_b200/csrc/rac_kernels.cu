@@ -146,6 +146,10 @@ __device__ __forceinline__ void quant_row1(const T *__restrict__ src, int8_t *__
   }
 }
 
+// Four warps per token (K low half, K high half, V low half, V high half of the row): a decode
+// step has only `batch` tokens, so the work of one token is spread to keep the kernel short.
+constexpr int kQuantParts = 4;
+
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(kRacThreads)
 rac_scatter_quant_kernel(const T *__restrict__ key, const T *__restrict__ value,
@@ -155,21 +159,30 @@ rac_scatter_quant_kernel(const T *__restrict__ key, const T *__restrict__ value,
                          const int32_t *__restrict__ k_offset, const float *__restrict__ v_descale,
                          const int32_t *__restrict__ v_offset, int64_t num_slots, int32_t *oob_count) {
   const int lane = threadIdx.x & 31;
-  const int64_t tok = (int64_t)blockIdx.x * kRacWarps + (threadIdx.x >> 5);
+  const int64_t unit = (int64_t)blockIdx.x * kRacWarps + (threadIdx.x >> 5);
+  const int64_t tok = unit / kQuantParts;
+  const int part = (int)(unit - tok * kQuantParts);
   if (tok >= num_tokens) return;
   const int64_t slot = __ldg(slot_mapping + tok);
   if (slot < 0) return;
   if (slot >= num_slots) {
-    if (lane == 0 && oob_count != nullptr) atomicAdd(oob_count, 1);
+    if (lane == 0 && part == 0 && oob_count != nullptr) atomicAdd(oob_count, 1);
     return;
   }
-  if (VEC) {
-    quant_row8<T>(key + tok * k_elems, key_cache + slot * k_elems, k_descale, k_offset, k_elems, lane);
-    if (v_elems) quant_row8<T>(value + tok * v_elems, value_cache + slot * v_elems, v_descale, v_offset, v_elems, lane);
-  } else {
-    quant_row1<T>(key + tok * k_elems, key_cache + slot * k_elems, k_descale, k_offset, k_elems, lane);
-    if (v_elems) quant_row1<T>(value + tok * v_elems, value_cache + slot * v_elems, v_descale, v_offset, v_elems, lane);
-  }
+  const bool is_v = part >= 2;
+  const int elems = is_v ? v_elems : k_elems;
+  if (elems == 0) return;
+  // split the row at a multiple of 8 elements so that both halves keep the vector alignment
+  const int half = ((elems / 2) + 7) & ~7;
+  const int e0 = (part & 1) ? min(half, elems) : 0, e1 = (part & 1) ? elems : min(half, elems);
+  if (e0 >= e1) return;
+  const T *src = (is_v ? value + tok * v_elems : key + tok * k_elems) + e0;
+  int8_t *dst = (is_v ? value_cache + slot * v_elems : key_cache + slot * k_elems) + e0;
+  const float *ds = (is_v ? v_descale : k_descale) + e0;
+  const int32_t *of = is_v ? v_offset : k_offset;
+  if (of != nullptr) of += e0;
+  if (VEC) quant_row8<T>(src, dst, ds, of, e1 - e0, lane);
+  else quant_row1<T>(src, dst, ds, of, e1 - e0, lane);
 }
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -248,7 +261,7 @@ extern "C" int msco_reshape_and_cache_quant(const void *key, const void *value, 
   if (k_row_elems > (int64_t)INT32_MAX || v_row_elems > (int64_t)INT32_MAX)
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: row too large");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t blocks64 = (num_tokens + kRacWarps - 1) / kRacWarps;
+  const int64_t blocks64 = (num_tokens * kQuantParts + kRacWarps - 1) / kRacWarps;
   if (blocks64 > 0x7fffffffLL) return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: too many tokens");
   const dim3 grid((unsigned)blocks64), block(kRacThreads);
   const bool vec = (k_row_elems % 8 == 0) && (v_row_elems % 8 == 0) && aligned16(key) && aligned16(k_descale) &&

@@ -409,6 +409,8 @@ Prepared Prepare(const PaInputs &in) {
 // Change detection of the host sequence lengths between consecutive calls of a thread
 // (the reference keeps them in the op's param and re-tiles on change).
 thread_local std::vector<int32_t> g_prev_context_lens;
+// Workspace bytes the last launch attempt of this thread needed (see ..._last_workspace_need).
+thread_local size_t g_last_workspace_need = 0;
 
 }  // namespace
 }  // namespace ms_custom_ops
@@ -461,6 +463,10 @@ extern "C" int ms_custom_ops_paged_attention(const MsPagedAttentionArgs *args, c
     if (p.batch == 0) return MSCO_OK;
     (void)CheckAndUpdate(p.context_lens, &g_prev_context_lens);
     PlanRef plan = PlanCache::Instance().GetOrCreate(p.desc, p.context_lens);
+    g_last_workspace_need = std::max<size_t>(msco_paged_attention_workspace_bytes(plan.get()), 256);
+    if (workspace == nullptr || workspace_bytes < g_last_workspace_need)
+      MS_VALUE_ERROR << "For PagedAttention, the workspace holds " << workspace_bytes << " bytes but this launch needs "
+                     << g_last_workspace_need << ".";
     return msco_paged_attention_launch(
         plan.get(), in.query.data(), in.key_cache.data(), in.value_cache.data(),
         static_cast<const int32_t *>(in.block_tables.data()), static_cast<const float *>(in.k_descale.data()),
@@ -468,6 +474,10 @@ extern "C" int ms_custom_ops_paged_attention(const MsPagedAttentionArgs *args, c
         static_cast<const int32_t *>(in.v_offset.data()), in.attn_mask.data(), out.data(), workspace,
         workspace_bytes, stream);
   });
+}
+
+extern "C" size_t ms_custom_ops_paged_attention_last_workspace_need(void) {
+  return ms_custom_ops::g_last_workspace_need;
 }
 
 extern "C" int ms_custom_ops_paged_attention_status(const void *workspace) {

@@ -191,8 +191,22 @@ def test_pa_reference_case_matrix(name):
                                   "int8_kv_offset", "gqa_int8_bf16", "bf16_int8_gqa_24to2",
                                   "bf16_int8_gqa_64to32", "bf16_int8_head128", "odd_heads", "large_seqlen_bf16"])
 def test_pa_both_kernels_agree_with_oracle(name):
-    # the same shapes without the mask, so that the TMA kernel is eligible
+    # the reference's shapes without the mask: both kernels against the oracle
     case = _st_case(name, mask_free=True)
+    out_g, info_g = _run_pa(case, _abi.KERNEL_GENERIC)
+    out_t, info_t = _run_pa(case, _abi.KERNEL_TMA)
+    assert info_g.kernel == 1 and info_t.kernel == 2
+    _check(case, out_g, name + "/generic")
+    _check(case, out_t, name + "/tma")
+
+
+@pytest.mark.parametrize("name", ["norm_mask_fp16", "norm_mask_bf16", "alibi_fp16", "alibi_bf16", "gqa_8to1_alibi",
+                                  "gqa_32to8_alibi", "odd_heads", "varied_seqlens", "gqa_int8_offset",
+                                  "bf16_int8_gqa_24to2", "bf16_int8_head128", "large_seqlen_bf16"])
+def test_pa_masked_cases_in_both_kernels(name):
+    # NORM / ALIBI additive masks: the general kernel and the TMA kernel against the oracle
+    case = _st_case(name)
+    assert case["mask_type"] in (1, 2)
     out_g, info_g = _run_pa(case, _abi.KERNEL_GENERIC)
     out_t, info_t = _run_pa(case, _abi.KERNEL_TMA)
     assert info_g.kernel == 1 and info_t.kernel == 2

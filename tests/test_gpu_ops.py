@@ -137,7 +137,7 @@ def test_plan_cache_and_length_change_between_steps():
         outs.append(to_np(ops.paged_attention(q, kc, vc, bt, lens, q_head_num=32, kv_head_num=8,
                                               qk_scale=c["qk_scale"])))
     st = ops.plan_cache_stats()
-    assert st["entries"] == 2 and st["hits"] >= 2
+    assert st["entries"] == 2 and st["hits"] >= 1
     assert np.array_equal(outs[0].view(np.uint16), outs[1].view(np.uint16))
     g = oracle.paged_attention_golden(c["query"], c["key_cache"], c["value_cache"], c["block_tables"], lens,
                                       c["qk_scale"])

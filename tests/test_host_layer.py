@@ -198,7 +198,8 @@ def test_kernel_selection_and_workspace():
     assert wide.rows_per_item == 16 and wide.work_items == 16
     assert _plan([100], d=64).info().kernel == 1       # head_dim 64 -> general kernel
     assert _plan([100], bs=48).info().kernel == 1
-    assert _plan([100], mask=1).info().kernel == 1
+    assert _plan([100], mask=1).info().kernel == 2      # additive masks run in the TMA kernel too
+    assert _plan([100], d=64, mask=2).info().kernel == 1
     assert _plan([100], kv="int8").info().kernel == 2
     with pytest.raises(_abi.MscoError):
         _plan([100], d=64, kernel=2)
