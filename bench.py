@@ -230,6 +230,22 @@ def run_gpu(args):
     # gathered layout: [rank, batch, q heads per rank, head_dim]; rank r's slice holds q heads
     # r*hq_local .. (r+1)*hq_local-1, i.e. out[b, h] = gathered[h // hq_local, b, h % hq_local]
     gathered = torch.empty((world,) + tuple(q.shape), dtype=q.dtype, device=dev) if world > 1 else None
+    # the exchange: this library's peer-store all-gather kernel (default) or NCCL (--nccl-gather)
+    peer = None
+    if world > 1 and not args.nccl_gather:
+        try:
+            peer = sharding.PeerGather(q.shape, q.dtype, dev)
+        except Exception as e:  # IPC mapping refused on this box: say so and use NCCL
+            print(f"peer all-gather unavailable ({e}); using NCCL", file=sys.stderr)
+        ok = torch.tensor([1 if peer is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            peer = None
+
+    def exchange(o):
+        if peer is not None:
+            return peer.gather(o)
+        return sharding.all_gather_outputs(o, gathered)
 
     def step():
         if spec.kv_int8:
@@ -238,7 +254,7 @@ def run_gpu(args):
             kernels.rac_scatter(key, val, kc, vc, slot)
         kernels.pa_launch(plan, q, kc, vc, bt, out_local, ws, kd, None, vd, None)
         if world > 1:
-            sharding.all_gather_outputs(out_local, gathered)
+            exchange(out_local)
 
     def barrier():
         if world > 1:
@@ -325,8 +341,7 @@ def run_gpu(args):
             ops.reshape_and_cache(d_key, d_val, kc, vc, d_slot, 0, 0)
         o = ops.paged_attention(d_q, kc, vc, d_bt, h_lens, **pa_kw)
         if world > 1:
-            sharding.all_gather_outputs(o, gathered)
-            o = gathered
+            o = exchange(o)
         h_out.copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the step's result is read on the host
 
@@ -344,6 +359,14 @@ def run_gpu(args):
     e2e_ms = float(t.item()) / args.steps
     clocks = sampler.stop() if sampler else None
     ops.paged_attention_check_status(dev)
+    gather_check = None
+    if peer is not None:
+        peer.check()
+        # the peer-store gather must equal NCCL's all-gather of the same slices, bit for bit
+        mine = exchange(out_local)
+        torch.cuda.synchronize()
+        sharding.all_gather_outputs(out_local, gathered)
+        gather_check = bool(torch.equal(mine.view(torch.int16), gathered.view(torch.int16)))
     h2d = sum(x.numel() * x.element_size() for x in parts)
     d2h = h_out.numel() * h_out.element_size()
 
@@ -406,19 +429,22 @@ def run_gpu(args):
                    "within_tolerance": bool(np.all(err <= tol + tol * np.abs(ref))), "tolerance": tol}
 
     kernels_per_step = 2 + (1 if info.partials > 0 or min(lens) == 0 else 0)  # scatter, attention, reduce
+    kernels_per_step += 1 if peer is not None else 0                          # peer all-gather
     line = {
         "metric": METRIC, "value": spec.batch / ms_step * 1e3, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16" if spec.dtype == "bfloat16" else "f16", "data": "synthetic",
         "config": workload_config(spec, lens, {
-            "parallelism": f"kv-head sharding x{world}" + (" + NCCL all-gather of outputs" if world > 1 else ""),
+            "parallelism": f"kv-head sharding x{world}" + (
+                "" if world == 1 else (" + peer-store all-gather of outputs over NVLink" if peer is not None
+                                       else " + NCCL all-gather of outputs")),
             "l2": f"inputs larger than L2: {alg_bytes / 1e6:.0f} MB of KV per GPU per step vs {L2_BYTES >> 20} MB",
             "launch": "CUDA graph replay" if graph is not None else "eager launches on one stream",
             "work_items": info.work_items, "split_partials": info.partials, "grid": info.grid}),
         "e2e": {"value": spec.batch / e2e_ms * 1e3, "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
         "gpu_launches": kernels_per_step * args.steps,
-        "roofline": roofline, "cpu_baseline": cpu, "parity_check": checked, "clocks": clocks,
+        "roofline": roofline, "cpu_baseline": cpu, "parity_check": checked, "gather_check": gather_check, "clocks": clocks,
         "achieved_gbs_step": alg_bytes / ms_step / 1e6,
     }
     print(json.dumps(line), flush=True)
@@ -443,6 +469,7 @@ def main():
     ap.add_argument("--workload", default="c2", help="c1..c5: benchmark configuration (default c2)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays of the step")
+    ap.add_argument("--nccl-gather", action="store_true", help="exchange outputs with NCCL instead of peer stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity check")
     ap.add_argument("--cpu-sample", type=int, default=64, help="sequences in the CPU sample")
     args = ap.parse_args()

@@ -217,6 +217,40 @@ int msco_paged_attention_launch_static(const MscoPaPlan *plan, const void *query
                                        const void *attn_mask, void *out, void *stream);
 int msco_paged_attention_status_static(const MscoPaPlan *plan);
 
+/* ------------------------------------------------------------------------
+ * All-gather of per-rank outputs over NVLink peer memory (kv-head sharding).
+ *
+ * The reference has no multi-device code on this path; with the cache split by
+ * kv head the one exchange of a step is the all-gather of each rank's
+ * [batch, q_heads / N, head_dim] output.  msco_peer_allgather launches one small
+ * kernel that stores the local slice into slot `rank` of every rank's gathered
+ * buffer (plain peer stores), publishes `step` in every rank's flag array and
+ * waits -- bounded -- until all ranks have published `step` here.  When it has
+ * completed, gathered[rank] holds all slices: [world][slice_bytes].
+ *
+ * Set-up (once): every rank allocates its gathered buffer (world * slice_bytes)
+ * and a zeroed uint32[world] flag array, exports both with msco_ipc_export,
+ * exchanges the 64-byte handles and offsets with its peers by any host channel
+ * and maps theirs with msco_ipc_import.  `ticket` (zeroed uint32) and `status`
+ * (zeroed int32; set to MSCO_ERR_TIMEOUT if a peer never arrives) are local
+ * device words.  Call with step = 1, 2, 3, ... ; alternate between two gathered
+ * buffers from step to step if a consumer may still read the previous one.
+ * ---------------------------------------------------------------------- */
+#define MSCO_MAX_PEERS 8
+#define MSCO_IPC_HANDLE_BYTES 64
+typedef struct MscoGatherDesc {
+  int32_t world, rank;
+  void *gathered[MSCO_MAX_PEERS];     /* gathered[r]: rank r's buffer as mapped in this process   */
+  uint32_t *flags[MSCO_MAX_PEERS];    /* flags[r]: rank r's uint32[world] as mapped in this process */
+  int64_t slice_bytes;                /* bytes of one rank's slice; multiple of 16                 */
+  unsigned int *ticket;               /* local device word, zero before the first call            */
+  int32_t *status;                    /* local device word, zero before the first call            */
+} MscoGatherDesc;
+int msco_ipc_export(const void *dev_ptr, unsigned char *handle /* [64] */, int64_t *offset);
+int msco_ipc_import(const unsigned char *handle, int64_t offset, void **dev_ptr);
+int msco_ipc_release(void *dev_ptr, int64_t offset);
+int msco_peer_allgather(const MscoGatherDesc *desc, const void *local_out, uint32_t step, void *stream);
+
 /* Kernel timing for benchmarks.  After msco_paged_attention_profile_enable(plan, 1) every launch
  * of this plan records a pair of CUDA events directly around the attention kernel (not around the
  * plan upload or the reduce kernel) into a ring of 64 pairs owned by the plan.

@@ -35,6 +35,16 @@ class MscoPaPlanInfo(C.Structure):
     ]
 
 
+MAX_PEERS = 8
+IPC_HANDLE_BYTES = 64
+
+
+class MscoGatherDesc(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("gathered", C.c_void_p * MAX_PEERS),
+                ("flags", C.c_void_p * MAX_PEERS), ("slice_bytes", C.c_int64), ("ticket", C.c_void_p),
+                ("status", C.c_void_p)]
+
+
 class MscoError(RuntimeError):
     def __init__(self, code, message):
         super().__init__(f"[msco error {code}] {message}")
@@ -51,6 +61,7 @@ EXPORTS = (
     "msco_paged_attention_plan_info", "msco_paged_attention_plan_destroy", "msco_paged_attention_launch",
     "msco_paged_attention_status", "msco_paged_attention_profile_enable", "msco_paged_attention_profile_read",
     "msco_paged_attention_launch_static", "msco_paged_attention_status_static",
+    "msco_ipc_export", "msco_ipc_import", "msco_ipc_release", "msco_peer_allgather",
 )
 
 
@@ -89,6 +100,14 @@ def lib():
     L.msco_paged_attention_launch_static.argtypes = [vp] * 12
     L.msco_paged_attention_status_static.restype = C.c_int
     L.msco_paged_attention_status_static.argtypes = [vp]
+    L.msco_ipc_export.restype = C.c_int
+    L.msco_ipc_export.argtypes = [vp, C.c_char_p, C.POINTER(i64)]
+    L.msco_ipc_import.restype = C.c_int
+    L.msco_ipc_import.argtypes = [C.c_char_p, i64, C.POINTER(vp)]
+    L.msco_ipc_release.restype = C.c_int
+    L.msco_ipc_release.argtypes = [vp, i64]
+    L.msco_peer_allgather.restype = C.c_int
+    L.msco_peer_allgather.argtypes = [C.POINTER(MscoGatherDesc), vp, C.c_uint32, vp]
     L.msco_paged_attention_profile_enable.restype = C.c_int
     L.msco_paged_attention_profile_enable.argtypes = [vp, i32]
     L.msco_paged_attention_profile_read.restype = C.c_int

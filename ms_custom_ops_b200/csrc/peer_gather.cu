@@ -1,0 +1,153 @@
+// All-gather of the per-rank attention outputs over NVLink peer memory.
+//
+// With the KV cache partitioned by kv head the only exchange of a decode step
+// is the all-gather of each rank's [batch, q_heads / N, head_dim] output: a few
+// hundred KB in total, i.e. a latency-bound collective.  Instead of a library
+// collective, one small kernel pushes the local slice with plain 16-byte
+// stores into the gathered buffer of every peer (mapped through CUDA IPC; no
+// TMA, no multicast), publishes a per-step flag in every peer's flag array
+// with a system-scope release, and then waits -- with an iteration limit -- for
+// the flags of all peers, so that when the kernel has completed the gathered
+// buffer of this rank holds every rank's slice.
+//
+// The kernels of the different ranks run on different GPUs (one process per
+// GPU); nothing here waits on another launch of the same GPU.
+#include <cuda.h>
+
+#include <cstring>
+
+#include "msco_common.cuh"
+
+namespace msco {
+namespace {
+
+constexpr int kPushThreads = 512;
+constexpr int kPushMaxBlocks = 16;
+constexpr uint32_t kPeerWaitLimit = 1u << 22;  // polls of ~100 ns: gives up after about half a second
+
+struct GatherArgs {
+  void *gathered[MSCO_MAX_PEERS];   // rank r's gathered buffer as mapped into this process
+  uint32_t *flags[MSCO_MAX_PEERS];  // rank r's flag array (uint32[world]) as mapped into this process
+  int64_t slice_bytes;
+  int world, rank;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(kPushThreads)
+peer_gather_kernel(GatherArgs a, const uint4 *__restrict__ local, uint32_t step, unsigned int *ticket,
+                   int32_t *status) {
+  __shared__ bool is_last;
+  const int64_t n16 = a.slice_bytes / 16;
+  // 1. push the local slice into slot `rank` of every rank's gathered buffer (own copy included)
+  for (int64_t i = (int64_t)blockIdx.x * kPushThreads + threadIdx.x; i < n16; i += (int64_t)gridDim.x * kPushThreads) {
+    const uint4 v = __ldg(local + i);
+    for (int r = 0; r < a.world; ++r)
+      reinterpret_cast<uint4 *>(static_cast<char *>(a.gathered[r]) + (int64_t)a.rank * a.slice_bytes)[i] = v;
+  }
+  // 2. the block that finishes last publishes the flags and waits for the peers
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int t = atomicAdd(ticket, 1u);
+    is_last = (t == gridDim.x - 1);
+    if (is_last) *ticket = 0u;  // ready for the next launch on this stream
+  }
+  __syncthreads();
+  if (!is_last) return;
+  if (threadIdx.x < a.world) {
+    const int r = threadIdx.x;
+    __threadfence_system();  // every block's pushes (ordered before its ticket) precede the flag
+    st_release_sys(a.flags[r] + a.rank, step);  // "rank's slice of step `step` is in your buffer"
+    const uint32_t *mine = a.flags[a.rank] + r; // peer r's announcement in my own flag array
+    bool ok = false;
+    for (uint32_t it = 0; it < kPeerWaitLimit; ++it) {
+      if ((int32_t)(ld_acquire_sys(mine) - step) >= 0) { ok = true; break; }
+      __nanosleep(100);
+    }
+    if (!ok) atomicExch(status, kStatusTimeout);  // a peer never arrived: report, do not hang
+  }
+}
+
+typedef CUresult (*GetAddressRangeFn)(CUdeviceptr *, size_t *, CUdeviceptr);
+
+}  // namespace
+}  // namespace msco
+
+using namespace msco;
+
+extern "C" int msco_ipc_export(const void *dev_ptr, unsigned char *handle, int64_t *offset) {
+  if (dev_ptr == nullptr || handle == nullptr || offset == nullptr)
+    return fail(MSCO_ERR_INVALID_ARG, "ipc_export: NULL argument");
+  static GetAddressRangeFn get_range = nullptr;
+  if (get_range == nullptr) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    MSCO_CUDA_CHECK(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q));
+    if (q != cudaDriverEntryPointSuccess || fn == nullptr)
+      return fail(MSCO_ERR_CUDA, "ipc_export: cuMemGetAddressRange is not available");
+    get_range = reinterpret_cast<GetAddressRangeFn>(fn);
+  }
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  const CUresult r = get_range(&base, &size, reinterpret_cast<CUdeviceptr>(dev_ptr));
+  if (r != CUDA_SUCCESS) return fail(MSCO_ERR_CUDA, "ipc_export: cuMemGetAddressRange failed (%d)", (int)r);
+  cudaIpcMemHandle_t h;
+  MSCO_CUDA_CHECK(cudaIpcGetMemHandle(&h, reinterpret_cast<void *>(base)));
+  static_assert(sizeof(h) == MSCO_IPC_HANDLE_BYTES, "unexpected IPC handle size");
+  memcpy(handle, &h, sizeof(h));
+  *offset = (int64_t)(reinterpret_cast<CUdeviceptr>(dev_ptr) - base);
+  return MSCO_OK;
+}
+
+extern "C" int msco_ipc_import(const unsigned char *handle, int64_t offset, void **dev_ptr) {
+  if (handle == nullptr || dev_ptr == nullptr) return fail(MSCO_ERR_INVALID_ARG, "ipc_import: NULL argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void *base = nullptr;
+  MSCO_CUDA_CHECK(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+  *dev_ptr = static_cast<char *>(base) + offset;
+  return MSCO_OK;
+}
+
+extern "C" int msco_ipc_release(void *dev_ptr, int64_t offset) {
+  if (dev_ptr == nullptr) return MSCO_OK;
+  MSCO_CUDA_CHECK(cudaIpcCloseMemHandle(static_cast<char *>(dev_ptr) - offset));
+  return MSCO_OK;
+}
+
+extern "C" int msco_peer_allgather(const MscoGatherDesc *desc, const void *local_out, uint32_t step,
+                                   void *stream) {
+  if (desc == nullptr || local_out == nullptr) return fail(MSCO_ERR_INVALID_ARG, "peer_allgather: NULL argument");
+  if (desc->world < 1 || desc->world > MSCO_MAX_PEERS || desc->rank < 0 || desc->rank >= desc->world)
+    return fail(MSCO_ERR_INVALID_ARG, "peer_allgather: bad rank %d of %d", desc->rank, desc->world);
+  if (desc->slice_bytes <= 0 || desc->slice_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(local_out) & 15))
+    return fail(MSCO_ERR_INVALID_ARG, "peer_allgather: slices must be 16-byte multiples and 16-byte aligned");
+  if (desc->ticket == nullptr || desc->status == nullptr)
+    return fail(MSCO_ERR_INVALID_ARG, "peer_allgather: ticket / status words are required");
+  GatherArgs a;
+  for (int r = 0; r < desc->world; ++r) {
+    if (desc->gathered[r] == nullptr || desc->flags[r] == nullptr)
+      return fail(MSCO_ERR_INVALID_ARG, "peer_allgather: rank %d's buffers are not mapped", r);
+    a.gathered[r] = desc->gathered[r];
+    a.flags[r] = desc->flags[r];
+  }
+  a.slice_bytes = desc->slice_bytes;
+  a.world = desc->world;
+  a.rank = desc->rank;
+  const int64_t n16 = desc->slice_bytes / 16;
+  int blocks = (int)((n16 + kPushThreads - 1) / kPushThreads);
+  blocks = blocks < 1 ? 1 : (blocks > kPushMaxBlocks ? kPushMaxBlocks : blocks);
+  peer_gather_kernel<<<blocks, kPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      a, static_cast<const uint4 *>(local_out), step, desc->ticket, desc->status);
+  MSCO_CUDA_CHECK(cudaGetLastError());
+  return MSCO_OK;
+}

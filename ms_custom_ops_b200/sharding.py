@@ -74,3 +74,93 @@ def all_gather_outputs(out_local, gathered=None, group=None):
     flat = gathered.view((world * out_local.shape[0],) + tuple(out_local.shape[1:]))
     dist.all_gather_into_tensor(flat, out_local.contiguous(), group=group)
     return gathered
+
+
+class PeerGather:
+    """All-gather of per-rank outputs by peer stores over NVLink (msco_peer_allgather).
+
+    Set-up exchanges CUDA IPC handles of each rank's gathered buffers and flag arrays through the
+    process group (host side); after that a gather is one small kernel per rank on the caller's
+    stream -- no library collective.  Two gathered buffers alternate from step to step, so a
+    consumer of step k may still be reading while step k+1 is pushed.
+
+        pg = PeerGather(out_local.shape, out_local.dtype, device)      # collective: call on all ranks
+        gathered = pg.gather(out_local)                                # [world, *out_local.shape]
+    """
+
+    def __init__(self, slice_shape, dtype, device, group=None):
+        import ctypes as C
+
+        import torch
+        import torch.distributed as dist
+
+        from . import _abi
+        self._abi, self._C, self._torch = _abi, C, torch
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > _abi.MAX_PEERS:
+            raise ValueError(f"at most {_abi.MAX_PEERS} ranks")
+        self.slice_shape = tuple(slice_shape)
+        self.slice_bytes = int(torch.empty(self.slice_shape, dtype=dtype, device="meta").numel()) * \
+            torch.empty((), dtype=dtype).element_size()
+        if self.slice_bytes % 16:
+            raise ValueError("slice size must be a multiple of 16 bytes")
+        L = _abi.lib()
+        # one arena per rank, exported once: [gathered 0 | gathered 1 | flags 0 | flags 1], 256-byte aligned parts
+        gbytes = self.world * self.slice_bytes
+        goff = [0, (gbytes + 255) // 256 * 256]
+        foff = [goff[1] * 2, goff[1] * 2 + 256]
+        self.arena = torch.zeros(foff[1] + 256, dtype=torch.uint8, device=device)
+        self.buffers = [self.arena[o:o + gbytes].view(dtype).view((self.world,) + self.slice_shape) for o in goff]
+        self.words = torch.zeros(4, dtype=torch.int32, device=device)  # [ticket, status, -, -]
+        torch.cuda.synchronize(device)
+        h = C.create_string_buffer(_abi.IPC_HANDLE_BYTES)
+        off = C.c_int64()
+        _abi.check(L.msco_ipc_export(C.c_void_p(self.arena.data_ptr()), h, C.byref(off)))
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, (bytes(h.raw), int(off.value)), group=group)
+        self._mapped = []  # (ptr, offset) of imported peer arenas, for release()
+        bases = []
+        for r in range(self.world):
+            if r == self.rank:
+                bases.append(self.arena.data_ptr())
+            else:
+                handle, roff = everyone[r]
+                p = C.c_void_p()
+                _abi.check(L.msco_ipc_import(handle, roff, C.byref(p)))
+                self._mapped.append((p.value, roff))
+                bases.append(p.value)
+        self.descs = []
+        for parity in range(2):
+            d = _abi.MscoGatherDesc()
+            d.world, d.rank, d.slice_bytes = self.world, self.rank, self.slice_bytes
+            d.ticket = self.words.data_ptr()
+            d.status = self.words.data_ptr() + 4
+            for r in range(self.world):
+                d.gathered[r] = bases[r] + goff[parity]
+                d.flags[r] = bases[r] + foff[parity]
+            self.descs.append(d)
+        self.step = 0
+        dist.barrier(group=group)  # every rank has mapped every buffer before the first push
+
+    def gather(self, out_local):
+        """Push `out_local` to every rank and wait for every rank's push; returns this rank's
+        gathered buffer [world, *slice_shape] (valid until the gather after next)."""
+        C, torch = self._C, self._torch
+        self.step += 1
+        parity = self.step & 1
+        # each parity has its own flag array, so its step counter advances by one per use
+        self._abi.check(self._abi.lib().msco_peer_allgather(
+            C.byref(self.descs[parity]), C.c_void_p(out_local.data_ptr()), C.c_uint32((self.step + 1) // 2),
+            C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return self.buffers[parity]
+
+    def check(self):
+        """After a synchronise: raises if a bounded wait for a peer expired."""
+        if int(self.words[1].item()) != 0:
+            raise self._abi.MscoError(self._abi.ERR_TIMEOUT, "peer all-gather: a peer's flag never arrived")
+
+    def release(self):
+        L = self._abi.lib()
+        for p, off in self._mapped:
+            L.msco_ipc_release(self._C.c_void_p(p), off)
+        self._mapped = []
