@@ -5,7 +5,9 @@
 libmsco_b200.so          CUDA kernels + thin C ABI      nvcc, sm_100a only
 libms_custom_ops_host.so C++ operator layer             g++, links the kernel library
 
-Both land next to this file so that they travel with the source tree.
+bench/msco_bench         standalone C++ benchmark       nvcc, links the kernel library
+
+All land inside this package so that they travel with the source tree.
 """
 from __future__ import annotations
 
@@ -73,9 +75,23 @@ def build_host(force=False):
     return HOST_LIB
 
 
+def build_bench(force=False):
+    """Standalone C++ benchmark harness (no Python at run time): bench/msco_bench."""
+    src = os.path.join(HERE, "bench", "msco_bench.cu")
+    exe = os.path.join(HERE, "bench", "msco_bench")
+    if not os.path.exists(src):
+        return None
+    if not force and not _stale(exe, [src, KERNEL_LIB, os.path.join(INCLUDE, "msco_b200.h")]):
+        return exe
+    _run([_nvcc(), "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-I", INCLUDE, "-o", exe, src,
+          "-L", HERE, "-lmsco_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/.."])
+    return exe
+
+
 def build_all(force=False, verbose_ptxas=False):
     build_kernels(force, verbose_ptxas)
     build_host(force)
+    build_bench(force)
 
 
 if __name__ == "__main__":
