@@ -428,6 +428,7 @@ def run_gpu(args):
                    "rel_l2": float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30)),
                    "within_tolerance": bool(np.all(err <= tol + tol * np.abs(ref))), "tolerance": tol}
 
+    scatter = measure_scatter(spec, dev, peak) if (world == 1 and "rac_tokens" in spec.extra) else None
     kernels_per_step = 2 + (1 if info.partials > 0 or min(lens) == 0 else 0)  # scatter, attention, reduce
     kernels_per_step += 1 if peer is not None else 0                          # peer all-gather
     line = {
@@ -445,12 +446,77 @@ def run_gpu(args):
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
         "gpu_launches": kernels_per_step * args.steps,
         "roofline": roofline, "cpu_baseline": cpu, "parity_check": checked, "gather_check": gather_check, "clocks": clocks,
+        "reshape_and_cache_prefill": scatter,
         "achieved_gbs_step": alg_bytes / ms_step / 1e6,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def measure_scatter(spec, dev, peak):
+    """Prefill-heavy reshape_and_cache of configuration 5: 16384 tokens (8 kv heads x 128) through an
+    injective random slot map into 4096 blocks of 128 with 5 % of the slots set to -1, bf16 copy and
+    bf16 -> int8 quantising variants.  Four distinct input / cache sets rotate (each > L2), the
+    four launches are captured in a CUDA graph and replayed, CUDA events around the replays."""
+    import torch
+    from ms_custom_ops_b200 import kernels
+    tokens, blocks, pad = spec.extra["rac_tokens"], spec.extra["rac_blocks"], spec.extra["pad_frac"]
+    c = spec.kv_heads * spec.head_size
+    tdt = torch.bfloat16 if spec.dtype == "bfloat16" else torch.float16
+    rng = np.random.default_rng(spec.seed)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(spec.seed)
+    out = {"tokens": tokens, "blocks": blocks, "padding_fraction": pad, "sets": 4,
+           "l2": "4 rotating input/cache sets, each larger than L2"}
+    kd = torch.rand(c, generator=gen, device=dev) * 0.04 + 0.01
+    vd = torch.rand(c, generator=gen, device=dev) * 0.04 + 0.01
+    for name, quant in (("copy", False), ("quant_int8", True)):
+        sets = []
+        for _ in range(4):
+            slots = rng.permutation(blocks * spec.block_size)[:tokens].astype(np.int32)
+            slots[rng.random(tokens) < pad] = -1
+            key = torch.randn((tokens, c), generator=gen, device=dev).to(tdt)
+            val = torch.randn((tokens, c), generator=gen, device=dev).to(tdt)
+            kc = torch.zeros((blocks, spec.block_size, spec.kv_heads, spec.head_size),
+                             dtype=torch.int8 if quant else tdt, device=dev)
+            sets.append((key, val, kc, torch.zeros_like(kc), torch.from_numpy(slots).to(dev), slots))
+
+        def go(i):
+            key, val, kc, vc, sl, _ = sets[i]
+            if quant:
+                kernels.rac_scatter_quant(key, val, kc, vc, sl, kd, vd)
+            else:
+                kernels.rac_scatter(key, val, kc, vc, sl)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(4):
+                go(i)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(4):
+                    go(i)
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (reps * 4)
+        nbytes = workloads.algorithmic_bytes_scatter(sets[0][5], c, 2, 1 if quant else 2, quant)
+        out[name] = {"ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / ms / 1e6,
+                     "frac": nbytes / ms / 1e6 / peak, "frac_of_8tbs": nbytes / ms / 1e6 / 8000.0,
+                     "tokens_per_s": tokens / ms * 1e3}
+        del sets, graph
+        torch.cuda.empty_cache()
+    return out
 
 
 def _to_np(t):
