@@ -62,7 +62,9 @@ template <bool KV8, int NT> struct Cfg {
   static constexpr int kOffDesc = kOffMl + kWarps * 16 * 2 * 4;     // 2 x 8 ints
   static constexpr int kOffBar = kOffDesc + 2 * 8 * 4;              // mbarriers
   static constexpr int kNumBars = 2 * kStages + 4;
-  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
+  static constexpr int kOffItemBase = kOffBar + kNumBars * 8 + 16;  // copy of the plan's item_base[]
+  static constexpr int kItemBaseCap = 1024;                          // sequences (+1) that fit
+  static constexpr int kSmemBytes = kOffItemBase + kItemBaseCap * 4;
   static constexpr int kDynSmem = kSmemBytes + 1024;                // slack for 1024-byte alignment
 };
 
@@ -126,12 +128,21 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       prefetch_tmap(&tm_k);
       prefetch_tmap(&tm_v);
     }
+    // stage the per-sequence item offsets in shared memory (one coalesced fetch) so that decoding a
+    // work item costs one global round trip instead of a chain of them
+    int32_t *ib = reinterpret_cast<int32_t *>(smem + C::kOffItemBase);
+    const bool ib_ok = pv.nseq + 1 <= C::kItemBaseCap;
+    if (ib_ok) {
+      for (int i = lane; i <= pv.nseq; i += 32) ib[i] = __ldg(pv.item_base + i);
+      __syncwarp();
+    }
+    const int32_t *ibs = ib_ok ? ib : nullptr;
     uint32_t st = 0, ph = 0;
     const int bs = p.block_size;
     const int bpt = kTile / bs;  // cache blocks per tile (divides 32)
     int qi = 0;
     for (int t = blockIdx.x; t < total; t += gridDim.x, ++qi) {
-      const WorkItem w = decode_item(pv, t, p.num_kv_heads, p.group, C::kRows);
+      const WorkItem w = decode_item(pv, t, p.num_kv_heads, p.group, C::kRows, ibs);
       const int qs = qi & 1;
       const uint32_t qph = (qi >> 1) & 1;
       if (!mbar_wait(&qempty[qs], qph ^ 1, kWaitLimit)) {
