@@ -158,15 +158,28 @@ void msco_paged_attention_plan_destroy(MscoPaPlan *plan);
  *   attn_mask    NORM [batch, 1, max_ctx], ALIBI [batch, num_q_heads, 1, max_ctx]
  *   out          [batch, num_q_heads, head_dim]                      q_dtype
  *   workspace    >= msco_paged_attention_workspace_bytes(plan), 256-byte aligned;
- *                holds the uploaded plan, the split partials and a status word.
- * The first bytes of the workspace are written by an async copy from the
- * plan's pinned host memory: the plan must outlive the launch. */
+ *                holds two status words, the plan words and the split partials.  It needs no
+ *                initialisation: errors are tagged with a per-launch epoch.
+ * Plans of up to 2304 words (about 280 sequences) travel as a kernel parameter; larger ones are
+ * copied into the workspace by an async copy from the plan's pinned host memory in front of the
+ * kernel: the plan must outlive the launch. */
 int msco_paged_attention_launch(const MscoPaPlan *plan, const void *query, const void *key_cache,
                                 const void *value_cache, const int32_t *block_tables,
                                 const float *k_descale, const int32_t *k_offset,
                                 const float *v_descale, const int32_t *v_offset,
                                 const void *attn_mask, void *out, void *workspace,
                                 size_t workspace_bytes, void *stream);
+
+/* One decode step in one call: reshape_and_cache of `num_tokens` new rows (key / value:
+ * [num_tokens, num_kv_heads * head_dim] in the query dtype; quantised on the way in when the plan's
+ * quant_type is 1) followed by the attention launch above on the same caches.  Same result as the
+ * two separate calls; the attention kernel is launched with programmatic stream serialisation
+ * behind the scatter kernel so that its set-up overlaps the scatter's tail. */
+int msco_decode_step(const MscoPaPlan *plan, const void *key, const void *value, void *key_cache,
+                     void *value_cache, const int32_t *slot_mapping, int64_t num_tokens, const void *query,
+                     const int32_t *block_tables, const float *k_descale, const int32_t *k_offset,
+                     const float *v_descale, const int32_t *v_offset, const void *attn_mask, void *out,
+                     void *workspace, size_t workspace_bytes, void *stream);
 
 /* After the stream has been synchronised: reads the status word the kernels
  * leave in the workspace.  MSCO_OK, MSCO_ERR_TIMEOUT (a bounded wait inside

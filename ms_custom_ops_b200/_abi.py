@@ -61,7 +61,7 @@ EXPORTS = (
     "msco_paged_attention_plan_info", "msco_paged_attention_plan_destroy", "msco_paged_attention_launch",
     "msco_paged_attention_status", "msco_paged_attention_profile_enable", "msco_paged_attention_profile_read",
     "msco_paged_attention_launch_static", "msco_paged_attention_status_static",
-    "msco_ipc_export", "msco_ipc_import", "msco_ipc_release", "msco_peer_allgather",
+    "msco_ipc_export", "msco_ipc_import", "msco_ipc_release", "msco_peer_allgather", "msco_decode_step",
 )
 
 
@@ -100,6 +100,8 @@ def lib():
     L.msco_paged_attention_launch_static.argtypes = [vp] * 12
     L.msco_paged_attention_status_static.restype = C.c_int
     L.msco_paged_attention_status_static.argtypes = [vp]
+    L.msco_decode_step.restype = C.c_int
+    L.msco_decode_step.argtypes = [vp] * 6 + [i64] + [vp] * 9 + [sz, vp]
     L.msco_ipc_export.restype = C.c_int
     L.msco_ipc_export.argtypes = [vp, C.c_char_p, C.POINTER(i64)]
     L.msco_ipc_import.restype = C.c_int

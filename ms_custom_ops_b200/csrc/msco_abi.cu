@@ -1,5 +1,7 @@
 // C ABI of libmsco_b200.so: error reporting, paged-attention planning and launch.
 #include <algorithm>
+#include <atomic>
+#include <chrono>
 #include <cmath>
 #include <cstring>
 #include <new>
@@ -167,7 +169,7 @@ extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *
   pl->kv_tokens = kv_tokens;
   pl->need_reduce = parts > 0 || nseq < batch;
   pl->grid = pl->kernel == kKernelTma ? (int)std::min<int64_t>(items, pl->num_sms) : (int)items;
-  pl->part_o_offset = align_up(pl->plan_bytes, 256);
+  pl->part_o_offset = align_up(kPlanRegionOffset + pl->plan_bytes, 256);
   const size_t part_o_bytes = (size_t)parts * d.num_q_heads * d.head_dim * 4;
   pl->part_ml_offset = align_up(pl->part_o_offset + part_o_bytes, 256);
   pl->workspace_bytes = align_up(pl->part_ml_offset + (size_t)parts * d.num_q_heads * 2 * 4, 256);
@@ -230,12 +232,36 @@ extern "C" void msco_paged_attention_plan_destroy(MscoPaPlan *plan) {
   delete plan;
 }
 
-extern "C" int msco_paged_attention_launch(const MscoPaPlan *plan, const void *query, const void *key_cache,
-                                           const void *value_cache, const int32_t *block_tables,
-                                           const float *k_descale, const int32_t *k_offset,
-                                           const float *v_descale, const int32_t *v_offset,
-                                           const void *attn_mask, void *out, void *workspace,
-                                           size_t workspace_bytes, void *stream) {
+namespace {
+
+// Launch epochs: every launch gets a fresh 32-bit tag; a kernel that reports an error writes the
+// tag next to the code, so stale words in a reused workspace are never mistaken for a new error
+// and nothing has to be cleared in front of a launch.
+std::atomic<uint32_t> g_epoch{(uint32_t)std::chrono::steady_clock::now().time_since_epoch().count() | 1u};
+
+// (workspace, epoch) of recent launches, for status queries that come without the plan
+std::mutex g_recent_mu;
+struct Recent { const void *ws; uint32_t epoch; };
+Recent g_recent[64] = {};
+unsigned g_recent_next = 0;
+
+void remember_launch(const void *ws, uint32_t epoch) {
+  std::lock_guard<std::mutex> g(g_recent_mu);
+  for (auto &r : g_recent)
+    if (r.ws == ws) { r.epoch = epoch; return; }
+  g_recent[g_recent_next++ % 64] = {ws, epoch};
+}
+bool recall_launch(const void *ws, uint32_t *epoch) {
+  std::lock_guard<std::mutex> g(g_recent_mu);
+  for (auto &r : g_recent)
+    if (r.ws == ws) { *epoch = r.epoch; return true; }
+  return false;
+}
+
+int pa_launch_impl(const MscoPaPlan *plan, const void *query, const void *key_cache, const void *value_cache,
+                   const int32_t *block_tables, const float *k_descale, const int32_t *k_offset,
+                   const float *v_descale, const int32_t *v_offset, const void *attn_mask, void *out,
+                   void *workspace, size_t workspace_bytes, void *stream, bool after_kernel) {
   if (plan == nullptr) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch: NULL plan");
   if (plan->batch == 0) return MSCO_OK;
   const MscoPaDesc &d = plan->desc;
@@ -265,7 +291,8 @@ extern "C" int msco_paged_attention_launch(const MscoPaPlan *plan, const void *q
   p.mask = d.mask_type ? attn_mask : nullptr;
   p.out = out;
   char *ws = static_cast<char *>(workspace);
-  p.plan = reinterpret_cast<int32_t *>(ws);
+  p.status = reinterpret_cast<int32_t *>(ws);
+  p.plan = reinterpret_cast<const int32_t *>(ws + kPlanRegionOffset);
   p.part_o = reinterpret_cast<float *>(ws + plan->part_o_offset);
   p.part_ml = reinterpret_cast<float *>(ws + plan->part_ml_offset);
   p.num_blocks = d.num_blocks;
@@ -276,31 +303,89 @@ extern "C" int msco_paged_attention_launch(const MscoPaPlan *plan, const void *q
   p.mask_type = d.mask_type; p.mask_dtype = d.mask_dtype;
   p.scale = d.qk_scale;
   p.scale_log2e = d.qk_scale * 1.4426950408889634f;
+  p.epoch = g_epoch.fetch_add(2u);
+  plan->last_epoch = p.epoch;
+  remember_launch(workspace, p.epoch);
 
-  MSCO_CUDA_CHECK(cudaMemcpyAsync(ws, plan->host_words, plan->plan_bytes, cudaMemcpyHostToDevice, st));
+  // small plans ride in the kernel parameters; larger ones are uploaded in front of the kernel
+  static thread_local PlanParam pp;
+  p.plan_in_param = plan->plan_words <= (size_t)kPlanParamWords ? 1 : 0;
+  if (p.plan_in_param) {
+    memcpy(pp.w, plan->host_words, plan->plan_bytes);
+  } else {
+    MSCO_CUDA_CHECK(cudaMemcpyAsync(ws + kPlanRegionOffset, plan->host_words, plan->plan_bytes,
+                                    cudaMemcpyHostToDevice, st));
+    after_kernel = false;  // a copy now sits between the previous kernel and ours
+  }
   cudaEvent_t *pe = nullptr;
   if (plan->profile && plan->total_items > 0) {
     pe = plan->prof_ev[plan->prof_count % MscoPaPlan::kProfRing];
     MSCO_CUDA_CHECK(cudaEventRecord(pe[0], st));
+    after_kernel = false;
   }
-  int rc = plan->kernel == kKernelTma ? launch_pa_tma(plan, p, st) : launch_pa_generic(plan, p, st);
+  int rc = plan->kernel == kKernelTma ? launch_pa_tma(plan, p, pp, st, after_kernel)
+                                      : launch_pa_generic(plan, p, pp, st);
   if (rc != MSCO_OK) return rc;
   if (pe != nullptr) {
     MSCO_CUDA_CHECK(cudaEventRecord(pe[1], st));
     ++plan->prof_count;
   }
-  if (plan->need_reduce) rc = launch_pa_reduce(plan, p, st);
+  if (plan->need_reduce) rc = launch_pa_reduce(plan, p, pp, st);
   return rc;
 }
 
+}  // namespace
+
+extern "C" int msco_paged_attention_launch(const MscoPaPlan *plan, const void *query, const void *key_cache,
+                                           const void *value_cache, const int32_t *block_tables,
+                                           const float *k_descale, const int32_t *k_offset,
+                                           const float *v_descale, const int32_t *v_offset,
+                                           const void *attn_mask, void *out, void *workspace,
+                                           size_t workspace_bytes, void *stream) {
+  return pa_launch_impl(plan, query, key_cache, value_cache, block_tables, k_descale, k_offset, v_descale, v_offset,
+                        attn_mask, out, workspace, workspace_bytes, stream, false);
+}
+
+// One decode step in one call: scatter the new token rows, then attention.  The attention kernel
+// is launched with programmatic stream serialisation behind the scatter kernel, so its set-up
+// overlaps the scatter's tail; it waits for the scatter's writes before it reads the cache.
+extern "C" int msco_decode_step(const MscoPaPlan *plan, const void *key, const void *value, void *key_cache,
+                                void *value_cache, const int32_t *slot_mapping, int64_t num_tokens,
+                                const void *query, const int32_t *block_tables, const float *k_descale,
+                                const int32_t *k_offset, const float *v_descale, const int32_t *v_offset,
+                                const void *attn_mask, void *out, void *workspace, size_t workspace_bytes,
+                                void *stream) {
+  if (plan == nullptr) return fail(MSCO_ERR_INVALID_ARG, "decode_step: NULL plan");
+  const MscoPaDesc &d = plan->desc;
+  const int64_t row = (int64_t)d.num_kv_heads * d.head_dim;
+  const int64_t slots = d.num_blocks * d.block_size;
+  int rc;
+  if (d.quant_type == 1) {
+    rc = msco_reshape_and_cache_quant(key, value, static_cast<int8_t *>(key_cache), static_cast<int8_t *>(value_cache),
+                                      slot_mapping, num_tokens, row, row, d.q_dtype, k_descale,
+                                      d.has_quant_offset ? k_offset : nullptr, v_descale,
+                                      d.has_quant_offset ? v_offset : nullptr, slots, nullptr, stream);
+  } else {
+    rc = msco_reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, num_tokens, row * 2, row * 2, slots,
+                                nullptr, stream);
+  }
+  if (rc != MSCO_OK) return rc;
+  return pa_launch_impl(plan, query, key_cache, value_cache, block_tables, k_descale, k_offset, v_descale, v_offset,
+                        attn_mask, out, workspace, workspace_bytes, stream, num_tokens > 0);
+}
+
 extern "C" int msco_paged_attention_status(const MscoPaPlan *plan, const void *workspace) {
-  // plan may be NULL: the status word is always the first word of the workspace
+  // plan may be NULL: the epoch of the last launch that used this workspace is remembered
   if (workspace == nullptr) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_status: NULL workspace");
   if (plan != nullptr && plan->batch == 0) return MSCO_OK;
-  int32_t status = 0;
-  MSCO_CUDA_CHECK(cudaMemcpy(&status, workspace, sizeof(status), cudaMemcpyDeviceToHost));
-  if (status == kStatusTimeout) return fail(MSCO_ERR_TIMEOUT, "paged_attention: a bounded wait inside the kernel expired");
-  if (status == kStatusOob) return fail(MSCO_ERR_OOB, "paged_attention: a block id outside the cache was met");
+  uint32_t epoch = 0;
+  if (plan != nullptr) epoch = plan->last_epoch;
+  else if (!recall_launch(workspace, &epoch)) return MSCO_OK;  // nothing was launched with it
+  int32_t words[2] = {0, 0};
+  MSCO_CUDA_CHECK(cudaMemcpy(words, workspace, sizeof(words), cudaMemcpyDeviceToHost));
+  if ((uint32_t)words[1] != epoch) return MSCO_OK;  // no kernel of that launch reported anything
+  if (words[0] == kStatusTimeout) return fail(MSCO_ERR_TIMEOUT, "paged_attention: a bounded wait inside the kernel expired");
+  if (words[0] == kStatusOob) return fail(MSCO_ERR_OOB, "paged_attention: a block id outside the cache was met");
   return MSCO_OK;
 }
 

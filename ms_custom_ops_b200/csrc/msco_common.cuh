@@ -39,7 +39,7 @@ inline int dtype_size(int dt) {
 }
 
 // ---- device plan layout (int32 words at the start of the PA workspace) ----
-// [0] status  [1] nseq  [2] total_items  [3] total_parts  [4] batch  [5] items_per_split  [6..7] pad
+// [0] unused  [1] nseq  [2] total_items  [3] total_parts  [4] batch  [5] items_per_split  [6..7] pad
 // then: item_base[nseq+1], seq_idx[nseq], seq_len[nseq], chunk[nseq], nsplit[nseq], part_base[nseq],
 //       b_nsplit[batch], b_part_base[batch]
 constexpr int kPlanHeaderWords = 8;
@@ -78,6 +78,13 @@ struct WorkItem {
 };
 
 #ifdef __CUDACC__
+// Error report of a kernel: the code and the epoch of the launch that hit it (the host compares
+// the epoch, so the words never need clearing).
+__device__ __forceinline__ void report_status(int32_t *status, uint32_t epoch, int code) {
+  status[1] = (int32_t)epoch;
+  atomicExch(status, code);
+}
+
 // ---- dtype conversion ------------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }

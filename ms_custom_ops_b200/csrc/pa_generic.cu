@@ -42,14 +42,14 @@ __device__ __forceinline__ float load_mask(const void *mask, int dtype, int64_t 
 }
 
 template <typename TQ, typename TKV>
-__global__ void __launch_bounds__(kGenThreads) pa_generic_kernel(PaParams p) {
+__global__ void __launch_bounds__(kGenThreads) pa_generic_kernel(PaParams p, const __grid_constant__ PlanParam pp) {
   __shared__ float q_s[kGenRows][kGenMaxD];            // q (times k_descale for int8 KV)
   __shared__ float koff_s[kGenMaxD];                    // k_offset of this kv head (int8 KV)
   __shared__ float acc_s[kGenWarps][kGenRows][kGenMaxD];
   __shared__ float m_s[kGenWarps][kGenRows], l_s[kGenWarps][kGenRows];
   __shared__ WorkItem item_s;
 
-  const PlanView pv = make_plan_view(p.plan);
+  const PlanView pv = make_plan_view(p.plan_in_param ? pp.w : p.plan);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) item_s = decode_item(pv, blockIdx.x, p.num_kv_heads, p.group, kGenRows);
   __syncthreads();
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(kGenThreads) pa_generic_kernel(PaParams p) {
     if (valid) {
       const int blk = __ldg(trow + tok / p.block_size);
       if (blk < 0 || blk >= p.num_blocks) {
-        atomicExch(p.plan, kStatusOob);
+        report_status(p.status, p.epoch, kStatusOob);
         valid = false;
       } else {
         row_off = ((int64_t)blk * p.block_size + tok % p.block_size) * tok_stride + (int64_t)w.kvh * D;
@@ -205,11 +205,11 @@ __global__ void __launch_bounds__(kGenThreads) pa_generic_kernel(PaParams p) {
 // the lanes in parallel (one split per lane, strided for more), the weights 2^(m_s - M) stay in
 // registers, and the partial rows are accumulated in split order with several loads in flight.
 template <typename TQ>
-__global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p) {
+__global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p, const __grid_constant__ PlanParam pp) {
   // launched with programmatic stream serialisation: wait here until the attention grid before us
   // has completed and its partials are visible (a no-op for an ordinary launch)
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const PlanView pv = make_plan_view(p.plan);
+  const PlanView pv = make_plan_view(p.plan_in_param ? pp.w : p.plan);
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= pv.batch * p.num_q_heads) return;
@@ -297,20 +297,20 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p) {
 
 }  // namespace
 
-int launch_pa_generic(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream) {
+int launch_pa_generic(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream) {
   if (plan->total_items == 0) return MSCO_OK;
   const dim3 grid(plan->total_items), block(kGenThreads);
   const int qd = plan->desc.q_dtype, kd = plan->desc.kv_dtype;
-  if (qd == MSCO_DTYPE_F16 && kd == MSCO_DTYPE_F16) pa_generic_kernel<__half, __half><<<grid, block, 0, stream>>>(p);
-  else if (qd == MSCO_DTYPE_BF16 && kd == MSCO_DTYPE_BF16) pa_generic_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, stream>>>(p);
-  else if (qd == MSCO_DTYPE_F16 && kd == MSCO_DTYPE_I8) pa_generic_kernel<__half, int8_t><<<grid, block, 0, stream>>>(p);
-  else if (qd == MSCO_DTYPE_BF16 && kd == MSCO_DTYPE_I8) pa_generic_kernel<__nv_bfloat16, int8_t><<<grid, block, 0, stream>>>(p);
+  if (qd == MSCO_DTYPE_F16 && kd == MSCO_DTYPE_F16) pa_generic_kernel<__half, __half><<<grid, block, 0, stream>>>(p, pp);
+  else if (qd == MSCO_DTYPE_BF16 && kd == MSCO_DTYPE_BF16) pa_generic_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, block, 0, stream>>>(p, pp);
+  else if (qd == MSCO_DTYPE_F16 && kd == MSCO_DTYPE_I8) pa_generic_kernel<__half, int8_t><<<grid, block, 0, stream>>>(p, pp);
+  else if (qd == MSCO_DTYPE_BF16 && kd == MSCO_DTYPE_I8) pa_generic_kernel<__nv_bfloat16, int8_t><<<grid, block, 0, stream>>>(p, pp);
   else return fail(MSCO_ERR_UNSUPPORTED, "paged_attention: unsupported dtype combination q=%d kv=%d", qd, kd);
   MSCO_CUDA_CHECK(cudaGetLastError());
   return MSCO_OK;
 }
 
-int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream) {
+int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream) {
   const int rows = plan->batch * plan->desc.num_q_heads;
   if (rows == 0) return MSCO_OK;
   cudaLaunchConfig_t cfg = {};
@@ -323,8 +323,8 @@ int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, cudaStream_t str
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (plan->desc.q_dtype == MSCO_DTYPE_F16) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__half>, p));
-  else MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__nv_bfloat16>, p));
+  if (plan->desc.q_dtype == MSCO_DTYPE_F16) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__half>, p, pp));
+  else MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__nv_bfloat16>, p, pp));
   return MSCO_OK;
 }
 

@@ -24,7 +24,10 @@ struct PaParams {
   const int32_t *v_offset;
   const void *mask;
   void *out;
-  int32_t *plan;   // device copy of the plan words; word 0 is the status
+  const int32_t *plan;  // device copy of the plan words (unused when the words travel as a kernel parameter)
+  int32_t *status;      // workspace words 0..1: [error code, launch epoch]
+  uint32_t epoch;       // identifies this launch in the status words
+  int32_t plan_in_param;  // the plan words are in the PlanParam kernel argument
   float *part_o;   // [total_parts, num_q_heads, head_dim] un-normalised partial outputs
   float *part_ml;  // [total_parts, num_q_heads, 2] (running max in log2 domain, running sum)
   int64_t num_blocks;
@@ -34,6 +37,14 @@ struct PaParams {
   float scale;        // qk_scale
   float scale_log2e;  // qk_scale * log2(e)
 };
+
+// Plans of up to kPlanParamWords words travel as a kernel parameter (no upload, no stream
+// operation in front of the attention kernel); larger ones are copied into the workspace.
+constexpr int kPlanParamWords = 2304;
+struct PlanParam {
+  int32_t w[kPlanParamWords];
+};
+constexpr size_t kPlanRegionOffset = 256;  // workspace: [status block | plan words | partials]
 
 constexpr int kKernelGeneric = 1;
 constexpr int kKernelTma = 2;
@@ -63,6 +74,7 @@ struct MscoPaPlan {
   mutable const void *tm_v_ptr = nullptr;
   alignas(64) mutable unsigned char tm_k[128];
   alignas(64) mutable unsigned char tm_v[128];
+  mutable uint32_t last_epoch = 0;  // epoch of the most recent launch (status check)
   // optional kernel timing (benchmarks): ring of event pairs recorded around the attention kernel
   static constexpr int kProfRing = 64;
   bool profile = false;
@@ -72,8 +84,12 @@ struct MscoPaPlan {
 
 namespace msco {
 // kernel launchers (defined next to the kernels)
-int launch_pa_generic(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream);
-int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream);
-int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream);
+// `pp`: the plan words as a kernel parameter (meaningful when p.plan_in_param); `after_kernel`:
+// the previous operation on the stream is a kernel of this library that triggers its dependents
+// early, so the launch may use programmatic stream serialisation.
+int launch_pa_generic(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream);
+int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream,
+                  bool after_kernel);
+int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream);
 bool pa_tma_supported(const MscoPaDesc &d);
 }  // namespace msco

@@ -90,7 +90,8 @@ __device__ __forceinline__ float load_mask_elem(const void *mask, int dtype, int
 
 template <typename T, bool KV8, int NT, bool MASK>
 __global__ void __launch_bounds__(Cfg<KV8, NT>::kThreads, 1)
-pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, PaParams p) {
+pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, PaParams p,
+              const __grid_constant__ PlanParam pp) {
   using C = Cfg<KV8, NT>;
   // fp16 arithmetic for int8 KV (integers up to 1279 are exact in fp16, not in bf16)
   using MT = typename std::conditional<KV8, __half, T>::type;
@@ -119,7 +120,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   }
   __syncthreads();
 
-  const PlanView pv = make_plan_view(p.plan);
+  const PlanView pv = make_plan_view(p.plan_in_param ? pp.w : p.plan);
   const int total = pv.total_items;
 
   if (warp == C::kWarps) {
@@ -137,6 +138,9 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       __syncwarp();
     }
     const int32_t *ibs = ib_ok ? ib : nullptr;
+    // when launched with programmatic stream serialisation right behind the cache-scatter kernel,
+    // everything above overlapped that kernel's tail; its writes must be visible from here on
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     uint32_t st = 0, ph = 0;
     const int bs = p.block_size;
     const int bpt = kTile / bs;  // cache blocks per tile (divides 32)
@@ -146,7 +150,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       const int qs = qi & 1;
       const uint32_t qph = (qi >> 1) & 1;
       if (!mbar_wait(&qempty[qs], qph ^ 1, kWaitLimit)) {
-        atomicExch(p.plan, kStatusTimeout);
+        report_status(p.status, p.epoch, kStatusTimeout);
         return;
       }
       if (lane == 0) {
@@ -169,7 +173,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         if (blk0 + lane < nblk_item) {
           my_id = __ldg(trow + blk0 + lane);
           if (my_id < 0 || my_id >= p.num_blocks) {
-            atomicExch(p.plan, kStatusOob);
+            report_status(p.status, p.epoch, kStatusOob);
             my_id = 0;  // stay inside the cache; the result of this item is undefined
           }
         }
@@ -180,7 +184,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll 1
           for (int op = 0; op < 2; ++op) {
             if (!mbar_wait(&empty[st], ph ^ 1, kWaitLimit)) {
-              atomicExch(p.plan, kStatusTimeout);
+              report_status(p.status, p.epoch, kStatusTimeout);
               return;
             }
             uint8_t *dst = smem + st * C::kStageBytes;
@@ -221,7 +225,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const int qs = qi & 1;
     const uint32_t qph = (qi >> 1) & 1;
     if (!mbar_wait(&qfull[qs], qph, kWaitLimit)) {
-      atomicExch(p.plan, kStatusTimeout);
+      report_status(p.status, p.epoch, kStatusTimeout);
       return;
     }
     const int *dsc = desc + qs * 8;
@@ -324,7 +328,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         }
       }
       if (!mbar_wait(&full[st], ph, kWaitLimit)) {
-        atomicExch(p.plan, kStatusTimeout);
+        report_status(p.status, p.epoch, kStatusTimeout);
         return;
       }
       if (active) {
@@ -411,7 +415,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
       // ---------------- O^T += V^T P^T ----------------
       if (!mbar_wait(&full[st], ph, kWaitLimit)) {
-        atomicExch(p.plan, kStatusTimeout);
+        report_status(p.status, p.epoch, kStatusTimeout);
         return;
       }
       if (active) {
@@ -589,8 +593,8 @@ int make_cache_tmap(CUtensorMap *tm, const void *cache, const MscoPaDesc &d) {
 }
 
 template <typename T, bool KV8, int NT, bool MASK>
-int launch_one(const MscoPaPlan *plan, const PaParams &p, const CUtensorMap &tk, const CUtensorMap &tv,
-               cudaStream_t stream) {
+int launch_one(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, const CUtensorMap &tk,
+               const CUtensorMap &tv, cudaStream_t stream, bool after_kernel) {
   using C = Cfg<KV8, NT>;
   static_assert(C::kDynSmem <= 232448, "shared memory budget of one SM exceeded");
   auto kfn = pa_tma_kernel<T, KV8, NT, MASK>;
@@ -601,8 +605,17 @@ int launch_one(const MscoPaPlan *plan, const PaParams &p, const CUtensorMap &tk,
   });
   if (attr_err != cudaSuccess)
     return fail(MSCO_ERR_CUDA, "paged_attention: cudaFuncSetAttribute failed: %s", cudaGetErrorString(attr_err));
-  kfn<<<dim3(plan->grid), dim3(C::kThreads), C::kDynSmem, stream>>>(tk, tv, p);
-  MSCO_CUDA_CHECK(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(plan->grid);
+  cfg.blockDim = dim3(C::kThreads);
+  cfg.dynamicSmemBytes = C::kDynSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = after_kernel ? 1 : 0;
+  MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kfn, tk, tv, p, pp));
   return MSCO_OK;
 }
 
@@ -614,7 +627,8 @@ bool pa_tma_supported(const MscoPaDesc &d) {
   return d.head_dim == kD && bs_ok && d.num_blocks * (int64_t)bs < (1ll << 31);
 }
 
-int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream) {
+int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream,
+                  bool after_kernel) {
   if (plan->total_items == 0) return MSCO_OK;
   if ((reinterpret_cast<uintptr_t>(p.q) & 15) || (reinterpret_cast<uintptr_t>(p.key_cache) & 15) ||
       (reinterpret_cast<uintptr_t>(p.value_cache) & 15) || (reinterpret_cast<uintptr_t>(p.out) & 7))
@@ -641,8 +655,8 @@ int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, cudaStream_t stream
   const bool masked = plan->desc.mask_type != 0;
 #define MSCO_GO(T, A, B)                                                   \
   do {                                                                     \
-    if (masked) return launch_one<T, A, B, true>(plan, p, tk, tv, stream); \
-    return launch_one<T, A, B, false>(plan, p, tk, tv, stream);            \
+    if (masked) return launch_one<T, A, B, true>(plan, p, pp, tk, tv, stream, after_kernel); \
+    return launch_one<T, A, B, false>(plan, p, pp, tk, tv, stream, after_kernel);            \
   } while (0)
   if (f16) {
     if (kv8) { if (g16) MSCO_GO(__half, true, 2); else MSCO_GO(__half, true, 1); }

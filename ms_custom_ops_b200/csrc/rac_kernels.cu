@@ -35,6 +35,9 @@ rac_scatter16_kernel(const uint4 *__restrict__ key, const uint4 *__restrict__ va
                      uint4 *__restrict__ key_cache, uint4 *__restrict__ value_cache,
                      const int32_t *__restrict__ slot_mapping, int64_t num_tokens, int k16, int v16,
                      int64_t num_slots, int32_t *oob_count) {
+  // a kernel launched behind this one with programmatic stream serialisation (the attention kernel
+  // of a fused decode step) may start its set-up now; it waits for this grid before reading the cache
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int64_t nwarps = (int64_t)gridDim.x * kRacWarps;
   const int total = k16 + v16;  // K chunks then V chunks, one flat index space
@@ -226,6 +229,7 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
                               const float *__restrict__ k_descale, const int32_t *__restrict__ k_offset,
                               const float *__restrict__ v_descale, const int32_t *__restrict__ v_offset,
                               int64_t num_slots, int32_t *oob_count, bool has_v) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see rac_scatter16_kernel
   const int lane = threadIdx.x & 31;
   const int64_t unit = (int64_t)blockIdx.x * kRacWarps + (threadIdx.x >> 5);
   const int64_t nunits = (int64_t)gridDim.x * kRacWarps;

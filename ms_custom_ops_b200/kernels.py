@@ -85,6 +85,16 @@ def pa_launch(plan: _abi.PaPlan, query, key_cache, value_cache, block_tables, ou
         workspace.numel() * workspace.element_size(), _stream()))
 
 
+def decode_step(plan: _abi.PaPlan, key, value, key_cache, value_cache, slot_mapping, query, block_tables, out,
+                workspace, k_descale=None, k_offset=None, v_descale=None, v_offset=None, mask=None):
+    """msco_decode_step on the current stream: cache scatter + attention in one call."""
+    _abi.check(_abi.lib().msco_decode_step(
+        plan.handle, _ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache), _ptr(slot_mapping),
+        slot_mapping.numel(), _ptr(query), _ptr(block_tables), _ptr(k_descale), _ptr(k_offset), _ptr(v_descale),
+        _ptr(v_offset), _ptr(mask), _ptr(out), _ptr(workspace), workspace.numel() * workspace.element_size(),
+        _stream()))
+
+
 def pa_status(plan: _abi.PaPlan, workspace) -> int:
     """Status word left by the kernels (synchronises); raises MscoError unless OK."""
     torch.cuda.current_stream().synchronize()
