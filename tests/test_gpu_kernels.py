@@ -314,6 +314,40 @@ def test_pa_batch_invariance_bitwise(kernel, kv8):
         assert np.array_equal(to_np(one).view(np.uint16)[0], full[i]), f"request {i} changed with the batch"
 
 
+@pytest.mark.parametrize("n,scale", [(2, 0.1), (3, 0.3), (1, 1.0)])
+def test_fused_decode_step_equals_separate_calls(n, scale):
+    # msco_decode_step (scatter + attention in one call, programmatic launch overlap) must give the
+    # same cache and the same output, bit for bit, as the two separate launches
+    spec = workloads.config_spec(n, scale)
+    c = workloads.decode_case(spec)
+    dev = {k: to_dev(c[k]) for k in ("query", "key", "value", "block_tables", "slot_mapping")}
+    kd, vd = to_dev(c["k_descale"]), to_dev(c["v_descale"])
+    lens = [int(x) for x in c["context_lens"]]
+    desc = kernels.make_pa_desc(dev["query"], to_dev(c["key_cache"]), dev["block_tables"], c["qk_scale"],
+                                1 if spec.kv_int8 else 0)
+    plan = _abi.PaPlan(desc, lens)
+    ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device="cuda")
+    results = []
+    for fused in (False, True):
+        kc, vc = to_dev(c["key_cache"]), to_dev(c["value_cache"])
+        out = torch.empty_like(dev["query"])
+        for _ in range(3):  # repeated launches reuse the workspace without clearing it
+            if fused:
+                kernels.decode_step(plan, dev["key"], dev["value"], kc, vc, dev["slot_mapping"], dev["query"],
+                                    dev["block_tables"], out, ws, kd, None, vd, None)
+            else:
+                if spec.kv_int8:
+                    kernels.rac_scatter_quant(dev["key"], dev["value"], kc, vc, dev["slot_mapping"], kd, vd)
+                else:
+                    kernels.rac_scatter(dev["key"], dev["value"], kc, vc, dev["slot_mapping"])
+                kernels.pa_launch(plan, dev["query"], kc, vc, dev["block_tables"], out, ws, kd, None, vd, None)
+        kernels.pa_status(plan, ws)
+        results.append((to_np(kc).copy(), to_np(out).copy()))
+    assert np.array_equal(results[0][0].view(np.uint8), results[1][0].view(np.uint8))
+    assert np.array_equal(results[0][1].view(np.uint16), results[1][1].view(np.uint16))
+    plan.close()
+
+
 def test_pa_out_of_range_block_id_is_reported_not_faulted():
     case = _st_case("gqa_32to8_alibi", mask_free=True)
     v = workloads.operator_view(case)
