@@ -15,6 +15,13 @@
  *                   compress_type, calc_type, scale_type, input_layout, mla_v_dim, input_format)
  *       reference: ops/c_api/paged_attention/paged_attention_op.yaml:2-88,
  *                  pybind definition ops/c_api/paged_attention/paged_attention_pynative.cc:743-777
+ *   paged_cache_load(key_cache, value_cache, block_tables, seq_lens, seq_starts, kv_cache_cfg,
+ *                    is_seq_lens_cumsum_type, has_seq_starts) -> (key_out, value_out)
+ *       reference: ops/c_api/paged_cache_load/paged_cache_load_op.yaml:2-28,
+ *                  pybind definition ops/c_api/paged_cache_load/paged_cache_load_pynative.cc:131-137
+ *   fa_update(lse, local_out, fa_update_type, sp) -> output
+ *       reference: ops/c_api/fa_update/fa_update_op.yaml:2-16,
+ *                  pybind definition ops/c_api/fa_update/fa_update_pynative.cc:88-91
  *
  * This is what a binding (pybind11, ctypes, a framework's custom-op adapter)
  * calls instead of the reference's `pyboost_*` functions.  Tensors are passed
@@ -128,6 +135,41 @@ size_t ms_custom_ops_paged_attention_last_workspace_need(void);
 /* After synchronising `stream`: MSCO_OK, MSCO_ERR_TIMEOUT or MSCO_ERR_OOB as
  * left in `workspace` by the last paged_attention launch that used it. */
 int ms_custom_ops_paged_attention_status(const void *workspace);
+
+/* paged_cache_load.  Shape / dtype inference of (key_out, value_out) after the operator's checks:
+ * both have rank 3, (sum_context_lens, num_heads, head_size_k / head_size_v), in the dtypes of the
+ * caches.  sum_context_lens is the sum of seq_lens (its last element in cumulative mode) when
+ * `seq_lens` is readable on the host (on_host != 0), else -1: a dimension only known at run time,
+ * as in the reference's infer function (paged_cache_load_graph.cc:25-44). */
+int ms_custom_ops_paged_cache_load_infer(const MsTensorDesc *key_cache, const MsTensorDesc *value_cache,
+                                         const MsTensorDesc *block_tables, const MsTensorDesc *seq_lens,
+                                         const MsTensorDesc *seq_starts, int64_t kv_cache_cfg,
+                                         int32_t is_seq_lens_cumsum_type, int32_t has_seq_starts,
+                                         int32_t *key_out_dtype, int32_t *value_out_dtype, int32_t *out_ndim,
+                                         int64_t *key_out_shape /* [MS_MAX_DIMS] */,
+                                         int64_t *value_out_shape /* [MS_MAX_DIMS] */);
+
+/* Bytes of device workspace the launch needs for this block table (0 for a malformed descriptor). */
+size_t ms_custom_ops_paged_cache_load_workspace_size(const MsTensorDesc *block_tables);
+
+/* Validate and launch on `stream`.  block_tables, seq_lens and seq_starts are device tensors (the
+ * kernels read them; nothing is copied to the host).  key_out / value_out are caller-allocated with
+ * the inferred shapes: their first dimension is the row count the caller computed from seq_lens; rows
+ * the lengths do not cover are never written past, rows no block was gathered into are zeroed.
+ * `workspace`: 4-byte aligned device memory of the size reported above, not shared with a launch in flight. */
+int ms_custom_ops_paged_cache_load(const MsTensorDesc *key_cache, const MsTensorDesc *value_cache,
+                                   const MsTensorDesc *block_tables, const MsTensorDesc *seq_lens,
+                                   const MsTensorDesc *seq_starts, int64_t kv_cache_cfg,
+                                   int32_t is_seq_lens_cumsum_type, int32_t has_seq_starts,
+                                   const MsTensorDesc *key_out, const MsTensorDesc *value_out, void *workspace,
+                                   size_t workspace_bytes, void *stream);
+
+/* fa_update.  Inference: output is Float32 (rows, head_size) for local_out (sp, rows, head_size). */
+int ms_custom_ops_fa_update_infer(const MsTensorDesc *lse, const MsTensorDesc *local_out, int64_t fa_update_type,
+                                  int64_t sp, int32_t *out_dtype, int32_t *out_ndim,
+                                  int64_t *out_shape /* [MS_MAX_DIMS] */);
+int ms_custom_ops_fa_update(const MsTensorDesc *lse, const MsTensorDesc *local_out, int64_t fa_update_type,
+                            int64_t sp, const MsTensorDesc *output, void *stream);
 
 const char *ms_custom_ops_last_error(void);
 int ms_custom_ops_last_error_kind(void);

@@ -94,6 +94,51 @@ int msco_reshape_and_cache_quant(const void *key, const void *value, int8_t *key
                                  int32_t *oob_count, void *stream);
 
 /* ------------------------------------------------------------------------
+ * paged_cache_load: gather the token rows of every sequence from the paged
+ * caches into contiguous outputs -- the inverse movement of reshape_and_cache.
+ * Replaces the device work behind npu_paged_cache_load
+ * (ops/c_api/paged_cache_load/paged_cache_load_pynative.cc:49-118), ND layout
+ * (kv_cache_cfg = 0; argument meaning ops/c_api/paged_cache_load/paged_cache_load_doc.md:8-24,
+ * arithmetic tests/st/test_custom_paged_cache_load.py:35-76):
+ *
+ *   key_cache   [num_blocks, block_size, k_row_bytes]   value_cache likewise with v_row_bytes
+ *   block_tables int32 [batch, max_blocks_per_seq]
+ *   seq_lens     int32 [batch] lengths, or [batch + 1] running sums when seq_lens_cumsum != 0
+ *   seq_starts   int32 [batch] or NULL: sequence i is read from block-table column
+ *                seq_starts[i] / block_size on (has_seq_starts of the operator)
+ *   key_out / value_out [sum_tokens, k_row_bytes / v_row_bytes]
+ *
+ * Rows are bytes: K and V may differ in element type and head size.  Blocks
+ * with a negative id contribute no rows (later rows move up) and the rows left
+ * at the end of the outputs are zeroed, as in the reference's golden.  Lengths,
+ * start columns or block ids out of range are skipped and counted in
+ * *oob_count (may be NULL); nothing is written outside the outputs.
+ * Everything is read on the device: no host copy of seq_lens is needed, and
+ * the call only enqueues two kernels on `stream`.  `workspace` (4-byte aligned,
+ * msco_paged_cache_load_workspace_bytes) holds the row offsets of every
+ * (sequence, block) pair and must not be shared with a call in flight.
+ * ---------------------------------------------------------------------- */
+size_t msco_paged_cache_load_workspace_bytes(int32_t batch, int32_t max_blocks_per_seq);
+int msco_paged_cache_load(const void *key_cache, const void *value_cache, const int32_t *block_tables,
+                          const int32_t *seq_lens, const int32_t *seq_starts, void *key_out,
+                          void *value_out, int32_t batch, int32_t max_blocks_per_seq, int32_t block_size,
+                          int32_t num_blocks, int64_t k_row_bytes, int64_t v_row_bytes, int64_t sum_tokens,
+                          int32_t seq_lens_cumsum, void *workspace, size_t workspace_bytes,
+                          int32_t *oob_count, void *stream);
+
+/* ------------------------------------------------------------------------
+ * fa_update (DECODE_UPDATE): merge `sp` partial attention outputs by their
+ * log-sum-exps.  Replaces the device work behind npu_fa_update
+ * (ops/c_api/fa_update/fa_update_pynative.cc:51-79; doc fa_update_doc.md:5-27;
+ * arithmetic tests/st/test_asd_faupdate.py:34-59):
+ *   lse [sp, rows] float32 (natural log), local_out [sp, rows, head_size] float32,
+ *   out [rows, head_size] float32 = sum_s softmax_s(lse)[s, row] * local_out[s, row, :].
+ * A row whose lse are all -inf gives zeros.  sp <= 64.
+ * ---------------------------------------------------------------------- */
+int msco_fa_update(const float *lse, const float *local_out, float *out, int64_t rows, int32_t head_size,
+                   int32_t sp, void *stream);
+
+/* ------------------------------------------------------------------------
  * paged_attention (decode: one query token per sequence).
  *
  * The descriptor carries what the reference puts into

@@ -1,6 +1,7 @@
-"""B200-native paged-KV decode operators: ``reshape_and_cache`` and ``paged_attention``.
+"""B200-native paged-KV decode operators: ``reshape_and_cache`` and ``paged_attention``, with the
+two operators either side of them, ``paged_cache_load`` and ``fa_update``.
 
-Drop-in for the two operators of the same names in ``ms_custom_ops``
+Drop-in for the operators of the same names in ``ms_custom_ops``
 (python/ms_custom_ops/__init__.py:76 re-exports them from the plugin module;
 pybind definitions at ops/c_api/reshape_and_cache/reshape_and_cache.cc:212-217
 and ops/c_api/paged_attention/paged_attention_pynative.cc:763-777): the same
@@ -26,6 +27,7 @@ from ._abi import MscoError  # noqa: F401
 from ._host import UnsupportedOnB200, plan_cache_clear, plan_cache_stats, registered_ops  # noqa: F401
 
 __all__ = ["reshape_and_cache", "reshape_and_cache_quant", "paged_attention", "paged_attention_infer",
+           "paged_cache_load", "paged_cache_load_infer", "fa_update", "fa_update_infer",
            "paged_attention_workspace_size", "paged_attention_check_status", "TensorSpec", "MscoError",
            "UnsupportedOnB200", "registered_ops", "plan_cache_stats", "plan_cache_clear"]
 
@@ -258,6 +260,108 @@ def _kw_to_positional(kw):
     if unknown:
         raise TypeError(f"paged_attention got unexpected arguments {sorted(unknown)}")
     return [kw.get(n) for n in _PA_OPTIONAL] + [kw.get(n, d) for n, d in _PA_ATTRS]
+
+
+# --------------------------------------------------------------------------
+# paged_cache_load
+# --------------------------------------------------------------------------
+_load_workspaces = {}  # (device index, stream handle) -> grow-only uint8 buffer (row offsets of the gather)
+
+
+def _host_int32(t):
+    """Host copy of an int32 vector given as a torch tensor (either side), numpy array or list."""
+    if isinstance(t, (list, tuple, np.ndarray)):
+        return np.ascontiguousarray(np.asarray(t))
+    return t.detach().cpu().numpy()  # a device tensor: synchronises, as the reference does
+
+
+def paged_cache_load_infer(key_cache, value_cache, block_tables, seq_lens, seq_starts=None, kv_cache_cfg=0,
+                           is_seq_lens_cumsum_type=False, has_seq_starts=False):
+    """Shapes and dtypes of (key_out, value_out) after the operator's checks, without touching a GPU.
+
+    Accepts TensorSpec or real tensors.  The row count is -1 when `seq_lens` carries no host values.
+    """
+    D = _Descs()
+    kd, vd, nd = C.c_int32(), C.c_int32(), C.c_int32()
+    ks, vs = (C.c_int64 * _host.MS_MAX_DIMS)(), (C.c_int64 * _host.MS_MAX_DIMS)()
+    _host.check(_host.lib().ms_custom_ops_paged_cache_load_infer(
+        D(key_cache), D(value_cache), D(block_tables), D(seq_lens, host_ok=True), D(seq_starts, host_ok=True),
+        int(kv_cache_cfg), int(bool(is_seq_lens_cumsum_type)), int(bool(has_seq_starts)), C.byref(kd), C.byref(vd),
+        C.byref(nd), ks, vs))
+    return ((tuple(ks[i] for i in range(nd.value)), _DT_NAMES[kd.value]),
+            (tuple(vs[i] for i in range(nd.value)), _DT_NAMES[vd.value]))
+
+
+def paged_cache_load(key_cache, value_cache, block_tables, seq_lens, seq_starts=None, kv_cache_cfg=0,
+                     is_seq_lens_cumsum_type=False, has_seq_starts=False):
+    """Gather the token rows of every sequence from the paged caches; returns ``(key_out, value_out)``.
+
+    key_cache / value_cache  [num_blocks, block_size, num_heads, head_size_k / head_size_v];
+                 fp16 / bf16 / int8, the two may differ
+    block_tables int32 [batch, block_indices]
+    seq_lens     int32 [batch] lengths, or [batch + 1] running sums with is_seq_lens_cumsum_type
+    seq_starts   int32 [batch] (has_seq_starts): sequence i is read from block-table column
+                 seq_starts[i] // block_size on
+    key_out / value_out  [sum of lengths, num_heads, head_size], cache dtypes
+    The row count is the sum of `seq_lens`, which is therefore read on the host as in the reference:
+    pass `seq_lens` as a CPU tensor / numpy array to avoid the device synchronisation.
+    """
+    import torch
+    lens_host = _host_int32(seq_lens)
+    (kshape, _), (vshape, _) = paged_cache_load_infer(
+        key_cache, value_cache, block_tables, lens_host, seq_starts, kv_cache_cfg, is_seq_lens_cumsum_type,
+        has_seq_starts)
+    dev = key_cache.device
+
+    def on_device(t):
+        if t is None or (hasattr(t, "is_cuda") and t.is_cuda):
+            return t
+        return torch.as_tensor(np.asarray(t) if not hasattr(t, "is_cuda") else t).to(dev, non_blocking=True)
+    block_tables, seq_lens, seq_starts = on_device(block_tables), on_device(seq_lens), on_device(seq_starts)
+    key_out = torch.empty(kshape, dtype=key_cache.dtype, device=dev)
+    value_out = torch.empty(vshape, dtype=value_cache.dtype, device=dev)
+    D = _Descs()
+    L = _host.lib()
+    need = L.ms_custom_ops_paged_cache_load_workspace_size(D(block_tables))
+    wkey = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    ws = _load_workspaces.get(wkey)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(int(need * 1.25), 1 << 16), dtype=torch.uint8, device=dev)
+        _load_workspaces[wkey] = ws
+    _host.check(L.ms_custom_ops_paged_cache_load(
+        D(key_cache), D(value_cache), D(block_tables), D(seq_lens), D(seq_starts), int(kv_cache_cfg),
+        int(bool(is_seq_lens_cumsum_type)), int(bool(has_seq_starts)), D(key_out), D(value_out),
+        C.c_void_p(ws.data_ptr()), ws.numel(), _stream()))
+    return key_out, value_out
+
+
+# --------------------------------------------------------------------------
+# fa_update
+# --------------------------------------------------------------------------
+def fa_update_infer(lse, local_out, fa_update_type=0, sp=1):
+    """Shape / dtype of the merged output after the operator's checks; TensorSpec or real tensors."""
+    D = _Descs()
+    dt, nd = C.c_int32(), C.c_int32()
+    shp = (C.c_int64 * _host.MS_MAX_DIMS)()
+    _host.check(_host.lib().ms_custom_ops_fa_update_infer(D(lse), D(local_out), int(fa_update_type), int(sp),
+                                                          C.byref(dt), C.byref(nd), shp))
+    return tuple(shp[i] for i in range(nd.value)), _DT_NAMES[dt.value]
+
+
+def fa_update(lse, local_out, fa_update_type=0, sp=1):
+    """Merge `sp` partial attention outputs by their log-sum-exps (DECODE_UPDATE).
+
+    lse        float32 [sp, rows]  (rows = batch * seq_len * head_num), natural logarithm
+    local_out  float32 [sp, rows, head_size], head_size a multiple of 8 in [8, 512]
+    returns    float32 [rows, head_size] = sum_s softmax_s(lse)[s, row] * local_out[s, row, :]
+    """
+    import torch
+    shape, _ = fa_update_infer(lse, local_out, fa_update_type, sp)
+    out = torch.empty(shape, dtype=torch.float32, device=local_out.device)
+    D = _Descs()
+    _host.check(_host.lib().ms_custom_ops_fa_update(D(lse), D(local_out), int(fa_update_type), int(sp), D(out),
+                                                    _stream()))
+    return out
 
 
 def paged_attention_check_status(device=None):

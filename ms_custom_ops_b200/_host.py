@@ -40,6 +40,8 @@ EXPORTS = (
     "ms_custom_ops_paged_attention_status", "ms_custom_ops_last_error",
     "ms_custom_ops_last_error_kind", "ms_custom_ops_num_ops", "ms_custom_ops_op_name",
     "ms_custom_ops_op_signature", "ms_custom_ops_plan_cache_stats", "ms_custom_ops_plan_cache_clear",
+    "ms_custom_ops_paged_cache_load_infer", "ms_custom_ops_paged_cache_load_workspace_size",
+    "ms_custom_ops_paged_cache_load", "ms_custom_ops_fa_update_infer", "ms_custom_ops_fa_update",
 )
 
 
@@ -73,6 +75,18 @@ def lib():
     L.ms_custom_ops_paged_attention_last_workspace_need.restype = C.c_size_t
     L.ms_custom_ops_paged_attention_status.restype = C.c_int
     L.ms_custom_ops_paged_attention_status.argtypes = [vp]
+    i32p, i64p = C.POINTER(C.c_int32), C.POINTER(i64)
+    L.ms_custom_ops_paged_cache_load_infer.restype = C.c_int
+    L.ms_custom_ops_paged_cache_load_infer.argtypes = [_TP] * 5 + [i64, C.c_int32, C.c_int32, i32p, i32p, i32p,
+                                                       i64p, i64p]
+    L.ms_custom_ops_paged_cache_load_workspace_size.restype = C.c_size_t
+    L.ms_custom_ops_paged_cache_load_workspace_size.argtypes = [_TP]
+    L.ms_custom_ops_paged_cache_load.restype = C.c_int
+    L.ms_custom_ops_paged_cache_load.argtypes = [_TP] * 5 + [i64, C.c_int32, C.c_int32, _TP, _TP, vp, C.c_size_t, vp]
+    L.ms_custom_ops_fa_update_infer.restype = C.c_int
+    L.ms_custom_ops_fa_update_infer.argtypes = [_TP, _TP, i64, i64, i32p, i32p, i64p]
+    L.ms_custom_ops_fa_update.restype = C.c_int
+    L.ms_custom_ops_fa_update.argtypes = [_TP, _TP, i64, i64, _TP, vp]
     L.ms_custom_ops_last_error.restype = C.c_char_p
     L.ms_custom_ops_last_error_kind.restype = C.c_int
     L.ms_custom_ops_num_ops.restype = C.c_int

@@ -53,6 +53,29 @@ def rac_scatter_quant(key, value, key_cache, value_cache, slot_mapping, k_descal
         _ptr(oob_count), _stream()))
 
 
+def cache_load_workspace_bytes(batch: int, max_blocks_per_seq: int) -> int:
+    return int(_abi.lib().msco_paged_cache_load_workspace_bytes(int(batch), int(max_blocks_per_seq)))
+
+
+def cache_load(key_cache, value_cache, block_tables, seq_lens, seq_starts, key_out, value_out, workspace,
+               seq_lens_cumsum=False, oob_count=None):
+    """msco_paged_cache_load on the current stream (gather the rows of every sequence)."""
+    nb, bs = key_cache.shape[0], key_cache.shape[1]
+    krow = key_cache[0, 0].numel() * key_cache.element_size()
+    vrow = value_cache[0, 0].numel() * value_cache.element_size()
+    _abi.check(_abi.lib().msco_paged_cache_load(
+        _ptr(key_cache), _ptr(value_cache), _ptr(block_tables), _ptr(seq_lens), _ptr(seq_starts), _ptr(key_out),
+        _ptr(value_out), block_tables.shape[0], block_tables.shape[1], bs, nb, krow, vrow, key_out.shape[0],
+        int(bool(seq_lens_cumsum)), _ptr(workspace), workspace.numel() * workspace.element_size(), _ptr(oob_count),
+        _stream()))
+
+
+def merge_partials(lse, local_out, out):
+    """msco_fa_update on the current stream: out[r] = sum_s softmax_s(lse)[s, r] * local_out[s, r]."""
+    sp, rows, hd = local_out.shape
+    _abi.check(_abi.lib().msco_fa_update(_ptr(lse), _ptr(local_out), _ptr(out), rows, hd, sp, _stream()))
+
+
 def make_pa_desc(query, key_cache, block_tables, qk_scale, quant_type=0, has_quant_offset=False,
                  mask=None, mask_type=0, kernel=_abi.KERNEL_AUTO) -> _abi.MscoPaDesc:
     d = _abi.MscoPaDesc()

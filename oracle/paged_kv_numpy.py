@@ -10,7 +10,8 @@ order where order matters (de-quantise -> gather -> grouped QK^T -> scale ->
 
 Parity status: `paged_attention_golden` and `reshape_and_cache_golden` are
 pinned by tests/golden (outputs of the reference's own golden functions on the
-same seeded inputs).  `reshape_and_cache_quant_golden` is "parity unpinned":
+same seeded inputs), and so are `paged_cache_load_golden` and
+`fa_update_golden`.  `reshape_and_cache_quant_golden` is "parity unpinned":
 the reference's reshape_and_cache has no quantising mode.
 """
 from __future__ import annotations
@@ -161,6 +162,47 @@ def paged_attention_golden(query, key_cache, value_cache, block_tables, context_
         o = np.matmul(p, np.transpose(vs, (1, 0, 2)))  # [hkv, g, dv]
         out[b] = o.reshape(hq, -1)
     return out
+
+
+def paged_cache_load_golden(key_cache, value_cache, block_tables, seq_lens, seq_starts=None,
+                            seq_lens_cumsum=False):
+    """Gather the token rows of every sequence from the paged caches (ND layout).
+
+    Follows tests/st/test_custom_paged_cache_load.py:35-76 (``golden_calc_nd``):
+      * sequence ``i`` has ``seq_lens[i]`` tokens, or ``seq_lens[i+1] - seq_lens[i]``
+        when `seq_lens` holds running sums (``seq_lens_cumsum``),
+      * its token ``j`` lies in block ``block_tables[i][seq_starts[i] // bs + j // bs]``
+        at offset ``j % bs`` (`seq_starts` absent: column ``j // bs``),
+      * a negative block id contributes no row and does not advance the output
+        row; the rows left over at the end stay zero.
+    The reference's golden ties the cumulative lengths to the presence of
+    `seq_starts`; the operator has one flag for each, so both are arguments.
+    Caches ``[num_blocks, bs, heads, head_size]``; returns
+    ``(key_out [sum, heads, dk], value_out [sum, heads, dv])`` in the cache dtypes.
+    """
+    kc, vc = np.asarray(key_cache), np.asarray(value_cache)
+    tables = np.asarray(block_tables)
+    lens = np.asarray(seq_lens).astype(np.int64).reshape(-1)
+    bs = kc.shape[1]
+    if seq_lens_cumsum:
+        total, lens = int(lens[-1]), np.diff(lens)
+    else:
+        total = int(lens.sum())
+    k_out = np.zeros((total,) + kc.shape[2:], dtype=kc.dtype)
+    v_out = np.zeros((total,) + vc.shape[2:], dtype=vc.dtype)
+    row = 0
+    for i, n in enumerate(lens):
+        n = int(n)
+        col0 = 0 if seq_starts is None else int(np.asarray(seq_starts)[i]) // bs
+        for j in range(0, n, bs):
+            bid = int(tables[i][col0 + j // bs])
+            if bid < 0:
+                continue
+            m = min(bs, n - j)
+            k_out[row:row + m] = kc[bid, :m]
+            v_out[row:row + m] = vc[bid, :m]
+            row += m
+    return k_out, v_out
 
 
 def fa_update_golden(lse, partial_out):

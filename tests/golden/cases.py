@@ -86,6 +86,58 @@ def rac_case(name):
             "slot_mapping": rng.permutation(t).astype(np.int32)}
 
 
+# paged_cache_load cases: (key dtype, value dtype, cumulative lengths + seq_starts, seed,
+#   (num_blocks, block_size, heads, head_size_k, head_size_v, batch, max_len)).
+# "ref" geometry = tests/st/test_custom_paged_cache_load.py:250 ([128, 128, 16, 144, 128, 16, 1], lengths 1..1024)
+_PCL_REF = (128, 128, 16, 144, 128, 16, 1024)
+PCL_CASES = {
+    "fp16_fp16_lens": ("float16", "float16", False, 201, _PCL_REF),
+    "bf16_int8_cumsum_starts": ("bfloat16", "int8", True, 202, _PCL_REF),
+    "int8_fp16_cumsum_starts": ("int8", "float16", True, 203, (32, 16, 4, 24, 40, 9, 150)),
+    "fp16_rows_2byte": ("float16", "float16", False, 204, (24, 8, 3, 5, 7, 7, 60)),
+    "fp16_int8_rows_1byte": ("float16", "int8", True, 205, (24, 8, 3, 5, 7, 7, 60)),
+    "bf16_bf16_block16": ("bfloat16", "bfloat16", False, 206, (256, 16, 8, 128, 128, 12, 300)),
+}
+
+# fa_update cases: (sp, rows, head_size, seed); shapes of tests/st/test_asd_faupdate.py:80-123 scaled in rows
+FA_CASES = {
+    "base_sp1": (1, 11 * 13, 8, 301),
+    "sp3_head128": (3, 260, 128, 302),
+    "sp8_head64": (8, 77, 64, 303),
+    "sp2_head512": (2, 19, 512, 304),
+}
+
+
+def pcl_case(name):
+    """Seeded inputs laid out like the reference test's generate_data_nd (:104-166): caches of small
+    integers, random block tables with 4 spare columns, seq_starts a multiple of block_size."""
+    import ml_dtypes
+    kd, vd, cumsum, seed, (nb, bs, heads, dk, dv, batch, max_len) = PCL_CASES[name]
+    rng = np.random.default_rng(seed)
+    npdt = {"float16": np.float16, "bfloat16": ml_dtypes.bfloat16, "int8": np.int8}
+    kc = rng.integers(1, 11, (nb, bs, heads, dk)).astype(npdt[kd])
+    vc = rng.integers(1, 11, (nb, bs, heads, dv)).astype(npdt[vd])
+    lens = rng.integers(1, max_len + 1, batch)
+    cols = (int(lens.max()) + bs - 1) // bs + 4
+    tables = rng.integers(0, nb, (batch, cols)).astype(np.int32)
+    out = {"key_cache": kc, "value_cache": vc, "block_tables": tables, "cumsum": cumsum}
+    if cumsum:
+        out["seq_lens"] = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        out["seq_starts"] = (rng.integers(0, 5, batch) * bs).astype(np.int32)
+    else:
+        out["seq_lens"] = lens.astype(np.int32)
+        out["seq_starts"] = None
+    return out
+
+
+def fa_case(name):
+    """lse and partial outputs uniform in [0, 1) as in tests/st/test_asd_faupdate.py:67-70."""
+    sp, rows, hd, seed = FA_CASES[name]
+    rng = np.random.default_rng(seed)
+    return {"lse": rng.random((sp, rows), dtype=np.float32), "local_out": rng.random((sp, rows, hd), dtype=np.float32),
+            "sp": sp}
+
+
 def digest(a) -> str:
     a = np.ascontiguousarray(a)
     return hashlib.sha256(a.view(np.uint8).tobytes()).hexdigest()

@@ -10,7 +10,8 @@ repository's seeded generators; the expected outputs come from the
 reference's `PagedAttentionDataGenerator.compute_golden_reference`
 (tests/st/test_custom_paged_attention.py:528-699) and
 `InferenceEngine.nd_inference` (tests/st/test_custom_reshape_and_cache.py:282-307),
-imported unchanged through a stub of the `mindspore` module.  For the
+`golden_calc_nd` (tests/st/test_custom_paged_cache_load.py:35-76) and `golden_calc`
+(tests/st/test_asd_faupdate.py:34-59), imported unchanged through a stub of the `mindspore` module.  For the
 reference-style attention cases the script also checks that our generator
 reproduces the reference generator's inputs bit for bit.
 
@@ -18,6 +19,8 @@ Written files (tests/golden/):
   pa_<case>.npz       golden output + sha256 of every input
   rac_<case>.npz      sha256 of the golden caches (and of the inputs)
   config1.npz         benchmark configuration 1: cache digests after the scatter + attention output
+  pcl_<case>.npz      sha256 of the gathered K / V (and of the input caches)
+  fa_<case>.npz       golden output of the partial-output merge
 """
 import math
 import os
@@ -71,6 +74,43 @@ def main(ref_root):
                             sha_in_key=np.array(cases.digest(c["key"])),
                             sha_in_key_cache=np.array(cases.digest(c["key_cache"])))
         print("rac", name)
+
+    import test_custom_paged_cache_load as tpcl
+    import test_asd_faupdate as tfa
+    from oracle import paged_kv_numpy as restated
+    for name, (kd, vd, cumsum, _seed, geo) in cases.PCL_CASES.items():
+        c = cases.pcl_case(name)
+        nb, bs, heads, dk, dv, batch, _ = geo
+        total = int(c["seq_lens"][-1]) if cumsum else int(c["seq_lens"].sum())
+        # float16 stands in for the reference's dtype tag where it only picks the dtype of the
+        # expected array: the rows are copied unchanged, and are compared in the cache dtype
+        gk, gv = tpcl.golden_calc_nd(batch, heads, dk, dv, bs, c["block_tables"], c["seq_lens"], c["seq_starts"],
+                                     c["key_cache"], c["value_cache"], msd[kd], msd[vd], total)
+        gk, gv = gk.astype(c["key_cache"].dtype), gv.astype(c["value_cache"].dtype)
+        ok, ov = restated.paged_cache_load_golden(c["key_cache"], c["value_cache"], c["block_tables"], c["seq_lens"],
+                                                  c["seq_starts"], cumsum)
+        assert cases.digest(ok) == cases.digest(gk) and cases.digest(ov) == cases.digest(gv), name
+        np.savez_compressed(os.path.join(HERE, f"pcl_{name}.npz"), sha_key_out=np.array(cases.digest(gk)),
+                            sha_value_out=np.array(cases.digest(gv)), rows=np.array(total),
+                            sha_in_key_cache=np.array(cases.digest(c["key_cache"])),
+                            sha_in_block_tables=np.array(cases.digest(c["block_tables"])))
+        print("pcl", name, gk.shape, gv.shape)
+
+    for name in cases.FA_CASES:
+        c = cases.fa_case(name)
+        g = np.asarray(tfa.golden_calc(c["lse"], c["local_out"]), dtype=np.float32)
+        g = g.reshape(c["local_out"].shape[1], c["local_out"].shape[2])
+        np.savez_compressed(os.path.join(HERE, f"fa_{name}.npz"), golden=g,
+                            sha_lse=np.array(cases.digest(c["lse"])))
+        print("fa", name, g.shape)
+    # the reference's full-size fa_update shapes (tests/st/test_asd_faupdate.py:95-123): restatement == golden
+    for sp, rows, hd in ((3, 1000 * 13, 128), (3, 2 * 4000 * 32, 128)):
+        rng = np.random.default_rng(sp * rows)
+        lse = rng.random((sp, rows), dtype=np.float32)
+        lo = rng.random((sp, rows, hd), dtype=np.float32)
+        g = np.asarray(tfa.golden_calc(lse, lo)).reshape(rows, hd)
+        assert np.allclose(restated.fa_update_golden(lse, lo), g, rtol=1e-5, atol=1e-6), (sp, rows, hd)
+        print("fa full size", sp, rows, hd, "restatement agrees")
 
     # benchmark configuration 1, exactly: scatter of the newest token, then attention
     spec = workloads.config_spec(1)

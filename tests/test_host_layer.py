@@ -34,15 +34,18 @@ def test_library_exports_every_declared_symbol(header, loader, listed):
 
 def test_registered_signatures_match_the_yaml_definitions():
     reg = ops.registered_ops()
-    for op, sub in (("reshape_and_cache", "reshape_and_cache"), ("paged_attention", "paged_attention")):
+    for op, sub in (("reshape_and_cache", "reshape_and_cache"), ("paged_attention", "paged_attention"),
+                    ("paged_cache_load", "paged_cache_load"), ("fa_update", "fa_update")):
         y = yaml.safe_load(open(os.path.join(ROOT, "ms_custom_ops_b200", "ops", "c_api", sub, op + "_op.yaml")))
         parts = []
         for name, spec in y[op]["args"].items():
-            parts.append(name if "default" not in spec else f"{name}={spec['default']}")
+            default = spec.get("default")
+            default = {"false": False, "true": True}.get(default, default) if isinstance(default, str) else default
+            parts.append(name if "default" not in spec else f"{name}={default}")
         assert reg[op] == f"{op}({', '.join(parts)})"
     # and the Python functions expose the same names, order and defaults
     import inspect
-    for op in ("reshape_and_cache", "paged_attention"):
+    for op in ("reshape_and_cache", "paged_attention", "paged_cache_load", "fa_update"):
         sig = inspect.signature(getattr(ops, op))
         got = ", ".join(n if p.default is inspect._empty else f"{n}={p.default}" for n, p in sig.parameters.items())
         assert reg[op] == f"{op}({got})"
@@ -131,6 +134,64 @@ def test_shape_and_type_rules():
         ops.paged_attention_infer(Q, KC, KC, BT, T((4,), "int32", on_host=False), **OKW)
     with pytest.raises(ops.MscoError, match="must be Int32"):
         ops.paged_attention_infer(Q, KC, KC, BT, np.array([1, 2, 3, 4], dtype=np.int64), **OKW)
+
+
+def test_paged_cache_load_infer_and_validation_without_a_gpu():
+    kc, vc, bt = T((128, 128, 16, 144), "bfloat16"), T((128, 128, 16, 128), "int8"), T((16, 12), "int32")
+    lens = np.arange(1, 17, dtype=np.int32)
+    # row count = sum of the lengths, or the last running sum; -1 when the lengths are not on the host
+    assert ops.paged_cache_load_infer(kc, vc, bt, lens) == (((136, 16, 144), "bfloat16"), ((136, 16, 128), "int8"))
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    starts = T((16,), "int32")
+    assert ops.paged_cache_load_infer(kc, vc, bt, cu, starts, 0, True, True)[0] == ((136, 16, 144), "bfloat16")
+    assert ops.paged_cache_load_infer(kc, vc, bt, T((16,), "int32"))[0][0][0] == -1
+    with pytest.raises(ops.MscoError, match="seq_lens dtype must be int32"):
+        ops.paged_cache_load_infer(kc, vc, bt, lens.astype(np.int64))
+    with pytest.raises(ops.UnsupportedOnB200, match="FRACTAL_NZ"):
+        ops.paged_cache_load_infer(kc, vc, bt, lens, None, 1)
+    with pytest.raises(ValueError, match="kv_cache_cfg must be 0"):
+        ops.paged_cache_load_infer(kc, vc, bt, lens, None, 5)
+    with pytest.raises(ValueError, match="exactly when has_seq_starts"):
+        ops.paged_cache_load_infer(kc, vc, bt, lens, starts, 0, False, False)
+    with pytest.raises(ValueError, match="17 elements"):
+        ops.paged_cache_load_infer(kc, vc, bt, lens, None, 0, True, False)
+    with pytest.raises(ValueError, match="batch = 16"):
+        ops.paged_cache_load_infer(kc, vc, bt, lens, T((15,), "int32"), 0, False, True)
+    with pytest.raises(ValueError, match="rank 4"):
+        ops.paged_cache_load_infer(T((128, 128, 2304), "bfloat16"), vc, bt, lens)
+    with pytest.raises(ValueError, match="agree in num_blocks"):
+        ops.paged_cache_load_infer(kc, T((128, 64, 16, 128), "int8"), bt, lens)
+    with pytest.raises(TypeError, match="Float16/BFloat16/Int8"):
+        ops.paged_cache_load_infer(T((128, 128, 16, 144), "float32"), vc, bt, lens)
+    with pytest.raises(TypeError, match="block_tables must be Int32"):
+        ops.paged_cache_load_infer(kc, vc, T((16, 12), "int64"), lens)
+    # the workspace holds one row offset per (sequence, block) pair plus one per sequence
+    L, D = _host.lib(), ops._Descs()
+    assert L.ms_custom_ops_paged_cache_load_workspace_size(D(bt)) == (16 + 16 + 16 * 12) * 4
+    assert _abi.lib().msco_paged_cache_load_workspace_bytes(16, 12) == (16 + 16 + 16 * 12) * 4
+    # zero-sized inputs are a successful no-op (no CUDA call is made)
+    assert L.ms_custom_ops_paged_cache_load(D(kc), D(vc), D(T((0, 12), "int32")), D(T((0,), "int32")), None, 0, 0, 0,
+                                            D(T((0, 16, 144), "bfloat16")), D(T((0, 16, 128), "int8")), None, 0,
+                                            None) == 0
+
+
+def test_fa_update_infer_and_validation_without_a_gpu():
+    assert ops.fa_update_infer(T((3, 13000), "float32"), T((3, 13000, 128), "float32"), 0, 3) == ((13000, 128), "float32")
+    with pytest.raises(ValueError, match="local_out dim must be 3, but got : 2"):
+        ops.fa_update_infer(T((3, 10), "float32"), T((3, 80), "float32"), 0, 3)
+    for hd in (4, 12, 520):
+        with pytest.raises(ValueError, match="head_size must be in range \\[8, 512\\] and be the multiple of 8"):
+            ops.fa_update_infer(T((3, 10), "float32"), T((3, 10, hd), "float32"), 0, 3)
+    with pytest.raises(ValueError, match="fa_update_type must be 0"):
+        ops.fa_update_infer(T((3, 10), "float32"), T((3, 10, 8), "float32"), 2, 3)
+    with pytest.raises(ValueError, match="sp must be in range"):
+        ops.fa_update_infer(T((9, 10), "float32"), T((9, 10, 8), "float32"), 0, 9)
+    with pytest.raises(ValueError, match="3 partitions but sp is 2"):
+        ops.fa_update_infer(T((3, 10), "float32"), T((3, 10, 8), "float32"), 0, 2)
+    with pytest.raises(ValueError, match="lse must be"):
+        ops.fa_update_infer(T((3, 11), "float32"), T((3, 10, 8), "float32"), 0, 3)
+    with pytest.raises(TypeError, match="must be Float32"):
+        ops.fa_update_infer(T((3, 10), "float16"), T((3, 10, 8), "float32"), 0, 3)
 
 
 def test_reshape_and_cache_validation_without_a_gpu():

@@ -83,6 +83,32 @@ def test_config1_fixture_reproduced_by_both_oracles():
         assert np.all(np.abs(out - g) <= 1e-3 * np.maximum(np.abs(g), 1.0))
 
 
+@pytest.mark.parametrize("name", sorted(cases.PCL_CASES))
+def test_cache_load_oracle_matches_reference_golden(name):
+    # stored digests of the reference's golden_calc_nd outputs on the same seeded inputs
+    c, fx = cases.pcl_case(name), _fx("pcl_" + name)
+    assert cases.digest(c["key_cache"]) == str(fx["sha_in_key_cache"])
+    k, v = oracle.paged_cache_load_golden(c["key_cache"], c["value_cache"], c["block_tables"], c["seq_lens"],
+                                          c["seq_starts"], c["cumsum"])
+    assert k.shape[0] == int(fx["rows"])
+    assert cases.digest(k) == str(fx["sha_key_out"]) and cases.digest(v) == str(fx["sha_value_out"])
+
+
+def test_cache_load_oracle_skips_negative_blocks():
+    kc = np.arange(4 * 2 * 1 * 2, dtype=np.int8).reshape(4, 2, 1, 2) + 1
+    tables = np.array([[1, -1, 3], [0, 2, -1]], np.int32)
+    k, v = oracle.paged_cache_load_golden(kc, kc, tables, np.array([5, 3], np.int32))
+    want = np.concatenate([kc[1], kc[3][:1], kc[0], kc[2][:1]])
+    assert np.array_equal(k[:6], want) and not k[6:].any() and k.shape[0] == 8 and np.array_equal(k, v)
+
+
+@pytest.mark.parametrize("name", sorted(cases.FA_CASES))
+def test_fa_update_oracle_matches_reference_golden(name):
+    c, fx = cases.fa_case(name), _fx("fa_" + name)
+    assert cases.digest(c["lse"]) == str(fx["sha_lse"])
+    np.testing.assert_allclose(oracle.fa_update_golden(c["lse"], c["local_out"]), fx["golden"], rtol=1e-6, atol=1e-7)
+
+
 def test_negative_slots_are_skipped_and_later_rows_win():
     rng = np.random.default_rng(0)
     kc = rng.integers(-100, 100, (4, 8, 2, 4)).astype(np.int8)
