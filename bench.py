@@ -426,6 +426,7 @@ def run_gpu(args):
                    "within_tolerance": bool(np.all(err <= tol + tol * np.abs(ref))), "tolerance": tol}
 
     scatter = measure_scatter(spec, dev, peak) if (world == 1 and "rac_tokens" in spec.extra) else None
+    adjacent = measure_adjacent(case, spec, dev, peak, not args.no_cpu) if (world == 1 and args.adjacent) else None
     kernels_per_step = 2 + (1 if info.partials > 0 or min(lens) == 0 else 0)  # scatter, attention, reduce
     kernels_per_step += 1 if peer is not None else 0                          # peer all-gather
     line = {
@@ -443,7 +444,7 @@ def run_gpu(args):
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
         "gpu_launches": kernels_per_step * args.steps,
         "roofline": roofline, "cpu_baseline": cpu, "parity_check": checked, "gather_check": gather_check, "clocks": clocks,
-        "reshape_and_cache_prefill": scatter,
+        "reshape_and_cache_prefill": scatter, "adjacent_ops": adjacent,
         "achieved_gbs_step": alg_bytes / ms_step / 1e6,
     }
     print(json.dumps(line), flush=True)
@@ -516,6 +517,85 @@ def measure_scatter(spec, dev, peak):
     return out
 
 
+def measure_adjacent(case, spec, dev, peak, with_cpu):
+    """The two operators either side of the decode path, on the same workload, one GPU:
+    paged_cache_load gathers every sequence of the batch out of the paged caches (reads and writes the
+    whole KV working set, far larger than L2), fa_update merges 3 partial outputs of 256000 rows x 128
+    (the reference test's largest shape; 524 MB per launch).  CUDA events around `reps` eager launches."""
+    import torch
+    from ms_custom_ops_b200 import kernels
+    out = {}
+    kc, vc, bt = case["key_cache"], case["value_cache"], case["block_tables"]
+    lens = np.asarray([int(x) for x in case["context_lens"]], dtype=np.int32)
+    total = int(lens.sum())
+    krow = kc[0, 0].numel() * kc.element_size()
+    vrow = vc[0, 0].numel() * vc.element_size()
+    lens_dev = torch.from_numpy(lens).to(dev)
+    ko = torch.empty((total,) + tuple(kc.shape[2:]), dtype=kc.dtype, device=dev)
+    vo = torch.empty((total,) + tuple(vc.shape[2:]), dtype=vc.dtype, device=dev)
+    ws = torch.empty(kernels.cache_load_workspace_bytes(bt.shape[0], bt.shape[1]), dtype=torch.uint8, device=dev)
+    oob = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+    ms = timed(lambda: kernels.cache_load(kc, vc, bt, lens_dev, None, ko, vo, ws, False, oob), 10)
+    nbytes = 2 * total * (krow + vrow)
+    out["paged_cache_load"] = {
+        "tokens": total, "ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / ms / 1e6,
+        "frac": nbytes / ms / 1e6 / peak, "frac_of_8tbs": nbytes / ms / 1e6 / 8000.0, "tokens_per_s": total / ms * 1e3,
+        "kernels_per_call": 2, "out_of_range_ids": int(oob.item()),
+        "l2": f"{nbytes / 2e6:.0f} MB read and as much written per launch vs {L2_BYTES >> 20} MB of L2"}
+    if with_cpu:
+        from oracle import paged_kv_numpy as oracle_np
+        hk, hv, hbt = _to_np(kc), _to_np(vc), bt.cpu().numpy()
+        oracle_np.paged_cache_load_golden(hk[:2], hv[:2], np.zeros((1, 1), np.int32), np.array([1], np.int32))
+        t0 = time.perf_counter()
+        gk, gv = oracle_np.paged_cache_load_golden(hk, hv, hbt, lens)
+        dt = time.perf_counter() - t0
+        out["paged_cache_load"]["cpu_baseline"] = {
+            "value": total / dt, "unit": "tokens/s", "cores": 1, "kind": "port",
+            "sample": "the whole batch, numpy restatement of the reference golden (block-wise copies)"}
+        out["paged_cache_load"]["bit_exact"] = bool(np.array_equal(_to_np(ko).view(np.uint8), gk.view(np.uint8)) and
+                                                    np.array_equal(_to_np(vo).view(np.uint8), gv.view(np.uint8)))
+        del hk, hv, gk, gv
+    del ko, vo
+    torch.cuda.empty_cache()
+
+    sp, rows, hd = 3, 2 * 4000 * 32, 128
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(spec.seed)
+    lse = torch.rand((sp, rows), generator=gen, device=dev) * 8 - 4
+    lo = torch.rand((sp, rows, hd), generator=gen, device=dev)
+    merged = torch.empty((rows, hd), dtype=torch.float32, device=dev)
+    ms = timed(lambda: kernels.merge_partials(lse, lo, merged), 20)
+    nbytes = (sp * rows * (hd + 1) + rows * hd) * 4
+    out["fa_update"] = {
+        "sp": sp, "rows": rows, "head_size": hd, "ms": ms, "algorithmic_bytes": nbytes,
+        "achieved_gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak, "frac_of_8tbs": nbytes / ms / 1e6 / 8000.0,
+        "rows_per_s": rows / ms * 1e3, "l2": f"{nbytes / 1e6:.0f} MB per launch vs {L2_BYTES >> 20} MB of L2"}
+    if with_cpu:
+        from oracle import paged_kv_numpy as oracle_np
+        n = 32768
+        hl, ho = lse[:, :n].cpu().numpy(), lo[:, :n].cpu().numpy()
+        t0 = time.perf_counter()
+        g = oracle_np.fa_update_golden(hl, ho)
+        dt = time.perf_counter() - t0
+        err = np.abs(merged[:n].cpu().numpy() - g)
+        out["fa_update"]["cpu_baseline"] = {"value": n / dt, "unit": "rows/s", "cores": 1, "kind": "port",
+                                            "sample": f"first {n} rows, numpy restatement of the reference golden"}
+        out["fa_update"]["max_abs_err"] = float(err.max())
+    return out
+
+
 def _to_np(t):
     import torch
     t = t.detach().cpu().contiguous()
@@ -534,6 +614,8 @@ def main():
     ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays of the step")
     ap.add_argument("--nccl-gather", action="store_true", help="exchange outputs with NCCL instead of peer stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity check")
+    ap.add_argument("--adjacent", action="store_true",
+                    help="also time paged_cache_load and fa_update on this workload (1 GPU)")
     ap.add_argument("--cpu-sample", type=int, default=64, help="sequences in the CPU sample")
     args = ap.parse_args()
     if args.impl == "reference":
