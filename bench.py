@@ -315,45 +315,108 @@ def run_gpu(args):
     for x in parts:
         offs.append(total)
         total += (x.numel() * x.element_size() + 255) // 256 * 256
-    h_stage = torch.empty(total, dtype=torch.uint8).pin_memory()
-    d_stage = torch.empty(total, dtype=torch.uint8, device=dev)
+    # two staging sets: step i + 1 is uploaded while step i computes
+    h_stage = [torch.empty(total, dtype=torch.uint8).pin_memory() for _ in range(2)]
+    d_stage = [torch.empty(total, dtype=torch.uint8, device=dev) for _ in range(2)]
 
     def view(buf, x, off):
         return buf[off:off + x.numel() * x.element_size()].view(x.dtype).view(x.shape)
-    for x, off in zip(parts, offs):
-        view(h_stage, x, off).copy_(x.cpu())
-    d_q, d_key, d_val, d_slot, d_bt = (view(d_stage, x, off) for x, off in zip(parts, offs))
+    for hs in h_stage:
+        for x, off in zip(parts, offs):
+            view(hs, x, off).copy_(x.cpu())
+    d_views = [tuple(view(ds, x, off) for x, off in zip(parts, offs)) for ds in d_stage]
     h_lens = torch.tensor(lens, dtype=torch.int32)
     out_shape = (world,) + tuple(q.shape) if world > 1 else tuple(q.shape)
-    h_out = torch.empty(out_shape, dtype=q.dtype).pin_memory()
+    h_out = [torch.empty(out_shape, dtype=q.dtype).pin_memory() for _ in range(2)]
     pa_kw = dict(q_head_num=hq_local, kv_head_num=hpr, qk_scale=case["qk_scale"])
     if spec.kv_int8:
         pa_kw.update(quant_type=1, k_descale=kd, v_descale=vd)
 
-    def e2e_step():
-        d_stage.copy_(h_stage, non_blocking=True)
+    def operators(slot_i):
+        d_q, d_key, d_val, d_slot, d_bt = d_views[slot_i]
         if spec.kv_int8:
             ops.reshape_and_cache_quant(d_key, d_val, kc, vc, d_slot, kd, vd)
         else:
             ops.reshape_and_cache(d_key, d_val, kc, vc, d_slot, 0, 0)
         o = ops.paged_attention(d_q, kc, vc, d_bt, h_lens, **pa_kw)
-        if world > 1:
-            o = exchange(o)
-        h_out.copy_(o, non_blocking=True)
+        return exchange(o) if world > 1 else o
+
+    # (1) serial: upload, operators, download, host waits -- the latency of one isolated step
+    def serial_step():
+        d_stage[0].copy_(h_stage[0], non_blocking=True)
+        o = operators(0)
+        h_out[0].copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the step's result is read on the host
 
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / args.steps
+    def time_loop(fn, finish=None):
+        for _ in range(3):
+            fn()
+        if finish is not None:
+            finish()
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        if finish is not None:
+            finish()
+        e1.record()
+        barrier()
+        tt = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item()) / args.steps
+    serial_ms = time_loop(serial_step)
+
+    # (2) pipelined, the serving loop: every step still uploads its inputs from pinned memory and
+    # has its result read on the host, but the upload of step i + 1 and the download of step i - 1
+    # run on copy streams while step i computes; the host reads a result two steps after its launch
+    # (before its pinned buffer is handed to the next download), so it never waits on the GPU
+    comp = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(2)]      # staging set uploaded
+    ev_done = [torch.cuda.Event() for _ in range(2)]    # operators that read the set have finished
+    ev_out = [torch.cuda.Event() for _ in range(2)]     # result is in pinned host memory
+    state = {"i": 0, "primed": False}
+    d_out = [torch.empty(out_shape, dtype=q.dtype, device=dev) for _ in range(2)] if world > 1 else None
+
+    def upload(slot_i):
+        s_in.wait_event(ev_done[slot_i])                 # the set's previous readers are done
+        with torch.cuda.stream(s_in):
+            d_stage[slot_i].copy_(h_stage[slot_i], non_blocking=True)
+            ev_in[slot_i].record(s_in)
+
+    def pipelined_step():
+        i = state["i"]
+        cur = i & 1
+        if not state["primed"]:
+            for e in ev_done + ev_out:
+                e.record(comp)
+            upload(cur)
+            state["primed"] = True
+        upload(cur ^ 1)                                  # next step's inputs, behind this step's kernels
+        comp.wait_event(ev_in[cur])
+        o = operators(cur)
+        if world > 1:
+            # the gathered buffer is written by the peers again two steps on: download a private copy
+            comp.wait_event(ev_out[cur])
+            d_out[cur].copy_(o)
+            o = d_out[cur]
+        ev_done[cur].record(comp)
+        ev_out[cur].synchronize()                        # the result of step i - 2 is read on the host
+        s_out.wait_event(ev_done[cur])
+        with torch.cuda.stream(s_out):
+            h_out[cur].copy_(o, non_blocking=True)
+            ev_out[cur].record(s_out)
+        if world == 1:
+            o.record_stream(s_out)
+        state["i"] = i + 1
+
+    def drain():
+        for e in ev_out:
+            e.synchronize()
+        comp.wait_stream(s_out)
+        comp.wait_stream(s_in)
+    e2e_ms = time_loop(pipelined_step, drain)
     clocks = sampler.stop() if sampler else None
     ops.paged_attention_check_status(dev)
     gather_check = None
@@ -365,7 +428,7 @@ def run_gpu(args):
         sharding.all_gather_outputs(out_local, gathered)
         gather_check = bool(torch.equal(mine.view(torch.int16), gathered.view(torch.int16)))
     h2d = sum(x.numel() * x.element_size() for x in parts)
-    d2h = h_out.numel() * h_out.element_size()
+    d2h = h_out[0].numel() * h_out[0].element_size()
 
     if rank != 0:
         if world > 1:
@@ -441,7 +504,10 @@ def run_gpu(args):
             "launch": "CUDA graph replay" if graph is not None else "eager launches on one stream",
             "work_items": info.work_items, "split_partials": info.partials, "grid": info.grid}),
         "e2e": {"value": spec.batch / e2e_ms * 1e3, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                "mode": "pipelined: copy streams move step i+1's inputs and step i-1's result while step i computes; "
+                        "two staging sets, results read on the host two steps after launch",
+                "serial_ms_per_step": serial_ms, "serial_value": spec.batch / serial_ms * 1e3},
         "gpu_launches": kernels_per_step * args.steps,
         "roofline": roofline, "cpu_baseline": cpu, "parity_check": checked, "gather_check": gather_check, "clocks": clocks,
         "reshape_and_cache_prefill": scatter, "adjacent_ops": adjacent,
