@@ -126,6 +126,14 @@ int ms_custom_ops_paged_attention_workspace_size(const MsPagedAttentionArgs *arg
 int ms_custom_ops_paged_attention(const MsPagedAttentionArgs *args, const MsTensorDesc *attention_out,
                                   void *workspace, size_t workspace_bytes, void *stream);
 
+/* Extension (no reference counterpart): the same operator with a second output, `lse_out` Float32
+ * (batch, q_head_num) = log of the sum over the context of exp(qk_scale * q.k + mask) (natural
+ * logarithm; -inf for an empty context).  It is what fa_update needs to merge attention outputs
+ * computed over different parts of a context (sequence-parallel decode).  Same workspace rules. */
+int ms_custom_ops_paged_attention_with_lse(const MsPagedAttentionArgs *args, const MsTensorDesc *attention_out,
+                                           const MsTensorDesc *lse_out, void *workspace, size_t workspace_bytes,
+                                           void *stream);
+
 /* Workspace bytes the calling thread's last ms_custom_ops_paged_attention call needed.  A caller
  * that keeps a grow-only workspace can skip the separate size query: launch with what it has and,
  * if the call fails because the workspace is too small (nothing was launched), grow it to this

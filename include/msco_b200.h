@@ -215,6 +215,16 @@ int msco_paged_attention_launch(const MscoPaPlan *plan, const void *query, const
                                 const void *attn_mask, void *out, void *workspace,
                                 size_t workspace_bytes, void *stream);
 
+/* Extension (the reference operator has no such output): the same launch that also writes
+ * lse[batch, num_q_heads] float32 = log(sum over the context of exp(qk_scale * q.k + mask)), natural
+ * logarithm, -inf for an empty context.  With it, outputs computed over different parts of a context
+ * (sequence-parallel decode) are merged exactly by msco_fa_update. */
+int msco_paged_attention_launch_lse(const MscoPaPlan *plan, const void *query, const void *key_cache,
+                                    const void *value_cache, const int32_t *block_tables,
+                                    const float *k_descale, const int32_t *k_offset, const float *v_descale,
+                                    const int32_t *v_offset, const void *attn_mask, void *out, float *lse,
+                                    void *workspace, size_t workspace_bytes, void *stream);
+
 /* One decode step in one call: reshape_and_cache of `num_tokens` new rows (key / value:
  * [num_tokens, num_kv_heads * head_dim] in the query dtype; quantised on the way in when the plan's
  * quant_type is 1) followed by the attention launch above on the same caches.  Same result as the

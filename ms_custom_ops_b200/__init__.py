@@ -27,7 +27,7 @@ from ._abi import MscoError  # noqa: F401
 from ._host import UnsupportedOnB200, plan_cache_clear, plan_cache_stats, registered_ops  # noqa: F401
 
 __all__ = ["reshape_and_cache", "reshape_and_cache_quant", "paged_attention", "paged_attention_infer",
-           "paged_cache_load", "paged_cache_load_infer", "fa_update", "fa_update_infer",
+           "paged_cache_load", "paged_cache_load_infer", "fa_update", "fa_update_infer", "paged_attention_with_lse",
            "paged_attention_workspace_size", "paged_attention_check_status", "TensorSpec", "MscoError",
            "UnsupportedOnB200", "registered_ops", "plan_cache_stats", "plan_cache_clear"]
 
@@ -203,26 +203,50 @@ def paged_attention(query, key_cache, value_cache, block_tables, context_lens, a
     reference accepts but this build does not implement raise UnsupportedOnB200; invalid
     combinations raise ValueError as in the reference.
     """
+    return _paged_attention(False, query, key_cache, value_cache, block_tables, context_lens, attn_mask,
+                            batch_run_status, k_descale, k_offset, v_descale, v_offset, razor_offset, p_scale, log_n,
+                            q_seq_lens, q_head_num, qk_scale, kv_head_num, mask_type, batch_run_status_enable,
+                            quant_type, out_data_type, has_quant_offset, compress_type, calc_type, scale_type,
+                            input_layout, mla_v_dim, input_format)
+
+
+def paged_attention_with_lse(query, key_cache, value_cache, block_tables, context_lens, **kw):
+    """Extension (no reference counterpart): ``paged_attention`` that also returns the log-sum-exp.
+
+    Same arguments as ``paged_attention`` (optional ones by keyword).  Returns ``(attention_out, lse)``
+    with ``lse`` float32 [batch, q_head_num] = log(sum over the context of exp(qk_scale * q.k + mask)),
+    -inf for an empty context: attention outputs computed over different parts of a context are merged
+    exactly by ``fa_update(stack(lse), stack(out.float()))``.
+    """
+    return _paged_attention(True, query, key_cache, value_cache, block_tables, context_lens, *_kw_to_positional(kw))
+
+
+def _paged_attention(with_lse, query, *rest):
     import torch
     D = _Descs()
-    a = _pa_args(D, query, key_cache, value_cache, block_tables, context_lens, attn_mask, batch_run_status,
-                 k_descale, k_offset, v_descale, v_offset, razor_offset, p_scale, log_n, q_seq_lens, q_head_num,
-                 qk_scale, kv_head_num, mask_type, batch_run_status_enable, quant_type, out_data_type,
-                 has_quant_offset, compress_type, calc_type, scale_type, input_layout, mla_v_dim, input_format)
+    a = _pa_args(D, query, *rest)
     L = _host.lib()
     out = torch.empty_like(query)
+    if with_lse:
+        lse = torch.empty(query.shape[:2], dtype=torch.float32, device=query.device)
+
+        def launch(ws):
+            return L.ms_custom_ops_paged_attention_with_lse(C.byref(a), D(out), D(lse), C.c_void_p(ws.data_ptr()),
+                                                            ws.numel(), _stream())
+    else:
+        def launch(ws):
+            return L.ms_custom_ops_paged_attention(C.byref(a), D(out), C.c_void_p(ws.data_ptr()), ws.numel(),
+                                                   _stream())
     # launch with the workspace at hand; if it is too small nothing was launched and the library
     # tells how much is needed (one validation + plan lookup per call in the steady state)
     ws = _workspace(query.device, 0)
-    rc = L.ms_custom_ops_paged_attention(C.byref(a), D(out), C.c_void_p(ws.data_ptr()), ws.numel(), _stream())
+    rc = launch(ws)
     if rc != 0:
         need = L.ms_custom_ops_paged_attention_last_workspace_need()
         if need <= ws.numel():
             _host.check(rc)
-        ws = _workspace(query.device, need)
-        _host.check(L.ms_custom_ops_paged_attention(C.byref(a), D(out), C.c_void_p(ws.data_ptr()), ws.numel(),
-                                                    _stream()))
-    return out
+        _host.check(launch(_workspace(query.device, need)))
+    return (out, lse) if with_lse else out
 
 
 def paged_attention_infer(query, key_cache, value_cache, block_tables, context_lens, **kw):

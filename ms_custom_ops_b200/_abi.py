@@ -62,7 +62,7 @@ EXPORTS = (
     "msco_paged_attention_status", "msco_paged_attention_profile_enable", "msco_paged_attention_profile_read",
     "msco_paged_attention_launch_static", "msco_paged_attention_status_static",
     "msco_ipc_export", "msco_ipc_import", "msco_ipc_release", "msco_peer_allgather", "msco_decode_step",
-    "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update",
+    "msco_paged_attention_launch_lse", "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update",
 )
 
 
@@ -101,6 +101,8 @@ def lib():
     L.msco_paged_attention_plan_destroy.argtypes = [vp]
     L.msco_paged_attention_launch.restype = C.c_int
     L.msco_paged_attention_launch.argtypes = [vp] * 12 + [sz, vp]
+    L.msco_paged_attention_launch_lse.restype = C.c_int
+    L.msco_paged_attention_launch_lse.argtypes = [vp] * 13 + [sz, vp]
     L.msco_paged_attention_status.restype = C.c_int
     L.msco_paged_attention_status.argtypes = [vp, vp]
     L.msco_paged_attention_launch_static.restype = C.c_int

@@ -42,6 +42,7 @@ EXPORTS = (
     "ms_custom_ops_op_signature", "ms_custom_ops_plan_cache_stats", "ms_custom_ops_plan_cache_clear",
     "ms_custom_ops_paged_cache_load_infer", "ms_custom_ops_paged_cache_load_workspace_size",
     "ms_custom_ops_paged_cache_load", "ms_custom_ops_fa_update_infer", "ms_custom_ops_fa_update",
+    "ms_custom_ops_paged_attention_with_lse",
 )
 
 
@@ -72,6 +73,8 @@ def lib():
     L.ms_custom_ops_paged_attention_workspace_size.argtypes = [ap, C.POINTER(C.c_size_t)]
     L.ms_custom_ops_paged_attention.restype = C.c_int
     L.ms_custom_ops_paged_attention.argtypes = [ap, _TP, vp, C.c_size_t, vp]
+    L.ms_custom_ops_paged_attention_with_lse.restype = C.c_int
+    L.ms_custom_ops_paged_attention_with_lse.argtypes = [ap, _TP, _TP, vp, C.c_size_t, vp]
     L.ms_custom_ops_paged_attention_last_workspace_need.restype = C.c_size_t
     L.ms_custom_ops_paged_attention_status.restype = C.c_int
     L.ms_custom_ops_paged_attention_status.argtypes = [vp]

@@ -261,7 +261,7 @@ bool recall_launch(const void *ws, uint32_t *epoch) {
 int pa_launch_impl(const MscoPaPlan *plan, const void *query, const void *key_cache, const void *value_cache,
                    const int32_t *block_tables, const float *k_descale, const int32_t *k_offset,
                    const float *v_descale, const int32_t *v_offset, const void *attn_mask, void *out,
-                   void *workspace, size_t workspace_bytes, void *stream, bool after_kernel) {
+                   void *workspace, size_t workspace_bytes, void *stream, bool after_kernel, float *lse = nullptr) {
   if (plan == nullptr) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch: NULL plan");
   if (plan->batch == 0) return MSCO_OK;
   const MscoPaDesc &d = plan->desc;
@@ -290,6 +290,7 @@ int pa_launch_impl(const MscoPaPlan *plan, const void *query, const void *key_ca
   }
   p.mask = d.mask_type ? attn_mask : nullptr;
   p.out = out;
+  p.lse = lse;
   char *ws = static_cast<char *>(workspace);
   p.status = reinterpret_cast<int32_t *>(ws);
   p.plan = reinterpret_cast<const int32_t *>(ws + kPlanRegionOffset);
@@ -344,6 +345,20 @@ extern "C" int msco_paged_attention_launch(const MscoPaPlan *plan, const void *q
                                            size_t workspace_bytes, void *stream) {
   return pa_launch_impl(plan, query, key_cache, value_cache, block_tables, k_descale, k_offset, v_descale, v_offset,
                         attn_mask, out, workspace, workspace_bytes, stream, false);
+}
+
+// The same launch with a second output: lse[batch, num_q_heads] (float32), the natural-log sum of
+// exp over the context of the scaled (and masked) scores -- what fa_update needs to merge outputs
+// computed over different parts of a context.  -inf for an empty context.
+extern "C" int msco_paged_attention_launch_lse(const MscoPaPlan *plan, const void *query, const void *key_cache,
+                                               const void *value_cache, const int32_t *block_tables,
+                                               const float *k_descale, const int32_t *k_offset,
+                                               const float *v_descale, const int32_t *v_offset,
+                                               const void *attn_mask, void *out, float *lse, void *workspace,
+                                               size_t workspace_bytes, void *stream) {
+  if (lse == nullptr) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch_lse: NULL lse");
+  return pa_launch_impl(plan, query, key_cache, value_cache, block_tables, k_descale, k_offset, v_descale, v_offset,
+                        attn_mask, out, workspace, workspace_bytes, stream, false, lse);
 }
 
 // One decode step in one call: scatter the new token rows, then attention.  The attention kernel

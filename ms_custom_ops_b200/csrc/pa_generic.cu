@@ -11,6 +11,8 @@
 //   M = max_s m_s,  out = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s
 // which is the log-sum-exp merge of the reference's fa_update golden
 // (tests/st/test_asd_faupdate.py:34-59) written for un-normalised partials.
+#include <math_constants.h>
+
 #include "msco_common.cuh"
 #include "pa_params.h"
 
@@ -23,6 +25,7 @@ constexpr int kGenRows = 8;    // q rows per work item
 constexpr int kGenMaxD = 256;  // head_dim limit
 constexpr int kGenDL = kGenMaxD / 32;
 constexpr float kNeg = -1.0e30f;
+constexpr float kLn2 = 0.6931471805599453f;
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -190,6 +193,7 @@ __global__ void __launch_bounds__(kGenThreads) pa_generic_kernel(PaParams p, con
         o = (o + vo) * __ldg(p.v_descale + w.kvh * D + d);
       }
       static_cast<TQ *>(p.out)[((int64_t)w.b * p.num_q_heads + hq) * D + d] = from_f32<TQ>(o);
+      if (d == 0 && p.lse != nullptr) p.lse[(int64_t)w.b * p.num_q_heads + hq] = (M + log2f(L)) * kLn2;
     } else {
       const int64_t prow = (int64_t)w.part * p.num_q_heads + hq;
       p.part_o[prow * D + d] = O;
@@ -218,8 +222,9 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p, const __grid
   if (ns == 1) return;  // written directly by the attention kernel
   const int D = p.head_dim;
   TQ *out = static_cast<TQ *>(p.out) + (int64_t)row * D;
-  if (ns == 0) {  // empty sequence: zeros, as the reference golden does
+  if (ns == 0) {  // empty sequence: zeros, as the reference golden does; no token: lse = -inf
     for (int d = lane; d < D; d += 32) out[d] = from_f32<TQ>(0.f);
+    if (lane == 0 && p.lse != nullptr) p.lse[row] = -CUDART_INF_F;
     return;
   }
   const int base = __ldg(pv.b_part_base + b);
@@ -266,6 +271,7 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p, const __grid
     pk.x = pack2<TQ>(r0, r1);
     pk.y = pack2<TQ>(r2, r3);
     *reinterpret_cast<uint2 *>(out + lane * 4) = pk;
+    if (lane == 0 && p.lse != nullptr) p.lse[row] = (M + log2f(L)) * kLn2;
     return;
   }
   float o[kGenDL];
@@ -293,6 +299,7 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p, const __grid
       out[d] = from_f32<TQ>(v);
     }
   }
+  if (lane == 0 && p.lse != nullptr) p.lse[row] = (M + log2f(L)) * kLn2;
 }
 
 }  // namespace

@@ -24,6 +24,7 @@ struct PaParams {
   const int32_t *v_offset;
   const void *mask;
   void *out;
+  float *lse;           // optional [batch, num_q_heads]: natural-log sum of exp of the scaled (+mask) scores
   const int32_t *plan;  // device copy of the plan words (unused when the words travel as a kernel parameter)
   int32_t *status;      // workspace words 0..1: [error code, launch epoch]
   uint32_t epoch;       // identifies this launch in the status words

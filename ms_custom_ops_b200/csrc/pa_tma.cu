@@ -41,6 +41,7 @@ constexpr int kD = 128;               // head_dim of this kernel
 constexpr int kMergeStride = 132;     // floats per merged row (bank-conflict padding)
 constexpr int kQSlotBytes = 16 * kD * 2;
 constexpr float kNeg = -1.0e30f;
+constexpr float kLn2 = 0.6931471805599453f;
 constexpr uint32_t kWaitLimit = 1u << 24;
 
 // NT = number of 8-row tiles of the q group (1: up to 8 rows, 2: up to 16).
@@ -56,7 +57,8 @@ template <bool KV8, int NT> struct Cfg {
   static constexpr int kMergeBytes = kWarps * kRows * kMergeStride * 4;
   static constexpr int kOffQ = kStages * kStageBytes;
   static constexpr int kOffQFrag = kOffQ + 2 * kQSlotBytes;         // int8 KV: scaled fp16 Q in fragment order
-  static constexpr int kQFragBytes = KV8 ? NT * 4 * 32 * 16 : 0;    // [row tile][k-step pair][lane] uint4
+  static constexpr int kQFragBytes = KV8 ? NT * 4 * 32 * 16 + 128 : 0;  // [row tile][k-step pair][lane] uint4, then
+                                                                         // 2 partial score offsets per q row (lse)
   static constexpr int kOffMerge = kOffQFrag + kQFragBytes;
   static constexpr int kOffMl = kOffMerge + kMergeBytes;            // [warp][16] float2
   static constexpr int kOffDesc = kOffMl + kWarps * 16 * 2 * 4;     // 2 x 8 ints
@@ -255,6 +257,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         // once per item, into fragment order: word (row tile, k-step pair, lane, 2 (ks & 1) + j)
         // holds the fp16 pair Q[8nt + gid][16ks + 4q4 + 2j, + 1] * k_descale.
         uint32_t *qfrag = reinterpret_cast<uint32_t *>(smem + C::kOffQFrag);
+        float *score_shift = reinterpret_cast<float *>(smem + C::kOffQFrag + NT * 4 * 32 * 16);
         const float *ksc = p.k_descale + kvh * kD;
         for (int u = tid; u < C::kRows * 64; u += C::kConsumerThreads) {
           const int r = u >> 6, dp = u & 63;  // q row, index of the pair of head-dim columns
@@ -265,7 +268,23 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             e1 = to_f32<T>(qsm[r * kD + 2 * dp + 1]) * sc.y;
           }
           const int ks = dp >> 3, qq = (dp >> 1) & 3, j = dp & 1;
-          qfrag[(((r >> 3) * 4 + (ks >> 1)) * 32 + (r & 7) * 4 + qq) * 4 + 2 * (ks & 1) + j] = pack2<__half>(e0, e1);
+          const uint32_t packed = pack2<__half>(e0, e1);
+          qfrag[(((r >> 3) * 4 + (ks >> 1)) * 32 + (r & 7) * 4 + qq) * 4 + 2 * (ks & 1) + j] = packed;
+          if (p.lse != nullptr) {
+            // the K bytes enter the MMA as k + 1152 instead of k + k_offset: every score of q row r is
+            // too large by sum_d Q~[r][d] (1152 - k_offset[d]).  The softmax does not see that, the
+            // log-sum-exp does: the warp (32 column pairs of one row) adds up its half of the sum.
+            const __half2 h2 = *reinterpret_cast<const __half2 *>(&packed);
+            float o0 = 1152.f, o1 = 1152.f;
+            if (p.k_offset != nullptr) {
+              o0 -= (float)__ldg(p.k_offset + kvh * kD + 2 * dp);
+              o1 -= (float)__ldg(p.k_offset + kvh * kD + 2 * dp + 1);
+            }
+            float part = fmaf(__low2float(h2), o0, __high2float(h2) * o1);
+#pragma unroll
+            for (int sh = 16; sh > 0; sh >>= 1) part += __shfl_xor_sync(0xffffffffu, part, sh);
+            if (lane == 0) score_shift[2 * r + (dp >> 5)] = part;
+          }
         }
         named_bar_sync(1, C::kConsumerThreads);
 #pragma unroll
@@ -526,6 +545,13 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           acc.z = fmaf(-1152.f, L, acc.z); acc.w = fmaf(-1152.f, L, acc.w);
         }
         const int hq = kvh * p.group + row0 + row;
+        if (p.lse != nullptr) {
+          if (KV8) {  // back to the scores of the true K values (see the Q conversion above)
+            const float *score_shift = reinterpret_cast<const float *>(smem + C::kOffQFrag + NT * 4 * 32 * 16);
+            M -= (score_shift[2 * row] + score_shift[2 * row + 1]) * p.scale_log2e;
+          }
+          if (nsplit == 1 && (u & 31) == 0) p.lse[(int64_t)b * p.num_q_heads + hq] = (M + log2f(L)) * kLn2;
+        }
         if (nsplit == 1) {
           const float inv = 1.f / L;
           float r0 = acc.x * inv, r1 = acc.y * inv, r2 = acc.z * inv, r3 = acc.w * inv;

@@ -100,8 +100,14 @@ def make_pa_desc(query, key_cache, block_tables, qk_scale, quant_type=0, has_qua
 
 
 def pa_launch(plan: _abi.PaPlan, query, key_cache, value_cache, block_tables, out, workspace,
-              k_descale=None, k_offset=None, v_descale=None, v_offset=None, mask=None):
-    """msco_paged_attention_launch on the current stream."""
+              k_descale=None, k_offset=None, v_descale=None, v_offset=None, mask=None, lse=None):
+    """msco_paged_attention_launch on the current stream (with `lse`: ..._launch_lse)."""
+    if lse is not None:
+        _abi.check(_abi.lib().msco_paged_attention_launch_lse(
+            plan.handle, _ptr(query), _ptr(key_cache), _ptr(value_cache), _ptr(block_tables), _ptr(k_descale),
+            _ptr(k_offset), _ptr(v_descale), _ptr(v_offset), _ptr(mask), _ptr(out), _ptr(lse), _ptr(workspace),
+            workspace.numel() * workspace.element_size(), _stream()))
+        return
     _abi.check(_abi.lib().msco_paged_attention_launch(
         plan.handle, _ptr(query), _ptr(key_cache), _ptr(value_cache), _ptr(block_tables), _ptr(k_descale),
         _ptr(k_offset), _ptr(v_descale), _ptr(v_offset), _ptr(mask), _ptr(out), _ptr(workspace),
@@ -127,15 +133,16 @@ def pa_status(plan: _abi.PaPlan, workspace) -> int:
 
 def paged_attention_raw(query, key_cache, value_cache, block_tables, context_lens, qk_scale, quant_type=0,
                         k_descale=None, k_offset=None, v_descale=None, v_offset=None, mask=None, mask_type=0,
-                        kernel=_abi.KERNEL_AUTO, check_status=True):
-    """Plan + launch + (optionally) status check in one call; returns (out, plan info)."""
+                        kernel=_abi.KERNEL_AUTO, check_status=True, lse=None):
+    """Plan + launch + (optionally) status check in one call; returns (out, plan info).
+    `lse`: optional float32 [batch, q_heads] tensor that receives the log-sum-exp of the scores."""
     desc = make_pa_desc(query, key_cache, block_tables, qk_scale, quant_type,
                         k_offset is not None, mask, mask_type, kernel)
     plan = _abi.PaPlan(desc, [int(x) for x in context_lens])
     ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device=query.device)
     out = torch.empty_like(query)
     pa_launch(plan, query, key_cache, value_cache, block_tables, out, ws, k_descale, k_offset, v_descale,
-              v_offset, mask)
+              v_offset, mask, lse)
     info = plan.info()
     if check_status:
         pa_status(plan, ws)

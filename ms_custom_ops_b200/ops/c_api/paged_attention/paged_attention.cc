@@ -448,31 +448,69 @@ extern "C" int ms_custom_ops_paged_attention_workspace_size(const MsPagedAttenti
   });
 }
 
+namespace ms_custom_ops {
+namespace {
+
+// Shared by the operator and its variant with the log-sum-exp output (lse_out undefined: none).
+int LaunchPagedAttention(const MsPagedAttentionArgs *args, const Tensor &out, const Tensor &lse_out, void *workspace,
+                         size_t workspace_bytes, void *stream) {
+  const PaInputs in = Unpack(args);
+  const Prepared p = Prepare(in);
+  if (!out.defined() || out.data() == nullptr)
+    MS_VALUE_ERROR << "For PagedAttention, attention_out must be allocated by the caller.";
+  if (out.dtype() != in.query.dtype() || out.shape() != in.query.shape())
+    MS_VALUE_ERROR << "For PagedAttention, attention_out must have query's shape and dtype.";
+  CheckContiguous(out, kOpName, "attention_out");
+  if (lse_out.defined()) {
+    if (lse_out.dtype() != MSCO_DTYPE_F32)
+      MS_TYPE_ERROR << "For PagedAttention, lse_out must be Float32, but got " << DTypeName(lse_out.dtype()) << ".";
+    if (lse_out.rank() != 2 || lse_out.dim(0) != in.query.dim(0) || lse_out.dim(1) != in.query.dim(1))
+      MS_VALUE_ERROR << "For PagedAttention, lse_out must be (batch, q_head_num) = (" << in.query.dim(0) << ", "
+                     << in.query.dim(1) << ").";
+    if (lse_out.data() == nullptr && p.batch != 0)
+      MS_VALUE_ERROR << "For PagedAttention, lse_out must be allocated by the caller.";
+    CheckContiguous(lse_out, kOpName, "lse_out");
+  }
+  if (p.batch == 0) return MSCO_OK;
+  (void)CheckAndUpdate(p.context_lens, &g_prev_context_lens);
+  PlanRef plan = PlanCache::Instance().GetOrCreate(p.desc, p.context_lens);
+  g_last_workspace_need = std::max<size_t>(msco_paged_attention_workspace_bytes(plan.get()), 256);
+  if (workspace == nullptr || workspace_bytes < g_last_workspace_need)
+    MS_VALUE_ERROR << "For PagedAttention, the workspace holds " << workspace_bytes << " bytes but this launch needs "
+                   << g_last_workspace_need << ".";
+  const int32_t *tables = static_cast<const int32_t *>(in.block_tables.data());
+  const float *kd = static_cast<const float *>(in.k_descale.data());
+  const float *vd = static_cast<const float *>(in.v_descale.data());
+  const int32_t *ko = static_cast<const int32_t *>(in.k_offset.data());
+  const int32_t *vo = static_cast<const int32_t *>(in.v_offset.data());
+  if (lse_out.defined())
+    return msco_paged_attention_launch_lse(plan.get(), in.query.data(), in.key_cache.data(), in.value_cache.data(),
+                                           tables, kd, ko, vd, vo, in.attn_mask.data(), out.data(),
+                                           static_cast<float *>(lse_out.data()), workspace, workspace_bytes, stream);
+  return msco_paged_attention_launch(plan.get(), in.query.data(), in.key_cache.data(), in.value_cache.data(), tables,
+                                     kd, ko, vd, vo, in.attn_mask.data(), out.data(), workspace, workspace_bytes,
+                                     stream);
+}
+
+}  // namespace
+}  // namespace ms_custom_ops
+
 extern "C" int ms_custom_ops_paged_attention(const MsPagedAttentionArgs *args, const MsTensorDesc *attention_out,
                                              void *workspace, size_t workspace_bytes, void *stream) {
   using namespace ms_custom_ops;
   return GuardedCall(kOpName, [&] {
-    const PaInputs in = Unpack(args);
-    const Prepared p = Prepare(in);
-    const Tensor out(attention_out);
-    if (!out.defined() || out.data() == nullptr)
-      MS_VALUE_ERROR << "For PagedAttention, attention_out must be allocated by the caller.";
-    if (out.dtype() != in.query.dtype() || out.shape() != in.query.shape())
-      MS_VALUE_ERROR << "For PagedAttention, attention_out must have query's shape and dtype.";
-    CheckContiguous(out, kOpName, "attention_out");
-    if (p.batch == 0) return MSCO_OK;
-    (void)CheckAndUpdate(p.context_lens, &g_prev_context_lens);
-    PlanRef plan = PlanCache::Instance().GetOrCreate(p.desc, p.context_lens);
-    g_last_workspace_need = std::max<size_t>(msco_paged_attention_workspace_bytes(plan.get()), 256);
-    if (workspace == nullptr || workspace_bytes < g_last_workspace_need)
-      MS_VALUE_ERROR << "For PagedAttention, the workspace holds " << workspace_bytes << " bytes but this launch needs "
-                     << g_last_workspace_need << ".";
-    return msco_paged_attention_launch(
-        plan.get(), in.query.data(), in.key_cache.data(), in.value_cache.data(),
-        static_cast<const int32_t *>(in.block_tables.data()), static_cast<const float *>(in.k_descale.data()),
-        static_cast<const int32_t *>(in.k_offset.data()), static_cast<const float *>(in.v_descale.data()),
-        static_cast<const int32_t *>(in.v_offset.data()), in.attn_mask.data(), out.data(), workspace,
-        workspace_bytes, stream);
+    return LaunchPagedAttention(args, Tensor(attention_out), Tensor(), workspace, workspace_bytes, stream);
+  });
+}
+
+extern "C" int ms_custom_ops_paged_attention_with_lse(const MsPagedAttentionArgs *args,
+                                                      const MsTensorDesc *attention_out, const MsTensorDesc *lse_out,
+                                                      void *workspace, size_t workspace_bytes, void *stream) {
+  using namespace ms_custom_ops;
+  return GuardedCall(kOpName, [&] {
+    const Tensor lse(lse_out);
+    if (!lse.defined()) MS_VALUE_ERROR << "For PagedAttention, lse_out must be provided.";
+    return LaunchPagedAttention(args, Tensor(attention_out), lse, workspace, workspace_bytes, stream);
   });
 }
 

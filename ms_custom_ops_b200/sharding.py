@@ -76,6 +76,63 @@ def all_gather_outputs(out_local, gathered=None, group=None):
     return gathered
 
 
+# --------------------------------------------------------------------------
+# Sequence sharding: the second axis, for contexts so long (or kv heads so few) that kv-head
+# sharding runs out.  Rank r holds a contiguous range of whole cache blocks of EVERY sequence,
+# computes attention over its part with the log-sum-exp as a second output, the ranks all-gather
+# (lse, output) and every rank merges them with fa_update -- exact, because
+# softmax over the whole context = sum_r exp(lse_r - lse) * softmax over part r.
+# --------------------------------------------------------------------------
+def seq_block_range(num_blocks_of_seq: int, rank: int, world: int):
+    """Half-open range of a sequence's block-table columns owned by `rank` (balanced, contiguous)."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} of {world}")
+    return rank * num_blocks_of_seq // world, (rank + 1) * num_blocks_of_seq // world
+
+
+def seq_shard_tables(block_tables, context_lens, block_size: int, rank: int, world: int):
+    """One rank's view of the block tables and lengths under sequence sharding.
+
+    Returns (local_tables int32 [batch, cols], local_lens int32 [batch]): row b holds the columns
+    seq_block_range(ceil(len_b / block_size), rank, world) of block_tables[b], left-aligned and padded
+    with 0; local_lens[b] is the number of context tokens in them (0 when the rank holds nothing of
+    a short sequence).  The newest token of a sequence lives on the rank that owns its last block.
+    """
+    tables = np.asarray(block_tables)
+    lens = np.asarray(context_lens).astype(np.int64).reshape(-1)
+    nblk = (lens + block_size - 1) // block_size
+    lo = rank * nblk // world
+    hi = (rank + 1) * nblk // world
+    cols = max(int((hi - lo).max()) if len(lens) else 0, 1)
+    local = np.zeros((len(lens), cols), dtype=np.int32)
+    for b in range(len(lens)):
+        local[b, :hi[b] - lo[b]] = tables[b, lo[b]:hi[b]]
+    local_lens = np.clip(np.minimum(lens, hi * block_size) - lo * block_size, 0, None).astype(np.int32)
+    return local, local_lens
+
+
+def seq_parallel_merge(out_local, lse_local, merge, group=None):
+    """All-gather the per-rank (output, lse) of a sequence-sharded decode step and merge them.
+
+    out_local [batch, q_heads, head_dim] (any float dtype), lse_local float32 [batch, q_heads];
+    `merge(lse [world, rows], partial [world, rows, head_dim]) -> [rows, head_dim]` is
+    ms_custom_ops_b200.fa_update on GPUs.  Returns float32 [batch, q_heads, head_dim] on every rank.
+    One collective: lse rides as an extra column of the float32 rows.
+    """
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    b, h, d = out_local.shape
+    packed = torch.empty((b * h, d + 1), dtype=torch.float32, device=out_local.device)
+    packed[:, :d] = out_local.reshape(b * h, d)
+    packed[:, d] = lse_local.reshape(b * h)
+    gathered = torch.empty((world * b * h, d + 1), dtype=torch.float32, device=out_local.device)
+    dist.all_gather_into_tensor(gathered, packed, group=group)
+    gathered = gathered.view(world, b * h, d + 1)
+    merged = merge(gathered[:, :, d].contiguous(), gathered[:, :, :d].contiguous())
+    return merged.view(b, h, d)
+
+
 class PeerGather:
     """All-gather of per-rank outputs by peer stores over NVLink (msco_peer_allgather).
 

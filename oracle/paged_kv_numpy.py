@@ -108,7 +108,7 @@ def _gather_seq(cache_f32, table_row, kv_len, block_size):
 
 def paged_attention_golden(query, key_cache, value_cache, block_tables, context_lens, scale,
                            k_descale=None, v_descale=None, k_offset=None, v_offset=None,
-                           mask=None, mask_type=0):
+                           mask=None, mask_type=0, return_lse=False):
     """float32 decode attention over a paged KV cache, one query token per sequence.
 
     Follows tests/st/test_custom_paged_attention.py:
@@ -121,7 +121,9 @@ def paged_attention_golden(query, key_cache, value_cache, block_tables, context_
       :880-903  additive masks: NORM ``mask[b, 0, :kl]`` (mask_type 1),
                 ALIBI ``mask[b, :, 0, :kl]`` (mask_type 2).
     Returns float32 ``[batch, q_heads, head_dim]``; the caller casts to the
-    query dtype as the reference does (:693-699).
+    query dtype as the reference does (:693-699).  With ``return_lse`` also
+    ``log(sum(exp(scores)))`` per (sequence, q head), -inf for an empty context
+    (the quantity tests/st/test_asd_faupdate.py:34-59 merges partial outputs by).
     """
     q = np.asarray(query).astype(np.float32)
     kc = np.asarray(key_cache).astype(np.float32)
@@ -140,6 +142,7 @@ def paged_attention_golden(query, key_cache, value_cache, block_tables, context_
     tables = np.asarray(block_tables)
     lens = np.asarray(context_lens).reshape(-1)
     out = np.zeros((nt, hq, vc.shape[3]), dtype=np.float32)
+    lse = np.full((nt, hq), -np.inf, dtype=np.float32)
     m = None if mask is None else np.asarray(mask).astype(np.float32)
     for b in range(nt):
         kl = int(lens[b])
@@ -161,7 +164,8 @@ def paged_attention_golden(query, key_cache, value_cache, block_tables, context_
         p = e / np.sum(e, axis=-1, keepdims=True)
         o = np.matmul(p, np.transpose(vs, (1, 0, 2)))  # [hkv, g, dv]
         out[b] = o.reshape(hq, -1)
-    return out
+        lse[b] = (smax[..., 0] + np.log(np.sum(e, axis=-1))).reshape(hq)
+    return (out, lse) if return_lse else out
 
 
 def paged_cache_load_golden(key_cache, value_cache, block_tables, seq_lens, seq_starts=None,

@@ -103,3 +103,65 @@ def test_two_rank_gloo_sharded_decode_matches_unsharded():
     for p in procs:
         assert p.exitcode == 0, "a rank failed or timed out"
     assert dict(ret) == {0: (True, True, True), 1: (True, True, True)}
+
+
+# ----------------------------------------------------------------------------- sequence sharding
+def test_seq_block_ranges_cover_every_block_once():
+    for nblk in (0, 1, 2, 5, 8, 64, 513):
+        for world in (1, 2, 3, 8):
+            ranges = [sharding.seq_block_range(nblk, r, world) for r in range(world)]
+            assert ranges[0][0] == 0 and ranges[-1][1] == nblk
+            assert all(ranges[i][1] == ranges[i + 1][0] for i in range(world - 1))
+            sizes = [hi - lo for lo, hi in ranges]
+            assert max(sizes) - min(sizes) <= 1
+
+
+def test_seq_shard_tables_lengths_and_columns():
+    tables = np.arange(3 * 6, dtype=np.int32).reshape(3, 6) + 100
+    lens = np.array([41, 3, 96], np.int32)  # block 16: 3, 1, 6 blocks
+    parts = [sharding.seq_shard_tables(tables, lens, 16, r, 4) for r in range(4)]
+    for b in range(3):
+        assert sum(int(p[1][b]) for p in parts) == lens[b]
+        cols = np.concatenate([p[0][b, :(int(p[1][b]) + 15) // 16] for p in parts])
+        assert np.array_equal(cols, tables[b, :(lens[b] + 15) // 16])
+    assert int(parts[0][1][1]) == 0 and int(parts[3][1][1]) == 3   # the short sequence lives on the last rank
+
+
+def _seq_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(11)
+        nb, bs, hkv, hq, d, batch = 48, 16, 2, 8, 32, 5
+        kc = rng.standard_normal((nb, bs, hkv, d)).astype(np.float32)
+        vc = rng.standard_normal((nb, bs, hkv, d)).astype(np.float32)
+        q = rng.standard_normal((batch, hq, d)).astype(np.float32)
+        lens = np.array([100, 7, 16, 33, 128], np.int32)
+        tables = np.stack([rng.permutation(nb)[:8] for _ in range(batch)]).astype(np.int32)
+        want = oracle.paged_attention_golden(q, kc, vc, tables, lens, 0.2)
+        lt, ll = sharding.seq_shard_tables(tables, lens, bs, rank, world)
+        o, lse = oracle.paged_attention_golden(q, kc, vc, lt, ll, 0.2, return_lse=True)
+
+        def merge(lse_all, parts):
+            return torch.from_numpy(oracle.fa_update_golden(lse_all.numpy(), parts.numpy()))
+        got = sharding.seq_parallel_merge(torch.from_numpy(o), torch.from_numpy(lse), merge).numpy()
+        ret[rank] = (bool(np.allclose(got, want, rtol=1e-5, atol=1e-6)), got.shape == want.shape,
+                     bool(np.isneginf(lse[ll == 0]).all()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gloo_sequence_sharded_decode_matches_unsharded():
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_seq_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+    for p in procs:
+        assert p.exitcode == 0, "a rank failed or timed out"
+    assert dict(ret) == {0: (True, True, True), 1: (True, True, True)}
