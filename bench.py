@@ -519,6 +519,160 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_gpu_seq_parallel(args):
+    """--seq-parallel: the second sharding axis.  Every rank holds ALL heads and a contiguous range of
+    whole cache blocks of every sequence; one step = scatter of the new rows (they land on the rank that
+    owns each sequence's last block), attention over the local part with the log-sum-exp as second
+    output, an all-gather of the per-rank (output, lse) records and their merge (fa_update arithmetic).
+    Same metric and timing rules as the default mode; `scaling` is "strong"."""
+    import torch
+    import torch.distributed as dist
+
+    from ms_custom_ops_b200 import _abi, kernels, sharding
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2 or world != args.gpus:
+        raise SystemExit("--seq-parallel needs torchrun with --gpus N >= 2 ranks")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=dev)
+
+    spec = workload_spec(args.workload)
+    # the same seeded caches on every rank (each rank only reads its own blocks of them)
+    case = workloads.decode_case_device(spec, dev, (0, spec.kv_heads))
+    lens = np.asarray([int(x) for x in case["context_lens"]], dtype=np.int32)
+    quant = 1 if spec.kv_int8 else 0
+    q, key, val = case["query"], case["key"], case["value"]
+    kc, vc, slot = case["key_cache"], case["value_cache"], case["slot_mapping"]
+    kd, vd = case["k_descale"], case["v_descale"]
+    tables_host = case["block_tables"].cpu().numpy()
+    lt, ll = sharding.seq_shard_tables(tables_host, lens, spec.block_size, rank, world)
+    bt_local = torch.from_numpy(lt).to(dev)
+    # the last rank's block range always ends with a sequence's last block: the new rows land there
+    slot_local = slot if rank == world - 1 else torch.full_like(slot, -1)
+
+    desc = kernels.make_pa_desc(q, kc, bt_local, case["qk_scale"], quant)
+    plan = _abi.PaPlan(desc, [int(x) for x in ll])
+    info = plan.info()
+    ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device=dev)
+    xch = sharding.SeqParallelExchange(spec.batch, spec.num_heads, spec.head_size, q.dtype, dev,
+                                       use_peer_stores=not args.nccl_gather)
+
+    def step():
+        if quant:
+            kernels.rac_scatter_quant(key, val, kc, vc, slot_local, kd, vd)
+        else:
+            kernels.rac_scatter(key, val, kc, vc, slot_local)
+        kernels.pa_launch(plan, q, kc, vc, bt_local, xch.out_local, ws, kd, None, vd, None, None, xch.lse_local)
+        return xch.exchange_and_merge()
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    kernels.pa_status(plan, ws)
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)).start() if rank == 0 else None
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    plan.profile_enable(True)
+    for _ in range(min(args.steps, 64)):
+        step()
+    torch.cuda.synchronize()
+    kernel_ms = plan.profile_read()
+    plan.profile_enable(False)
+    clocks = sampler.stop() if sampler else None
+    xch.check()
+    merged = step().clone()
+    torch.cuda.synchronize()
+
+    # end to end, serial: upload query / new rows, step, download the merged output, host waits
+    parts = [q, key, val]
+    h_parts = [x.cpu().pin_memory() for x in parts]
+    h_out = torch.empty(merged.shape, dtype=merged.dtype).pin_memory()
+
+    def e2e_step():
+        for d_x, h_x in zip(parts, h_parts):
+            d_x.copy_(h_x, non_blocking=True)
+        h_out.copy_(step(), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / args.steps
+
+    if rank == 0:
+        kvb = 1 if spec.kv_int8 else 2
+        alg_bytes = workloads.algorithmic_bytes_attention([int(x) for x in ll], spec.num_heads, spec.kv_heads,
+                                                          spec.head_size, kvb, quant=spec.kv_int8)
+        peak, peak_src = measured_hbm_peak()
+        roofline = {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None,
+                    "kernel": "pa_tma_kernel" if info.kernel == 2 else "pa_generic_kernel", "peak_source": peak_src,
+                    "algorithmic_bytes": alg_bytes, "note": "rank 0's part of every context"}
+        if kernel_ms:
+            kms = statistics.mean(kernel_ms)
+            roofline.update(achieved=alg_bytes / kms / 1e6, frac=alg_bytes / kms / 1e6 / peak, kernel_ms=kms,
+                            frac_of_8tbs=alg_bytes / kms / 1e6 / 8000.0, launches_timed=len(kernel_ms))
+        checked = None
+        if not args.no_cpu:
+            from oracle import c_oracle
+            nseq = min(spec.batch, 8)
+            host = {"query": _to_np(q[:nseq]), "key": _to_np(key[:nseq]), "value": _to_np(val[:nseq]),
+                    "key_cache": _to_np(kc), "value_cache": _to_np(vc), "block_tables": tables_host[:nseq],
+                    "slot_mapping": slot[:nseq].cpu().numpy(), "context_lens": lens[:nseq],
+                    "qk_scale": case["qk_scale"], "k_descale": None if kd is None else kd.cpu().numpy(),
+                    "v_descale": None if vd is None else vd.cpu().numpy()}
+            # rank 0 only wrote the rows it owns into its copy of the caches: let the oracle scatter all
+            ref = cpu_step(c_oracle, host, host_threads())
+            got = merged[:nseq].float().cpu().numpy()
+            err = np.abs(got - ref)
+            tol = 2e-2 if spec.kv_int8 else 1e-2
+            checked = {"sequences": nseq, "max_abs_err": float(err.max()), "max_abs_golden": float(np.abs(ref).max()),
+                       "within_tolerance": bool(np.all(err <= tol + tol * np.abs(ref))), "tolerance": tol}
+        launches = 3 + (1 if info.partials > 0 or int(ll.min()) == 0 else 0) + (0 if args.nccl_gather else 1)
+        line = {
+            "metric": METRIC, "value": spec.batch / ms_step * 1e3, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16" if spec.dtype == "bfloat16" else "f16", "data": "synthetic",
+            "config": workload_config(spec, [int(x) for x in lens], {
+                "parallelism": f"sequence sharding x{world}: block ranges of every context per rank, all heads; "
+                               + ("NCCL" if args.nccl_gather else "peer-store") + " all-gather of (output, lse) records, "
+                               "fa_update merge on every rank",
+                "l2": f"inputs larger than L2: {alg_bytes / 1e6:.0f} MB of KV on rank 0 per step vs {L2_BYTES >> 20} MB",
+                "launch": "eager launches on one stream", "work_items": info.work_items,
+                "split_partials": info.partials, "grid": info.grid}),
+            "e2e": {"value": spec.batch / e2e_ms * 1e3, "unit": UNIT,
+                    "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in parts),
+                    "d2h_bytes_per_step": h_out.numel() * h_out.element_size(), "ms_per_step": e2e_ms,
+                    "mode": "serial: upload, step, download, host waits"},
+            "gpu_launches": launches * args.steps, "roofline": roofline, "cpu_baseline": None,
+            "parity_check": checked, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    xch.release()
+    dist.destroy_process_group()
+
+
 def measure_scatter(spec, dev, peak):
     """Prefill-heavy reshape_and_cache of configuration 5: 16384 tokens (8 kv heads x 128) through an
     injective random slot map into 4096 blocks of 128 with 5 % of the slots set to -1, bf16 copy and
@@ -680,12 +834,16 @@ def main():
     ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays of the step")
     ap.add_argument("--nccl-gather", action="store_true", help="exchange outputs with NCCL instead of peer stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity check")
+    ap.add_argument("--seq-parallel", action="store_true",
+                    help="shard every context over the ranks (all heads per rank) instead of the kv heads")
     ap.add_argument("--adjacent", action="store_true",
                     help="also time paged_cache_load and fa_update on this workload (1 GPU)")
     ap.add_argument("--cpu-sample", type=int, default=64, help="sequences in the CPU sample")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.seq_parallel:
+        run_gpu_seq_parallel(args)
     else:
         run_gpu(args)
 

@@ -138,6 +138,15 @@ int msco_paged_cache_load(const void *key_cache, const void *value_cache, const 
 int msco_fa_update(const float *lse, const float *local_out, float *out, int64_t rows, int32_t head_size,
                    int32_t sp, void *stream);
 
+/* Extension (no reference counterpart): the same merge for partial outputs that are not one packed
+ * float32 tensor.  `dtype` (MSCO_DTYPE_F32 / F16 / BF16) is the element type of local_out AND out
+ * (what paged attention writes); partition s starts `lse_stride` floats after partition s - 1 in lse
+ * and `local_out_stride` elements after it in local_out, so that the per-rank (output, lse) records of
+ * an all-gathered buffer are merged where they lie.  head_size must be a multiple of 4; local_out, out
+ * and the partition stride must be aligned to four elements. */
+int msco_fa_update_strided(const float *lse, int64_t lse_stride, const void *local_out, int64_t local_out_stride,
+                           int32_t dtype, void *out, int64_t rows, int32_t head_size, int32_t sp, void *stream);
+
 /* ------------------------------------------------------------------------
  * paged_attention (decode: one query token per sequence).
  *

@@ -62,7 +62,7 @@ EXPORTS = (
     "msco_paged_attention_status", "msco_paged_attention_profile_enable", "msco_paged_attention_profile_read",
     "msco_paged_attention_launch_static", "msco_paged_attention_status_static",
     "msco_ipc_export", "msco_ipc_import", "msco_ipc_release", "msco_peer_allgather", "msco_decode_step",
-    "msco_paged_attention_launch_lse", "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update",
+    "msco_paged_attention_launch_lse", "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update", "msco_fa_update_strided",
 )
 
 
@@ -89,6 +89,8 @@ def lib():
     L.msco_paged_cache_load.argtypes = [vp] * 7 + [i32] * 4 + [i64] * 3 + [i32, vp, sz, vp, vp]
     L.msco_fa_update.restype = C.c_int
     L.msco_fa_update.argtypes = [vp, vp, vp, i64, i32, i32, vp]
+    L.msco_fa_update_strided.restype = C.c_int
+    L.msco_fa_update_strided.argtypes = [vp, i64, vp, i64, i32, vp, i64, i32, i32, vp]
     L.msco_paged_attention_split_tokens.restype = i32
     L.msco_paged_attention_split_tokens.argtypes = [i32, i32]
     L.msco_paged_attention_plan.restype = C.c_int

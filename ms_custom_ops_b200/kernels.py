@@ -76,6 +76,14 @@ def merge_partials(lse, local_out, out):
     _abi.check(_abi.lib().msco_fa_update(_ptr(lse), _ptr(local_out), _ptr(out), rows, hd, sp, _stream()))
 
 
+def merge_partials_strided(lse, lse_stride, local_out, local_out_stride, out, sp):
+    """msco_fa_update_strided on the current stream.  `lse` / `local_out` point at partition 0; partition s
+    lies lse_stride floats / local_out_stride elements further; `out` [rows, head_size] has local_out's dtype."""
+    rows, hd = out.shape[-2] if out.dim() == 2 else out.numel() // out.shape[-1], out.shape[-1]
+    _abi.check(_abi.lib().msco_fa_update_strided(_ptr(lse), int(lse_stride), _ptr(local_out), int(local_out_stride),
+                                                 msco_dtype(out.dtype), _ptr(out), rows, hd, int(sp), _stream()))
+
+
 def make_pa_desc(query, key_cache, block_tables, qk_scale, quant_type=0, has_quant_offset=False,
                  mask=None, mask_type=0, kernel=_abi.KERNEL_AUTO) -> _abi.MscoPaDesc:
     d = _abi.MscoPaDesc()

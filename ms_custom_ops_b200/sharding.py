@@ -133,6 +133,59 @@ def seq_parallel_merge(out_local, lse_local, merge, group=None):
     return merged.view(b, h, d)
 
 
+class SeqParallelExchange:
+    """Device side of a sequence-sharded decode step: the all-gather of the per-rank (output, lse)
+    records and their merge.
+
+    Every rank's attention launch writes its output (query dtype) and its log-sum-exps (float32) into
+    ONE record buffer, `out_local` and `lse_local` being views of it; `exchange_and_merge()` all-gathers
+    the raw records (this library's peer-store kernel over NVLink, or NCCL) and merges them where they
+    lie with msco_fa_update_strided.  No packing or conversion kernel in between.
+    """
+
+    def __init__(self, batch, q_heads, head_dim, dtype, device, use_peer_stores=True, group=None):
+        import torch
+        import torch.distributed as dist
+        from . import kernels
+        self._torch, self._dist, self._kernels, self.group = torch, dist, kernels, group
+        self.world = dist.get_world_size(group)
+        es = torch.empty((), dtype=dtype).element_size()
+        rows = batch * q_heads
+        n_out = rows * head_dim * es
+        self.off_lse = (n_out + 255) // 256 * 256
+        self.rec_bytes = (self.off_lse + rows * 4 + 255) // 256 * 256
+        self.es, self.rows = es, rows
+        self.record = torch.zeros(self.rec_bytes, dtype=torch.uint8, device=device)
+        self.out_local = self.record[:n_out].view(dtype).view(batch, q_heads, head_dim)
+        self.lse_local = self.record[self.off_lse:self.off_lse + rows * 4].view(torch.float32).view(batch, q_heads)
+        self.merged = torch.empty((batch, q_heads, head_dim), dtype=dtype, device=device)
+        self.peer = PeerGather((self.rec_bytes,), torch.uint8, device, group) if use_peer_stores else None
+        self.gathered = None if use_peer_stores else torch.empty((self.world, self.rec_bytes), dtype=torch.uint8,
+                                                                 device=device)
+
+    def exchange_and_merge(self):
+        """All-gather the records, merge; returns the merged output [batch, q_heads, head_dim]."""
+        torch = self._torch
+        if self.peer is not None:
+            g = self.peer.gather(self.record)
+        else:
+            g = self.gathered
+            self._dist.all_gather_into_tensor(g.view(-1), self.record, group=self.group)
+        lse0 = g[0, self.off_lse:self.off_lse + self.rows * 4].view(torch.float32)
+        out0 = g[0, :self.rows * self.merged.shape[-1] * self.es].view(self.merged.dtype)
+        self._kernels.merge_partials_strided(lse0, self.rec_bytes // 4, out0, self.rec_bytes // self.es,
+                                             self.merged.view(self.rows, -1), self.world)
+        return self.merged
+
+    def check(self):
+        if self.peer is not None:
+            self.peer.check()
+
+    def release(self):
+        if self.peer is not None:
+            self.peer.release()
+
+
 class PeerGather:
     """All-gather of per-rank outputs by peer stores over NVLink (msco_peer_allgather).
 

@@ -96,3 +96,29 @@ def test_sequence_sharded_decode_equals_unsharded(config, world):
     g = oracle.paged_attention_golden(v["query"], v["key_cache"], v["value_cache"], v["block_tables"], lens,
                                       v["qk_scale"], v["k_descale"], v["v_descale"])
     assert_close(to_np(merged), g, tol, f"c{config} merged vs oracle, {world} ranks")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_strided_merge_of_gathered_records(dtype):
+    # records as the sequence-sharded step all-gathers them: [output rows | lse], one per rank
+    sp, rows, hd = 4, 96, 128
+    es = torch.empty((), dtype=dtype).element_size()
+    off_lse = (rows * hd * es + 255) // 256 * 256
+    rec = (off_lse + rows * 4 + 255) // 256 * 256
+    g = torch.zeros(sp, rec, dtype=torch.uint8, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    outs = torch.randn(sp, rows, hd, device="cuda", generator=gen).to(dtype)
+    lses = torch.randn(sp, rows, device="cuda", generator=gen) * 3
+    lses[1, 5] = -float("inf")
+    for s in range(sp):
+        g[s, :rows * hd * es].view(dtype).view(rows, hd).copy_(outs[s])
+        g[s, off_lse:off_lse + rows * 4].view(torch.float32).copy_(lses[s])
+    merged = torch.empty(rows, hd, dtype=dtype, device="cuda")
+    kernels.merge_partials_strided(g[0, off_lse:].view(torch.float32), rec // 4, g[0, :rows * hd * es].view(dtype),
+                                   rec // es, merged, sp)
+    want = oracle.fa_update_golden(to_np(lses), to_np(outs.float()))
+    tol = {torch.float32: 1e-6, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[dtype]
+    np.testing.assert_allclose(to_np(merged.float()), want, rtol=tol, atol=tol)
+    # and the packed float32 operator gives the same as the strided entry on packed float32 input
+    if dtype == torch.float32:
+        assert torch.equal(ops.fa_update(lses, outs, 0, sp), merged)
