@@ -210,6 +210,9 @@ __global__ void __launch_bounds__(kGenThreads) pa_generic_kernel(PaParams p, con
 // registers, and the partial rows are accumulated in split order with several loads in flight.
 template <typename TQ>
 __global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p, const __grid_constant__ PlanParam pp) {
+  // a kernel launched behind this one with programmatic stream serialisation (the peer all-gather
+  // of a sharded step) may become resident now; it waits for this grid before it reads the output
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // launched with programmatic stream serialisation: wait here until the attention grid before us
   // has completed and its partials are visible (a no-op for an ordinary launch)
   asm volatile("griddepcontrol.wait;" ::: "memory");

@@ -46,9 +46,13 @@ peer_gather_kernel(GatherArgs a, const uint4 *__restrict__ local, uint32_t step,
                    int32_t *status) {
   __shared__ bool is_last;
   const int64_t n16 = a.slice_bytes / 16;
+  // launched with programmatic stream serialisation: the kernels of this library that produce
+  // `local` let their dependents start early; wait here until they have completed and their
+  // writes are visible (a no-op behind anything else)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // 1. push the local slice into slot `rank` of every rank's gathered buffer (own copy included)
   for (int64_t i = (int64_t)blockIdx.x * kPushThreads + threadIdx.x; i < n16; i += (int64_t)gridDim.x * kPushThreads) {
-    const uint4 v = __ldg(local + i);
+    const uint4 v = __ldcg(local + i);
     for (int r = 0; r < a.world; ++r)
       reinterpret_cast<uint4 *>(static_cast<char *>(a.gathered[r]) + (int64_t)a.rank * a.slice_bytes)[i] = v;
   }
@@ -146,8 +150,16 @@ extern "C" int msco_peer_allgather(const MscoGatherDesc *desc, const void *local
   const int64_t n16 = desc->slice_bytes / 16;
   int blocks = (int)((n16 + kPushThreads - 1) / kPushThreads);
   blocks = blocks < 1 ? 1 : (blocks > kPushMaxBlocks ? kPushMaxBlocks : blocks);
-  peer_gather_kernel<<<blocks, kPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      a, static_cast<const uint4 *>(local_out), step, desc->ticket, desc->status);
-  MSCO_CUDA_CHECK(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(kPushThreads);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, peer_gather_kernel, a, static_cast<const uint4 *>(local_out), step,
+                                     desc->ticket, desc->status));
   return MSCO_OK;
 }
