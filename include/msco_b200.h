@@ -224,6 +224,17 @@ int msco_paged_attention_launch(const MscoPaPlan *plan, const void *query, const
                                 const void *attn_mask, void *out, void *workspace,
                                 size_t workspace_bytes, void *stream);
 
+/* Multi-token (speculative) queries, calc_type = 1 of the operator (q_seq_len of
+ * CustomASDPagedAttentionParam, paged_attention_graph.cc:758-762): every query token is a row of the
+ * decode batch -- plan with one context length per TOKEN (its sequence's), launch with a block table
+ * that has one row per token.  This helper builds that table on the device:
+ * dst[i, :] = src[host_row_of[i], :] for i < out_rows (src [src_rows, cols], dst [out_rows, cols], both
+ * device int32).  host_row_of is host memory (copied into device_row_of, out_rows device int32s, on
+ * `stream`; it may be freed when the call returns).  The SPEC mask [tokens, max_context] is then the
+ * NORM decode mask of that batch (mask_type 1, mask_batch_stride = max_context). */
+int msco_expand_rows_i32(const int32_t *src, int32_t src_rows, int32_t cols, const int32_t *host_row_of,
+                         int32_t out_rows, int32_t *dst, int32_t *device_row_of, void *stream);
+
 /* Extension (the reference operator has no such output): the same launch that also writes
  * lse[batch, num_q_heads] float32 = log(sum over the context of exp(qk_scale * q.k + mask)), natural
  * logarithm, -inf for an empty context.  With it, outputs computed over different parts of a context

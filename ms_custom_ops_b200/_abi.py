@@ -62,7 +62,7 @@ EXPORTS = (
     "msco_paged_attention_status", "msco_paged_attention_profile_enable", "msco_paged_attention_profile_read",
     "msco_paged_attention_launch_static", "msco_paged_attention_status_static",
     "msco_ipc_export", "msco_ipc_import", "msco_ipc_release", "msco_peer_allgather", "msco_decode_step",
-    "msco_paged_attention_launch_lse", "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update", "msco_fa_update_strided",
+    "msco_paged_attention_launch_lse", "msco_expand_rows_i32", "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update", "msco_fa_update_strided",
 )
 
 
@@ -103,6 +103,8 @@ def lib():
     L.msco_paged_attention_plan_destroy.argtypes = [vp]
     L.msco_paged_attention_launch.restype = C.c_int
     L.msco_paged_attention_launch.argtypes = [vp] * 12 + [sz, vp]
+    L.msco_expand_rows_i32.restype = C.c_int
+    L.msco_expand_rows_i32.argtypes = [vp, i32, i32, C.POINTER(i32), i32, vp, vp, vp]
     L.msco_paged_attention_launch_lse.restype = C.c_int
     L.msco_paged_attention_launch_lse.argtypes = [vp] * 13 + [sz, vp]
     L.msco_paged_attention_status.restype = C.c_int

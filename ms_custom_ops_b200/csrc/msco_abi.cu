@@ -347,6 +347,43 @@ extern "C" int msco_paged_attention_launch(const MscoPaPlan *plan, const void *q
                         attn_mask, out, workspace, workspace_bytes, stream, false);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Multi-token (speculative) queries: every query token becomes a row of the decode batch that shares
+// the block table of its sequence.  This builds the per-token block table on the device.
+// ---------------------------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(256)
+expand_rows_kernel(const int32_t *__restrict__ src, const int32_t *__restrict__ row_of, int32_t *__restrict__ dst,
+                   int out_rows, int cols) {
+  const int64_t total = (int64_t)out_rows * cols;
+  for (int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * 256) {
+    const int r = (int)(idx / cols);
+    dst[idx] = __ldg(src + (int64_t)__ldg(row_of + r) * cols + (idx - (int64_t)r * cols));
+  }
+}
+}  // namespace
+
+extern "C" int msco_expand_rows_i32(const int32_t *src, int32_t src_rows, int32_t cols, const int32_t *host_row_of,
+                                    int32_t out_rows, int32_t *dst, int32_t *device_row_of, void *stream) {
+  if (src_rows < 0 || cols < 0 || out_rows < 0) return fail(MSCO_ERR_INVALID_ARG, "expand_rows: negative size");
+  if (out_rows == 0 || cols == 0) return MSCO_OK;
+  if (src == nullptr || host_row_of == nullptr || dst == nullptr || device_row_of == nullptr)
+    return fail(MSCO_ERR_INVALID_ARG, "expand_rows: NULL argument");
+  for (int32_t i = 0; i < out_rows; ++i)
+    if (host_row_of[i] < 0 || host_row_of[i] >= src_rows)
+      return fail(MSCO_ERR_INVALID_ARG, "expand_rows: row %d of the output names source row %d of %d", i,
+                  host_row_of[i], src_rows);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // pageable source: staged before the call returns, the caller may free it right away
+  MSCO_CUDA_CHECK(cudaMemcpyAsync(device_row_of, host_row_of, (size_t)out_rows * sizeof(int32_t),
+                                  cudaMemcpyHostToDevice, st));
+  const int64_t total = (int64_t)out_rows * cols;
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>((total + 255) / 256, 148 * 8));
+  expand_rows_kernel<<<grid, 256, 0, st>>>(src, device_row_of, dst, out_rows, cols);
+  MSCO_CUDA_CHECK(cudaGetLastError());
+  return MSCO_OK;
+}
+
 // The same launch with a second output: lse[batch, num_q_heads] (float32), the natural-log sum of
 // exp over the context of the scaled (and masked) scores -- what fa_update needs to merge outputs
 // computed over different parts of a context.  -inf for an empty context.

@@ -275,13 +275,14 @@ void CheckBuiltForB200(const PaInputs &in) {
                    << " (full int8 QKV) is not built for B200; quant_type 0 and 1 are.";
   if (a.quant_type != kQuantUnquant && a.quant_type != kQuantDequantFusion)
     MS_VALUE_ERROR << "For PagedAttention, quant_type is invalid, got " << a.quant_type << ".";
-  if (a.mask_type == kMaskSpec || a.mask_type == kMaskFree)
-    MS_UNSUPPORTED << "For PagedAttention, mask_type=" << a.mask_type
-                   << " is not built for B200; mask_type 0 (none), 1 (NORM) and 2 (ALIBI) are.";
   if (a.mask_type < 0 || a.mask_type > kMaskFree)
     MS_VALUE_ERROR << "For PagedAttention, mask_type is invalid, got " << a.mask_type << ".";
-  if (a.calc_type == kCalcSpec)
-    MS_UNSUPPORTED << "For PagedAttention, calc_type=1 (multi-token / MTP queries) is not built for B200.";
+  if (a.mask_type == kMaskFree || (a.mask_type == kMaskSpec && a.calc_type != kCalcSpec))
+    MS_UNSUPPORTED << "For PagedAttention, mask_type=" << a.mask_type << " is not built for B200; mask_type 0 (none), "
+                   << "1 (NORM), 2 (ALIBI), and 3 (SPEC) together with calc_type=1 are.";
+  if (a.calc_type == kCalcSpec && (a.mask_type == kMaskNorm || a.mask_type == kMaskAlibi))
+    MS_UNSUPPORTED << "For PagedAttention, calc_type=1 (multi-token queries) is built for B200 with mask_type 0 "
+                   << "(none) or 3 (SPEC); the prefill-shaped NORM / ALIBI masks are not.";
   if (a.compress_type != kCompressNone)
     MS_UNSUPPORTED << "For PagedAttention, compress_type=" << a.compress_type << " is not built for B200.";
   if (a.scale_type != kScaleTor)
@@ -296,9 +297,20 @@ void CheckBuiltForB200(const PaInputs &in) {
 
 struct Prepared {
   MscoPaDesc desc;
-  std::vector<int32_t> context_lens;
-  int64_t batch = 0;
+  std::vector<int32_t> context_lens;  // one per row of the decode batch (per query token with calc_type = 1)
+  int64_t batch = 0;                  // rows of the decode batch = query.dim(0)
+  // calc_type = 1 (multi-token queries): every query token is a row of the decode batch that shares
+  // the block table and the context length of its sequence (paged_attention_graph.cc:758-762, q_seq_len)
+  bool multi_token = false;
+  std::vector<int32_t> seq_of_row;  // sequence (row of block_tables) of every query token
 };
+
+// Bytes behind the plan's workspace that hold the per-token block table and its row index.
+size_t TokenTableBytes(const Prepared &p) {
+  if (!p.multi_token) return 0;
+  const size_t cells = static_cast<size_t>(p.batch) * static_cast<size_t>(p.desc.max_blocks_per_seq);
+  return (cells * 4 + 255) / 256 * 256 + (static_cast<size_t>(p.batch) * 4 + 255) / 256 * 256;
+}
 
 Prepared Prepare(const PaInputs &in) {
   const MsPagedAttentionArgs &a = *in.a;
@@ -312,6 +324,31 @@ Prepared Prepare(const PaInputs &in) {
   Prepared p;
   p.context_lens = GetInt32VectorFromHostTensor(in.context_lens, kOpName, "context_lens");
   p.batch = in.query.dim(0);
+  const int64_t num_seqs = static_cast<int64_t>(p.context_lens.size());
+  if (a.calc_type == kCalcSpec) {
+    if (!in.q_seq_lens.defined())
+      MS_RUNTIME_ERROR << "For " << kOpName << ", calc_type is SPEC(MTP), q_seq_lens must be provided.";
+    const std::vector<int32_t> q_lens = GetInt32VectorFromHostTensor(in.q_seq_lens, kOpName, "q_seq_lens");
+    if (static_cast<int64_t>(q_lens.size()) != num_seqs)
+      MS_VALUE_ERROR << "For PagedAttention, q_seq_lens has " << q_lens.size() << " entries but context_lens has "
+                     << num_seqs << ".";
+    std::vector<int32_t> per_token;
+    for (int64_t b = 0; b < num_seqs; ++b) {
+      if (q_lens[b] < 0) MS_VALUE_ERROR << "For PagedAttention, q_seq_lens must not be negative, but got " << q_lens[b] << ".";
+      for (int32_t t = 0; t < q_lens[b]; ++t) {
+        p.seq_of_row.push_back(static_cast<int32_t>(b));
+        per_token.push_back(p.context_lens[b]);
+      }
+    }
+    if (static_cast<int64_t>(per_token.size()) != p.batch)
+      MS_VALUE_ERROR << "For PagedAttention, q_seq_lens sum to " << per_token.size() << " but query holds " << p.batch
+                     << " tokens.";
+    if (in.block_tables.dim(0) != num_seqs)
+      MS_VALUE_ERROR << "For PagedAttention, block_tables has " << in.block_tables.dim(0) << " rows but there are "
+                     << num_seqs << " sequences.";
+    p.context_lens.swap(per_token);
+    p.multi_token = true;
+  }
   const int64_t hq = in.query.dim(1), d = in.query.dim(2);
   const int64_t hkv = in.key_cache.dim(2);
   if (hq != a.q_head_num)
@@ -326,7 +363,7 @@ Prepared Prepare(const PaInputs &in) {
   if (static_cast<int64_t>(p.context_lens.size()) != p.batch)
     MS_VALUE_ERROR << "For PagedAttention, context_lens has " << p.context_lens.size()
                    << " entries but query holds " << p.batch << " tokens (decode: one token per sequence).";
-  if (in.block_tables.dim(0) != p.batch)
+  if (!p.multi_token && in.block_tables.dim(0) != p.batch)
     MS_VALUE_ERROR << "For PagedAttention, block_tables has " << in.block_tables.dim(0) << " rows but the batch is "
                    << p.batch << ".";
   if (in.block_tables.dtype() != MSCO_DTYPE_I32)
@@ -384,7 +421,13 @@ Prepared Prepare(const PaInputs &in) {
       MS_VALUE_ERROR << "For PagedAttention, attn_mask must be provided when mask_type is " << a.mask_type << ".";
     const Tensor &m = in.attn_mask;
     const int64_t max_len = p.context_lens.empty() ? 0 : *std::max_element(p.context_lens.begin(), p.context_lens.end());
-    if (a.mask_type == kMaskNorm) {  // decode: [batch, 1, max_context]
+    if (a.mask_type == kMaskSpec) {  // [tokens, max_context]: the NORM decode mask of the per-token batch
+      if (m.rank() != 2 || m.dim(0) != p.batch)
+        MS_VALUE_ERROR << "For PagedAttention, the SPEC mask must have shape (num_tokens, max_context).";
+      ds.mask_type = kMaskNorm;
+      ds.mask_batch_stride = m.dim(1);
+      ds.mask_head_stride = 0;
+    } else if (a.mask_type == kMaskNorm) {  // decode: [batch, 1, max_context]
       if (m.rank() != 3 || m.dim(0) != p.batch || m.dim(1) != 1)
         MS_VALUE_ERROR << "For PagedAttention, the NORM mask of a decode step must have shape (batch, 1, max_context).";
       ds.mask_batch_stride = m.dim(2);
@@ -443,7 +486,9 @@ extern "C" int ms_custom_ops_paged_attention_workspace_size(const MsPagedAttenti
     const PaInputs in = Unpack(args);
     const Prepared p = Prepare(in);
     PlanRef plan = PlanCache::Instance().GetOrCreate(p.desc, p.context_lens);
-    if (bytes) *bytes = std::max<size_t>(msco_paged_attention_workspace_bytes(plan.get()), 256);
+    if (bytes)
+      *bytes = (std::max<size_t>(msco_paged_attention_workspace_bytes(plan.get()), 256) + 255) / 256 * 256 +
+               TokenTableBytes(p);
     return MSCO_OK;
   });
 }
@@ -474,11 +519,25 @@ int LaunchPagedAttention(const MsPagedAttentionArgs *args, const Tensor &out, co
   if (p.batch == 0) return MSCO_OK;
   (void)CheckAndUpdate(p.context_lens, &g_prev_context_lens);
   PlanRef plan = PlanCache::Instance().GetOrCreate(p.desc, p.context_lens);
-  g_last_workspace_need = std::max<size_t>(msco_paged_attention_workspace_bytes(plan.get()), 256);
+  const size_t plan_ws = (std::max<size_t>(msco_paged_attention_workspace_bytes(plan.get()), 256) + 255) / 256 * 256;
+  g_last_workspace_need = plan_ws + TokenTableBytes(p);
   if (workspace == nullptr || workspace_bytes < g_last_workspace_need)
     MS_VALUE_ERROR << "For PagedAttention, the workspace holds " << workspace_bytes << " bytes but this launch needs "
                    << g_last_workspace_need << ".";
   const int32_t *tables = static_cast<const int32_t *>(in.block_tables.data());
+  if (p.multi_token) {
+    // one block-table row per query token, built behind the plan's part of the workspace
+    const size_t cells = static_cast<size_t>(p.batch) * static_cast<size_t>(p.desc.max_blocks_per_seq);
+    int32_t *token_tables = reinterpret_cast<int32_t *>(static_cast<char *>(workspace) + plan_ws);
+    int32_t *row_index = reinterpret_cast<int32_t *>(static_cast<char *>(workspace) + plan_ws +
+                                                     (cells * 4 + 255) / 256 * 256);
+    const int rc = msco_expand_rows_i32(tables, static_cast<int32_t>(in.block_tables.dim(0)),
+                                        p.desc.max_blocks_per_seq, p.seq_of_row.data(),
+                                        static_cast<int32_t>(p.batch), token_tables, row_index, stream);
+    if (rc != MSCO_OK) return rc;
+    tables = token_tables;
+  }
+  workspace_bytes = plan_ws;
   const float *kd = static_cast<const float *>(in.k_descale.data());
   const float *vd = static_cast<const float *>(in.v_descale.data());
   const int32_t *ko = static_cast<const int32_t *>(in.k_offset.data());

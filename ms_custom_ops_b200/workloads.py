@@ -45,8 +45,9 @@ def _round_to(a32: np.ndarray, dtype: str) -> np.ndarray:
 # --------------------------------------------------------------------------
 def st_style_case(seed, num_heads, kv_heads, head_size, block_size, num_blocks, context_lens,
                   q_dtype="float16", kv_dtype=None, quant_type=0, has_quant_offset=False,
-                  mask_type=0, qk_scale=None):
-    """Inputs of one reference-style decode test (one query token per sequence).
+                  mask_type=0, qk_scale=None, q_seq_lens=None):
+    """Inputs of one reference-style decode test (one query token per sequence; with `q_seq_lens`
+    several per sequence, the multi-token / speculative form with the SPEC mask, mask_type 3).
 
     Draw order and distributions follow the reference generator
     (tests/st/test_custom_paged_attention.py:87-92,176-190,196-246,280-299):
@@ -57,7 +58,8 @@ def st_style_case(seed, num_heads, kv_heads, head_size, block_size, num_blocks, 
     rng = np.random.default_rng(seed)
     random.seed(seed)
     batch = len(context_lens)
-    q32 = rng.uniform(-1.0, 1.0, (batch, num_heads, head_size))
+    num_tokens = batch if q_seq_lens is None else int(sum(q_seq_lens))
+    q32 = rng.uniform(-1.0, 1.0, (num_tokens, num_heads, head_size))
     if q_dtype == "float16":
         query = q32.astype(np.float16)
     else:
@@ -93,6 +95,15 @@ def st_style_case(seed, num_heads, kv_heads, head_size, block_size, num_blocks, 
             if kl:
                 bias = (np.arange(kl, dtype=np.int32) - kl + 1).astype(np.float32)
                 mask[i, :, :, :kl] = slopes.reshape(-1, 1, 1) * bias.reshape(1, 1, -1)
+    elif mask_type == 3:  # SPEC (:509-524): causal inside the window of the last q_len context positions
+        ql_all = [1] * batch if q_seq_lens is None else list(q_seq_lens)
+        mask = np.zeros((num_tokens, max(context_lens)), dtype=np.float32)
+        pre = 0
+        for ql, kl in zip(ql_all, context_lens):
+            if ql and kl:
+                start = max(0, kl - ql)
+                mask[pre:pre + ql, start:kl] = np.triu(np.ones((ql, ql), dtype=np.float32), 1) * -10000.0
+            pre += ql
     k_descale = v_descale = k_offset = v_offset = None
     if quant_type == 1:
         k_descale = rng.integers(-1, 2, size=(kv_heads * head_size,)).astype(np.float32)
@@ -103,6 +114,7 @@ def st_style_case(seed, num_heads, kv_heads, head_size, block_size, num_blocks, 
     return {
         "query": query, "key_cache": kc, "value_cache": vc, "block_tables": tables,
         "context_lens": np.array(context_lens, dtype=np.int32), "mask": mask, "mask_type": mask_type,
+        "q_seq_lens": None if q_seq_lens is None else np.array(q_seq_lens, dtype=np.int32),
         "k_descale": k_descale, "v_descale": v_descale, "k_offset": k_offset, "v_offset": v_offset,
         "q_dtype": q_dtype, "kv_dtype": kv_dtype, "quant_type": quant_type,
         "has_quant_offset": has_quant_offset,

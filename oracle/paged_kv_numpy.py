@@ -108,7 +108,7 @@ def _gather_seq(cache_f32, table_row, kv_len, block_size):
 
 def paged_attention_golden(query, key_cache, value_cache, block_tables, context_lens, scale,
                            k_descale=None, v_descale=None, k_offset=None, v_offset=None,
-                           mask=None, mask_type=0, return_lse=False):
+                           mask=None, mask_type=0, return_lse=False, q_seq_lens=None):
     """float32 decode attention over a paged KV cache, one query token per sequence.
 
     Follows tests/st/test_custom_paged_attention.py:
@@ -120,7 +120,11 @@ def paged_attention_golden(query, key_cache, value_cache, block_tables, context_
       :644-646  sequences of length 0 produce zeros,
       :880-903  additive masks: NORM ``mask[b, 0, :kl]`` (mask_type 1),
                 ALIBI ``mask[b, :, 0, :kl]`` (mask_type 2).
-    Returns float32 ``[batch, q_heads, head_dim]``; the caller casts to the
+      :641-693  with ``q_seq_lens`` (multi-token queries) sequence ``b`` owns
+                ``q_seq_lens[b]`` consecutive query rows, each attending the whole
+                context of the sequence,
+      :877-879  SPEC ``mask[token, :kl]`` per query row (mask_type 3).
+    Returns float32 ``[tokens, q_heads, head_dim]``; the caller casts to the
     query dtype as the reference does (:693-699).  With ``return_lse`` also
     ``log(sum(exp(scores)))`` per (sequence, q head), -inf for an empty context
     (the quantity tests/st/test_asd_faupdate.py:34-59 merges partial outputs by).
@@ -144,12 +148,18 @@ def paged_attention_golden(query, key_cache, value_cache, block_tables, context_
     out = np.zeros((nt, hq, vc.shape[3]), dtype=np.float32)
     lse = np.full((nt, hq), -np.inf, dtype=np.float32)
     m = None if mask is None else np.asarray(mask).astype(np.float32)
-    for b in range(nt):
-        kl = int(lens[b])
+    # one entry per query row: (row, sequence it belongs to)
+    if q_seq_lens is None:
+        rows = [(b, b) for b in range(nt)]
+    else:
+        rows = [(t, b) for b, (t0, n) in enumerate(zip(np.concatenate([[0], np.cumsum(q_seq_lens)[:-1]]),
+                                                       q_seq_lens)) for t in range(int(t0), int(t0) + int(n))]
+    for b, seq in rows:
+        kl = int(lens[seq])
         if kl == 0:
             continue
-        ks = _gather_seq(kc, tables[b], kl, bs)  # [kl, hkv, d]
-        vs = _gather_seq(vc, tables[b], kl, bs)
+        ks = _gather_seq(kc, tables[seq], kl, bs)  # [kl, hkv, d]
+        vs = _gather_seq(vc, tables[seq], kl, bs)
         qg = q[b].reshape(hkv, g, d)
         scores = np.matmul(qg, np.transpose(ks, (1, 2, 0))) * np.float32(scale)  # [hkv, g, kl]
         if m is not None:
@@ -157,8 +167,10 @@ def paged_attention_golden(query, key_cache, value_cache, block_tables, context_
                 scores = scores + m[b, :, 0, :kl].reshape(hkv, g, kl)
             elif mask_type == 1:  # NORM decode [tokens, 1, max_ctx]
                 scores = scores + m[b, 0, :kl][None, None, :]
+            elif mask_type == 3:  # SPEC [tokens, max_ctx]
+                scores = scores + m[b, :kl][None, None, :]
             else:
-                raise ValueError("oracle supports decode masks NORM(1)/ALIBI(2) only")
+                raise ValueError("oracle supports the masks NORM(1) / ALIBI(2) of decode and SPEC(3)")
         smax = np.max(scores, axis=-1, keepdims=True)
         e = np.exp(scores - smax)
         p = e / np.sum(e, axis=-1, keepdims=True)

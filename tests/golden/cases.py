@@ -59,6 +59,24 @@ RAC_CASES = {
 }
 
 
+# multi-token (speculative) query cases: (seed, heads, kv_heads, head_size, block_size, num_blocks,
+#   q_seq_lens, context_lens, dtype, qk_scale); SPEC mask.  Shapes of the reference's MTP / lookahead tests
+#   (tests/st/test_custom_paged_attention.py:1673-1696, 2753-2830).
+MTP_CASES = {
+    "spec_mtp_fp16": (3002, 32, 1, 128, 128, 64, [2, 2, 2, 2], [192, 193, 194, 195], "float16", 0.01),
+    "spec_mtp_bf16": (3002, 32, 1, 128, 128, 64, [2, 2, 2, 2], [192, 193, 194, 195], "bfloat16", 0.01),
+    "lookahead_mixed": (9001, 32, 32, 128, 128, 64, [1, 15, 30, 6], [10, 64, 64, 64], "float16", None),
+    "lookahead_block16": (9003, 32, 32, 128, 16, 256, [1, 15, 30, 6], [10, 64, 64, 64], "float16", None),
+    "lookahead_gqa_bf16": (9004, 16, 4, 64, 32, 128, [3, 1, 8], [515, 40, 1300], "bfloat16", None),
+}
+
+
+def mtp_case(name):
+    from ms_custom_ops_b200 import workloads
+    seed, h, kvh, hd, bs, nb, qlens, lens, dt, scale = MTP_CASES[name]
+    return workloads.st_style_case(seed, h, kvh, hd, bs, nb, lens, dt, None, 0, False, 3, scale, q_seq_lens=qlens)
+
+
 def st_case(name, mask_free=False):
     from ms_custom_ops_b200 import workloads
     seed, h, kvh, hd, bs, nb, lens, qd, kvd, quant, off, scale, mask = ST_CASES[name]

@@ -17,6 +17,7 @@ reproduces the reference generator's inputs bit for bit.
 
 Written files (tests/golden/):
   pa_<case>.npz       golden output + sha256 of every input
+  pa_mtp_<case>.npz   the same for the multi-token (speculative) query cases
   rac_<case>.npz      sha256 of the golden caches (and of the inputs)
   config1.npz         benchmark configuration 1: cache digests after the scatter + attention output
   pcl_<case>.npz      sha256 of the gathered K / V (and of the input caches)
@@ -64,6 +65,21 @@ def main(ref_root):
         np.savez_compressed(os.path.join(HERE, f"pa_{name}.npz"), golden=np.asarray(golden),
                             **{f"sha_{k}": np.array(v) for k, v in digests.items()})
         print("pa", name, golden.dtype, golden.shape)
+
+    for name, (seed, h, kvh, hd, bs, nb, qlens, lens, dt, _scale) in cases.MTP_CASES.items():
+        case = cases.mtp_case(name)
+        gen = tpa.PagedAttentionDataGenerator(seed)
+        ref_in = gen.generate_inputs(h, kvh, hd, bs, nb, qlens, lens, msd[dt], msd[dt], 3, 0, False)
+        for key in ("query", "key_cache", "value_cache", "block_tables", "mask"):
+            assert np.array_equal(np.asarray(ref_in[key]).astype(np.float32),
+                                  np.asarray(case[key]).astype(np.float32)), (name, key)
+        golden = gen.compute_golden_reference(
+            ref_in["query"], ref_in["key_cache"], ref_in["value_cache"], ref_in["block_tables"],
+            ref_in["q_seq_lens"], ref_in["kv_seq_lens"], case["qk_scale"], ref_in["mask"], 3)
+        np.savez_compressed(os.path.join(HERE, f"pa_mtp_{name}.npz"), golden=np.asarray(golden),
+                            sha_query=np.array(cases.digest(case["query"])),
+                            sha_key_cache=np.array(cases.digest(case["key_cache"])))
+        print("pa_mtp", name, golden.dtype, golden.shape)
 
     for name in cases.RAC_CASES:
         c = cases.rac_case(name)

@@ -90,7 +90,9 @@ def test_infer_returns_query_shape_and_dtype():
     (dict(q_head_num=32, kv_head_num=8, mask_type=4), ValueError, "MASK_FREE is only supported on 310P"),
     (dict(q_head_num=32, kv_head_num=8, mask_type=1), ValueError, "attn_mask must be provided"),
     # accepted by the reference, not built here
-    (dict(q_head_num=32, kv_head_num=8, calc_type=1), ops.UnsupportedOnB200, "calc_type=1"),
+    (dict(q_head_num=32, kv_head_num=8, calc_type=1), ops.MscoError, "q_seq_lens must be provided"),
+    (dict(q_head_num=32, kv_head_num=8, calc_type=1, q_seq_lens=[1, 1, 1, 1], mask_type=1,
+          attn_mask=T((4, 1, 1024), "float16")), ops.UnsupportedOnB200, "prefill-shaped"),
     (dict(q_head_num=32, kv_head_num=8, mask_type=3), ops.UnsupportedOnB200, "mask_type=3"),
     (dict(q_head_num=32, kv_head_num=8, scale_type=1), ops.UnsupportedOnB200, "LogN"),
     (dict(q_head_num=32, kv_head_num=8, input_layout=1), ops.UnsupportedOnB200, "BNSD"),
@@ -134,6 +136,31 @@ def test_shape_and_type_rules():
         ops.paged_attention_infer(Q, KC, KC, BT, T((4,), "int32", on_host=False), **OKW)
     with pytest.raises(ops.MscoError, match="must be Int32"):
         ops.paged_attention_infer(Q, KC, KC, BT, np.array([1, 2, 3, 4], dtype=np.int64), **OKW)
+
+
+def test_multi_token_queries_infer_and_validation():
+    # calc_type = 1: query holds sum(q_seq_lens) tokens, block tables / context_lens one row per sequence
+    q6 = T((6, 32, 128), "float16")
+    mtp = dict(OKW, calc_type=1, q_seq_lens=[2, 1, 3, 0])
+    assert ops.paged_attention_infer(q6, KC, KC, BT, LENS, **mtp) == ((6, 32, 128), "float16")
+    spec = dict(mtp, mask_type=3, attn_mask=T((6, 1024), "float16"))
+    assert ops.paged_attention_infer(q6, KC, KC, BT, LENS, **spec)[0] == (6, 32, 128)
+    with pytest.raises(ValueError, match="sum to 6 but query holds 4"):
+        ops.paged_attention_infer(Q, KC, KC, BT, LENS, **mtp)
+    with pytest.raises(ValueError, match="q_seq_lens has 3 entries"):
+        ops.paged_attention_infer(q6, KC, KC, BT, LENS, **dict(mtp, q_seq_lens=[2, 2, 2]))
+    with pytest.raises(ValueError, match="must not be negative"):
+        ops.paged_attention_infer(q6, KC, KC, BT, LENS, **dict(mtp, q_seq_lens=[7, -1, 0, 0]))
+    with pytest.raises(ValueError, match="SPEC mask must have shape"):
+        ops.paged_attention_infer(q6, KC, KC, BT, LENS, **dict(spec, attn_mask=T((4, 1024), "float16")))
+    with pytest.raises(ValueError, match="the mask covers 512"):
+        ops.paged_attention_infer(q6, KC, KC, BT, LENS, **dict(spec, attn_mask=T((6, 512), "float16")))
+    with pytest.raises(ValueError, match="block_tables has 5 rows"):
+        ops.paged_attention_infer(q6, KC, KC, T((5, 8), "int32"), LENS, **mtp)
+    # the workspace also holds one block-table row and one index per query token
+    plain = ops.paged_attention_workspace_size(Q, KC, KC, BT, LENS, **OKW)
+    one_each = ops.paged_attention_workspace_size(Q, KC, KC, BT, LENS, **dict(OKW, calc_type=1, q_seq_lens=[1] * 4))
+    assert one_each == (plain + 255) // 256 * 256 + 256 + 256
 
 
 def test_paged_cache_load_infer_and_validation_without_a_gpu():

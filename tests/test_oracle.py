@@ -83,6 +83,25 @@ def test_config1_fixture_reproduced_by_both_oracles():
         assert np.all(np.abs(out - g) <= 1e-3 * np.maximum(np.abs(g), 1.0))
 
 
+@pytest.mark.parametrize("name", sorted(cases.MTP_CASES))
+def test_multi_token_oracle_matches_reference_golden(name):
+    # several query tokens per sequence with the SPEC mask: stored outputs of the reference's golden
+    c, fx = cases.mtp_case(name), _fx("pa_mtp_" + name)
+    assert cases.digest(c["query"]) == str(fx["sha_query"]) and cases.digest(c["key_cache"]) == str(fx["sha_key_cache"])
+    out = oracle.paged_attention_golden(c["query"], c["key_cache"], c["value_cache"], c["block_tables"],
+                                        c["context_lens"], c["qk_scale"], mask=c["mask"], mask_type=3,
+                                        q_seq_lens=c["q_seq_lens"])
+    g = fx["golden"].astype(np.float32)
+    assert out.shape == g.shape == (int(c["q_seq_lens"].sum()),) + c["query"].shape[1:]
+    np.testing.assert_allclose(out, g, rtol=0, atol=5e-4 if c["q_dtype"] == "float16" else 1e-6)
+    # the mask is causal inside the window of new tokens: the last token of a sequence sees everything,
+    # so it equals plain decode attention over the same context
+    last = np.cumsum(c["q_seq_lens"]) - 1
+    plain = oracle.paged_attention_golden(c["query"][last], c["key_cache"], c["value_cache"], c["block_tables"],
+                                          c["context_lens"], c["qk_scale"])
+    np.testing.assert_allclose(out[last], plain, rtol=1e-6, atol=1e-7)
+
+
 @pytest.mark.parametrize("name", sorted(cases.PCL_CASES))
 def test_cache_load_oracle_matches_reference_golden(name):
     # stored digests of the reference's golden_calc_nd outputs on the same seeded inputs
