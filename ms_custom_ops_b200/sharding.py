@@ -97,6 +97,8 @@ def seq_shard_tables(block_tables, context_lens, block_size: int, rank: int, wor
     seq_block_range(ceil(len_b / block_size), rank, world) of block_tables[b], left-aligned and padded
     with 0; local_lens[b] is the number of context tokens in them (0 when the rank holds nothing of
     a short sequence).  The newest token of a sequence lives on the rank that owns its last block.
+    Additive masks index absolute context positions, so a masked launch over a part needs the mask
+    columns of that part (column offset lo * block_size); the helpers here cover the mask-free case.
     """
     tables = np.asarray(block_tables)
     lens = np.asarray(context_lens).astype(np.int64).reshape(-1)
