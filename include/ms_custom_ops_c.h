@@ -18,10 +18,10 @@
  *   paged_cache_load(key_cache, value_cache, block_tables, seq_lens, seq_starts, kv_cache_cfg,
  *                    is_seq_lens_cumsum_type, has_seq_starts) -> (key_out, value_out)
  *       reference: ops/c_api/paged_cache_load/paged_cache_load_op.yaml:2-28,
- *                  pybind definition ops/c_api/paged_cache_load/paged_cache_load_pynative.cc:131-137
+ *                  pybind definition ops/c_api/paged_cache_load/paged_cache_load_pynative.cc:129-134
  *   fa_update(lse, local_out, fa_update_type, sp) -> output
  *       reference: ops/c_api/fa_update/fa_update_op.yaml:2-16,
- *                  pybind definition ops/c_api/fa_update/fa_update_pynative.cc:88-91
+ *                  pybind definition ops/c_api/fa_update/fa_update_pynative.cc:85-88
  *
  * This is what a binding (pybind11, ctypes, a framework's custom-op adapter)
  * calls instead of the reference's `pyboost_*` functions.  Tensors are passed
@@ -148,7 +148,7 @@ int ms_custom_ops_paged_attention_status(const void *workspace);
  * both have rank 3, (sum_context_lens, num_heads, head_size_k / head_size_v), in the dtypes of the
  * caches.  sum_context_lens is the sum of seq_lens (its last element in cumulative mode) when
  * `seq_lens` is readable on the host (on_host != 0), else -1: a dimension only known at run time,
- * as in the reference's infer function (paged_cache_load_graph.cc:25-44). */
+ * as in the reference's infer function (paged_cache_load_graph.cc:23-60). */
 int ms_custom_ops_paged_cache_load_infer(const MsTensorDesc *key_cache, const MsTensorDesc *value_cache,
                                          const MsTensorDesc *block_tables, const MsTensorDesc *seq_lens,
                                          const MsTensorDesc *seq_starts, int64_t kv_cache_cfg,

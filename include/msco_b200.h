@@ -97,8 +97,8 @@ int msco_reshape_and_cache_quant(const void *key, const void *value, int8_t *key
  * paged_cache_load: gather the token rows of every sequence from the paged
  * caches into contiguous outputs -- the inverse movement of reshape_and_cache.
  * Replaces the device work behind npu_paged_cache_load
- * (ops/c_api/paged_cache_load/paged_cache_load_pynative.cc:49-118), ND layout
- * (kv_cache_cfg = 0; argument meaning ops/c_api/paged_cache_load/paged_cache_load_doc.md:8-24,
+ * (ops/c_api/paged_cache_load/paged_cache_load_pynative.cc:48-117), ND layout
+ * (kv_cache_cfg = 0; argument meaning ops/c_api/paged_cache_load/paged_cache_load_doc.md:9-27,
  * arithmetic tests/st/test_custom_paged_cache_load.py:35-76):
  *
  *   key_cache   [num_blocks, block_size, k_row_bytes]   value_cache likewise with v_row_bytes
@@ -129,7 +129,7 @@ int msco_paged_cache_load(const void *key_cache, const void *value_cache, const 
 /* ------------------------------------------------------------------------
  * fa_update (DECODE_UPDATE): merge `sp` partial attention outputs by their
  * log-sum-exps.  Replaces the device work behind npu_fa_update
- * (ops/c_api/fa_update/fa_update_pynative.cc:51-79; doc fa_update_doc.md:5-27;
+ * (ops/c_api/fa_update/fa_update_pynative.cc:48-77; doc fa_update_doc.md:3-24;
  * arithmetic tests/st/test_asd_faupdate.py:34-59):
  *   lse [sp, rows] float32 (natural log), local_out [sp, rows, head_size] float32,
  *   out [rows, head_size] float32 = sum_s softmax_s(lse)[s, row] * local_out[s, row, :].

@@ -1,6 +1,6 @@
 // fa_update for B200: merge `sp` partial attention outputs of the same rows by their log-sum-exps,
 //   out[r, :] = sum_s w[s, r] * local_out[s, r, :],   w[s, r] = exp(lse[s, r]) / sum_s' exp(lse[s', r])
-// (the DECODE_UPDATE of the reference: ops/c_api/fa_update/fa_update_doc.md:5-27, golden
+// (the DECODE_UPDATE of the reference: ops/c_api/fa_update/fa_update_doc.md:3-24, golden
 // tests/st/test_asd_faupdate.py:34-59).  The operator is float32 throughout; the strided entry point
 // also takes fp16 / bf16 partial outputs (what paged attention writes) with any distance between
 // the partitions, so that an all-gathered buffer is merged in place.

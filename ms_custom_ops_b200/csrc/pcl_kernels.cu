@@ -242,7 +242,7 @@ extern "C" int msco_paged_cache_load(const void *key_cache, const void *value_ca
   if (batch < 0 || max_blocks_per_seq < 0 || block_size < 0 || num_blocks < 0 || k_row_bytes < 0 ||
       v_row_bytes < 0 || sum_tokens < 0)
     return fail(MSCO_ERR_INVALID_ARG, "paged_cache_load: negative size");
-  // zero-sized inputs: the reference skips execution (paged_cache_load_graph.cc:84-101)
+  // zero-sized inputs: the reference skips execution (paged_cache_load_graph.cc:80-97)
   if (batch == 0 || max_blocks_per_seq == 0 || block_size == 0 || num_blocks == 0 || sum_tokens == 0 ||
       (k_row_bytes == 0 && v_row_bytes == 0))
     return MSCO_OK;

@@ -1,10 +1,10 @@
 // fa_update: operator glue for the B200 plugin.
 //
 // Mirrors the operator the reference registers in ops/c_api/fa_update:
-//   fa_update_common.h:23-35       input order lse, local_out, fa_update_type, sp; local_out has rank 3
-//   fa_update_pynative.cc:51-79    eager entry: rank and head_size checks, output (rows, head_size)
-//   fa_update_graph.cc:25-49       the same checks at infer time; the output is Float32
-//   fa_update_doc.md:9-27          lse (sp, rows) and local_out (sp, rows, head_size) are Float32,
+//   fa_update_common.h:23-37       input order lse, local_out, fa_update_type, sp; local_out has rank 3
+//   fa_update_pynative.cc:48-77    eager entry: rank and head_size checks, output (rows, head_size)
+//   fa_update_graph.cc:23-42       the same checks at infer time; the output is Float32
+//   fa_update_doc.md:7-24          lse (sp, rows) and local_out (sp, rows, head_size) are Float32,
 //                                  fa_update_type 0 = DECODE_UPDATE is the only mode, sp in [1, 8]
 // The device work is msco_fa_update (libmsco_b200.so).
 #include "ms_custom_ops_c.h"

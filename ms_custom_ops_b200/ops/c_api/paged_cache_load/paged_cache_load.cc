@@ -1,12 +1,12 @@
 // paged_cache_load: operator glue for the B200 plugin.
 //
 // Mirrors the operator the reference registers in ops/c_api/paged_cache_load:
-//   paged_cache_load_common.h:28-44     input order, ND = 0 / NZ = 1 cache formats
-//   paged_cache_load_pynative.cc:49-118 eager entry: seq_lens must be int32; the output row count is
+//   paged_cache_load_common.h:26-43     input order, ND = 0 / NZ = 1 cache formats
+//   paged_cache_load_pynative.cc:48-117 eager entry: seq_lens must be int32; the output row count is
 //                                       the sum of seq_lens, or its last element in cumulative mode;
 //                                       key_out [sum, heads, head_size_k], value_out [sum, heads, head_size_v]
-//   paged_cache_load_graph.cc:84-101    execution is skipped when an input has a zero dimension
-//   paged_cache_load_doc.md:8-24        argument meaning; cumulative lengths and seq_starts are ND-only
+//   paged_cache_load_graph.cc:80-97    execution is skipped when an input has a zero dimension
+//   paged_cache_load_doc.md:9-27        argument meaning; cumulative lengths and seq_starts are ND-only
 // The device work is msco_paged_cache_load (libmsco_b200.so).  FRACTAL_NZ (kv_cache_cfg = 1) is an
 // Ascend cube-unit layout and is not built for B200.
 #include "ms_custom_ops_c.h"

@@ -106,7 +106,7 @@ def rac_case(name):
 
 # paged_cache_load cases: (key dtype, value dtype, cumulative lengths + seq_starts, seed,
 #   (num_blocks, block_size, heads, head_size_k, head_size_v, batch, max_len)).
-# "ref" geometry = tests/st/test_custom_paged_cache_load.py:250 ([128, 128, 16, 144, 128, 16, 1], lengths 1..1024)
+# "ref" geometry = tests/st/test_custom_paged_cache_load.py:268 ([128, 128, 16, 144, 128, 16, 1], lengths 1..1024)
 _PCL_REF = (128, 128, 16, 144, 128, 16, 1024)
 PCL_CASES = {
     "fp16_fp16_lens": ("float16", "float16", False, 201, _PCL_REF),
@@ -127,7 +127,7 @@ FA_CASES = {
 
 
 def pcl_case(name):
-    """Seeded inputs laid out like the reference test's generate_data_nd (:104-166): caches of small
+    """Seeded inputs laid out like the reference test's generate_data_nd (:112-166): caches of small
     integers, random block tables with 4 spare columns, seq_starts a multiple of block_size."""
     import ml_dtypes
     kd, vd, cumsum, seed, (nb, bs, heads, dk, dv, batch, max_len) = PCL_CASES[name]
