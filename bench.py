@@ -775,15 +775,18 @@ def measure_adjacent(case, spec, dev, peak, with_cpu):
         "kernels_per_call": 2, "out_of_range_ids": int(oob.item()),
         "l2": f"{nbytes / 2e6:.0f} MB read and as much written per launch vs {L2_BYTES >> 20} MB of L2"}
     if with_cpu:
-        from oracle import paged_kv_numpy as oracle_np
+        from oracle import c_oracle
         hk, hv, hbt = _to_np(kc), _to_np(vc), bt.cpu().numpy()
-        oracle_np.paged_cache_load_golden(hk[:2], hv[:2], np.zeros((1, 1), np.int32), np.array([1], np.int32))
-        t0 = time.perf_counter()
-        gk, gv = oracle_np.paged_cache_load_golden(hk, hv, hbt, lens)
-        dt = time.perf_counter() - t0
+        cores = host_threads()
+        c_oracle.paged_cache_load(hk[:2], hv[:2], np.zeros((1, 1), np.int32), np.array([1], np.int32), threads=cores)
+        t_best = float("inf")
+        for _ in range(3):
+            t0 = time.perf_counter()
+            gk, gv = c_oracle.paged_cache_load(hk, hv, hbt, lens, threads=cores)
+            t_best = min(t_best, time.perf_counter() - t0)
         out["paged_cache_load"]["cpu_baseline"] = {
-            "value": total / dt, "unit": "tokens/s", "cores": 1, "kind": "port",
-            "sample": "the whole batch, numpy restatement of the reference golden (block-wise copies)"}
+            "value": total / t_best, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": "the whole batch, best of 3; C restatement of the reference golden, OpenMP over sequences"}
         out["paged_cache_load"]["bit_exact"] = bool(np.array_equal(_to_np(ko).view(np.uint8), gk.view(np.uint8)) and
                                                     np.array_equal(_to_np(vo).view(np.uint8), gv.view(np.uint8)))
         del hk, hv, gk, gv
@@ -803,15 +806,18 @@ def measure_adjacent(case, spec, dev, peak, with_cpu):
         "achieved_gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak, "frac_of_8tbs": nbytes / ms / 1e6 / 8000.0,
         "rows_per_s": rows / ms * 1e3, "l2": f"{nbytes / 1e6:.0f} MB per launch vs {L2_BYTES >> 20} MB of L2"}
     if with_cpu:
-        from oracle import paged_kv_numpy as oracle_np
-        n = 32768
-        hl, ho = lse[:, :n].cpu().numpy(), lo[:, :n].cpu().numpy()
-        t0 = time.perf_counter()
-        g = oracle_np.fa_update_golden(hl, ho)
-        dt = time.perf_counter() - t0
-        err = np.abs(merged[:n].cpu().numpy() - g)
-        out["fa_update"]["cpu_baseline"] = {"value": n / dt, "unit": "rows/s", "cores": 1, "kind": "port",
-                                            "sample": f"first {n} rows, numpy restatement of the reference golden"}
+        from oracle import c_oracle
+        cores = host_threads()
+        hl, ho = lse.cpu().numpy(), lo.cpu().numpy()
+        t_best = float("inf")
+        for _ in range(3):
+            t0 = time.perf_counter()
+            g = c_oracle.fa_update(hl, ho, threads=cores)
+            t_best = min(t_best, time.perf_counter() - t0)
+        err = np.abs(merged.cpu().numpy() - g)
+        out["fa_update"]["cpu_baseline"] = {
+            "value": rows / t_best, "unit": "rows/s", "cores": cores, "kind": "port",
+            "sample": "all rows, best of 3; C restatement of the reference golden, OpenMP over rows"}
         out["fa_update"]["max_abs_err"] = float(err.max())
     return out
 

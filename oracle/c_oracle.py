@@ -35,6 +35,8 @@ def lib():
         L.pko_max_threads.restype = C.c_int
         L.pko_reshape_and_cache.restype = None
         L.pko_reshape_and_cache_quant.restype = None
+        L.pko_paged_cache_load.restype = C.c_int64
+        L.pko_fa_update.restype = None
         _lib = L
     return _lib
 
@@ -113,3 +115,33 @@ def reshape_and_cache_quant(key, value, key_cache, value_cache, slot_mapping, k_
                                       C.c_int64(k.size // max(t, 1)), C.c_int64(0 if v is None else v.size // max(t, 1)),
                                       _p(kd), _p(ko), _p(vd), _p(vo), C.c_int(threads))
     return kc, vc
+
+
+def paged_cache_load(key_cache, value_cache, block_tables, seq_lens, seq_starts=None, seq_lens_cumsum=False,
+                     threads=0):
+    """Same contract as paged_kv_numpy.paged_cache_load_golden (ND layout), sequences over threads."""
+    kc, vc = np.ascontiguousarray(key_cache), np.ascontiguousarray(value_cache)
+    bt = np.ascontiguousarray(block_tables, dtype=np.int32)
+    lens = np.ascontiguousarray(seq_lens, dtype=np.int32).reshape(-1)
+    st = None if seq_starts is None else np.ascontiguousarray(seq_starts, dtype=np.int32)
+    total = int(lens[-1]) if seq_lens_cumsum else int(lens.sum())
+    ko = np.empty((total,) + kc.shape[2:], dtype=kc.dtype)
+    vo = np.empty((total,) + vc.shape[2:], dtype=vc.dtype)
+    rc = lib().pko_paged_cache_load(
+        _p(kc), _p(vc), _p(bt), _p(lens), _p(st), _p(ko), _p(vo), C.c_int(bt.shape[0]), C.c_int(bt.shape[1]),
+        C.c_int(kc.shape[1]), C.c_int64(kc[0, 0].nbytes), C.c_int64(vc[0, 0].nbytes), C.c_int64(total),
+        C.c_int(1 if seq_lens_cumsum else 0), C.c_int(threads))
+    if rc < 0:
+        raise RuntimeError("pko_paged_cache_load failed")
+    return ko, vo
+
+
+def fa_update(lse, local_out, threads=0):
+    """Same contract as paged_kv_numpy.fa_update_golden: float32 [rows, head_size]."""
+    l = np.ascontiguousarray(lse, dtype=np.float32)
+    x = np.ascontiguousarray(local_out, dtype=np.float32)
+    sp, rows, hd = x.shape
+    out = np.empty((rows, hd), dtype=np.float32)
+    lib().pko_fa_update(_p(l), _p(x), _p(out), C.c_int64(rows), C.c_int(hd), C.c_int(sp), C.c_int(threads))
+    return out
+

@@ -227,4 +227,74 @@ void pko_reshape_and_cache_quant(const void *key, const void *value, int in_dtyp
   }
 }
 
+/* paged_cache_load, ND layout (tests/st/test_custom_paged_cache_load.py:35-76): gather the rows of
+   every sequence; blocks with a negative id contribute no rows and do not advance the output row, the
+   rows left at the end are zero.  Two passes: first output row of every sequence (serial prefix over
+   the valid rows), then the copies, sequences spread over threads.  Rows in bytes.  Returns the
+   number of rows written. */
+int64_t pko_paged_cache_load(const void *key_cache, const void *value_cache, const int32_t *block_tables,
+                             const int32_t *seq_lens, const int32_t *seq_starts, void *key_out, void *value_out,
+                             int batch, int max_blocks, int block_size, int64_t k_row_bytes, int64_t v_row_bytes,
+                             int64_t sum_tokens, int cumsum, int threads) {
+  if (threads <= 0) threads = omp_get_max_threads();
+  int64_t *first = (int64_t *)malloc(sizeof(int64_t) * (size_t)(batch + 1));
+  if (!first) return -1;
+  first[0] = 0;
+  for (int i = 0; i < batch; ++i) {
+    const int n = cumsum ? seq_lens[i + 1] - seq_lens[i] : seq_lens[i];
+    const int off = seq_starts ? seq_starts[i] / block_size : 0;
+    int64_t rows = 0;
+    for (int j = 0; j < n; j += block_size) {
+      const int col = off + j / block_size;
+      if (col < max_blocks && block_tables[(int64_t)i * max_blocks + col] >= 0)
+        rows += (n - j < block_size) ? n - j : block_size;
+    }
+    first[i + 1] = first[i] + rows;
+  }
+#pragma omp parallel for num_threads(threads) schedule(dynamic, 1)
+  for (int i = 0; i < batch; ++i) {
+    const int n = cumsum ? seq_lens[i + 1] - seq_lens[i] : seq_lens[i];
+    const int off = seq_starts ? seq_starts[i] / block_size : 0;
+    int64_t row = first[i];
+    for (int j = 0; j < n; j += block_size) {
+      const int col = off + j / block_size;
+      if (col >= max_blocks) break;
+      const int64_t bid = block_tables[(int64_t)i * max_blocks + col];
+      if (bid < 0) continue;
+      const int64_t m = (n - j < block_size) ? n - j : block_size;
+      memcpy((char *)key_out + row * k_row_bytes, (const char *)key_cache + bid * block_size * k_row_bytes,
+             (size_t)(m * k_row_bytes));
+      memcpy((char *)value_out + row * v_row_bytes, (const char *)value_cache + bid * block_size * v_row_bytes,
+             (size_t)(m * v_row_bytes));
+      row += m;
+    }
+  }
+  const int64_t written = first[batch];
+  free(first);
+  if (written < sum_tokens) {
+    memset((char *)key_out + written * k_row_bytes, 0, (size_t)((sum_tokens - written) * k_row_bytes));
+    memset((char *)value_out + written * v_row_bytes, 0, (size_t)((sum_tokens - written) * v_row_bytes));
+  }
+  return written;
+}
+
+/* fa_update (tests/st/test_asd_faupdate.py:34-59): out[r] = sum_s exp(lse[s][r]) / sum_s' exp(lse[s'][r])
+   * local_out[s][r], float32, rows spread over threads. */
+void pko_fa_update(const float *lse, const float *local_out, float *out, int64_t rows, int head_size, int sp,
+                   int threads) {
+  if (threads <= 0) threads = omp_get_max_threads();
+#pragma omp parallel for num_threads(threads) schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    float sum = 0.f;
+    for (int s = 0; s < sp; ++s) sum += expf(lse[(int64_t)s * rows + r]);
+    float *o = out + r * head_size;
+    for (int d = 0; d < head_size; ++d) o[d] = 0.f;
+    for (int s = 0; s < sp; ++s) {
+      const float w = expf(lse[(int64_t)s * rows + r]) / sum;
+      const float *x = local_out + ((int64_t)s * rows + r) * head_size;
+      for (int d = 0; d < head_size; ++d) o[d] += w * x[d];
+    }
+  }
+}
+
 int pko_max_threads(void) { return omp_get_max_threads(); }

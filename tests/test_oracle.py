@@ -113,6 +113,31 @@ def test_cache_load_oracle_matches_reference_golden(name):
     assert cases.digest(k) == str(fx["sha_key_out"]) and cases.digest(v) == str(fx["sha_value_out"])
 
 
+@pytest.mark.parametrize("name", sorted(cases.PCL_CASES))
+def test_c_cache_load_matches_reference_golden(name):
+    c, fx = cases.pcl_case(name), _fx("pcl_" + name)
+    k, v = c_oracle.paged_cache_load(c["key_cache"], c["value_cache"], c["block_tables"], c["seq_lens"],
+                                     c["seq_starts"], c["cumsum"])
+    assert cases.digest(k) == str(fx["sha_key_out"]) and cases.digest(v) == str(fx["sha_value_out"])
+
+
+def test_c_cache_load_and_merge_agree_with_numpy_on_irregular_input():
+    rng = np.random.default_rng(8)
+    kc = rng.integers(-128, 128, (12, 4, 2, 3)).astype(np.int8)
+    vc = rng.standard_normal((12, 4, 2, 5)).astype(np.float16)
+    tables = rng.integers(-2, 12, (7, 9)).astype(np.int32)
+    lens = rng.integers(0, 21, 7)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    starts = (rng.integers(0, 12, 7)).astype(np.int32)
+    for args in ((lens.astype(np.int32), None, False), (cu, starts, True), (cu, None, True)):
+        a = oracle.paged_cache_load_golden(kc, vc, tables, *args)
+        b = c_oracle.paged_cache_load(kc, vc, tables, *args)
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    lse = rng.standard_normal((5, 333)).astype(np.float32) * 3
+    parts = rng.standard_normal((5, 333, 24)).astype(np.float32)
+    np.testing.assert_allclose(c_oracle.fa_update(lse, parts), oracle.fa_update_golden(lse, parts), rtol=2e-6, atol=1e-7)
+
+
 def test_cache_load_oracle_skips_negative_blocks():
     kc = np.arange(4 * 2 * 1 * 2, dtype=np.int8).reshape(4, 2, 1, 2) + 1
     tables = np.array([[1, -1, 3], [0, 2, -1]], np.int32)
