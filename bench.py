@@ -737,6 +737,43 @@ def measure_scatter(spec, dev, peak):
     return out
 
 
+def cpu_leg_cache_load(kc, vc, bt, lens, ko, vo):
+    """CPU baseline and bit-exactness check of one paged_cache_load: the C restatement of the reference
+    golden on all host cores over the same caches (torch tensors in, device or host)."""
+    from oracle import c_oracle
+    hk, hv, hbt = _to_np(kc), _to_np(vc), bt.cpu().numpy()
+    cores = host_threads()
+    total = int(np.asarray(lens).sum())
+    c_oracle.paged_cache_load(hk[:2], hv[:2], np.zeros((1, 1), np.int32), np.array([1], np.int32), threads=cores)
+    t_best = float("inf")
+    for _ in range(3):
+        t0 = time.perf_counter()
+        gk, gv = c_oracle.paged_cache_load(hk, hv, hbt, lens, threads=cores)
+        t_best = min(t_best, time.perf_counter() - t0)
+    return {
+        "cpu_baseline": {"value": total / t_best, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": "the whole batch, best of 3; C restatement of the reference golden, "
+                                   "OpenMP over sequences"},
+        "bit_exact": bool(np.array_equal(_to_np(ko).view(np.uint8), gk.view(np.uint8)) and
+                          np.array_equal(_to_np(vo).view(np.uint8), gv.view(np.uint8)))}
+
+
+def cpu_leg_fa_update(lse, lo, merged):
+    """CPU baseline and error of one fa_update: the C restatement of the reference golden, all cores."""
+    from oracle import c_oracle
+    cores = host_threads()
+    hl, ho = lse.cpu().numpy(), lo.cpu().numpy()
+    t_best = float("inf")
+    for _ in range(3):
+        t0 = time.perf_counter()
+        g = c_oracle.fa_update(hl, ho, threads=cores)
+        t_best = min(t_best, time.perf_counter() - t0)
+    return {
+        "cpu_baseline": {"value": hl.shape[1] / t_best, "unit": "rows/s", "cores": cores, "kind": "port",
+                         "sample": "all rows, best of 3; C restatement of the reference golden, OpenMP over rows"},
+        "max_abs_err": float(np.abs(merged.cpu().numpy() - g).max())}
+
+
 def measure_adjacent(case, spec, dev, peak, with_cpu):
     """The two operators either side of the decode path, on the same workload, one GPU:
     paged_cache_load gathers every sequence of the batch out of the paged caches (reads and writes the
@@ -775,21 +812,7 @@ def measure_adjacent(case, spec, dev, peak, with_cpu):
         "kernels_per_call": 2, "out_of_range_ids": int(oob.item()),
         "l2": f"{nbytes / 2e6:.0f} MB read and as much written per launch vs {L2_BYTES >> 20} MB of L2"}
     if with_cpu:
-        from oracle import c_oracle
-        hk, hv, hbt = _to_np(kc), _to_np(vc), bt.cpu().numpy()
-        cores = host_threads()
-        c_oracle.paged_cache_load(hk[:2], hv[:2], np.zeros((1, 1), np.int32), np.array([1], np.int32), threads=cores)
-        t_best = float("inf")
-        for _ in range(3):
-            t0 = time.perf_counter()
-            gk, gv = c_oracle.paged_cache_load(hk, hv, hbt, lens, threads=cores)
-            t_best = min(t_best, time.perf_counter() - t0)
-        out["paged_cache_load"]["cpu_baseline"] = {
-            "value": total / t_best, "unit": "tokens/s", "cores": cores, "kind": "port",
-            "sample": "the whole batch, best of 3; C restatement of the reference golden, OpenMP over sequences"}
-        out["paged_cache_load"]["bit_exact"] = bool(np.array_equal(_to_np(ko).view(np.uint8), gk.view(np.uint8)) and
-                                                    np.array_equal(_to_np(vo).view(np.uint8), gv.view(np.uint8)))
-        del hk, hv, gk, gv
+        out["paged_cache_load"].update(cpu_leg_cache_load(kc, vc, bt, lens, ko, vo))
     del ko, vo
     torch.cuda.empty_cache()
 
@@ -806,19 +829,7 @@ def measure_adjacent(case, spec, dev, peak, with_cpu):
         "achieved_gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak, "frac_of_8tbs": nbytes / ms / 1e6 / 8000.0,
         "rows_per_s": rows / ms * 1e3, "l2": f"{nbytes / 1e6:.0f} MB per launch vs {L2_BYTES >> 20} MB of L2"}
     if with_cpu:
-        from oracle import c_oracle
-        cores = host_threads()
-        hl, ho = lse.cpu().numpy(), lo.cpu().numpy()
-        t_best = float("inf")
-        for _ in range(3):
-            t0 = time.perf_counter()
-            g = c_oracle.fa_update(hl, ho, threads=cores)
-            t_best = min(t_best, time.perf_counter() - t0)
-        err = np.abs(merged.cpu().numpy() - g)
-        out["fa_update"]["cpu_baseline"] = {
-            "value": rows / t_best, "unit": "rows/s", "cores": cores, "kind": "port",
-            "sample": "all rows, best of 3; C restatement of the reference golden, OpenMP over rows"}
-        out["fa_update"]["max_abs_err"] = float(err.max())
+        out["fa_update"].update(cpu_leg_fa_update(lse, lo, merged))
     return out
 
 

@@ -35,3 +35,33 @@ def test_reference_arm_prints_one_contract_line():
 def test_reference_arm_runs_on_rank_zero_only():
     r = _run({"RANK": "1", "WORLD_SIZE": "2"}, "--gpus", "2")
     assert r.returncode == 0 and r.stdout.strip() == ""
+
+
+def test_cpu_legs_of_the_adjacent_operators():
+    # the CPU side of `bench.py --adjacent` (C restatements timed on the host cores, outputs checked),
+    # fed with host tensors that already hold the right answers
+    import importlib.util
+
+    import numpy as np
+    import torch
+
+    from oracle import paged_kv_numpy as oracle
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    rng = np.random.default_rng(0)
+    kc = torch.from_numpy(rng.standard_normal((20, 16, 2, 8)).astype(np.float32)).to(torch.bfloat16)
+    vc = torch.from_numpy(rng.integers(-100, 100, (20, 16, 2, 8)).astype(np.int8))
+    bt = torch.from_numpy(rng.integers(0, 20, (3, 5)).astype(np.int32))
+    lens = np.array([70, 1, 33], np.int32)
+    gk, gv = oracle.paged_cache_load_golden(kc.view(torch.int16).numpy(), vc.numpy(), bt.numpy(), lens)
+    leg = bench.cpu_leg_cache_load(kc, vc, bt, lens, torch.from_numpy(gk).view(torch.bfloat16), torch.from_numpy(gv))
+    assert leg["bit_exact"] is True and leg["cpu_baseline"]["value"] > 0 and leg["cpu_baseline"]["cores"] >= 1
+    wrong = torch.from_numpy(gv.copy())
+    wrong[5] += 1
+    assert bench.cpu_leg_cache_load(kc, vc, bt, lens, torch.from_numpy(gk).view(torch.bfloat16), wrong)["bit_exact"] is False
+    lse = torch.from_numpy(rng.standard_normal((3, 50)).astype(np.float32))
+    lo = torch.from_numpy(rng.standard_normal((3, 50, 16)).astype(np.float32))
+    merged = torch.from_numpy(oracle.fa_update_golden(lse.numpy(), lo.numpy()))
+    leg = bench.cpu_leg_fa_update(lse, lo, merged)
+    assert leg["max_abs_err"] < 1e-5 and leg["cpu_baseline"]["unit"] == "rows/s"
