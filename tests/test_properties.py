@@ -89,3 +89,20 @@ def test_split_rule_is_a_function_of_length_and_dtype_only(n, dt):
     assert t >= 512 and t % 128 == 0
     # longer contexts never get smaller splits
     assert L.msco_paged_attention_split_tokens(n + 1, dt) >= t
+
+
+def test_algorithmic_bytes_formulas_match_the_stated_per_unit_figures():
+    # the roofline numerators: 512 B (16-bit) / 256 B (int8) per context token per kv head at head_dim 128,
+    # plus Q in / O out; 8196 B per valid token for the bf16 copy scatter of 8 x 128 rows
+    from ms_custom_ops_b200 import workloads
+    lens = [1000, 24, 4096]
+    kv = workloads.algorithmic_bytes_attention(lens, 32, 8, 128, 2)
+    assert kv == sum(lens) * 8 * 512 + 3 * 32 * 128 * 4
+    kv8 = workloads.algorithmic_bytes_attention(lens, 64, 8, 128, 1, quant=True)
+    assert kv8 == sum(lens) * 8 * 256 + 3 * 64 * 128 * 4 + 2 * 8 * 128 * 4
+    slots = np.array([5, -1, 9, 2, -1], np.int32)
+    assert workloads.algorithmic_bytes_scatter(slots, 1024, 2, 2) == 3 * 8192 + 5 * 4
+    assert workloads.algorithmic_bytes_scatter(slots, 1024, 2, 1, quant=True) == 3 * 6144 + 5 * 4 + 2 * 1024 * 4
+    # benchmark configuration 2 as published: 64 sequences, 32 q / 8 kv heads, bf16
+    spec = workloads.config_spec(2)
+    assert (spec.batch, spec.num_heads, spec.kv_heads, spec.head_size, spec.block_size) == (64, 32, 8, 128, 128)
