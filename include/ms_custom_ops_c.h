@@ -69,6 +69,17 @@ int ms_custom_ops_reshape_and_cache(const MsTensorDesc *key, const MsTensorDesc 
                                     const MsTensorDesc *slot_mapping, int64_t cache_mode, int64_t head_num,
                                     void *stream);
 
+/* Shape / dtype inference of the operator's placeholder output after the operator's checks: key's
+ * shape and dtype (CustomReshapeAndCacheOpFuncImpl::InferShape / InferType,
+ * ops/c_api/reshape_and_cache/reshape_and_cache.cc:66-75).  Graph-mode frameworks need it to wire the
+ * side-effect operator into a graph; the eager entry point has no output
+ * (PyboostRunner::Call<0>, reshape_and_cache.cc:204-210) and nothing is ever written to it. */
+int ms_custom_ops_reshape_and_cache_infer(const MsTensorDesc *key, const MsTensorDesc *value,
+                                          const MsTensorDesc *key_cache, const MsTensorDesc *value_cache,
+                                          const MsTensorDesc *slot_mapping, int64_t cache_mode, int64_t head_num,
+                                          int32_t *out_dtype, int32_t *out_ndim,
+                                          int64_t *out_shape /* [MS_MAX_DIMS] */);
+
 /* Extension (no reference counterpart): quantise fp16/bf16 rows to the int8
  * cache on the way in; inverse of paged_attention's quant_type = 1 formula. */
 int ms_custom_ops_reshape_and_cache_quant(const MsTensorDesc *key, const MsTensorDesc *value,
@@ -190,6 +201,13 @@ const char *ms_custom_ops_op_signature(int index);
 /* Plan cache (the role of the reference's tiling cache): statistics and reset. */
 void ms_custom_ops_plan_cache_stats(int64_t *hits, int64_t *misses, int64_t *entries);
 void ms_custom_ops_plan_cache_clear(void);
+/* How the misses were served: by re-planning an existing plan in place (no allocation), or by
+ * building a new plan.  In a decode loop, where every step is a miss, only `recycled` grows. */
+void ms_custom_ops_plan_cache_miss_stats(int64_t *recycled, int64_t *created);
+/* The pinned plan memory pool behind the plans (role of the reference's TilingMemMgr,
+ * ops/framework/ms_kernels_internal/tiling_mem_mgr.cc:82-137): same six numbers as
+ * msco_plan_arena_stats. */
+void ms_custom_ops_plan_arena_stats(int64_t *stats /* [6] */);
 
 #ifdef __cplusplus
 }

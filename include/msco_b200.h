@@ -194,10 +194,24 @@ int32_t msco_paged_attention_split_tokens(int32_t context_len, int32_t kv_dtype)
 
 /* Build the launch plan from the host copy of context_lens (the reference
  * reads the same host values into its param: paged_attention_graph.cc:773-776,
- * paged_attention_pynative.cc:686-692).  Pure host work; allocates only host
- * (pinned) memory owned by the plan. */
+ * paged_attention_pynative.cc:686-692).  Pure host work.  The plan words live in
+ * a block of a pooled page-locked arena (the role of the reference's
+ * TilingMemMgr, ops/framework/ms_kernels_internal/tiling_mem_mgr.cc:82-137,
+ * 224-238): slabs are obtained once, blocks are recycled, so planning does not
+ * call cudaHostAlloc / cudaFreeHost in the steady state. */
 int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *host_context_lens, int32_t batch,
                               MscoPaPlan **plan);
+/* Re-plan in place for new lengths (the reference re-tiles when the lengths change,
+ * paged_attention_graph.cc:808-856): same descriptor, new context_lens, any batch.  The plan keeps
+ * its arena block (a larger one is taken only when the batch outgrows it) and its tensor maps, so a
+ * decode loop that re-plans every step allocates nothing.  Launches already enqueued are unaffected
+ * (they carry their plan words with them; for plans too large for that the call first waits for the
+ * pending upload).  Not thread-safe against launches of the same plan object.  On failure the plan
+ * must not be launched again before a successful re-plan. */
+int msco_paged_attention_replan(MscoPaPlan *plan, const int32_t *host_context_lens, int32_t batch);
+/* Counters of the plan arena: [0] slabs obtained (cudaHostAlloc calls), [1] their bytes, [2] blocks
+ * in use, [3] block requests served, [4] requests larger than a slab, [5] 1 if page-locked. */
+void msco_plan_arena_stats(int64_t *stats /* [6] */);
 size_t msco_paged_attention_workspace_bytes(const MscoPaPlan *plan);
 int msco_paged_attention_plan_info(const MscoPaPlan *plan, MscoPaPlanInfo *info);
 void msco_paged_attention_plan_destroy(MscoPaPlan *plan);
@@ -212,8 +226,10 @@ void msco_paged_attention_plan_destroy(MscoPaPlan *plan);
  *   attn_mask    NORM [batch, 1, max_ctx], ALIBI [batch, num_q_heads, 1, max_ctx]
  *   out          [batch, num_q_heads, head_dim]                      q_dtype
  *   workspace    >= msco_paged_attention_workspace_bytes(plan), 256-byte aligned;
- *                holds two status words, the plan words and the split partials.  It needs no
- *                initialisation: errors are tagged with a per-launch epoch.
+ *                holds two status words, the plan words, the kernel's scheduling words (work-item
+ *                ticket, one arrival counter per split group) and the split partials.  It needs no
+ *                initialisation: errors are tagged with a per-launch epoch and the launch zeroes the
+ *                scheduling words itself (a small memset in front of the kernel).
  * Plans of up to 2304 words (about 280 sequences) travel as a kernel parameter; larger ones are
  * copied into the workspace by an async copy from the plan's pinned host memory in front of the
  * kernel: the plan must outlive the launch. */
@@ -249,7 +265,9 @@ int msco_paged_attention_launch_lse(const MscoPaPlan *plan, const void *query, c
  * [num_tokens, num_kv_heads * head_dim] in the query dtype; quantised on the way in when the plan's
  * quant_type is 1) followed by the attention launch above on the same caches.  Same result as the
  * two separate calls; the attention kernel is launched with programmatic stream serialisation
- * behind the scatter kernel so that its set-up overlaps the scatter's tail. */
+ * behind the scatter kernel so that its set-up overlaps the scatter's tail, and the scatter kernel
+ * zeroes the attention kernel's scheduling words on its way: two kernel launches per step, the
+ * split partials being merged by the attention kernel itself. */
 int msco_decode_step(const MscoPaPlan *plan, const void *key, const void *value, void *key_cache,
                      void *value_cache, const int32_t *slot_mapping, int64_t num_tokens, const void *query,
                      const int32_t *block_tables, const float *k_descale, const int32_t *k_offset,
@@ -259,7 +277,8 @@ int msco_decode_step(const MscoPaPlan *plan, const void *key, const void *value,
 /* After the stream has been synchronised: reads the status word the kernels
  * leave in the workspace.  MSCO_OK, MSCO_ERR_TIMEOUT (a bounded wait inside
  * the kernel expired) or MSCO_ERR_OOB (a block id outside the cache was met;
- * the affected tokens were skipped).  Synchronous device-to-host copy.  `plan`
+ * the affected tokens were skipped).  Reads the two words with a synchronous
+ * cudaMemcpy (device to host, default stream semantics).  `plan`
  * may be NULL (the status word is the first word of the workspace). */
 int msco_paged_attention_status(const MscoPaPlan *plan, const void *workspace);
 
@@ -295,7 +314,11 @@ int msco_paged_attention_status(const MscoPaPlan *plan, const void *workspace);
  * launches that can overlap on the GPU (different streams, or graph branches)
  * would write the same bytes at the same time: serialise them.
  * msco_paged_attention_status_static reads the status word of the last launch
- * on the current device (after synchronising the stream).
+ * on the current device (after synchronising the stream) with a synchronous
+ * cudaMemcpy of two words out of the array.  The array's address is cached per
+ * device ordinal of the calling process's primary context: a process that
+ * drives one device through several CUDA contexts must use this entry point
+ * from one of them only.
  * ---------------------------------------------------------------------- */
 #define MSCO_STATIC_SCRATCH_BYTES (16u << 20)
 int msco_paged_attention_launch_static(const MscoPaPlan *plan, const void *query, const void *key_cache,

@@ -19,14 +19,18 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import threading
+import weakref
 
 import numpy as np
 
 from . import _abi, _host
 from ._abi import MscoError  # noqa: F401
-from ._host import UnsupportedOnB200, plan_cache_clear, plan_cache_stats, registered_ops  # noqa: F401
+from ._host import (UnsupportedOnB200, plan_arena_stats, plan_cache_clear, plan_cache_stats,  # noqa: F401
+                    registered_ops)
 
-__all__ = ["reshape_and_cache", "reshape_and_cache_quant", "paged_attention", "paged_attention_infer",
+__all__ = ["reshape_and_cache", "reshape_and_cache_infer", "reshape_and_cache_quant", "paged_attention",
+           "paged_attention_infer", "plan_arena_stats",
            "paged_cache_load", "paged_cache_load_infer", "fa_update", "fa_update_infer", "paged_attention_with_lse",
            "paged_attention_workspace_size", "paged_attention_check_status", "TensorSpec", "MscoError",
            "UnsupportedOnB200", "registered_ops", "plan_cache_stats", "plan_cache_clear"]
@@ -61,7 +65,11 @@ def _contig_strides(shape):
     return list(reversed(st))
 
 
-_desc_cache = {}  # (data_ptr, shape, strides, dtype, is_cuda) -> (MsTensorDesc, pointer): descriptors are immutable
+# id(tensor) -> (weak reference, data_ptr, shape, MsTensorDesc, pointer).  A decode loop passes the same
+# tensor objects step after step; a descriptor is reused while the object is alive and still has the
+# address and shape it was built from (strides only change together with one of those or through a
+# view, which is another object).
+_desc_cache = {}
 
 
 class _Descs:
@@ -87,16 +95,16 @@ class _Descs:
             shape, strides = a.shape, [s // max(a.itemsize, 1) for s in a.strides]
             d.data, d.dtype, d.on_host = a.ctypes.data, _dtype_code(str(a.dtype)), 1
         else:  # torch tensor
-            key = (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype, t.is_cuda)
-            hit = _desc_cache.get(key)
+            hit = _desc_cache.get(id(t))
+            ptr = t.data_ptr()
+            if hit is not None and hit[0]() is t and hit[1] == ptr and hit[2] == t.shape:
+                return hit[4]
             self.keep.append(t)
-            if hit is not None:
-                return hit[1]
-            shape, strides = key[1], key[2]
-            d.data, d.dtype, d.on_host = key[0], _dtype_code(t.dtype), 0 if t.is_cuda else 1
+            shape, strides = tuple(t.shape), tuple(t.stride())
+            d.data, d.dtype, d.on_host = ptr, _dtype_code(t.dtype), 0 if t.is_cuda else 1
             if len(_desc_cache) > 4096:
                 _desc_cache.clear()
-            _desc_cache[key] = (d, C.pointer(d))
+            _desc_cache[id(t)] = (weakref.ref(t), ptr, t.shape, d, C.pointer(d))
         if len(shape) > _host.MS_MAX_DIMS:
             raise ValueError("tensors of more than 8 dimensions are not supported")
         d.ndim = len(shape)
@@ -125,12 +133,29 @@ def reshape_and_cache(key, value=None, key_cache=None, value_cache=None, slot_ma
     cache_mode    0 = ND (1 = FRACTAL_NZ is Ascend-only and raises UnsupportedOnB200)
     head_num      only used by the NZ layout
 
-    Returns None (the reference returns a placeholder tensor that carries no data).
+    Returns None, like the reference's eager entry point (it registers no output:
+    ops/c_api/reshape_and_cache/reshape_and_cache.cc:204-210); the placeholder output a graph-mode
+    framework sees is described by ``reshape_and_cache_infer``.
     """
     D = _Descs()
-    _host.check(_host.lib().ms_custom_ops_reshape_and_cache(
-        D(key), D(value), D(key_cache), D(value_cache), D(slot_mapping), int(cache_mode), int(head_num), _stream()))
+    rc = _host.lib().ms_custom_ops_reshape_and_cache(
+        D(key), D(value), D(key_cache), D(value_cache), D(slot_mapping), int(cache_mode), int(head_num), _stream())
+    if rc:
+        _host.check(rc)
     return None
+
+
+def reshape_and_cache_infer(key, value=None, key_cache=None, value_cache=None, slot_mapping=None, cache_mode=0,
+                            head_num=0):
+    """Shape / dtype of the operator's placeholder output (key's) after the operator's checks, without
+    touching a GPU.  Accepts TensorSpec or real tensors; returns (shape tuple, dtype name)."""
+    D = _Descs()
+    dt, nd = C.c_int32(), C.c_int32()
+    shp = (C.c_int64 * _host.MS_MAX_DIMS)()
+    _host.check(_host.lib().ms_custom_ops_reshape_and_cache_infer(
+        D(key), D(value), D(key_cache), D(value_cache), D(slot_mapping), int(cache_mode), int(head_num),
+        C.byref(dt), C.byref(nd), shp))
+    return tuple(shp[i] for i in range(nd.value)), _DT_NAMES[dt.value]
 
 
 def reshape_and_cache_quant(key, value, key_cache, value_cache, slot_mapping, k_descale, v_descale,
@@ -155,7 +180,16 @@ def _pa_args(D, query, key_cache, value_cache, block_tables, context_lens, attn_
              k_descale, k_offset, v_descale, v_offset, razor_offset, p_scale, log_n, q_seq_lens, q_head_num,
              qk_scale, kv_head_num, mask_type, batch_run_status_enable, quant_type, out_data_type,
              has_quant_offset, compress_type, calc_type, scale_type, input_layout, mla_v_dim, input_format):
-    a = _host.MsPagedAttentionArgs()
+    # one argument block per thread and attribute set: the scalar fields are written once
+    attrs = (q_head_num, qk_scale, kv_head_num, mask_type, batch_run_status_enable, quant_type, out_data_type,
+             has_quant_offset, compress_type, calc_type, scale_type, input_layout, mla_v_dim, input_format)
+    cache = _tls.__dict__.setdefault("pa_args", {})
+    a = cache.get(attrs)
+    fresh = a is None
+    if fresh:
+        if len(cache) > 64:
+            cache.clear()
+        a = cache[attrs] = _host.MsPagedAttentionArgs()
     a.query, a.key_cache, a.value_cache, a.block_tables = D(query), D(key_cache), D(value_cache), D(block_tables)
     a.context_lens = D(context_lens, host_ok=True)
     a.attn_mask = D(attn_mask)
@@ -163,6 +197,8 @@ def _pa_args(D, query, key_cache, value_cache, block_tables, context_lens, attn_
     a.k_descale, a.k_offset, a.v_descale, a.v_offset = D(k_descale), D(k_offset), D(v_descale), D(v_offset)
     a.razor_offset, a.p_scale, a.log_n = D(razor_offset), D(p_scale), D(log_n)
     a.q_seq_lens = D(q_seq_lens, host_ok=True)
+    if not fresh:
+        return a
     a.q_head_num, a.qk_scale, a.kv_head_num = int(q_head_num), float(qk_scale), int(kv_head_num)
     a.mask_type, a.batch_run_status_enable = int(mask_type), int(bool(batch_run_status_enable))
     a.quant_type, a.out_data_type, a.has_quant_offset = int(quant_type), int(out_data_type), int(bool(has_quant_offset))
@@ -171,12 +207,15 @@ def _pa_args(D, query, key_cache, value_cache, block_tables, context_lens, attn_
     return a
 
 
+_tls = threading.local()
 _workspaces = {}  # (device index, stream handle) -> grow-only uint8 buffer
 
 
-def _workspace(device, nbytes):
+def _workspace(device, nbytes, stream_handle=None):
     import torch
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    if stream_handle is None:
+        stream_handle = torch.cuda.current_stream(device).cuda_stream
+    key = (device.index, stream_handle)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(int(nbytes * 1.25), 1 << 20), dtype=torch.uint8, device=device)
@@ -227,25 +266,27 @@ def _paged_attention(with_lse, query, *rest):
     a = _pa_args(D, query, *rest)
     L = _host.lib()
     out = torch.empty_like(query)
+    dev = query.device
+    sh = torch.cuda.current_stream(dev).cuda_stream
+    stream = C.c_void_p(sh)
     if with_lse:
-        lse = torch.empty(query.shape[:2], dtype=torch.float32, device=query.device)
+        lse = torch.empty(query.shape[:2], dtype=torch.float32, device=dev)
 
         def launch(ws):
             return L.ms_custom_ops_paged_attention_with_lse(C.byref(a), D(out), D(lse), C.c_void_p(ws.data_ptr()),
-                                                            ws.numel(), _stream())
+                                                            ws.numel(), stream)
     else:
         def launch(ws):
-            return L.ms_custom_ops_paged_attention(C.byref(a), D(out), C.c_void_p(ws.data_ptr()), ws.numel(),
-                                                   _stream())
+            return L.ms_custom_ops_paged_attention(C.byref(a), D(out), C.c_void_p(ws.data_ptr()), ws.numel(), stream)
     # launch with the workspace at hand; if it is too small nothing was launched and the library
     # tells how much is needed (one validation + plan lookup per call in the steady state)
-    ws = _workspace(query.device, 0)
+    ws = _workspace(dev, 0, sh)
     rc = launch(ws)
     if rc != 0:
         need = L.ms_custom_ops_paged_attention_last_workspace_need()
         if need <= ws.numel():
             _host.check(rc)
-        _host.check(launch(_workspace(query.device, need)))
+        _host.check(launch(_workspace(dev, need, sh)))
     return (out, lse) if with_lse else out
 
 

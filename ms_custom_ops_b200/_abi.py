@@ -62,7 +62,7 @@ EXPORTS = (
     "msco_paged_attention_status", "msco_paged_attention_profile_enable", "msco_paged_attention_profile_read",
     "msco_paged_attention_launch_static", "msco_paged_attention_status_static",
     "msco_ipc_export", "msco_ipc_import", "msco_ipc_release", "msco_peer_allgather", "msco_decode_step",
-    "msco_paged_attention_launch_lse", "msco_expand_rows_i32", "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update", "msco_fa_update_strided",
+    "msco_paged_attention_launch_lse", "msco_expand_rows_i32", "msco_paged_attention_replan", "msco_plan_arena_stats", "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update", "msco_fa_update_strided",
 )
 
 
@@ -95,6 +95,10 @@ def lib():
     L.msco_paged_attention_split_tokens.argtypes = [i32, i32]
     L.msco_paged_attention_plan.restype = C.c_int
     L.msco_paged_attention_plan.argtypes = [C.POINTER(MscoPaDesc), C.POINTER(i32), i32, C.POINTER(vp)]
+    L.msco_paged_attention_replan.restype = C.c_int
+    L.msco_paged_attention_replan.argtypes = [vp, C.POINTER(i32), i32]
+    L.msco_plan_arena_stats.restype = None
+    L.msco_plan_arena_stats.argtypes = [C.POINTER(i64)]
     L.msco_paged_attention_workspace_bytes.restype = sz
     L.msco_paged_attention_workspace_bytes.argtypes = [vp]
     L.msco_paged_attention_plan_info.restype = C.c_int
@@ -136,6 +140,14 @@ def check(code):
         raise MscoError(code, lib().msco_last_error().decode("utf-8", "replace"))
 
 
+def plan_arena_stats():
+    """Counters of the pinned plan arena (see msco_plan_arena_stats)."""
+    buf = (C.c_int64 * 6)()
+    lib().msco_plan_arena_stats(buf)
+    names = ("slabs", "slab_bytes", "blocks_in_use", "block_allocs", "oversize_allocs", "pinned")
+    return dict(zip(names, (int(v) for v in buf)))
+
+
 class PaPlan:
     """Owner of one MscoPaPlan (host-side launch plan for a vector of context lengths)."""
 
@@ -151,6 +163,17 @@ class PaPlan:
     @property
     def handle(self):
         return self._h
+
+    def replan(self, context_lens):
+        """Re-plan in place for new lengths (same descriptor); `context_lens` is a list or an int32
+        numpy array.  Keeps the plan's pinned block and tensor maps: no allocation."""
+        if hasattr(context_lens, "ctypes"):
+            ptr, n = context_lens.ctypes.data_as(C.POINTER(C.c_int32)), int(context_lens.size)
+        else:
+            n = len(context_lens)
+            ptr = (C.c_int32 * n)(*[int(x) for x in context_lens])
+        check(lib().msco_paged_attention_replan(self._h, ptr, n))
+        self.batch = n
 
     @property
     def workspace_bytes(self) -> int:

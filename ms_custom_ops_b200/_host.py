@@ -42,7 +42,8 @@ EXPORTS = (
     "ms_custom_ops_op_signature", "ms_custom_ops_plan_cache_stats", "ms_custom_ops_plan_cache_clear",
     "ms_custom_ops_paged_cache_load_infer", "ms_custom_ops_paged_cache_load_workspace_size",
     "ms_custom_ops_paged_cache_load", "ms_custom_ops_fa_update_infer", "ms_custom_ops_fa_update",
-    "ms_custom_ops_paged_attention_with_lse",
+    "ms_custom_ops_paged_attention_with_lse", "ms_custom_ops_reshape_and_cache_infer",
+    "ms_custom_ops_plan_cache_miss_stats", "ms_custom_ops_plan_arena_stats",
 )
 
 
@@ -66,6 +67,13 @@ def lib():
     L.ms_custom_ops_reshape_and_cache.argtypes = [_TP] * 5 + [i64, i64, vp]
     L.ms_custom_ops_reshape_and_cache_quant.restype = C.c_int
     L.ms_custom_ops_reshape_and_cache_quant.argtypes = [_TP] * 9 + [vp]
+    L.ms_custom_ops_reshape_and_cache_infer.restype = C.c_int
+    L.ms_custom_ops_reshape_and_cache_infer.argtypes = [_TP] * 5 + [i64, i64, C.POINTER(C.c_int32),
+                                                        C.POINTER(C.c_int32), C.POINTER(i64)]
+    L.ms_custom_ops_plan_cache_miss_stats.restype = None
+    L.ms_custom_ops_plan_cache_miss_stats.argtypes = [C.POINTER(i64)] * 2
+    L.ms_custom_ops_plan_arena_stats.restype = None
+    L.ms_custom_ops_plan_arena_stats.argtypes = [C.POINTER(i64)]
     ap = C.POINTER(MsPagedAttentionArgs)
     L.ms_custom_ops_paged_attention_infer.restype = C.c_int
     L.ms_custom_ops_paged_attention_infer.argtypes = [ap, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(i64)]
@@ -129,7 +137,18 @@ def registered_ops():
 def plan_cache_stats():
     h, m, e = C.c_int64(), C.c_int64(), C.c_int64()
     lib().ms_custom_ops_plan_cache_stats(C.byref(h), C.byref(m), C.byref(e))
-    return {"hits": h.value, "misses": m.value, "entries": e.value}
+    r, c = C.c_int64(), C.c_int64()
+    lib().ms_custom_ops_plan_cache_miss_stats(C.byref(r), C.byref(c))
+    return {"hits": h.value, "misses": m.value, "entries": e.value, "recycled": r.value, "created": c.value}
+
+
+def plan_arena_stats():
+    """Counters of the pinned memory pool the plans live in (no pinned allocation on the step path:
+    `slabs` stops growing after start-up)."""
+    buf = (C.c_int64 * 6)()
+    lib().ms_custom_ops_plan_arena_stats(buf)
+    names = ("slabs", "slab_bytes", "blocks_in_use", "block_allocs", "oversize_allocs", "pinned")
+    return dict(zip(names, (int(v) for v in buf)))
 
 
 def plan_cache_clear():

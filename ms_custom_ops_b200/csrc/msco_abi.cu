@@ -9,6 +9,7 @@
 
 #include "msco_common.cuh"
 #include "pa_params.h"
+#include "plan_arena.h"
 
 namespace msco {
 
@@ -75,14 +76,34 @@ static int validate_desc(const MscoPaDesc &d) {
   return MSCO_OK;
 }
 
-extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *host_context_lens,
-                                         int32_t batch, MscoPaPlan **out_plan) {
-  if (desc == nullptr || out_plan == nullptr || batch < 0 || (batch > 0 && host_context_lens == nullptr))
-    return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: NULL argument");
-  *out_plan = nullptr;
-  int rc = validate_desc(*desc);
-  if (rc != MSCO_OK) return rc;
-  const MscoPaDesc &d = *desc;
+namespace {
+
+// SM count of the current device, looked up once per device ordinal (148 when there is none).
+int current_sm_count() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    (void)cudaGetLastError();  // no device (planning only): keep the B200 default
+    return 148;
+  }
+  if (dev >= 0 && dev < 64) {
+    const int c = cached[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
+  }
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+    (void)cudaGetLastError();
+    return 148;
+  }
+  if (dev >= 0 && dev < 64) cached[dev].store(sms, std::memory_order_relaxed);
+  return sms;
+}
+
+// Fills `pl` (descriptor already set) for one vector of context lengths.  The plan words live in a
+// block of the pinned arena that the plan keeps across calls: a re-plan with a batch of the same size
+// class touches no allocator at all.
+int fill_plan(MscoPaPlan *pl, const int32_t *host_context_lens, int32_t batch) {
+  const MscoPaDesc &d = pl->desc;
   const int64_t cap = (int64_t)d.max_blocks_per_seq * d.block_size;
   for (int b = 0; b < batch; ++b) {
     if (host_context_lens[b] < 0)
@@ -93,30 +114,15 @@ extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *
                   "paged_attention_plan: context_lens[%d] = %d exceeds the block table (%d blocks of %d)", b,
                   host_context_lens[b], d.max_blocks_per_seq, d.block_size);
   }
-  MscoPaPlan *pl = new (std::nothrow) MscoPaPlan();
-  if (pl == nullptr) return fail(MSCO_ERR_INTERNAL, "paged_attention_plan: out of host memory");
-  pl->desc = d;
   pl->batch = batch;
   const int g = d.num_q_heads / d.num_kv_heads;
-  const bool tma_ok = pa_tma_supported(d);
-  if (d.kernel == kKernelTma && !tma_ok) {
-    delete pl;
-    return fail(MSCO_ERR_UNSUPPORTED, "paged_attention_plan: the TMA kernel needs head_dim 128 and block_size 16/32/64/128");
-  }
-  pl->kernel = (d.kernel == kKernelGeneric || !tma_ok) ? kKernelGeneric : kKernelTma;
-  pl->rows_per_item = (pl->kernel == kKernelTma && g > 8) ? 16 : 8;
   const int nqb = (g + pl->rows_per_item - 1) / pl->rows_per_item;
   const int items_per_split = d.num_kv_heads * nqb;
+  pl->num_sms = current_sm_count();
 
-  int dev = 0, sms = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess &&
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
-    pl->num_sms = sms;
-  else
-    (void)cudaGetLastError();  // no device (planning only): keep the B200 default
-
-  // sequences with tokens, longest first (stable), so that the big items lead the round-robin
-  std::vector<int> order;
+  // sequences with tokens, longest first (stable), so that the big items lead the work list
+  static thread_local std::vector<int> order;
+  order.clear();
   for (int b = 0; b < batch; ++b)
     if (host_context_lens[b] > 0) order.push_back(b);
   std::stable_sort(order.begin(), order.end(),
@@ -125,16 +131,15 @@ extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *
   pl->nseq = nseq;
   pl->plan_words = kPlanHeaderWords + (size_t)(nseq + 1) + 5 * (size_t)nseq + 2 * (size_t)batch;
   pl->plan_bytes = pl->plan_words * 4;
-  if (cudaHostAlloc(reinterpret_cast<void **>(&pl->host_words), std::max<size_t>(pl->plan_bytes, 64),
-                    cudaHostAllocDefault) == cudaSuccess) {
-    pl->host_pinned = true;
-  } else {
-    (void)cudaGetLastError();
-    pl->host_words = static_cast<int32_t *>(malloc(std::max<size_t>(pl->plan_bytes, 64)));
-    if (pl->host_words == nullptr) {
-      delete pl;
-      return fail(MSCO_ERR_INTERNAL, "paged_attention_plan: out of host memory");
-    }
+  if (pl->upload_pending) {  // an async copy out of the old words may still be queued
+    MSCO_CUDA_CHECK(cudaEventSynchronize(pl->upload_done));
+    pl->upload_pending = false;
+  }
+  if (pl->host_words == nullptr || pl->host_capacity < pl->plan_bytes) {
+    if (pl->host_words != nullptr) PlanArena::Instance().Free(pl->host_words, pl->host_capacity);
+    pl->host_capacity = 0;
+    pl->host_words = static_cast<int32_t *>(PlanArena::Instance().Alloc(pl->plan_bytes, &pl->host_capacity));
+    if (pl->host_words == nullptr) return fail(MSCO_ERR_INTERNAL, "paged_attention_plan: out of host memory");
   }
   int32_t *w = pl->host_words;
   memset(w, 0, pl->plan_bytes);
@@ -156,10 +161,7 @@ extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *
     if (ns > 1) parts += ns;
     max_splits = std::max(max_splits, ns);
     kv_tokens += len;
-    if (items > 0x7fffffffLL) {
-      msco_paged_attention_plan_destroy(pl);
-      return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: too many work items");
-    }
+    if (items > 0x7fffffffLL) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: too many work items");
   }
   item_base[nseq] = (int32_t)items;
   w[0] = 0; w[1] = nseq; w[2] = (int32_t)items; w[3] = (int32_t)parts; w[4] = batch; w[5] = items_per_split;
@@ -167,14 +169,61 @@ extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *
   pl->total_parts = (int)parts;
   pl->max_splits = max_splits;
   pl->kv_tokens = kv_tokens;
-  pl->need_reduce = parts > 0 || nseq < batch;
+  // the TMA kernel merges its split partials itself (the CTA that stores the last partial of a group
+  // does it); the reduce kernel is then only needed to zero the rows of empty sequences
+  pl->fused_merge = pl->kernel == kKernelTma;
+  pl->need_reduce = pl->fused_merge ? nseq < batch : (parts > 0 || nseq < batch);
   pl->grid = pl->kernel == kKernelTma ? (int)std::min<int64_t>(items, pl->num_sms) : (int)items;
-  pl->part_o_offset = align_up(kPlanRegionOffset + pl->plan_bytes, 256);
+  pl->num_groups = pl->fused_merge ? nseq * items_per_split : 0;
+  pl->sync_offset = align_up(kPlanRegionOffset + pl->plan_bytes, 256);
+  pl->sync_bytes = pl->fused_merge ? align_up((size_t)(kSyncHeaderWords + pl->num_groups) * 4, 256) : 0;
+  pl->part_o_offset = pl->sync_offset + pl->sync_bytes;
   const size_t part_o_bytes = (size_t)parts * d.num_q_heads * d.head_dim * 4;
   pl->part_ml_offset = align_up(pl->part_o_offset + part_o_bytes, 256);
   pl->workspace_bytes = align_up(pl->part_ml_offset + (size_t)parts * d.num_q_heads * 2 * 4, 256);
+  return MSCO_OK;
+}
+
+}  // namespace
+
+extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *host_context_lens,
+                                         int32_t batch, MscoPaPlan **out_plan) {
+  if (desc == nullptr || out_plan == nullptr || batch < 0 || (batch > 0 && host_context_lens == nullptr))
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: NULL argument");
+  *out_plan = nullptr;
+  int rc = validate_desc(*desc);
+  if (rc != MSCO_OK) return rc;
+  const MscoPaDesc &d = *desc;
+  const bool tma_ok = pa_tma_supported(d);
+  if (d.kernel == kKernelTma && !tma_ok)
+    return fail(MSCO_ERR_UNSUPPORTED, "paged_attention_plan: the TMA kernel needs head_dim 128 and block_size 16/32/64/128");
+  MscoPaPlan *pl = new (std::nothrow) MscoPaPlan();
+  if (pl == nullptr) return fail(MSCO_ERR_INTERNAL, "paged_attention_plan: out of host memory");
+  pl->desc = d;
+  const int g = d.num_q_heads / d.num_kv_heads;
+  pl->kernel = (d.kernel == kKernelGeneric || !tma_ok) ? kKernelGeneric : kKernelTma;
+  pl->rows_per_item = (pl->kernel == kKernelTma && g > 8) ? 16 : 8;
+  rc = fill_plan(pl, host_context_lens, batch);
+  if (rc != MSCO_OK) {
+    msco_paged_attention_plan_destroy(pl);
+    return rc;
+  }
   *out_plan = pl;
   return MSCO_OK;
+}
+
+extern "C" int msco_paged_attention_replan(MscoPaPlan *plan, const int32_t *host_context_lens, int32_t batch) {
+  if (plan == nullptr || batch < 0 || (batch > 0 && host_context_lens == nullptr))
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention_replan: NULL argument");
+  return fill_plan(plan, host_context_lens, batch);
+}
+
+extern "C" void msco_plan_arena_stats(int64_t *stats /* [6] */) {
+  if (stats == nullptr) return;
+  PlanArenaStats st;
+  PlanArena::Instance().Stats(&st);
+  stats[0] = st.slabs; stats[1] = st.slab_bytes; stats[2] = st.blocks_in_use;
+  stats[3] = st.block_allocs; stats[4] = st.oversize_allocs; stats[5] = st.pinned;
 }
 
 extern "C" size_t msco_paged_attention_workspace_bytes(const MscoPaPlan *plan) {
@@ -226,9 +275,11 @@ extern "C" void msco_paged_attention_plan_destroy(MscoPaPlan *plan) {
   if (plan->prof_ev[0][0] != nullptr)
     for (int i = 0; i < MscoPaPlan::kProfRing; ++i)
       for (int j = 0; j < 2; ++j) cudaEventDestroy(plan->prof_ev[i][j]);
-  if (plan->host_words != nullptr) {
-    if (plan->host_pinned) cudaFreeHost(plan->host_words); else free(plan->host_words);
+  if (plan->upload_done != nullptr) {
+    if (plan->upload_pending) cudaEventSynchronize(plan->upload_done);
+    cudaEventDestroy(plan->upload_done);
   }
+  if (plan->host_words != nullptr) PlanArena::Instance().Free(plan->host_words, plan->host_capacity);
   delete plan;
 }
 
@@ -261,7 +312,8 @@ bool recall_launch(const void *ws, uint32_t *epoch) {
 int pa_launch_impl(const MscoPaPlan *plan, const void *query, const void *key_cache, const void *value_cache,
                    const int32_t *block_tables, const float *k_descale, const int32_t *k_offset,
                    const float *v_descale, const int32_t *v_offset, const void *attn_mask, void *out,
-                   void *workspace, size_t workspace_bytes, void *stream, bool after_kernel, float *lse = nullptr) {
+                   void *workspace, size_t workspace_bytes, void *stream, bool after_kernel, float *lse = nullptr,
+                   bool sync_cleared = false) {
   if (plan == nullptr) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch: NULL plan");
   if (plan->batch == 0) return MSCO_OK;
   const MscoPaDesc &d = plan->desc;
@@ -294,6 +346,8 @@ int pa_launch_impl(const MscoPaPlan *plan, const void *query, const void *key_ca
   char *ws = static_cast<char *>(workspace);
   p.status = reinterpret_cast<int32_t *>(ws);
   p.plan = reinterpret_cast<const int32_t *>(ws + kPlanRegionOffset);
+  p.sync = reinterpret_cast<uint32_t *>(ws + plan->sync_offset);
+  p.fused_merge = plan->fused_merge ? 1 : 0;
   p.part_o = reinterpret_cast<float *>(ws + plan->part_o_offset);
   p.part_ml = reinterpret_cast<float *>(ws + plan->part_ml_offset);
   p.num_blocks = d.num_blocks;
@@ -316,7 +370,18 @@ int pa_launch_impl(const MscoPaPlan *plan, const void *query, const void *key_ca
   } else {
     MSCO_CUDA_CHECK(cudaMemcpyAsync(ws + kPlanRegionOffset, plan->host_words, plan->plan_bytes,
                                     cudaMemcpyHostToDevice, st));
+    // a re-plan rewrites host_words: it waits for this event first
+    if (plan->upload_done == nullptr)
+      MSCO_CUDA_CHECK(cudaEventCreateWithFlags(&plan->upload_done, cudaEventDisableTiming));
+    MSCO_CUDA_CHECK(cudaEventRecord(plan->upload_done, st));
+    plan->upload_pending = true;
     after_kernel = false;  // a copy now sits between the previous kernel and ours
+  }
+  // the scheduling words (work-item ticket, per-group arrival counters) start at zero: either the
+  // kernel in front of us cleared them on its way (fused decode step) or a small memset does
+  if (plan->sync_bytes != 0 && plan->total_items > 0 && !sync_cleared) {
+    MSCO_CUDA_CHECK(cudaMemsetAsync(ws + plan->sync_offset, 0, plan->sync_bytes, st));
+    after_kernel = false;
   }
   cudaEvent_t *pe = nullptr;
   if (plan->profile && plan->total_items > 0) {
@@ -411,19 +476,32 @@ extern "C" int msco_decode_step(const MscoPaPlan *plan, const void *key, const v
   const MscoPaDesc &d = plan->desc;
   const int64_t row = (int64_t)d.num_kv_heads * d.head_dim;
   const int64_t slots = d.num_blocks * d.block_size;
+  if (plan->batch != 0 && (workspace == nullptr || workspace_bytes < plan->workspace_bytes))
+    return fail(MSCO_ERR_INVALID_ARG, "decode_step: workspace too small (%zu < %zu)", workspace_bytes,
+                plan->workspace_bytes);
+  // the scatter kernel also zeroes the attention kernel's scheduling words, which saves the memset
+  // (and the launch boundary it would put between the two kernels)
+  uint32_t *clear = nullptr;
+  int clear_words = 0;
+  if (plan->batch != 0 && plan->sync_bytes != 0 && plan->total_items > 0) {
+    clear = reinterpret_cast<uint32_t *>(static_cast<char *>(workspace) + plan->sync_offset);
+    clear_words = (int)(plan->sync_bytes / 4);
+  }
+  bool cleared = false;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc;
   if (d.quant_type == 1) {
-    rc = msco_reshape_and_cache_quant(key, value, static_cast<int8_t *>(key_cache), static_cast<int8_t *>(value_cache),
-                                      slot_mapping, num_tokens, row, row, d.q_dtype, k_descale,
-                                      d.has_quant_offset ? k_offset : nullptr, v_descale,
-                                      d.has_quant_offset ? v_offset : nullptr, slots, nullptr, stream);
+    rc = launch_rac_quant(key, value, static_cast<int8_t *>(key_cache), static_cast<int8_t *>(value_cache),
+                          slot_mapping, num_tokens, row, row, d.q_dtype, k_descale,
+                          d.has_quant_offset ? k_offset : nullptr, v_descale,
+                          d.has_quant_offset ? v_offset : nullptr, slots, nullptr, st, clear, clear_words, &cleared);
   } else {
-    rc = msco_reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, num_tokens, row * 2, row * 2, slots,
-                                nullptr, stream);
+    rc = launch_rac(key, value, key_cache, value_cache, slot_mapping, num_tokens, row * 2, row * 2, slots, nullptr, st,
+                    clear, clear_words, &cleared);
   }
   if (rc != MSCO_OK) return rc;
   return pa_launch_impl(plan, query, key_cache, value_cache, block_tables, k_descale, k_offset, v_descale, v_offset,
-                        attn_mask, out, workspace, workspace_bytes, stream, num_tokens > 0);
+                        attn_mask, out, workspace, workspace_bytes, stream, num_tokens > 0, nullptr, cleared);
 }
 
 extern "C" int msco_paged_attention_status(const MscoPaPlan *plan, const void *workspace) {

@@ -75,6 +75,8 @@ __host__ __device__ inline PlanView make_plan_view(const int32_t *w) {
 // of sequence `b` against KV tokens [tok0, tok1).
 struct WorkItem {
   int b, kvh, row0, nrows, tok0, tok1, nsplit, part;
+  int grp;    // index of the (sequence, kv head, q-row block) group: one arrival counter per group
+  int part0;  // partial row of the group's first split (part = part0 + split)
 };
 
 #ifdef __CUDACC__
@@ -139,7 +141,9 @@ __device__ __forceinline__ WorkItem decode_item(const PlanView &pv, int t, int n
   w.nsplit = __ldg(pv.nsplit + s);
   w.tok0 = split * c;
   w.tok1 = min(len, w.tok0 + c);
-  w.part = __ldg(pv.part_base + s) + split;
+  w.part0 = __ldg(pv.part_base + s);
+  w.part = w.part0 + split;
+  w.grp = s * nps + hh;
   return w;
 }
 

@@ -14,6 +14,7 @@
 #include <math_constants.h>
 
 #include "msco_common.cuh"
+#include "pa_merge.cuh"
 #include "pa_params.h"
 
 namespace msco {
@@ -231,6 +232,10 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p, const __grid
     return;
   }
   const int base = __ldg(pv.b_part_base + b);
+  if (D == 128) {  // same code as the attention kernel's own epilogue: identical bits
+    merge_row_d128<TQ>(p, b, hq, ns, base, lane);
+    return;
+  }
   const int64_t hq_stride = p.num_q_heads;
   // pass 1: M = max_s m_s (lanes stride over the splits)
   float M = kNeg;
@@ -239,44 +244,6 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p, const __grid
   M = warp_max(M);
   const int kvh = hq / p.group;
   float L = 0.f;
-  if (D == 128) {
-    // lane owns 4 consecutive head-dim columns; splits in blocks of 32 (weights in registers)
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = 0; s0 < ns; s0 += 32) {
-      float f_mine = 0.f, l_mine = 0.f;
-      if (s0 + lane < ns) {
-        const float2 ml = __ldg(reinterpret_cast<const float2 *>(p.part_ml + ((int64_t)(base + s0 + lane) * hq_stride + hq) * 2));
-        f_mine = exp2f(ml.x - M);
-        l_mine = ml.y;
-      }
-      const int cnt = min(32, ns - s0);
-#pragma unroll 8
-      for (int j = 0; j < cnt; ++j) {  // split order: bit-reproducible
-        const float f = __shfl_sync(0xffffffffu, f_mine, j);
-        const float lj = __shfl_sync(0xffffffffu, l_mine, j);
-        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.part_o + ((int64_t)(base + s0 + j) * hq_stride + hq) * 128) + lane);
-        L = fmaf(lj, f, L);
-        acc.x = fmaf(v.x, f, acc.x); acc.y = fmaf(v.y, f, acc.y);
-        acc.z = fmaf(v.z, f, acc.z); acc.w = fmaf(v.w, f, acc.w);
-      }
-    }
-    const float inv = 1.f / L;
-    float r0 = acc.x * inv, r1 = acc.y * inv, r2 = acc.z * inv, r3 = acc.w * inv;
-    if (p.v_descale != nullptr) {
-      const float4 vs = __ldg(reinterpret_cast<const float4 *>(p.v_descale + kvh * 128) + lane);
-      if (p.v_offset != nullptr) {
-        const int4 vo = __ldg(reinterpret_cast<const int4 *>(p.v_offset + kvh * 128) + lane);
-        r0 += (float)vo.x; r1 += (float)vo.y; r2 += (float)vo.z; r3 += (float)vo.w;
-      }
-      r0 *= vs.x; r1 *= vs.y; r2 *= vs.z; r3 *= vs.w;
-    }
-    uint2 pk;
-    pk.x = pack2<TQ>(r0, r1);
-    pk.y = pack2<TQ>(r2, r3);
-    *reinterpret_cast<uint2 *>(out + lane * 4) = pk;
-    if (lane == 0 && p.lse != nullptr) p.lse[row] = (M + log2f(L)) * kLn2;
-    return;
-  }
   float o[kGenDL];
 #pragma unroll
   for (int i = 0; i < kGenDL; ++i) o[i] = 0.f;

@@ -31,6 +31,11 @@ struct PaParams {
   int32_t plan_in_param;  // the plan words are in the PlanParam kernel argument
   float *part_o;   // [total_parts, num_q_heads, head_dim] un-normalised partial outputs
   float *part_ml;  // [total_parts, num_q_heads, 2] (running max in log2 domain, running sum)
+  // Scheduling words of the persistent kernel, zero when the kernel starts: sync[0] is the work-item
+  // ticket, sync[kSyncHeaderWords + g] counts the splits of group g (sequence, kv head, q-row block)
+  // that have stored their partial; the CTA that brings it to the split count merges the group.
+  uint32_t *sync;
+  int32_t fused_merge;  // the attention kernel merges the split partials itself (no reduce kernel)
   int64_t num_blocks;
   int64_t mask_batch_stride, mask_head_stride;
   int num_q_heads, num_kv_heads, head_dim, block_size, group, rows_per_item, max_blocks_per_seq;
@@ -45,7 +50,8 @@ constexpr int kPlanParamWords = 2304;
 struct PlanParam {
   int32_t w[kPlanParamWords];
 };
-constexpr size_t kPlanRegionOffset = 256;  // workspace: [status block | plan words | partials]
+constexpr size_t kPlanRegionOffset = 256;  // workspace: [status block | plan words | scheduling words | partials]
+constexpr int kSyncHeaderWords = 4;        // scheduling words: [ticket, 3 unused, one counter per group]
 
 constexpr int kKernelGeneric = 1;
 constexpr int kKernelTma = 2;
@@ -62,10 +68,19 @@ struct MscoPaPlan {
   int nseq = 0, total_items = 0, total_parts = 0, max_splits = 0;
   bool need_reduce = false;
   int64_t kv_tokens = 0;
-  int32_t *host_words = nullptr;  // pinned when a CUDA device is present
-  bool host_pinned = false;
+  // plan words: a block of the pooled pinned arena (plan_arena.h), kept across re-plans
+  int32_t *host_words = nullptr;
+  size_t host_capacity = 0;     // bytes of that block
   size_t plan_words = 0;
   size_t plan_bytes = 0;        // bytes uploaded per launch
+  // an async copy of host_words (plans too large for the kernel parameters) may still be queued
+  // when the plan is rewritten: the event is recorded behind the copy and waited for before a re-plan
+  mutable cudaEvent_t upload_done = nullptr;
+  mutable bool upload_pending = false;
+  bool fused_merge = false;     // the attention kernel merges the split partials itself
+  int num_groups = 0;           // (sequence with tokens, kv head, q-row block) triples
+  size_t sync_offset = 0;       // scheduling words inside the workspace
+  size_t sync_bytes = 0;
   size_t part_o_offset = 0;     // byte offsets inside the workspace
   size_t part_ml_offset = 0;
   size_t workspace_bytes = 0;
@@ -92,5 +107,15 @@ int launch_pa_generic(const MscoPaPlan *plan, const PaParams &p, const PlanParam
 int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream,
                   bool after_kernel);
 int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream);
+// reshape_and_cache launchers that can also zero `clear_words` 32-bit words at `clear` (the attention
+// kernel's scheduling words) on their way; *cleared tells whether the launched kernel does it
+int launch_rac(const void *key, const void *value, void *key_cache, void *value_cache, const int32_t *slot_mapping,
+               int64_t num_tokens, int64_t k_row_bytes, int64_t v_row_bytes, int64_t num_slots, int32_t *oob_count,
+               cudaStream_t stream, uint32_t *clear, int clear_words, bool *cleared);
+int launch_rac_quant(const void *key, const void *value, int8_t *key_cache, int8_t *value_cache,
+                     const int32_t *slot_mapping, int64_t num_tokens, int64_t k_row_elems, int64_t v_row_elems,
+                     int32_t in_dtype, const float *k_descale, const int32_t *k_offset, const float *v_descale,
+                     const int32_t *v_offset, int64_t num_slots, int32_t *oob_count, cudaStream_t stream,
+                     uint32_t *clear, int clear_words, bool *cleared);
 bool pa_tma_supported(const MscoPaDesc &d);
 }  // namespace msco

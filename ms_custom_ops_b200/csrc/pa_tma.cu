@@ -32,6 +32,7 @@
 #include <type_traits>
 
 #include "msco_common.cuh"
+#include "pa_merge.cuh"
 #include "pa_params.h"
 
 namespace msco {
@@ -43,6 +44,7 @@ constexpr int kQSlotBytes = 16 * kD * 2;
 constexpr float kNeg = -1.0e30f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr uint32_t kWaitLimit = 1u << 24;
+constexpr int kDescInts = 12;         // work-item descriptor handed from the producer to the consumers
 
 // NT = number of 8-row tiles of the q group (1: up to 8 rows, 2: up to 16).
 template <bool KV8, int NT> struct Cfg {
@@ -61,8 +63,8 @@ template <bool KV8, int NT> struct Cfg {
                                                                          // 2 partial score offsets per q row (lse)
   static constexpr int kOffMerge = kOffQFrag + kQFragBytes;
   static constexpr int kOffMl = kOffMerge + kMergeBytes;            // [warp][16] float2
-  static constexpr int kOffDesc = kOffMl + kWarps * 16 * 2 * 4;     // 2 x 8 ints
-  static constexpr int kOffBar = kOffDesc + 2 * 8 * 4;              // mbarriers
+  static constexpr int kOffDesc = kOffMl + kWarps * 16 * 2 * 4;     // 2 x kDescInts ints, then the merge flag
+  static constexpr int kOffBar = kOffDesc + 2 * kDescInts * 4 + 16; // mbarriers
   static constexpr int kNumBars = 2 * kStages + 4;
   static constexpr int kOffItemBase = kOffBar + kNumBars * 8 + 16;  // copy of the plan's item_base[]
   static constexpr int kItemBaseCap = 1024;                          // sequences (+1) that fit
@@ -146,19 +148,33 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     uint32_t st = 0, ph = 0;
     const int bs = p.block_size;
     const int bpt = kTile / bs;  // cache blocks per tile (divides 32)
-    int qi = 0;
-    for (int t = blockIdx.x; t < total; t += gridDim.x, ++qi) {
-      const WorkItem w = decode_item(pv, t, p.num_kv_heads, p.group, C::kRows, ibs);
+    // Work items are handed out by a ticket (the list is longest-first): the first item of a CTA is
+    // its own index, every further one comes from an atomic counter in the workspace that is zero
+    // when the kernel starts.  Which CTA computes an item has no influence on the item's bits.
+    int t = blockIdx.x;
+    for (int qi = 0;; ++qi) {
       const int qs = qi & 1;
       const uint32_t qph = (qi >> 1) & 1;
       if (!mbar_wait(&qempty[qs], qph ^ 1, kWaitLimit)) {
         report_status(p.status, p.epoch, kStatusTimeout);
         return;
       }
+      if (t >= total) {  // no work left: tell the consumers
+        if (lane == 0) {
+          desc[qs * kDescInts] = -1;
+          mbar_arrive(&qfull[qs]);
+        }
+        break;
+      }
+      const WorkItem w = decode_item(pv, t, p.num_kv_heads, p.group, C::kRows, ibs);
+      // next ticket: its latency hides behind this item's loads
+      int t_next = 0;
+      if (lane == 0) t_next = (int)gridDim.x + (int)atomicAdd(p.sync, 1u);
       if (lane == 0) {
-        int *d = desc + qs * 8;
+        int *d = desc + qs * kDescInts;
         d[0] = w.b; d[1] = w.kvh; d[2] = w.row0; d[3] = w.nrows;
         d[4] = w.tok0; d[5] = w.tok1; d[6] = w.nsplit; d[7] = w.part;
+        d[8] = w.grp; d[9] = w.part0;
         const uint32_t qbytes = (uint32_t)w.nrows * kD * 2;
         mbar_arrive_expect_tx(&qfull[qs], qbytes);
         const char *qsrc = static_cast<const char *>(p.q) +
@@ -204,6 +220,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           }
         }
       }
+      t = __shfl_sync(0xffffffffu, t_next, 0);
     }
     return;
   }
@@ -222,17 +239,26 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   const int tid = threadIdx.x;
 
   uint32_t st = 0, ph = 0;
-  int qi = 0;
-  for (int t = blockIdx.x; t < total; t += gridDim.x, ++qi) {
+  // Deferred merge of split partials.  When an item of a multi-split group has stored its partial,
+  // one thread bumps the group's arrival counter; the answer is looked at one item later (so its
+  // latency costs nothing), and if this CTA was the last arriver all warps merge the group then.
+  volatile int *merge_flag = reinterpret_cast<volatile int *>(desc + 2 * kDescInts);
+  bool pend = false;                 // a counter bump of this CTA awaits its answer (uniform)
+  unsigned pend_old = 0;             // the answer (thread 0 only)
+  int pend_b = 0, pend_hq0 = 0, pend_nrows = 0, pend_ns = 0, pend_part0 = 0;
+  for (int qi = 0;; ++qi) {
     const int qs = qi & 1;
     const uint32_t qph = (qi >> 1) & 1;
     if (!mbar_wait(&qfull[qs], qph, kWaitLimit)) {
       report_status(p.status, p.epoch, kStatusTimeout);
       return;
     }
-    const int *dsc = desc + qs * 8;
-    const int b = dsc[0], kvh = dsc[1], row0 = dsc[2], nrows = dsc[3];
+    const int *dsc = desc + qs * kDescInts;
+    const int b = dsc[0];
+    if (b < 0) break;  // the producer found no further work item
+    const int kvh = dsc[1], row0 = dsc[2], nrows = dsc[3];
     const int tok0 = dsc[4], tok1 = dsc[5], nsplit = dsc[6], part = dsc[7];
+    const int grp = dsc[8], part0 = dsc[9];
 
     // ---- Q^T fragments (B operand): lane holds q row 8nt + gid, rows >= nrows are zero ----
     uint32_t qb[8][NT][2];
@@ -519,7 +545,15 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         w0[db] = o[mt][nt][2]; w1[db] = o[mt][nt][3];
       }
     }
+    if (pend && tid == 0) *merge_flag = (pend_old == (unsigned)(pend_ns - 1)) ? 1 : 0;
     named_bar_sync(1, C::kConsumerThreads);
+    if (pend) {
+      if (*merge_flag) {
+        __threadfence();  // the other CTAs' partials were fenced before their counter bumps
+        for (int r = warp; r < pend_nrows; r += C::kWarps) merge_row_d128<T>(p, pend_b, pend_hq0 + r, pend_ns, pend_part0, lane);
+      }
+      pend = false;
+    }
     for (int u = tid; u < C::kRows * 32; u += C::kConsumerThreads) {
       const int row = u >> 5, c4 = (u & 31) * 4;  // four consecutive head-dim columns of one row
       if (row < nrows) {
@@ -574,7 +608,26 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         }
       }
     }
+    const bool bump = nsplit > 1 && p.fused_merge != 0;
     named_bar_sync(1, C::kConsumerThreads);  // merge buffers are reused by the next item
+    if (bump) {
+      if (tid == 0) {
+        // the barrier ordered every thread's partial stores before this fence, the fence orders them
+        // (cumulatively) before the counter moves
+        __threadfence();
+        pend_old = atomicAdd(p.sync + kSyncHeaderWords + grp, 1u);
+      }
+      pend = true;
+      pend_b = b; pend_hq0 = kvh * p.group + row0; pend_nrows = nrows; pend_ns = nsplit; pend_part0 = part0;
+    }
+  }
+  if (pend) {  // the last item of this CTA: look at the answer now
+    if (tid == 0) *merge_flag = (pend_old == (unsigned)(pend_ns - 1)) ? 1 : 0;
+    named_bar_sync(1, C::kConsumerThreads);
+    if (*merge_flag) {
+      __threadfence();
+      for (int r = warp; r < pend_nrows; r += C::kWarps) merge_row_d128<T>(p, pend_b, pend_hq0 + r, pend_ns, pend_part0, lane);
+    }
   }
 }
 

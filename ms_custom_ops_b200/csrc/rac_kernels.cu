@@ -7,6 +7,7 @@
 #include <algorithm>
 
 #include "msco_common.cuh"
+#include "pa_params.h"
 
 namespace msco {
 namespace {
@@ -34,10 +35,12 @@ __global__ void __launch_bounds__(kRacThreads)
 rac_scatter16_kernel(const uint4 *__restrict__ key, const uint4 *__restrict__ value,
                      uint4 *__restrict__ key_cache, uint4 *__restrict__ value_cache,
                      const int32_t *__restrict__ slot_mapping, int64_t num_tokens, int k16, int v16,
-                     int64_t num_slots, int32_t *oob_count) {
+                     int64_t num_slots, int32_t *oob_count, uint32_t *__restrict__ clear, int clear_words) {
   // a kernel launched behind this one with programmatic stream serialisation (the attention kernel
   // of a fused decode step) may start its set-up now; it waits for this grid before reading the cache
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // scheduling words of that attention kernel: zeroed here, on the way
+  for (int i = blockIdx.x * kRacThreads + threadIdx.x; i < clear_words; i += gridDim.x * kRacThreads) clear[i] = 0u;
   const int lane = threadIdx.x & 31;
   const int64_t nwarps = (int64_t)gridDim.x * kRacWarps;
   const int total = k16 + v16;  // K chunks then V chunks, one flat index space
@@ -198,23 +201,43 @@ rac_scatter_quant_kernel(const T *__restrict__ key, const T *__restrict__ value,
 }
 
 // Fast path of the quantising scatter for rows of up to 1024 channels (K and V alike).
-// Warps stride over the tokens, four tokens in flight at a time, and each warp owns a fixed
-// quarter of the row pair (K low / K high / V low / V high), so a lane's channels never change:
-// the reciprocals of the scales and the offsets are loaded once into registers.
-// rint(x / d) is taken from y = x * (1 / d) whenever y is provably on the same side of every
-// half-integer as the correctly rounded quotient: |y| < 4096 and y at least 0.002 away from
-// k + 0.5 (y and fl(x / d) differ by less than 2 ulp <= 0.001 there).  Otherwise -- ties, huge
-// quotients, zero or non-finite scales -- the IEEE division is done.  Saturation, NaN -> 0 and the
-// final rounding are one cvt.rni.sat.s8.f32.  Bit-identical to the division everywhere.
+// Warps stride over the tokens and each warp owns whole K rows or whole V rows, so a lane's channels
+// never change: the reciprocals of the scales and the offsets are loaded once into registers.
+//
+// rint(x / d) without a division, exactly: with r = fl(1 / d) and e = x * r (the exact product),
+//   z = fma(x, r, M), M = 1.5 * 2^23   rounds e to the nearest integer (ties to even) for |e| < 2^22,
+//   q = z - M                          is that integer, t = fma(x, r, -q) = e - q its distance to e.
+// e differs from x / d by less than |e| * 2^-24 * 1.01 < 0.0003 for |e| < 4097, and the correctly
+// rounded quotient from x / d by at most half an ulp <= 0.00025, so |t| <= 0.498 and |q| < 4096 put
+// fl(x / d) strictly within 0.5 of q: rint(fl(x / d)) = q.  Otherwise -- ties, huge quotients, zero,
+// denormal or non-finite scales, NaN -- the IEEE division is done.  The result is clamped to
+// [-128, 127] as a float (NaN -> 0 first) and M is added once more: the low byte of the sum's bit
+// pattern is the two's-complement int8.  No conversion instruction on the path; four results are
+// packed with three byte permutes.  Bit-identical to the division everywhere.
+template <bool HAS_OFF>
 __device__ __forceinline__ uint32_t quant_fast(float x, float r, float off, const float *dptr) {
-  const float y = x * r;
-  const float z = y + 12582912.f;        // 1.5 * 2^23: the add rounds y to the nearest integer (ties to even)
-  float q = z - 12582912.f;              // = rint(y) while |y| < 2^22
-  const float t = y - q;                 // in [-0.5, 0.5]
-  if (!((fabsf(y) < 4096.f) && (fabsf(t) <= 0.498f))) q = rintf(__fdiv_rn(x, __ldg(dptr)));
-  int32_t out;
-  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(out) : "f"(__fsub_rn(q, off)));  // q - off is integral (or inf / NaN)
-  return (uint32_t)out & 0xffu;
+  const float kMagic = 12582912.f;
+  const float z = fmaf(x, r, kMagic);
+  const float q = z - kMagic;
+  const float t = fmaf(x, r, -q);
+  float v;
+  if ((fabsf(q) < 4096.f) && (fabsf(t) <= 0.498f)) {
+    v = HAS_OFF ? q - off : q;  // integral, |v| <= 8192
+  } else {
+    v = rintf(__fdiv_rn(x, __ldg(dptr)));
+    if (HAS_OFF) v = __fsub_rn(v, off);
+    if (v != v) v = 0.f;
+  }
+  v = fminf(fmaxf(v, -128.f), 127.f);
+  return __float_as_uint(v + kMagic);  // low byte: the int8
+}
+// byte 0 of four words -> one word
+__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+  uint32_t t0, t1, o;
+  asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(t0) : "r"(w0), "r"(w1));
+  asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(t1) : "r"(w2), "r"(w3));
+  asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(o) : "r"(t0), "r"(t1));
+  return o;
 }
 
 // One warp quantises whole K rows or whole V rows (fixed per warp), striding over the tokens with
@@ -228,8 +251,10 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
                               const int32_t *__restrict__ slot_mapping, int64_t num_tokens, int elems,
                               const float *__restrict__ k_descale, const int32_t *__restrict__ k_offset,
                               const float *__restrict__ v_descale, const int32_t *__restrict__ v_offset,
-                              int64_t num_slots, int32_t *oob_count, bool has_v) {
+                              int64_t num_slots, int32_t *oob_count, bool has_v,
+                              uint32_t *__restrict__ clear, int clear_words) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see rac_scatter16_kernel
+  for (int i = blockIdx.x * kRacThreads + threadIdx.x; i < clear_words; i += gridDim.x * kRacThreads) clear[i] = 0u;
   const int lane = threadIdx.x & 31;
   const int64_t unit = (int64_t)blockIdx.x * kRacWarps + (threadIdx.x >> 5);
   const int64_t nunits = (int64_t)gridDim.x * kRacWarps;
@@ -292,12 +317,11 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
         const int e = lane * 8 + it * 256;
         if (e < elems) {
           const T *x = reinterpret_cast<const T *>(&cur[it]);
-          uint32_t lo = 0, hi = 0;
+          uint32_t w[8];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            lo |= quant_fast(to_f32<T>(x[i]), r[it][i], HAS_OFF ? o[it][i] : 0.f, ds + e + i) << (8 * i);
-            hi |= quant_fast(to_f32<T>(x[i + 4]), r[it][i + 4], HAS_OFF ? o[it][i + 4] : 0.f, ds + e + i + 4) << (8 * i);
-          }
+          for (int i = 0; i < 8; ++i)
+            w[i] = quant_fast<HAS_OFF>(to_f32<T>(x[i]), r[it][i], HAS_OFF ? o[it][i] : 0.f, ds + e + i);
+          const uint32_t lo = pack_low_bytes(w[0], w[1], w[2], w[3]), hi = pack_low_bytes(w[4], w[5], w[6], w[7]);
           asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(dst + it * 256), "r"(lo), "r"(hi) : "memory");
         }
       }
@@ -319,6 +343,16 @@ extern "C" int msco_reshape_and_cache(const void *key, const void *value, void *
                                       const int32_t *slot_mapping, int64_t num_tokens, int64_t k_row_bytes,
                                       int64_t v_row_bytes, int64_t num_slots, int32_t *oob_count,
                                       void *stream) {
+  bool cleared = false;
+  return launch_rac(key, value, key_cache, value_cache, slot_mapping, num_tokens, k_row_bytes, v_row_bytes, num_slots,
+                    oob_count, static_cast<cudaStream_t>(stream), nullptr, 0, &cleared);
+}
+
+int msco::launch_rac(const void *key, const void *value, void *key_cache, void *value_cache,
+                     const int32_t *slot_mapping, int64_t num_tokens, int64_t k_row_bytes, int64_t v_row_bytes,
+                     int64_t num_slots, int32_t *oob_count, cudaStream_t st, uint32_t *clear, int clear_words,
+                     bool *cleared) {
+  *cleared = false;
   if (num_tokens < 0 || k_row_bytes < 0 || v_row_bytes < 0 || num_slots < 0)
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache: negative size");
   // zero-sized inputs: the reference skips execution (reshape_and_cache.cc:90-119)
@@ -331,7 +365,6 @@ extern "C" int msco_reshape_and_cache(const void *key, const void *value, void *
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache: key, key_cache and slot_mapping must not be NULL");
   if (k_row_bytes > (int64_t)INT32_MAX || v_row_bytes > (int64_t)INT32_MAX)
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache: row too large");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t blocks64 = (num_tokens + kRacWarps - 1) / kRacWarps;
   if (blocks64 > 0x7fffffffLL) return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache: too many tokens");
   const dim3 grid((unsigned)blocks64), block(kRacThreads);
@@ -354,12 +387,13 @@ extern "C" int msco_reshape_and_cache(const void *key, const void *value, void *
     if (k16 + v16 > 128) {
       rac_scatter16_kernel<8, true><<<grid16, block, 0, st>>>(
           (const uint4 *)key, (const uint4 *)value, (uint4 *)key_cache, (uint4 *)value_cache, slot_mapping,
-          num_tokens, k16, v16, num_slots, oob_count);
+          num_tokens, k16, v16, num_slots, oob_count, clear, clear_words);
     } else {
       rac_scatter16_kernel<4, true><<<grid16, block, 0, st>>>(
           (const uint4 *)key, (const uint4 *)value, (uint4 *)key_cache, (uint4 *)value_cache, slot_mapping,
-          num_tokens, k16, v16, num_slots, oob_count);
+          num_tokens, k16, v16, num_slots, oob_count, clear, clear_words);
     }
+    *cleared = clear_words > 0;
   } else if (k_row_bytes % 2 == 0 && v_row_bytes % 2 == 0 && (((uintptr_t)key | (uintptr_t)key_cache |
              (uintptr_t)value | (uintptr_t)value_cache) & 1) == 0) {
     rac_scatter2_kernel<<<grid, block, 0, st>>>((const uint16_t *)key, (const uint16_t *)value,
@@ -382,6 +416,18 @@ extern "C" int msco_reshape_and_cache_quant(const void *key, const void *value, 
                                             int32_t in_dtype, const float *k_descale, const int32_t *k_offset,
                                             const float *v_descale, const int32_t *v_offset, int64_t num_slots,
                                             int32_t *oob_count, void *stream) {
+  bool cleared = false;
+  return launch_rac_quant(key, value, key_cache, value_cache, slot_mapping, num_tokens, k_row_elems, v_row_elems,
+                          in_dtype, k_descale, k_offset, v_descale, v_offset, num_slots, oob_count,
+                          static_cast<cudaStream_t>(stream), nullptr, 0, &cleared);
+}
+
+int msco::launch_rac_quant(const void *key, const void *value, int8_t *key_cache, int8_t *value_cache,
+                           const int32_t *slot_mapping, int64_t num_tokens, int64_t k_row_elems, int64_t v_row_elems,
+                           int32_t in_dtype, const float *k_descale, const int32_t *k_offset, const float *v_descale,
+                           const int32_t *v_offset, int64_t num_slots, int32_t *oob_count, cudaStream_t st,
+                           uint32_t *clear, int clear_words, bool *cleared) {
+  *cleared = false;
   if (num_tokens < 0 || k_row_elems < 0 || v_row_elems < 0 || num_slots < 0)
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: negative size");
   if (in_dtype != MSCO_DTYPE_F16 && in_dtype != MSCO_DTYPE_BF16)
@@ -395,7 +441,6 @@ extern "C" int msco_reshape_and_cache_quant(const void *key, const void *value, 
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: key, key_cache, slot_mapping, k_descale required");
   if (k_row_elems > (int64_t)INT32_MAX || v_row_elems > (int64_t)INT32_MAX)
     return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: row too large");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t blocks64 = (num_tokens * kQuantParts + kRacWarps - 1) / kRacWarps;
   if (blocks64 > 0x7fffffffLL) return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_quant: too many tokens");
   const dim3 grid((unsigned)blocks64), block(kRacThreads);
@@ -416,11 +461,12 @@ extern "C" int msco_reshape_and_cache_quant(const void *key, const void *value, 
 #define MSCO_QF(T, OFF)                                                                                     \
   rac_scatter_quant_fast_kernel<T, OFF><<<gridf, block, 0, st>>>(                                           \
       (const T *)key, (const T *)value, key_cache, value_cache, slot_mapping, num_tokens, (int)k_row_elems, \
-      k_descale, k_offset, v_descale, v_offset, num_slots, oob_count, has_v)
+      k_descale, k_offset, v_descale, v_offset, num_slots, oob_count, has_v, clear, clear_words)
     if (in_dtype == MSCO_DTYPE_F16) { if (has_off) MSCO_QF(__half, true); else MSCO_QF(__half, false); }
     else { if (has_off) MSCO_QF(__nv_bfloat16, true); else MSCO_QF(__nv_bfloat16, false); }
 #undef MSCO_QF
     MSCO_CUDA_CHECK(cudaGetLastError());
+    *cleared = clear_words > 0;
     return MSCO_OK;
   }
 #define MSCO_LAUNCH_Q(T, VEC)                                                                             \

@@ -166,6 +166,27 @@ extern "C" int ms_custom_ops_reshape_and_cache(const MsTensorDesc *key, const Ms
   });
 }
 
+// Placeholder output of the registered operator: key's shape and dtype
+// (CustomReshapeAndCacheOpFuncImpl, reshape_and_cache.cc:66-75 of the reference), after the checks.
+extern "C" int ms_custom_ops_reshape_and_cache_infer(const MsTensorDesc *key, const MsTensorDesc *value,
+                                                     const MsTensorDesc *key_cache, const MsTensorDesc *value_cache,
+                                                     const MsTensorDesc *slot_mapping, int64_t cache_mode,
+                                                     int64_t head_num, int32_t *out_dtype, int32_t *out_ndim,
+                                                     int64_t *out_shape) {
+  using namespace ms_custom_ops;
+  (void)head_num;
+  return GuardedCall(kOpName, [&] {
+    const Tensor k(key);
+    (void)CheckAndDescribe(k, GetTensorOrEmpty(value), GetTensorOrEmpty(key_cache), GetTensorOrEmpty(value_cache),
+                           GetTensorOrEmpty(slot_mapping), cache_mode, false);
+    if (out_dtype) *out_dtype = k.dtype();
+    if (out_ndim) *out_ndim = static_cast<int32_t>(k.rank());
+    if (out_shape)
+      for (size_t i = 0; i < k.rank(); ++i) out_shape[i] = k.dim(i);
+    return MSCO_OK;
+  });
+}
+
 extern "C" int ms_custom_ops_reshape_and_cache_quant(const MsTensorDesc *key, const MsTensorDesc *value,
                                                      const MsTensorDesc *key_cache, const MsTensorDesc *value_cache,
                                                      const MsTensorDesc *slot_mapping, const MsTensorDesc *k_descale,

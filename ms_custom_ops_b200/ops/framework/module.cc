@@ -58,3 +58,7 @@ extern "C" void ms_custom_ops_plan_cache_stats(int64_t *hits, int64_t *misses, i
   ms_custom_ops::PlanCache::Instance().Stats(hits, misses, entries);
 }
 extern "C" void ms_custom_ops_plan_cache_clear(void) { ms_custom_ops::PlanCache::Instance().Clear(); }
+extern "C" void ms_custom_ops_plan_cache_miss_stats(int64_t *recycled, int64_t *created) {
+  ms_custom_ops::PlanCache::Instance().MissStats(recycled, created);
+}
+extern "C" void ms_custom_ops_plan_arena_stats(int64_t *stats) { msco_plan_arena_stats(stats); }

@@ -31,17 +31,34 @@ uint64_t HashBytes(const void *data, size_t len, uint64_t seed) {
   return mix(h);
 }
 
-PlanKey MakePlanKey(const MscoPaDesc &desc, const std::vector<int32_t> &lens) {
-  // field by field: the struct has padding bytes that must not enter the key
-  const int64_t f[] = {desc.q_dtype, desc.kv_dtype, desc.num_q_heads, desc.num_kv_heads, desc.head_dim,
-                       desc.block_size, desc.num_blocks, desc.max_blocks_per_seq, desc.quant_type,
-                       desc.has_quant_offset, desc.mask_type, desc.mask_dtype, desc.mask_batch_stride,
-                       desc.mask_head_stride, desc.kernel, static_cast<int64_t>(lens.size())};
+namespace {
+// field by field: the struct has padding bytes that must not enter a key
+struct DescFields {
+  int64_t f[16];
   uint32_t scale_bits;
-  memcpy(&scale_bits, &desc.qk_scale, 4);
+};
+DescFields FieldsOf(const MscoPaDesc &desc) {
+  DescFields d = {{desc.q_dtype, desc.kv_dtype, desc.num_q_heads, desc.num_kv_heads, desc.head_dim,
+                   desc.block_size, desc.num_blocks, desc.max_blocks_per_seq, desc.quant_type,
+                   desc.has_quant_offset, desc.mask_type, desc.mask_dtype, desc.mask_batch_stride,
+                   desc.mask_head_stride, desc.kernel, desc.reserved},
+                  0};
+  memcpy(&d.scale_bits, &desc.qk_scale, 4);
+  return d;
+}
+}  // namespace
+
+uint64_t MakeDescHash(const MscoPaDesc &desc) {
+  const DescFields d = FieldsOf(desc);
+  return HashBytes(d.f, sizeof(d.f), 0x452821e638d01377ull ^ d.scale_bits);
+}
+
+PlanKey MakePlanKey(const MscoPaDesc &desc, const std::vector<int32_t> &lens) {
+  DescFields d = FieldsOf(desc);
+  d.f[15] = static_cast<int64_t>(lens.size());
   PlanKey k;
-  k.h1 = HashBytes(f, sizeof(f), 0x243f6a8885a308d3ull ^ scale_bits);
-  k.h2 = HashBytes(f, sizeof(f), 0x13198a2e03707344ull + scale_bits);
+  k.h1 = HashBytes(d.f, sizeof(d.f), 0x243f6a8885a308d3ull ^ d.scale_bits);
+  k.h2 = HashBytes(d.f, sizeof(d.f), 0x13198a2e03707344ull + d.scale_bits);
   k.h1 = HashBytes(lens.data(), lens.size() * sizeof(int32_t), k.h1);
   k.h2 = HashBytes(lens.data(), lens.size() * sizeof(int32_t), k.h2);
   return k;
@@ -88,33 +105,74 @@ PlanRef PlanCache::GetOrCreate(const MscoPaDesc &desc, const std::vector<int32_t
     }
     ++misses_;
   }
-  // plan outside the lock: pure host work, may take tens of microseconds
-  MscoPaPlan *plan = nullptr;
-  const int rc = msco_paged_attention_plan(&desc, lens.data(), static_cast<int32_t>(lens.size()), &plan);
-  if (rc != MSCO_OK) {
+  auto throw_plan_error = [](int rc) {
     ErrorBuilder b(rc == MSCO_ERR_UNSUPPORTED ? MS_ERR_KIND_UNSUPPORTED
                    : rc == MSCO_ERR_INVALID_ARG ? MS_ERR_KIND_VALUE : MS_ERR_KIND_RUNTIME, rc);
     b << "For PagedAttention, planning failed: " << msco_last_error();
     b.Throw();
+  };
+  const uint64_t desc_hash = MakeDescHash(desc);
+  // Recycle: take the least recently used unreferenced plan of the same descriptor out of the cache
+  // and re-plan it in place for the new lengths (no allocation in the steady state).
+  std::unique_ptr<Entry> reuse;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    auto cnt = per_desc_.find(desc_hash);
+    if (cnt != per_desc_.end() && static_cast<size_t>(cnt->second) >= per_desc_keep_) {
+      for (auto it = lru_.end(); it != lru_.begin();) {
+        --it;
+        Entry *e = *it;
+        if (e->refs == 0 && e->desc_hash == desc_hash) {
+          auto mit = map_.find(e->key);
+          reuse = std::move(mit->second);
+          map_.erase(mit);
+          lru_.erase(it);
+          --cnt->second;
+          break;
+        }
+      }
+    }
+  }
+  // plan outside the lock: pure host work
+  MscoPaPlan *plan = nullptr;
+  if (reuse) {
+    plan = reuse->plan;
+    const int rc = msco_paged_attention_replan(plan, lens.data(), static_cast<int32_t>(lens.size()));
+    if (rc != MSCO_OK) {
+      msco_paged_attention_plan_destroy(plan);  // its contents are undefined now
+      throw_plan_error(rc);
+    }
+  } else {
+    const int rc = msco_paged_attention_plan(&desc, lens.data(), static_cast<int32_t>(lens.size()), &plan);
+    if (rc != MSCO_OK) throw_plan_error(rc);
   }
   std::lock_guard<std::mutex> g(mu_);
   auto it = map_.find(key);
   if (it != map_.end()) {  // another thread planned the same key meanwhile
-    msco_paged_attention_plan_destroy(plan);
+    RetireLocked(plan);
     Entry *e = it->second.get();
     ++e->refs;
     return PlanRef(this, e, e->plan);
   }
-  auto e = std::make_unique<Entry>();
+  if (reuse) ++recycled_; else ++created_;
+  std::unique_ptr<Entry> e = reuse ? std::move(reuse) : std::make_unique<Entry>();
   e->key = key;
+  e->desc_hash = desc_hash;
   e->plan = plan;
   e->refs = 1;
   lru_.push_front(e.get());
   e->lru_it = lru_.begin();
   Entry *raw = e.get();
   map_.emplace(key, std::move(e));
+  ++per_desc_[desc_hash];
   EvictLocked();
   return PlanRef(this, raw, plan);
+}
+
+void PlanCache::MissStats(int64_t *recycled, int64_t *created) {
+  std::lock_guard<std::mutex> g(mu_);
+  if (recycled) *recycled = recycled_;
+  if (created) *created = created_;
 }
 
 void PlanCache::Release(void *entry) {
@@ -141,6 +199,7 @@ void PlanCache::EvictLocked() {
     if (e->refs == 0) {
       RetireLocked(e->plan);
       const PlanKey key = e->key;
+      --per_desc_[e->desc_hash];
       it = lru_.erase(it);
       map_.erase(key);
     }
@@ -161,13 +220,14 @@ void PlanCache::Clear() {
     if (e->refs == 0) {
       RetireLocked(e->plan);
       const PlanKey key = e->key;
+      --per_desc_[e->desc_hash];
       it = lru_.erase(it);
       map_.erase(key);
     } else {
       ++it;
     }
   }
-  hits_ = misses_ = 0;
+  hits_ = misses_ = recycled_ = created_ = 0;
 }
 
 }  // namespace ms_custom_ops

@@ -6,8 +6,16 @@
 // function of the operator attributes, the tensor shapes / dtypes and the host
 // values of context_lens, so it is computed once per distinct key and reused.
 // Entries are reference counted; only unreferenced entries are evicted, least
-// recently used first; destruction of evicted plans is deferred so that a
-// launch still reading a plan's pinned host buffer is never cut off.
+// recently used first.
+//
+// In a decode loop every length grows every step, so every step is a miss.  A
+// miss therefore does not build a new plan when it can avoid it: once a few
+// plans of the same descriptor exist, the least recently used unreferenced one
+// is re-planned in place (msco_paged_attention_replan) and re-keyed.  Its plan
+// words stay in the same block of the kernel library's pinned arena, its tensor
+// maps stay valid, and the step path touches no allocator -- the role of the
+// reference's TilingMemMgr (ops/framework/ms_kernels_internal/tiling_mem_mgr.cc:82-137,
+// 224-238), which serves tiling buffers from memory set aside at start-up.
 #ifndef MS_CUSTOM_OPS_B200_FRAMEWORK_PLAN_CACHE_H_
 #define MS_CUSTOM_OPS_B200_FRAMEWORK_PLAN_CACHE_H_
 
@@ -35,6 +43,8 @@ struct PlanKeyHash {
 };
 
 PlanKey MakePlanKey(const MscoPaDesc &desc, const std::vector<int32_t> &context_lens);
+// Hash of the descriptor alone (what a re-plan must leave unchanged).
+uint64_t MakeDescHash(const MscoPaDesc &desc);
 
 class PlanCache;
 
@@ -63,6 +73,9 @@ class PlanCache {
   // Returns the cached plan for (desc, lens), building it on a miss.  Throws OpError on failure.
   PlanRef GetOrCreate(const MscoPaDesc &desc, const std::vector<int32_t> &context_lens);
   void Stats(int64_t *hits, int64_t *misses, int64_t *entries);
+  // misses served by re-planning an existing plan in place / by building a new plan
+  void MissStats(int64_t *recycled, int64_t *created);
+  void set_per_desc_keep(size_t n) { per_desc_keep_ = n; }
   void Clear();
   void set_capacity(size_t n) { capacity_ = n; }
 
@@ -70,6 +83,7 @@ class PlanCache {
   friend class PlanRef;
   struct Entry {
     PlanKey key;
+    uint64_t desc_hash = 0;
     MscoPaPlan *plan = nullptr;
     int refs = 0;
     std::list<Entry *>::iterator lru_it;
@@ -84,8 +98,10 @@ class PlanCache {
   std::unordered_map<PlanKey, std::unique_ptr<Entry>, PlanKeyHash> map_;
   std::list<Entry *> lru_;            // front = most recently used
   std::deque<MscoPaPlan *> retired_;  // evicted plans awaiting destruction
+  std::unordered_map<uint64_t, int> per_desc_;  // entries per descriptor hash
   size_t capacity_ = 256;
-  int64_t hits_ = 0, misses_ = 0;
+  size_t per_desc_keep_ = 4;  // plans of one descriptor kept before misses start recycling them
+  int64_t hits_ = 0, misses_ = 0, recycled_ = 0, created_ = 0;
 };
 
 }  // namespace ms_custom_ops

@@ -246,14 +246,14 @@ def test_reshape_and_cache_validation_without_a_gpu():
     assert call(T((0, 512), "float16"), None, cache, None, T((0,), "int32")) == 0
 
 
-def _plan(lens, hq=32, hkv=8, d=128, bs=128, kv="bfloat16", kernel=0, mask=0):
+def _plan(lens, hq=32, hkv=8, d=128, bs=128, kv="bfloat16", kernel=0, mask=0, max_blocks=None):
     desc = _abi.MscoPaDesc()
     desc.q_dtype = _abi.DTYPE_BF16
     desc.kv_dtype = {"bfloat16": _abi.DTYPE_BF16, "int8": _abi.DTYPE_I8}[kv]
     desc.quant_type = 1 if kv == "int8" else 0
     desc.num_q_heads, desc.num_kv_heads, desc.head_dim, desc.block_size = hq, hkv, d, bs
     desc.num_blocks = 1 << 20
-    desc.max_blocks_per_seq = (max(lens + [1]) + bs - 1) // bs
+    desc.max_blocks_per_seq = max_blocks or (max(list(lens) + [1]) + bs - 1) // bs
     desc.qk_scale = 0.1
     desc.kernel = kernel
     desc.mask_type = mask
@@ -310,3 +310,83 @@ def test_plan_cache_hits_on_repeated_lengths():
     assert st["misses"] == 2 and st["hits"] == 2 and st["entries"] == 2
     ops.plan_cache_clear()
     assert ops.plan_cache_stats()["entries"] == 0
+
+
+def test_plan_cache_entries_follow_the_misses_until_recycling_starts():
+    ops.plan_cache_clear()
+    for i in range(3):
+        ops.paged_attention_workspace_size(Q, KC, KC, BT, [100 + i, 200, 1024, 5], **OKW)
+    st = ops.plan_cache_stats()
+    assert st["misses"] == 3 and st["created"] == 3 and st["recycled"] == 0
+    ops.plan_cache_clear()
+
+
+def test_decode_loop_replans_in_place_without_pinned_allocations():
+    """Every decode step grows every length, so every step is a plan-cache miss.  After the first few
+    plans of a descriptor exist, a miss re-plans one of them in place: no plan is created, no block of
+    the pinned arena is requested, no slab is added (the role of the reference's TilingMemMgr,
+    ops/framework/ms_kernels_internal/tiling_mem_mgr.cc:82-137)."""
+    ops.plan_cache_clear()
+    q, kc, bt = T((64, 32, 128), "bfloat16"), T((4096, 128, 8, 128), "bfloat16"), T((64, 80), "int32")
+    rng = np.random.default_rng(0)
+    lens = rng.integers(2048, 8192, 64).astype(np.int32)
+    kw = dict(q_head_num=32, kv_head_num=8, qk_scale=0.088)
+    for _ in range(8):   # warm-up: the first plans of this descriptor are built
+        lens += 1
+        ops.paged_attention_workspace_size(q, kc, kc, bt, lens, **kw)
+    c0, a0 = ops.plan_cache_stats(), ops.plan_arena_stats()
+    sizes = []
+    for _ in range(200):
+        lens += 1
+        sizes.append(ops.paged_attention_workspace_size(q, kc, kc, bt, lens, **kw))
+    c1, a1 = ops.plan_cache_stats(), ops.plan_arena_stats()
+    assert c1["misses"] - c0["misses"] == 200 and c1["hits"] == c0["hits"]
+    assert c1["recycled"] - c0["recycled"] == 200 and c1["created"] == c0["created"]
+    assert a1["slabs"] == a0["slabs"] and a1["block_allocs"] == a0["block_allocs"]
+    assert a1["blocks_in_use"] == a0["blocks_in_use"] and c1["entries"] == c0["entries"]
+    assert sizes[-1] >= sizes[0]
+    ops.plan_cache_clear()
+
+
+def test_replan_equals_a_fresh_plan():
+    rng = np.random.default_rng(1)
+    base = rng.integers(1, 9000, 37).astype(np.int32)
+    plan = _plan([int(x) for x in base], hq=32, hkv=8, max_blocks=(20000 + 127) // 128)
+    for _ in range(5):
+        lens = rng.integers(0, 20000, int(rng.integers(1, 300))).astype(np.int32)
+        plan.replan(lens)
+        fresh = _plan([int(x) for x in lens], hq=32, hkv=8, max_blocks=(20000 + 127) // 128)
+        a, b = plan.info(), fresh.info()
+        for f in ("kernel", "grid", "work_items", "partials", "max_splits", "rows_per_item", "kv_tokens"):
+            assert getattr(a, f) == getattr(b, f), f
+        assert plan.workspace_bytes == fresh.workspace_bytes
+    with pytest.raises(_abi.MscoError, match="exceeds the block table"):
+        plan.replan([10 ** 7])
+
+
+def test_plan_arena_recycles_blocks():
+    a0 = _abi.plan_arena_stats()
+    plans = [_plan([100 + i] * 16) for i in range(50)]
+    a1 = _abi.plan_arena_stats()
+    assert a1["blocks_in_use"] - a0["blocks_in_use"] == 50
+    for p in plans:
+        p.close()
+    again = [_plan([100 + i] * 16) for i in range(50)]
+    a2 = _abi.plan_arena_stats()
+    assert a2["slabs"] == a1["slabs"] and a2["blocks_in_use"] == a1["blocks_in_use"]
+    for p in again:
+        p.close()
+    assert _abi.plan_arena_stats()["blocks_in_use"] == a0["blocks_in_use"]
+
+
+def test_reshape_and_cache_infer_returns_the_placeholder_of_the_reference():
+    # CustomReshapeAndCacheOpFuncImpl: the (never written) output has key's shape and dtype
+    k2, c = T((4, 1024), "float16"), T((8, 128, 8, 128), "float16")
+    assert ops.reshape_and_cache_infer(k2, k2, c, c, T((4,), "int32")) == ((4, 1024), "float16")
+    k3 = T((2, 3, 1024), "bfloat16")
+    cb = T((8, 128, 8, 128), "bfloat16")
+    assert ops.reshape_and_cache_infer(k3, None, cb, None, T((6,), "int32")) == ((2, 3, 1024), "bfloat16")
+    with pytest.raises(ops.UnsupportedOnB200):
+        ops.reshape_and_cache_infer(k2, k2, c, c, T((4,), "int32"), cache_mode=1)
+    with pytest.raises(ValueError):
+        ops.reshape_and_cache_infer(k2, k2, c, c, T((5,), "int32"))
