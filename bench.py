@@ -4,14 +4,18 @@
 
 One step = one decode step over one batch of synthetic sequences: the newest
 token's K/V rows are scattered into the paged cache (reshape_and_cache), then
-paged attention runs over every sequence's context.  The metric is decode
-tokens per second (= sequences per step / step time), whole job.
+paged attention runs over every sequence's context.  Steps follow one another
+as in a serving loop: every step every sequence is one token longer.  The
+metric is decode tokens per second (= sequences per step / step time), whole job.
 
 Printed JSON line (rank 0):
   value      device-timed throughput with every input resident in HBM
   e2e        the same step through the operator API with the step's inputs in pinned host memory:
              host->device copies of query / new rows / slots / block tables and the device->host
-             read of the attention output are inside the timed region
+             read of the attention output are inside the timed region; `value` is the serial loop
+             (the host waits for every step's result), the pipelined figure is printed beside it
+  configs    the other benchmark configurations (c3 int8 KV, c4 long skewed, c5 mixed decode, and
+             the prefill-heavy scatter of c5): throughput, attention-kernel time, roofline, parity
   roofline   the attention kernel alone: algorithmic bytes / its CUDA-event duration, against the
              measured HBM copy bandwidth (MEASURED_PEAKS.json, else the stated fallback)
   cpu_baseline  the CPU restatement of the reference golden (oracle/, all host cores), timed on
@@ -190,52 +194,161 @@ def run_reference(args):
 # ----------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------
-def run_gpu(args):
+def cpu_numpy_config1():
+    """The numpy restatement of the reference golden (per-sequence gather + BLAS, one core for the
+    gather loop) on configuration 1 exactly: the second CPU figure beside the C / OpenMP one."""
+    from oracle import paged_kv_numpy as onp
+    spec = workloads.config_spec(1)
+    c = workloads.decode_case(spec)
+    best = float("inf")
+    for _ in range(3):
+        t0 = time.perf_counter()
+        gk, gv = onp.reshape_and_cache_golden(c["key"], c["value"], c["key_cache"], c["value_cache"], c["slot_mapping"])
+        onp.paged_attention_golden(c["query"], gk, gv, c["block_tables"], c["context_lens"], c["qk_scale"])
+        best = min(best, time.perf_counter() - t0)
+    return {"value": spec.batch / best, "unit": UNIT, "cores": 1, "kind": "port",
+            "sample": f"configuration 1 exactly ({spec.batch} sequences, {int(c['context_lens'].sum())} context tokens), "
+                      "best of 3; numpy restatement of the reference numpy golden"}
+
+
+class DecodeLoop:
+    """One workload on this rank's GPU, stepped the way a serving loop steps it: every step appends one
+    token to every sequence (context_lens grow by one, slot_mapping moves to the new position, a fresh
+    cache block is used when a sequence crosses a block boundary), so every step needs a new launch
+    plan -- the plan object is re-planned in place (msco_paged_attention_replan) -- and the step is one
+    msco_decode_step call: cache scatter + attention, two kernel launches."""
+
+    def __init__(self, ctx, spec, total_steps):
+        import torch
+        from ms_custom_ops_b200 import _abi, kernels, sharding
+        self.torch, self.kernels, self.ctx, self.spec = torch, kernels, ctx, spec
+        world, rank, dev = ctx["world"], ctx["rank"], ctx["dev"]
+        if spec.kv_heads % world != 0:
+            raise SystemExit(f"{spec.kv_heads} kv heads cannot be split over {world} GPUs")
+        self.hpr = spec.kv_heads // world
+        self.h0, self.h1 = sharding.kv_head_range(rank, world, spec.kv_heads)
+        self.hq_local = self.hpr * (spec.num_heads // spec.kv_heads)
+        self.total_steps = total_steps
+        case = self.case = workloads.decode_case_device(spec, dev, (self.h0, self.h1), growth_steps=total_steps + 2)
+        self.lens0 = np.asarray(case["context_lens"], dtype=np.int32)
+        self.tables_host = case["block_tables_host"]
+        # slot_mapping of every step, resident on the device and in host memory
+        bs = spec.block_size
+        last = self.lens0.astype(np.int64)[None, :] + np.arange(total_steps + 2, dtype=np.int64)[:, None] - 1
+        rows = np.arange(spec.batch)[None, :]
+        slots = np.where(last >= 0, self.tables_host[rows, np.maximum(last, 0) // bs].astype(np.int64) * bs
+                         + np.maximum(last, 0) % bs, -1).astype(np.int32)
+        # sequences that start empty stay out of the scatter until they have a token
+        self.slots_host = torch.from_numpy(slots)
+        self.slots_dev = self.slots_host.to(dev)
+        self.cur_lens = self.lens0.copy()          # lengths of the step being issued (updated in place)
+        self.h_lens = torch.from_numpy(self.cur_lens)  # the same memory as a CPU tensor (operator API)
+        self.i = 0                                 # index of the next step
+        self.quant = 1 if spec.kv_int8 else 0
+        q, kc, bt = case["query"], case["key_cache"], case["block_tables"]
+        self.desc = kernels.make_pa_desc(q, kc, bt, case["qk_scale"], self.quant)
+        self.plan = _abi.PaPlan(self.desc, [int(x) for x in self.lens0 + total_steps + 1])
+        ws_bytes = self.plan.workspace_bytes       # partial count grows with the lengths: the last step's is the largest
+        self.plan.replan(self.lens0)
+        self.info0 = self.plan.info()
+        self.ws = torch.empty(max(ws_bytes, self.plan.workspace_bytes, 256), dtype=torch.uint8, device=dev)
+        self.out_local = torch.empty_like(q)
+
+    def lens_at(self, i):
+        return self.lens0 + np.int32(i)
+
+    def step(self):
+        """One device-resident decode step (everything it reads is in HBM already)."""
+        c, i = self.case, self.i
+        np.add(self.lens0, np.int32(i), out=self.cur_lens)
+        self.plan.replan(self.cur_lens)
+        self.kernels.decode_step(self.plan, c["key"], c["value"], c["key_cache"], c["value_cache"], self.slots_dev[i],
+                                 c["query"], c["block_tables"], self.out_local, self.ws, c["k_descale"], None,
+                                 c["v_descale"], None)
+        self.i = i + 1
+
+    def algorithmic_bytes(self, first_step, nsteps):
+        """Mean algorithmic bytes per launch over steps [first_step, first_step + nsteps)."""
+        spec = self.spec
+        kvb = 1 if spec.kv_int8 else 2
+        lens_mid = self.lens0.astype(np.float64) + first_step + (nsteps - 1) / 2.0
+        fixed = workloads.algorithmic_bytes_attention(np.zeros(spec.batch), self.hq_local, self.hpr, spec.head_size,
+                                                      kvb, quant=spec.kv_int8)
+        return float(lens_mid.sum()) * 2 * self.hpr * spec.head_size * kvb + fixed
+
+    def cpu_check(self, args, out_gpu, step_index):
+        """CPU baseline (C / OpenMP restatement of the reference golden, all host cores) on the state of
+        step `step_index`, and the comparison of the GPU output of that step with it."""
+        from oracle import c_oracle
+        c, spec = self.case, self.spec
+        nseq = min(spec.batch, args.cpu_sample)
+        lens = self.lens_at(step_index)[:nseq]
+        kd, vd = c["k_descale"], c["v_descale"]
+        # the step's rows are in the cache already; the scatter is idempotent, so the CPU step that
+        # scatters them again reproduces the state the GPU step read
+        host = {"query": _to_np(c["query"][:nseq]), "key": _to_np(c["key"][:nseq]), "value": _to_np(c["value"][:nseq]),
+                "key_cache": _to_np(c["key_cache"]), "value_cache": _to_np(c["value_cache"]),
+                "block_tables": self.tables_host[:nseq], "slot_mapping": self.slots_host[step_index][:nseq].numpy(),
+                "context_lens": lens, "qk_scale": c["qk_scale"],
+                "k_descale": None if kd is None else kd.cpu().numpy(),
+                "v_descale": None if vd is None else vd.cpu().numpy()}
+        cores = host_threads()
+        ref = cpu_step(c_oracle, host, cores)  # warm-up + reference output
+        reps, t_best = 0, float("inf")
+        t_begin = time.perf_counter()
+        while reps < 3 and time.perf_counter() - t_begin < args.cpu_seconds:
+            t0 = time.perf_counter()
+            cpu_step(c_oracle, host, cores)
+            t_best = min(t_best, time.perf_counter() - t0)
+            reps += 1
+        if reps == 0:
+            t0 = time.perf_counter()
+            cpu_step(c_oracle, host, cores)
+            t_best, reps = time.perf_counter() - t0, 1
+        sample = (f"{nseq} of {spec.batch} sequences ({int(lens.sum())} context tokens), kv heads {self.h0}..{self.h1 - 1}, "
+                  f"best of {reps}; C restatement of the reference numpy golden, OpenMP")
+        cpu = {"value": nseq / t_best, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        got = out_gpu[:nseq].float().cpu().numpy()
+        err = np.abs(got - ref)
+        tol = 2e-2 if spec.kv_int8 else (1e-2 if spec.dtype == "bfloat16" else 5e-3)
+        checked = {"sequences": nseq, "max_abs_err": float(err.max()), "max_abs_golden": float(np.abs(ref).max()),
+                   "rel_l2": float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30)),
+                   "within_tolerance": bool(np.all(err <= tol + tol * np.abs(ref))), "tolerance": tol}
+        return cpu, checked
+
+    def release(self):
+        self.plan.close()
+        self.case = self.ws = self.out_local = self.slots_dev = None
+        self.torch.cuda.empty_cache()
+
+
+def measure_decode(ctx, spec, args, full):
+    """Times one workload.  Device-resident loop: `repeats` loops of exactly `steps` steps each, CUDA
+    events, max over ranks, the median loop is reported.  Then the attention kernel alone (event pairs
+    around it), and -- for the headline workload (`full`) -- the end-to-end loops through the operator
+    API with the step's inputs in pinned host memory.  Ends with the CPU leg / parity check."""
     import torch
     import torch.distributed as dist
 
     import ms_custom_ops_b200 as ops
-    from ms_custom_ops_b200 import _abi, kernels, sharding
+    from ms_custom_ops_b200 import sharding
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus and world > 1:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-
-    spec = workload_spec(args.workload)
-    if spec.kv_heads % world != 0:
-        raise SystemExit(f"{spec.kv_heads} kv heads cannot be split over {world} GPUs")
-    hpr = spec.kv_heads // world                      # kv heads per rank
-    h0, h1 = sharding.kv_head_range(rank, world, spec.kv_heads)
-    g = spec.num_heads // spec.kv_heads
-    case = workloads.decode_case_device(spec, dev, (h0, h1))
-    lens = [int(x) for x in case["context_lens"]]
-    quant = 1 if spec.kv_int8 else 0
+    world, rank, dev = ctx["world"], ctx["rank"], ctx["dev"]
+    K, W, R = args.steps, max(args.warmup, 3), max(args.repeats, 1)
+    nprof = min(K, 64)
+    total_steps = W + R * K + nprof + (2 * (3 + K) + 8 if full else 0) + 8
+    loop = DecodeLoop(ctx, spec, total_steps)
+    case = loop.case
     q, key, val = case["query"], case["key"], case["value"]
-    kc, vc, bt, slot = case["key_cache"], case["value_cache"], case["block_tables"], case["slot_mapping"]
+    kc, vc, bt = case["key_cache"], case["value_cache"], case["block_tables"]
     kd, vd = case["k_descale"], case["v_descale"]
-    hq_local = hpr * g
-
-    desc = kernels.make_pa_desc(q, kc, bt, case["qk_scale"], quant)
-    plan = _abi.PaPlan(desc, lens)
-    info = plan.info()
-    ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device=dev)
-    out_local = torch.empty_like(q)
-    # gathered layout: [rank, batch, q heads per rank, head_dim]; rank r's slice holds q heads
-    # r*hq_local .. (r+1)*hq_local-1, i.e. out[b, h] = gathered[h // hq_local, b, h % hq_local]
     gathered = torch.empty((world,) + tuple(q.shape), dtype=q.dtype, device=dev) if world > 1 else None
     # the exchange: this library's peer-store all-gather kernel (default) or NCCL (--nccl-gather)
     peer = None
     if world > 1 and not args.nccl_gather:
         try:
             peer = sharding.PeerGather(q.shape, q.dtype, dev)
-        except Exception as e:  # IPC mapping refused on this box: say so and use NCCL
+        except Exception as e:  # mapping a peer's memory may be refused: say so and fall back to NCCL
             print(f"peer all-gather unavailable ({e}); using NCCL", file=sys.stderr)
         ok = torch.tensor([1 if peer is not None else 0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
@@ -248,69 +361,140 @@ def run_gpu(args):
         return sharding.all_gather_outputs(o, gathered)
 
     def step():
-        # one fused call: cache scatter, then attention launched behind it with programmatic
-        # stream serialisation (msco_decode_step)
-        kernels.decode_step(plan, key, val, kc, vc, slot, q, bt, out_local, ws, kd, None, vd, None)
+        loop.step()
         if world > 1:
-            exchange(out_local)
+            exchange(loop.out_local)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(ms):
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     # ---- device-resident timed region ------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(W):
         step()
-    kernels.pa_status(plan, ws)
-    graph = None
-    if args.graph and world > 1:
-        # capturing the NCCL all-gather hung both ranks on this pool; graphs are a 1-GPU option
-        print("--graph is ignored with more than one GPU", file=sys.stderr)
-    if args.graph and world == 1:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            step()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
-                step()
-        torch.cuda.current_stream().wait_stream(side)
-        for _ in range(2):
-            graph.replay()
-    # clocks are sampled from the start of the device-timed region to the end of the end-to-end
-    # region (the GPU is busy throughout)
-    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)).start() if rank == 0 else None
-    barrier()
+    loop.kernels.pa_status(loop.plan, loop.ws)
+    # clocks are sampled from the start of the device-timed region to the end of the end-to-end region
+    sampler = None
+    if rank == 0 and full:
+        sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)).start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        if graph is not None:
-            graph.replay()
-        else:
+    loops_ms = []
+    first_timed = loop.i
+    for _ in range(R):
+        barrier()
+        e0.record()
+        for _ in range(K):
             step()
-    e1.record()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
+        e1.record()
+        barrier()
+        loops_ms.append(max_over_ranks(e0.elapsed_time(e1)) / K)
+    ms_step = statistics.median(loops_ms)
     # duration of the attention kernel alone: the same steps once more with the library's event pairs
     # recorded directly around that kernel (the pairs would sit between the kernels of the timed
     # region and break their programmatic overlap, so they are taken in a pass of their own)
-    plan.profile_enable(True)
-    for _ in range(min(args.steps, 64)):
+    loop.plan.profile_enable(True)
+    first_prof = loop.i
+    for _ in range(nprof):
         step()
     torch.cuda.synchronize()
-    kernel_ms = plan.profile_read()
-    plan.profile_enable(False)
-    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
+    kernel_ms = loop.plan.profile_read()
+    loop.plan.profile_enable(False)
+    info = loop.plan.info()
 
-    # ---- end-to-end through the operator API, inputs in pinned host memory ----------------
-    # the step's inputs live in ONE pinned host staging buffer (query | new K rows | new V rows |
-    # slot_mapping | block_tables, each 256-byte aligned) and travel in one host->device copy; the
-    # operators read device views of the staging area
-    parts = [q, key, val, slot, bt]
+    spec_b = spec.batch
+    result = {"value": spec_b / ms_step * 1e3, "ms_per_step": ms_step, "loops_ms_per_step": loops_ms,
+              "first_timed_step": first_timed}
+    e2e = None
+    if full:
+        e2e = measure_e2e(ctx, loop, args, exchange, barrier, max_over_ranks)
+    clocks = sampler.stop() if sampler else None
+    ops.paged_attention_check_status(dev)
+    gather_check = None
+    if peer is not None:
+        peer.check()
+        # the peer-store gather must equal NCCL's all-gather of the same slices, bit for bit
+        mine = exchange(loop.out_local)
+        torch.cuda.synchronize()
+        sharding.all_gather_outputs(loop.out_local, gathered)
+        gather_check = bool(torch.equal(mine.view(torch.int16), gathered.view(torch.int16)))
+
+    # ---- roofline of the attention kernel (rank 0's shard) ----------------------------------
+    alg_bytes = loop.algorithmic_bytes(first_prof, nprof)
+    peak, peak_src = measured_hbm_peak()
+    roofline = {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None,
+                "kernel": "pa_tma_kernel" if info.kernel == 2 else "pa_generic_kernel",
+                "peak_source": peak_src, "algorithmic_bytes": alg_bytes}
+    if kernel_ms:
+        kms = statistics.mean(kernel_ms)
+        roofline.update(achieved=alg_bytes / kms / 1e6, frac=alg_bytes / kms / 1e6 / peak, kernel_ms=kms,
+                        frac_of_8tbs=alg_bytes / kms / 1e6 / 8000.0, launches_timed=len(kernel_ms))
+    # DRAM traffic of one launch: dram__bytes_read.sum + dram__bytes_write.sum of the ncu captures
+    # summarised in profiles/pa_tma_kernel_*.md, per context token per kv head, scaled to this
+    # launch (traffic grows in proportion to the tokens read; measured on one GPU holding all heads)
+    if info.kernel == 2:
+        per = NCU_DRAM_BYTES_PER_TOKEN_HEAD["int8" if spec.kv_int8 else "16bit"]
+        roofline["traffic"] = per * float(loop.lens_at(first_prof + nprof // 2).sum()) * loop.hpr
+        roofline["traffic_source"] = ("ncu capture of config " + ("3" if spec.kv_int8 else "2") +
+                                      " on one GPU, scaled by tokens x kv heads of this rank")
+
+    # ---- CPU baseline on the same workload (also the full-size parity check) ---------------
+    cpu = checked = None
+    if rank == 0 and not args.no_cpu:
+        last = loop.i
+        loop.step()                 # one more step whose output is compared (its index: `last`)
+        torch.cuda.synchronize()
+        cpu, checked = loop.cpu_check(args, loop.out_local, last)
+
+    launches_per_step = 2 + (1 if min(loop.lens0) == 0 else 0) + (1 if peer is not None else 0)
+    result.update({
+        "roofline": roofline, "cpu_baseline": cpu, "parity_check": checked, "gather_check": gather_check,
+        "clocks": clocks, "e2e": e2e, "kernels_per_step": launches_per_step,
+        "achieved_gbs_step": alg_bytes / ms_step / 1e6, "alg_bytes": alg_bytes,
+        "config": workload_config(spec, loop.lens_at(first_timed), {
+            "parallelism": f"kv-head sharding x{world}" + (
+                "" if world == 1 else (" + peer-store all-gather of outputs over NVLink" if peer is not None
+                                       else " + NCCL all-gather of outputs")),
+            "l2": f"inputs larger than L2: {alg_bytes / 1e6:.0f} MB of KV per GPU per step vs {L2_BYTES >> 20} MB",
+            "launch": "real decode loop: every step appends one token per sequence (context_lens + 1, slot_mapping "
+                      "moves, block tables hold the blocks reserved for the growth), the plan is re-planned in place "
+                      "every step, eager launches on one stream (cache scatter + attention, split partials merged "
+                      "inside the attention kernel)",
+            "timing": f"median of {R} loops of {K} steps each",
+            "work_items": info.work_items, "split_partials": info.partials, "grid": info.grid}),
+    })
+    if peer is not None:
+        peer.release()
+    loop.release()
+    return result
+
+
+def measure_e2e(ctx, loop, args, exchange, barrier, max_over_ranks):
+    """End to end through the operator API (`reshape_and_cache` + `paged_attention`, the calls a user of
+    the reference makes), inputs in pinned host memory: every step uploads query / new rows / slots /
+    block tables in ONE packed host->device copy and downloads the output into pinned memory.
+    Every step is a plan-cache miss (the lengths grew), served by re-planning in place.
+    serial    upload -> operators -> download -> the host waits for the result: what one batch of
+              autoregressive decode can do, since step i + 1 needs step i's result
+    pipelined two independent batches in flight: the upload of step i + 1 and the download of step
+              i - 1 run on copy streams while step i computes"""
+    import torch
+
+    import ms_custom_ops_b200 as ops
+
+    world, dev = ctx["world"], ctx["dev"]
+    spec, case, K = loop.spec, loop.case, args.steps
+    q, key, val = case["query"], case["key"], case["value"]
+    kc, vc, bt = case["key_cache"], case["value_cache"], case["block_tables"]
+    kd, vd = case["k_descale"], case["v_descale"]
+    slot0 = loop.slots_dev[0]
+    parts = [q, key, val, slot0, bt]
     offs, total = [], 0
     for x in parts:
         offs.append(total)
@@ -324,13 +508,19 @@ def run_gpu(args):
     for hs in h_stage:
         for x, off in zip(parts, offs):
             view(hs, x, off).copy_(x.cpu())
+    h_slot = [view(hs, slot0, offs[3]) for hs in h_stage]
     d_views = [tuple(view(ds, x, off) for x, off in zip(parts, offs)) for ds in d_stage]
-    h_lens = torch.tensor(lens, dtype=torch.int32)
     out_shape = (world,) + tuple(q.shape) if world > 1 else tuple(q.shape)
     h_out = [torch.empty(out_shape, dtype=q.dtype).pin_memory() for _ in range(2)]
-    pa_kw = dict(q_head_num=hq_local, kv_head_num=hpr, qk_scale=case["qk_scale"])
+    pa_kw = dict(q_head_num=loop.hq_local, kv_head_num=loop.hpr, qk_scale=case["qk_scale"])
     if spec.kv_int8:
         pa_kw.update(quant_type=1, k_descale=kd, v_descale=vd)
+    h_lens = loop.h_lens
+
+    def set_step(j, slot_i):
+        """Host state of step j: lengths (read by the operator on the host) and the slots in staging set slot_i."""
+        np.add(loop.lens0, np.int32(j), out=loop.cur_lens)
+        h_slot[slot_i].copy_(loop.slots_host[j])
 
     def operators(slot_i):
         d_q, d_key, d_val, d_slot, d_bt = d_views[slot_i]
@@ -341,12 +531,7 @@ def run_gpu(args):
         o = ops.paged_attention(d_q, kc, vc, d_bt, h_lens, **pa_kw)
         return exchange(o) if world > 1 else o
 
-    # (1) serial: upload, operators, download, host waits -- the latency of one isolated step
-    def serial_step():
-        d_stage[0].copy_(h_stage[0], non_blocking=True)
-        o = operators(0)
-        h_out[0].copy_(o, non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the step's result is read on the host
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     def time_loop(fn, finish=None):
         for _ in range(3):
@@ -354,46 +539,57 @@ def run_gpu(args):
         if finish is not None:
             finish()
         barrier()
+        c0, a0 = ops.plan_cache_stats(), ops.plan_arena_stats()
         e0.record()
-        for _ in range(args.steps):
+        for _ in range(K):
             fn()
         if finish is not None:
             finish()
         e1.record()
         barrier()
-        tt = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        return float(tt.item()) / args.steps
-    serial_ms = time_loop(serial_step)
+        c1, a1 = ops.plan_cache_stats(), ops.plan_arena_stats()
+        stats = {"steps": K, "misses": c1["misses"] - c0["misses"], "hits": c1["hits"] - c0["hits"],
+                 "replanned_in_place": c1["recycled"] - c0["recycled"], "plans_created": c1["created"] - c0["created"],
+                 "pinned_slabs_added": a1["slabs"] - a0["slabs"], "arena_blocks_taken": a1["block_allocs"] - a0["block_allocs"]}
+        return max_over_ranks(e0.elapsed_time(e1)) / K, stats
 
-    # (2) pipelined, the serving loop: every step still uploads its inputs from pinned memory and
-    # has its result read on the host, but the upload of step i + 1 and the download of step i - 1
-    # run on copy streams while step i computes; the host reads a result two steps after its launch
-    # (before its pinned buffer is handed to the next download), so it never waits on the GPU
+    # (1) serial
+    def serial_step():
+        set_step(loop.i, 0)
+        d_stage[0].copy_(h_stage[0], non_blocking=True)
+        o = operators(0)
+        h_out[0].copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the step's result is read on the host
+        loop.i += 1
+    serial_ms, serial_stats = time_loop(serial_step)
+
+    # (2) pipelined
     comp = torch.cuda.current_stream()
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     ev_in = [torch.cuda.Event() for _ in range(2)]      # staging set uploaded
     ev_done = [torch.cuda.Event() for _ in range(2)]    # operators that read the set have finished
     ev_out = [torch.cuda.Event() for _ in range(2)]     # result is in pinned host memory
-    state = {"i": 0, "primed": False}
+    state = {"n": 0, "primed": False}
     d_out = [torch.empty(out_shape, dtype=q.dtype, device=dev) for _ in range(2)] if world > 1 else None
 
-    def upload(slot_i):
+    def upload(slot_i, j):
+        ev_in[slot_i].synchronize()                      # the set's previous upload has left the pinned buffer
+        h_slot[slot_i].copy_(loop.slots_host[j])
         s_in.wait_event(ev_done[slot_i])                 # the set's previous readers are done
         with torch.cuda.stream(s_in):
             d_stage[slot_i].copy_(h_stage[slot_i], non_blocking=True)
             ev_in[slot_i].record(s_in)
 
     def pipelined_step():
-        i = state["i"]
-        cur = i & 1
+        n, j = state["n"], loop.i
+        cur = n & 1
         if not state["primed"]:
-            for e in ev_done + ev_out:
+            for e in ev_done + ev_out + ev_in:
                 e.record(comp)
-            upload(cur)
+            upload(cur, j)
             state["primed"] = True
-        upload(cur ^ 1)                                  # next step's inputs, behind this step's kernels
+        upload(cur ^ 1, j + 1)                           # next step's inputs, behind this step's kernels
+        np.add(loop.lens0, np.int32(j), out=loop.cur_lens)
         comp.wait_event(ev_in[cur])
         o = operators(cur)
         if world > 1:
@@ -409,111 +605,91 @@ def run_gpu(args):
             ev_out[cur].record(s_out)
         if world == 1:
             o.record_stream(s_out)
-        state["i"] = i + 1
+        state["n"] = n + 1
+        loop.i = j + 1
 
     def drain():
         for e in ev_out:
             e.synchronize()
         comp.wait_stream(s_out)
         comp.wait_stream(s_in)
-    e2e_ms = time_loop(pipelined_step, drain)
-    clocks = sampler.stop() if sampler else None
-    ops.paged_attention_check_status(dev)
-    gather_check = None
-    if peer is not None:
-        peer.check()
-        # the peer-store gather must equal NCCL's all-gather of the same slices, bit for bit
-        mine = exchange(out_local)
-        torch.cuda.synchronize()
-        sharding.all_gather_outputs(out_local, gathered)
-        gather_check = bool(torch.equal(mine.view(torch.int16), gathered.view(torch.int16)))
+    pipe_ms, pipe_stats = time_loop(pipelined_step, drain)
     h2d = sum(x.numel() * x.element_size() for x in parts)
     d2h = h_out[0].numel() * h_out[0].element_size()
+    b = spec.batch
+    return {"value": b / serial_ms * 1e3, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "ms_per_step": serial_ms,
+            "mode": "serial: upload -> reshape_and_cache + paged_attention (operator API) -> download -> host waits; "
+                    "lengths grow every step, every step re-plans",
+            "plan_cache": serial_stats,
+            "pipelined_value": b / pipe_ms * 1e3, "pipelined_ms_per_step": pipe_ms,
+            "pipelined_mode": "two independent batches in flight: copy streams move step i+1's inputs and step i-1's "
+                              "result while step i computes; results read on the host two steps after launch",
+            "pipelined_plan_cache": pipe_stats}
 
-    if rank != 0:
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
-        return
 
-    # ---- roofline of the attention kernel --------------------------------------------------
-    kvb = 1 if spec.kv_int8 else 2
-    alg_bytes = workloads.algorithmic_bytes_attention(lens, hq_local, hpr, spec.head_size, kvb, quant=spec.kv_int8)
-    peak, peak_src = measured_hbm_peak()
-    roofline = {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None,
-                "kernel": "pa_tma_kernel" if info.kernel == 2 else "pa_generic_kernel",
-                "peak_source": peak_src, "algorithmic_bytes": alg_bytes}
-    if kernel_ms:
-        kms = statistics.mean(kernel_ms)
-        roofline.update(achieved=alg_bytes / kms / 1e6, frac=alg_bytes / kms / 1e6 / peak, kernel_ms=kms,
-                        frac_of_8tbs=alg_bytes / kms / 1e6 / 8000.0, launches_timed=len(kernel_ms))
-    # DRAM traffic of one launch: dram__bytes_read.sum + dram__bytes_write.sum of the ncu captures
-    # summarised in profiles/pa_tma_kernel_*.md, per context token per kv head, scaled to this
-    # launch (traffic grows in proportion to the tokens read)
-    if info.kernel == 2:
-        roofline["traffic"] = NCU_DRAM_BYTES_PER_TOKEN_HEAD["int8" if spec.kv_int8 else "16bit"] * sum(lens) * hpr
-        roofline["traffic_source"] = "ncu capture of config " + ("3" if spec.kv_int8 else "2") + ", scaled by tokens"
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
 
-    # ---- CPU baseline on the same workload (also the full-size parity check) ---------------
-    cpu = None
-    checked = None
-    if not args.no_cpu:
-        from oracle import c_oracle
-        nseq = min(spec.batch, args.cpu_sample)
-        # pre-scatter state is gone (the steps wrote the rows); the scatter is idempotent, so the
-        # current cache is the post-scatter cache and the CPU step reproduces the same result
-        host = {"query": _to_np(q[:nseq]), "key": _to_np(key[:nseq]), "value": _to_np(val[:nseq]),
-                "key_cache": _to_np(kc), "value_cache": _to_np(vc),
-                "block_tables": bt[:nseq].cpu().numpy(), "slot_mapping": slot[:nseq].cpu().numpy(),
-                "context_lens": np.array(lens[:nseq], dtype=np.int32), "qk_scale": case["qk_scale"],
-                "k_descale": None if kd is None else kd.cpu().numpy(),
-                "v_descale": None if vd is None else vd.cpu().numpy()}
-        cores = host_threads()
-        ref = cpu_step(c_oracle, host, cores)  # warm-up + reference output
-        reps, t_best = 0, float("inf")
-        t_begin = time.perf_counter()
-        while reps < 3 and time.perf_counter() - t_begin < 20.0:
-            t0 = time.perf_counter()
-            cpu_step(c_oracle, host, cores)
-            t_best = min(t_best, time.perf_counter() - t0)
-            reps += 1
-        sample = (f"{nseq} of {spec.batch} sequences ({int(sum(lens[:nseq]))} context tokens), kv heads {h0}..{h1 - 1}, "
-                  f"best of {reps}; C restatement of the reference numpy golden, OpenMP")
-        cpu = {"value": nseq / t_best, "unit": UNIT, "cores": cores, "kind": "port",
-               "sample": sample}
-        got = out_local[:nseq].float().cpu().numpy()
-        err = np.abs(got - ref)
-        tol = 2e-2 if spec.kv_int8 else 1e-2
-        checked = {"sequences": nseq, "max_abs_err": float(err.max()), "max_abs_golden": float(np.abs(ref).max()),
-                   "rel_l2": float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30)),
-                   "within_tolerance": bool(np.all(err <= tol + tol * np.abs(ref))), "tolerance": tol}
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = {"world": world, "rank": rank, "dev": dev}
 
-    scatter = measure_scatter(spec, dev, peak) if (world == 1 and "rac_tokens" in spec.extra) else None
-    adjacent = measure_adjacent(case, spec, dev, peak, not args.no_cpu) if (world == 1 and args.adjacent) else None
-    kernels_per_step = 2 + (1 if info.partials > 0 or min(lens) == 0 else 0)  # scatter, attention, reduce
-    kernels_per_step += 1 if peer is not None else 0                          # peer all-gather
-    line = {
-        "metric": METRIC, "value": spec.batch / ms_step * 1e3, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16" if spec.dtype == "bfloat16" else "f16", "data": "synthetic",
-        "config": workload_config(spec, lens, {
-            "parallelism": f"kv-head sharding x{world}" + (
-                "" if world == 1 else (" + peer-store all-gather of outputs over NVLink" if peer is not None
-                                       else " + NCCL all-gather of outputs")),
-            "l2": f"inputs larger than L2: {alg_bytes / 1e6:.0f} MB of KV per GPU per step vs {L2_BYTES >> 20} MB",
-            "launch": "CUDA graph replay" if graph is not None else "eager launches on one stream",
-            "work_items": info.work_items, "split_partials": info.partials, "grid": info.grid}),
-        "e2e": {"value": spec.batch / e2e_ms * 1e3, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                "mode": "pipelined: copy streams move step i+1's inputs and step i-1's result while step i computes; "
-                        "two staging sets, results read on the host two steps after launch",
-                "serial_ms_per_step": serial_ms, "serial_value": spec.batch / serial_ms * 1e3},
-        "gpu_launches": kernels_per_step * args.steps,
-        "roofline": roofline, "cpu_baseline": cpu, "parity_check": checked, "gather_check": gather_check, "clocks": clocks,
-        "reshape_and_cache_prefill": scatter, "adjacent_ops": adjacent,
-        "achieved_gbs_step": alg_bytes / ms_step / 1e6,
-    }
-    print(json.dumps(line), flush=True)
+    spec = workload_spec(args.workload)
+    head = measure_decode(ctx, spec, args, full=True)
+
+    # ---- the other benchmark configurations, same loop, device-timed + kernel roofline + parity ----
+    extras = {}
+    if not args.no_extra:
+        names = ["c3", "c4", "c5"] if world == 1 else ["c4"]
+        for name in names:
+            if name == args.workload.lower():
+                continue
+            r = measure_decode(ctx, workload_spec(name), args, full=False)
+            if rank == 0:
+                rf = r["roofline"]
+                extras[name] = {
+                    "workload": r["config"]["workload"], "kv_tokens": r["config"]["kv_tokens"],
+                    "parallelism": r["config"]["parallelism"], "value": r["value"], "unit": UNIT,
+                    "ms_per_step": r["ms_per_step"], "attention_kernel_ms": rf.get("kernel_ms"),
+                    "roofline": {k: rf.get(k) for k in ("achieved", "peak", "frac", "frac_of_8tbs", "algorithmic_bytes",
+                                                        "kernel", "peak_source")},
+                    "parity_check": r["parity_check"], "gather_check": r["gather_check"],
+                    "cpu_baseline": r["cpu_baseline"], "work_items": r["config"]["work_items"],
+                    "split_partials": r["config"]["split_partials"]}
+    peak, _ = measured_hbm_peak()
+    scatter = adjacent = None
+    if world == 1 and not args.no_extra:
+        scatter = measure_scatter(workload_spec("c5"), dev, peak)
+        if rank == 0:
+            extras["rac_prefill"] = scatter
+    if world == 1 and args.adjacent:
+        case = workloads.decode_case_device(spec, dev, (0, spec.kv_heads))
+        adjacent = measure_adjacent(case, spec, dev, peak, not args.no_cpu)
+
+    if rank == 0:
+        cpu_np = None if args.no_cpu else cpu_numpy_config1()
+        line = {
+            "metric": METRIC, "value": head["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if spec.dtype == "bfloat16" else "f16",
+            "data": "synthetic", "config": head["config"], "e2e": head["e2e"],
+            "gpu_launches": head["kernels_per_step"] * args.steps,
+            "roofline": head["roofline"], "cpu_baseline": head["cpu_baseline"], "cpu_baseline_numpy": cpu_np,
+            "parity_check": head["parity_check"], "gather_check": head["gather_check"], "clocks": head["clocks"],
+            "loops_ms_per_step": head["loops_ms_per_step"], "achieved_gbs_step": head["achieved_gbs_step"],
+            "configs": extras, "adjacent_ops": adjacent,
+        }
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -848,7 +1024,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c2", help="c1..c5: benchmark configuration (default c2)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays of the step")
+    ap.add_argument("--repeats", type=int, default=5, help="timed loops of --steps steps each; the median is reported")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="only the headline workload (skip the `configs` entries: c3, c4, c5, prefill scatter)")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="time budget of one CPU baseline leg")
     ap.add_argument("--nccl-gather", action="store_true", help="exchange outputs with NCCL instead of peer stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity check")
     ap.add_argument("--seq-parallel", action="store_true",

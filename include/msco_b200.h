@@ -356,6 +356,9 @@ typedef struct MscoGatherDesc {
   int64_t slice_bytes;                /* bytes of one rank's slice; multiple of 16                 */
   unsigned int *ticket;               /* local device word, zero before the first call            */
   int32_t *status;                    /* local device word, zero before the first call            */
+  uint32_t wait_polls;                /* polls (about 0.1 us apart) before the wait for a peer gives up and
+                                         sets *status = MSCO_ERR_TIMEOUT; 0 = the default, 2^22 (about half a second) */
+  uint32_t reserved;
 } MscoGatherDesc;
 int msco_ipc_export(const void *dev_ptr, unsigned char *handle /* [64] */, int64_t *offset);
 int msco_ipc_import(const unsigned char *handle, int64_t offset, void **dev_ptr);

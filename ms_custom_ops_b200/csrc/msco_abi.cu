@@ -3,6 +3,7 @@
 #include <atomic>
 #include <chrono>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <numeric>
@@ -196,13 +197,17 @@ extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *
   const MscoPaDesc &d = *desc;
   const bool tma_ok = pa_tma_supported(d);
   if (d.kernel == kKernelTma && !tma_ok)
-    return fail(MSCO_ERR_UNSUPPORTED, "paged_attention_plan: the TMA kernel needs head_dim 128 and block_size 16/32/64/128");
+    return fail(MSCO_ERR_UNSUPPORTED,
+                "paged_attention_plan: the TMA kernel needs head_dim 128 (or 64 / 256 with a 16-bit cache) and "
+                "block_size 16/32/64/128 (at most 64 for head_dim 256)");
   MscoPaPlan *pl = new (std::nothrow) MscoPaPlan();
   if (pl == nullptr) return fail(MSCO_ERR_INTERNAL, "paged_attention_plan: out of host memory");
   pl->desc = d;
   const int g = d.num_q_heads / d.num_kv_heads;
   pl->kernel = (d.kernel == kKernelGeneric || !tma_ok) ? kKernelGeneric : kKernelTma;
-  pl->rows_per_item = (pl->kernel == kKernelTma && g > 8) ? 16 : 8;
+  pl->rows_per_item = pl->kernel == kKernelTma ? pa_tma_rows_per_item(d) : 8;
+  (void)g;
+  if (const char *e = getenv("MSCO_PA_INT8_SUBS")) pl->int8_subs = atoi(e) == 2 ? 2 : 1;
   rc = fill_plan(pl, host_context_lens, batch);
   if (rc != MSCO_OK) {
     msco_paged_attention_plan_destroy(pl);

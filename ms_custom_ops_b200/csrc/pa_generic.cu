@@ -232,10 +232,10 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p, const __grid
     return;
   }
   const int base = __ldg(pv.b_part_base + b);
-  if (D == 128) {  // same code as the attention kernel's own epilogue: identical bits
-    merge_row_d128<TQ>(p, b, hq, ns, base, lane);
-    return;
-  }
+  // same code as the TMA kernel's own epilogue: identical bits
+  if (D == 128) { merge_row<TQ, 128>(p, b, hq, ns, base, lane); return; }
+  if (D == 64) { merge_row<TQ, 64>(p, b, hq, ns, base, lane); return; }
+  if (D == 256) { merge_row<TQ, 256>(p, b, hq, ns, base, lane); return; }
   const int64_t hq_stride = p.num_q_heads;
   // pass 1: M = max_s m_s (lanes stride over the splits)
   float M = kNeg;

@@ -1,4 +1,4 @@
-// Merge of the split-KV partials of one output row (head_dim 128), shared by the reduce kernel and by
+// Merge of the split-KV partials of one output row (head_dim 64 / 128 / 256), shared by the reduce kernel and by
 // the attention kernel's own epilogue so that both produce the same bits.
 //
 // The partials hold, per split s, the running maximum m_s (log2 domain), the running sum l_s and the
@@ -20,9 +20,12 @@ __device__ __forceinline__ float merge_warp_max(float v) {
 }
 
 // One warp merges row (b, hq): `ns` >= 2 splits whose partial rows start at part index `base`.
+// D = head_dim (64, 128 or 256): a lane owns D / 32 consecutive columns.
 // All loads bypass L1 (ld.global.cg): the partials may have been written by other SMs of the same grid.
-template <typename TQ>
-__device__ __forceinline__ void merge_row_d128(const PaParams &p, int b, int hq, int ns, int base, int lane) {
+template <typename TQ, int D>
+__device__ __forceinline__ void merge_row(const PaParams &p, int b, int hq, int ns, int base, int lane) {
+  static_assert(D == 64 || D == 128 || D == 256, "head_dim 64, 128 or 256");
+  constexpr int kCols = D / 32;  // columns per lane: 2, 4 or 8
   constexpr float kNegBig = -1.0e30f;
   constexpr float kLn2f = 0.6931471805599453f;
   const int64_t hq_stride = p.num_q_heads;
@@ -33,8 +36,10 @@ __device__ __forceinline__ void merge_row_d128(const PaParams &p, int b, int hq,
   M = merge_warp_max(M);
   const int kvh = hq / p.group;
   float L = 0.f;
-  // lane owns 4 consecutive head-dim columns; splits in blocks of 32 (weights in registers)
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float acc[kCols];
+#pragma unroll
+  for (int c = 0; c < kCols; ++c) acc[c] = 0.f;
+  // splits in blocks of 32 (weights in registers), accumulated in split order: bit-reproducible
   for (int s0 = 0; s0 < ns; s0 += 32) {
     float f_mine = 0.f, l_mine = 0.f;
     if (s0 + lane < ns) {
@@ -45,30 +50,50 @@ __device__ __forceinline__ void merge_row_d128(const PaParams &p, int b, int hq,
     }
     const int cnt = min(32, ns - s0);
 #pragma unroll 8
-    for (int j = 0; j < cnt; ++j) {  // split order: bit-reproducible
+    for (int j = 0; j < cnt; ++j) {
       const float f = __shfl_sync(0xffffffffu, f_mine, j);
       const float lj = __shfl_sync(0xffffffffu, l_mine, j);
-      const float4 v =
-          __ldcg(reinterpret_cast<const float4 *>(p.part_o + ((int64_t)(base + s0 + j) * hq_stride + hq) * 128) + lane);
+      const float *src = p.part_o + ((int64_t)(base + s0 + j) * hq_stride + hq) * D + lane * kCols;
+      float v[kCols];
+      if (kCols == 2) {
+        const float2 t = __ldcg(reinterpret_cast<const float2 *>(src));
+        v[0] = t.x; v[1] = t.y;
+      } else {
+#pragma unroll
+        for (int c = 0; c < kCols; c += 4) {
+          const float4 t = __ldcg(reinterpret_cast<const float4 *>(src + c));
+          v[c] = t.x; v[c + 1] = t.y; v[c + 2] = t.z; v[c + 3] = t.w;
+        }
+      }
       L = fmaf(lj, f, L);
-      acc.x = fmaf(v.x, f, acc.x); acc.y = fmaf(v.y, f, acc.y);
-      acc.z = fmaf(v.z, f, acc.z); acc.w = fmaf(v.w, f, acc.w);
+#pragma unroll
+      for (int c = 0; c < kCols; ++c) acc[c] = fmaf(v[c], f, acc[c]);
     }
   }
   const float inv = 1.f / L;
-  float r0 = acc.x * inv, r1 = acc.y * inv, r2 = acc.z * inv, r3 = acc.w * inv;
+  float r[kCols];
+#pragma unroll
+  for (int c = 0; c < kCols; ++c) r[c] = acc[c] * inv;
   if (p.v_descale != nullptr) {
-    const float4 vs = __ldg(reinterpret_cast<const float4 *>(p.v_descale + kvh * 128) + lane);
-    if (p.v_offset != nullptr) {
-      const int4 vo = __ldg(reinterpret_cast<const int4 *>(p.v_offset + kvh * 128) + lane);
-      r0 += (float)vo.x; r1 += (float)vo.y; r2 += (float)vo.z; r3 += (float)vo.w;
+#pragma unroll
+    for (int c = 0; c < kCols; ++c) {
+      const int d = lane * kCols + c;
+      if (p.v_offset != nullptr) r[c] += (float)__ldg(p.v_offset + kvh * D + d);
+      r[c] *= __ldg(p.v_descale + kvh * D + d);
     }
-    r0 *= vs.x; r1 *= vs.y; r2 *= vs.z; r3 *= vs.w;
   }
-  uint2 pk;
-  pk.x = pack2<TQ>(r0, r1);
-  pk.y = pack2<TQ>(r2, r3);
-  *reinterpret_cast<uint2 *>(static_cast<TQ *>(p.out) + row * 128 + lane * 4) = pk;
+  TQ *dst = static_cast<TQ *>(p.out) + row * D + lane * kCols;
+  if (kCols == 2) {
+    *reinterpret_cast<uint32_t *>(dst) = pack2<TQ>(r[0], r[1]);
+  } else {
+#pragma unroll
+    for (int c = 0; c < kCols; c += 4) {
+      uint2 pk;
+      pk.x = pack2<TQ>(r[c], r[c + 1]);
+      pk.y = pack2<TQ>(r[c + 2], r[c + 3]);
+      *reinterpret_cast<uint2 *>(dst + c) = pk;
+    }
+  }
   if (lane == 0 && p.lse != nullptr) p.lse[row] = (M + log2f(L)) * kLn2f;
 }
 

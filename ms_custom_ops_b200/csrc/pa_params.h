@@ -78,6 +78,7 @@ struct MscoPaPlan {
   mutable cudaEvent_t upload_done = nullptr;
   mutable bool upload_pending = false;
   bool fused_merge = false;     // the attention kernel merges the split partials itself
+  int int8_subs = 1;            // int8 KV, up to 8 q rows: 16-token sub-tiles per consumer warp (1 or 2)
   int num_groups = 0;           // (sequence with tokens, kv head, q-row block) triples
   size_t sync_offset = 0;       // scheduling words inside the workspace
   size_t sync_bytes = 0;
@@ -118,4 +119,5 @@ int launch_rac_quant(const void *key, const void *value, int8_t *key_cache, int8
                      const int32_t *v_offset, int64_t num_slots, int32_t *oob_count, cudaStream_t stream,
                      uint32_t *clear, int clear_words, bool *cleared);
 bool pa_tma_supported(const MscoPaDesc &d);
+int pa_tma_rows_per_item(const MscoPaDesc &d);
 }  // namespace msco

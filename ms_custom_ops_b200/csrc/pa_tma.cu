@@ -1,13 +1,13 @@
 // Paged-attention decode for B200: persistent TMA-fed split-KV kernel.
 //
 // HBM-bound: every K/V byte of the context is read exactly once.  One
-// persistent CTA per SM walks a static round-robin list of work items
-// (sequence, kv head, q-row block, KV split).  A producer warp streams K and V
+// persistent CTA per SM takes work items (sequence, kv head, q-row block, KV
+// split) from a longest-first list by a ticket.  A producer warp streams K and V
 // tiles of the paged cache into a ring of shared-memory stages with tiled TMA
 // loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) that complete
 // on mbarriers; the stream runs ahead across item boundaries, so the memory
-// pipe never drains between items.  Each consumer warp owns 16 tokens of a
-// tile and keeps an independent online-softmax state (m, l, O) for the GQA
+// pipe never drains between items.  Each consumer warp owns 16 (or 32) tokens
+// of a tile and keeps an independent online-softmax state (m, l, O) for the GQA
 // group of q rows.
 //
 // The micro-tiles put the TOKENS on the M side of mma.sync m16n8k16 and the q
@@ -21,11 +21,13 @@
 // which the softmax cancels; for V it stays in the accumulators and
 // 1152 * l is subtracted once per item.  The row sums l are accumulated by the
 // tensor cores from the same rounded probabilities (a tile of ones in place
-// of V^T).  k_descale is folded into Q once per item, v_descale / v_offset
-// are applied once to the output.  At the end of an item the warps' states are merged through shared
-// memory and written either as the final output (one split) or as an fp32
-// partial (m, l, O) for the reduce kernel.
+// of V^T).  k_descale is folded into Q once per item by a helper warp, v_descale /
+// v_offset are applied once to the output.  At the end of an item the warps' states are
+// merged through shared memory and written either as the final output (one split) or
+// as an fp32 partial (m, l, O); the CTA that stores the last partial of a
+// (sequence, kv head, q-row block) group merges the group's partials itself.
 //
+// Head dimensions: 128 (16-bit and int8 KV), 64 and 256 (16-bit KV).
 // Algorithmic bytes per context token: 2 * head_dim * sizeof(kv) per kv head.
 #include <cuda.h>
 
@@ -38,34 +40,44 @@
 namespace msco {
 namespace {
 
-constexpr int kD = 128;               // head_dim of this kernel
-constexpr int kMergeStride = 132;     // floats per merged row (bank-conflict padding)
-constexpr int kQSlotBytes = 16 * kD * 2;
 constexpr float kNeg = -1.0e30f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr uint32_t kWaitLimit = 1u << 24;
-constexpr int kDescInts = 12;         // work-item descriptor handed from the producer to the consumers
+constexpr int kDescInts = 12;  // work-item descriptor handed from the producer to the consumers
 
-// NT = number of 8-row tiles of the q group (1: up to 8 rows, 2: up to 16).
-template <bool KV8, int NT> struct Cfg {
-  static constexpr int kWarps = (KV8 && NT == 1) ? 16 : 8;  // consumer warps, 16 tokens each
-  static constexpr int kTile = kWarps * 16;                 // tokens per tile
-  static constexpr int kThreads = (kWarps + 1) * 32;
+// D = head_dim, NT = number of 8-row tiles of the q group (1: up to 8 rows, 2: up to 16),
+// SUBS = 16-token sub-tiles per consumer warp and tile.
+template <int D, bool KV8, int NT, int SUBS> struct Cfg {
+  static_assert(D == 64 || D == 128 || D == 256, "head_dim 64, 128 or 256");
+  static_assert(!KV8 || D == 128, "int8 KV: head_dim 128");
+  static_assert(SUBS == 1 || (SUBS == 2 && KV8 && NT == 1), "two sub-tiles per warp: int8 KV, up to 8 q rows");
+  static_assert(D != 256 || NT == 1, "head_dim 256: up to 8 q rows per item");
+  static constexpr int kWarps = D == 256 ? 4 : ((KV8 && NT == 1 && SUBS == 1) ? 16 : 8);  // consumer warps
+  static constexpr int kTile = kWarps * 16 * SUBS;          // tokens per tile
+  static constexpr int kAux = KV8 ? 1 : 0;                  // helper warp that prepares Q (int8 KV)
+  static constexpr int kThreads = (kWarps + 1 + kAux) * 32;
   static constexpr int kConsumerThreads = kWarps * 32;
-  static constexpr int kRowBytes = KV8 ? kD : 2 * kD;       // one token row of one head
+  static constexpr int kRowBytes = KV8 ? D : 2 * D;         // one token row of one head
+  static constexpr int kBoxes = kRowBytes / 128;            // 128-byte TMA boxes per token row
   static constexpr int kStageBytes = kTile * kRowBytes;     // 16 / 32 KB
-  static constexpr int kStages = KV8 ? (NT == 1 ? 4 : 8) : (NT == 1 ? 5 : 4);
+  static constexpr int kStages = D == 64 ? 8 : (D == 256 ? 5 : (KV8 ? (NT == 1 ? 4 : 8) : (NT == 1 ? 5 : 4)));
   static constexpr int kRows = 8 * NT;
+  static constexpr int kKSteps = D / 16;                    // 16-wide slices of the head dimension
+  static constexpr int kMergeStride = D + 4;                // floats per merged row (bank-conflict padding)
+  static constexpr int kMergeBufs = SUBS == 2 ? 2 : 1;      // two: no barrier between the items' merges
   static constexpr int kMergeBytes = kWarps * kRows * kMergeStride * 4;
+  static constexpr int kMlBytes = kWarps * 16 * 2 * 4;      // [warp][16] float2
+  static constexpr int kQSlotBytes = 16 * D * 2;
   static constexpr int kOffQ = kStages * kStageBytes;
   static constexpr int kOffQFrag = kOffQ + 2 * kQSlotBytes;         // int8 KV: scaled fp16 Q in fragment order
   static constexpr int kQFragBytes = KV8 ? NT * 4 * 32 * 16 + 128 : 0;  // [row tile][k-step pair][lane] uint4, then
                                                                          // 2 partial score offsets per q row (lse)
-  static constexpr int kOffMerge = kOffQFrag + kQFragBytes;
-  static constexpr int kOffMl = kOffMerge + kMergeBytes;            // [warp][16] float2
-  static constexpr int kOffDesc = kOffMl + kWarps * 16 * 2 * 4;     // 2 x kDescInts ints, then the merge flag
-  static constexpr int kOffBar = kOffDesc + 2 * kDescInts * 4 + 16; // mbarriers
-  static constexpr int kNumBars = 2 * kStages + 4;
+  static constexpr int kOffMerge = kOffQFrag + 2 * kQFragBytes;
+  static constexpr int kOffMl = kOffMerge + kMergeBufs * kMergeBytes;
+  static constexpr int kOffDesc = kOffMl + kMergeBufs * kMlBytes;   // 2 x kDescInts ints, 2 merge flags (+ pad),
+                                                                    // 4 x 8 ints: groups awaiting their merge
+  static constexpr int kOffBar = kOffDesc + 2 * kDescInts * 4 + 16 + 4 * 8 * 4;  // mbarriers
+  static constexpr int kNumBars = 2 * kStages + 6;
   static constexpr int kOffItemBase = kOffBar + kNumBars * 8 + 16;  // copy of the plan's item_base[]
   static constexpr int kItemBaseCap = 1024;                          // sequences (+1) that fit
   static constexpr int kSmemBytes = kOffItemBase + kItemBaseCap * 4;
@@ -92,23 +104,24 @@ __device__ __forceinline__ float load_mask_elem(const void *mask, int dtype, int
   return __ldg(static_cast<const float *>(mask) + idx);
 }
 
-template <typename T, bool KV8, int NT, bool MASK>
-__global__ void __launch_bounds__(Cfg<KV8, NT>::kThreads, 1)
+template <typename T, int D, bool KV8, int NT, bool MASK, int SUBS>
+__global__ void __launch_bounds__(Cfg<D, KV8, NT, SUBS>::kThreads, 1)
 pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, PaParams p,
               const __grid_constant__ PlanParam pp) {
-  using C = Cfg<KV8, NT>;
+  using C = Cfg<D, KV8, NT, SUBS>;
   // fp16 arithmetic for int8 KV (integers up to 1279 are exact in fp16, not in bf16)
   using MT = typename std::conditional<KV8, __half, T>::type;
   constexpr int kTile = C::kTile;
+  constexpr int kKS = C::kKSteps;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + C::kOffBar);
   uint64_t *full = bars, *empty = bars + C::kStages;
-  uint64_t *qfull = bars + 2 * C::kStages, *qempty = qfull + 2;
+  uint64_t *qfull = bars + 2 * C::kStages, *qempty = qfull + 2, *qready = qfull + 4;
   int *desc = reinterpret_cast<int *>(smem + C::kOffDesc);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // let the reduce kernel (launched with programmatic stream serialisation) become resident now;
+  // a kernel launched behind this one with programmatic stream serialisation may become resident now;
   // it blocks in griddepcontrol.wait until this grid has completed
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) {
@@ -119,6 +132,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     for (int i = 0; i < 2; ++i) {
       mbar_init(&qfull[i], 1);
       mbar_init(&qempty[i], C::kWarps);
+      mbar_init(&qready[i], 1);
     }
     fence_barrier_init();
   }
@@ -175,11 +189,11 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         d[0] = w.b; d[1] = w.kvh; d[2] = w.row0; d[3] = w.nrows;
         d[4] = w.tok0; d[5] = w.tok1; d[6] = w.nsplit; d[7] = w.part;
         d[8] = w.grp; d[9] = w.part0;
-        const uint32_t qbytes = (uint32_t)w.nrows * kD * 2;
+        const uint32_t qbytes = (uint32_t)w.nrows * D * 2;
         mbar_arrive_expect_tx(&qfull[qs], qbytes);
         const char *qsrc = static_cast<const char *>(p.q) +
-                           ((int64_t)w.b * p.num_q_heads + w.kvh * p.group + w.row0) * (kD * 2);
-        bulk_load(smem + C::kOffQ + qs * kQSlotBytes, qsrc, qbytes, &qfull[qs]);
+                           ((int64_t)w.b * p.num_q_heads + w.kvh * p.group + w.row0) * (D * 2);
+        bulk_load(smem + C::kOffQ + qs * C::kQSlotBytes, qsrc, qbytes, &qfull[qs]);
       }
       const int ntok = w.tok1 - w.tok0;
       const int nblk_item = (ntok + bs - 1) / bs;
@@ -212,8 +226,11 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
               if (lane == 0) {
                 const CUtensorMap *tm = op == 0 ? &tm_k : &tm_v;
                 const int z = id * bs;
-                tma_load_3d(dst + j * bs * 128, tm, 0, w.kvh, z, &full[st]);
-                if (!KV8) tma_load_3d(dst + kTile * 128 + j * bs * 128, tm, 64, w.kvh, z, &full[st]);
+                // one 128-byte box per 64 elements (16-bit) / 128 elements (int8) of the head dimension;
+                // x is a multiple of 64 elements = 128 bytes: TMA's 16-byte rule holds by construction
+#pragma unroll
+                for (int bx = 0; bx < C::kBoxes; ++bx)
+                  tma_load_3d(dst + bx * (kTile * 128) + j * bs * 128, tm, bx * (KV8 ? 128 : 64), w.kvh, z, &full[st]);
               }
             }
             if (++st == C::kStages) { st = 0; ph ^= 1; }
@@ -225,13 +242,68 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     return;
   }
 
+  if (C::kAux && warp == C::kWarps + 1) {
+    // ======================= Q-preparation warp (int8 KV) =======================
+    // k_descale is folded into Q, and inside each 16-wide group of the head dimension the
+    // contraction index is permuted so that the four bytes a lane gets from ldmatrix
+    // (d = 16ks + 4q4 .. +3) are its two A registers.  This warp converts the rows of the NEXT item
+    // while the consumers still work on the current one: word (row tile, k-step pair, lane,
+    // 2 (ks & 1) + j) holds the fp16 pair Q[8nt + gid][16ks + 4q4 + 2j, + 1] * k_descale.
+    for (int qi = 0;; ++qi) {
+      const int qs = qi & 1;
+      const uint32_t qph = (qi >> 1) & 1;
+      if (!mbar_wait(&qfull[qs], qph, kWaitLimit)) {
+        report_status(p.status, p.epoch, kStatusTimeout);
+        return;
+      }
+      const int *dsc = desc + qs * kDescInts;
+      const int b = dsc[0];
+      if (b < 0) {
+        if (lane == 0) mbar_arrive(&qready[qs]);
+        return;
+      }
+      const int kvh = dsc[1], nrows = dsc[3];
+      const T *qsm = reinterpret_cast<const T *>(smem + C::kOffQ + qs * C::kQSlotBytes);
+      uint32_t *qfrag = reinterpret_cast<uint32_t *>(smem + C::kOffQFrag + qs * C::kQFragBytes);
+      float *score_shift = reinterpret_cast<float *>(smem + C::kOffQFrag + qs * C::kQFragBytes + NT * 4 * 32 * 16);
+      const float *ksc = p.k_descale + kvh * D;
+      for (int u = lane; u < C::kRows * 64; u += 32) {
+        const int r = u >> 6, dp = u & 63;  // q row, index of the pair of head-dim columns
+        float e0 = 0.f, e1 = 0.f;
+        if (r < nrows) {
+          const float2 sc = __ldg(reinterpret_cast<const float2 *>(ksc + 2 * dp));
+          e0 = to_f32<T>(qsm[r * D + 2 * dp]) * sc.x;
+          e1 = to_f32<T>(qsm[r * D + 2 * dp + 1]) * sc.y;
+        }
+        const int ks = dp >> 3, qq = (dp >> 1) & 3, j = dp & 1;
+        const uint32_t packed = pack2<__half>(e0, e1);
+        qfrag[(((r >> 3) * 4 + (ks >> 1)) * 32 + (r & 7) * 4 + qq) * 4 + 2 * (ks & 1) + j] = packed;
+        if (p.lse != nullptr) {
+          // the K bytes enter the MMA as k + 1152 instead of k + k_offset: every score of q row r is
+          // too large by sum_d Q~[r][d] (1152 - k_offset[d]).  The softmax does not see that, the
+          // log-sum-exp does: the warp (32 column pairs of one row) adds up its half of the sum.
+          const __half2 h2 = *reinterpret_cast<const __half2 *>(&packed);
+          float o0 = 1152.f, o1 = 1152.f;
+          if (p.k_offset != nullptr) {
+            o0 -= (float)__ldg(p.k_offset + kvh * D + 2 * dp);
+            o1 -= (float)__ldg(p.k_offset + kvh * D + 2 * dp + 1);
+          }
+          float part = fmaf(__low2float(h2), o0, __high2float(h2) * o1);
+#pragma unroll
+          for (int sh = 16; sh > 0; sh >>= 1) part += __shfl_xor_sync(0xffffffffu, part, sh);
+          if (lane == 0) score_shift[2 * r + (dp >> 5)] = part;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&qready[qs]);  // release: the fragments are visible to whoever waits
+    }
+  }
+
   // ======================= consumer warps =======================
   const int gid = lane >> 2, q4 = lane & 3;
-  const int t0 = warp * 16;                  // this warp's token rows inside a tile
+  const int t0 = warp * 16 * SUBS;           // this warp's token rows inside a tile
   const int mat = lane >> 3, mr = lane & 7;  // ldmatrix: matrix id and row supplied by this lane
   const uint32_t stage0 = smem_u32(smem);
-  float *mbuf = reinterpret_cast<float *>(smem + C::kOffMerge);
-  float2 *mlbuf = reinterpret_cast<float2 *>(smem + C::kOffMl);
   // byte offsets of the ldmatrix rows this lane supplies (swizzle: 16-byte chunk ^= row & 7)
   //   K 16-bit, K int8, V int8: matrices 1,3 are the tokens +8;  V 16-bit: matrices 2,3
   const uint32_t row_m1 = (uint32_t)(t0 + (mat & 1) * 8 + mr) * 128u;
@@ -239,17 +311,53 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   const int tid = threadIdx.x;
 
   uint32_t st = 0, ph = 0;
-  // Deferred merge of split partials.  When an item of a multi-split group has stored its partial,
-  // one thread bumps the group's arrival counter; the answer is looked at one item later (so its
-  // latency costs nothing), and if this CTA was the last arriver all warps merge the group then.
+  // Merge of split partials, two steps behind.  When an item of a multi-split group has stored its
+  // partial ("stored"), one thread bumps the group's arrival counter at the next item's barrier
+  // (every thread's stores are ordered before it by then) -- "bumped"; the answer is looked at one
+  // item later still, so neither the fence nor the atomic's latency is ever waited for, and if this
+  // CTA was the last arriver all warps merge the group then.
   volatile int *merge_flag = reinterpret_cast<volatile int *>(desc + 2 * kDescInts);
-  bool pend = false;                 // a counter bump of this CTA awaits its answer (uniform)
-  unsigned pend_old = 0;             // the answer (thread 0 only)
-  int pend_b = 0, pend_hq0 = 0, pend_nrows = 0, pend_ns = 0, pend_part0 = 0;
+  // [slot][b, first q head, rows, splits, first partial, counter index]: written by thread 0 when an item
+  // has stored its partial, read by everybody one and two barriers later
+  volatile int *pinfo = reinterpret_cast<volatile int *>(desc + 2 * kDescInts + 4);
+  int n_stored = 0;                              // multi-split items finished so far (uniform)
+  bool has_stored = false, has_bumped = false;   // uniform over the consumer threads
+  unsigned bumped_old = 0;                       // the counter's answer (thread 0 only)
+  int nround = 0;                                // rounds so far: the flag words alternate
+  // one round of that pipeline: `pre` before a barrier of the consumer threads, `post` after it
+  auto merge_round_pre = [&]() {
+    if (has_bumped && tid == 0) {
+      const int ns = pinfo[((n_stored - (has_stored ? 2 : 1)) & 3) * 8 + 3];
+      merge_flag[nround & 1] = (bumped_old == (unsigned)(ns - 1)) ? 1 : 0;
+    }
+  };
+  auto merge_round_post = [&]() {
+    if (has_bumped) {
+      if (merge_flag[nround & 1]) {
+        const volatile int *g = pinfo + ((n_stored - (has_stored ? 2 : 1)) & 3) * 8;
+        const int gb = g[0], ghq0 = g[1], gnrows = g[2], gns = g[3], gpart0 = g[4];
+        __threadfence();  // the other CTAs' partials were fenced before their counter bumps
+        for (int r = warp; r < gnrows; r += C::kWarps) merge_row<T, D>(p, gb, ghq0 + r, gns, gpart0, lane);
+      }
+      has_bumped = false;
+    }
+    if (has_stored) {
+      if (tid == 0) {
+        // the barrier ordered every thread's partial stores before this fence, the fence orders them
+        // (cumulatively) before the counter moves
+        __threadfence();
+        bumped_old = atomicAdd(p.sync + kSyncHeaderWords + pinfo[((n_stored - 1) & 3) * 8 + 5], 1u);
+      }
+      has_bumped = true;
+      has_stored = false;
+    }
+    ++nround;
+  };
+
   for (int qi = 0;; ++qi) {
     const int qs = qi & 1;
     const uint32_t qph = (qi >> 1) & 1;
-    if (!mbar_wait(&qfull[qs], qph, kWaitLimit)) {
+    if (!mbar_wait(KV8 ? &qready[qs] : &qfull[qs], qph, kWaitLimit)) {
       report_status(p.status, p.epoch, kStatusTimeout);
       return;
     }
@@ -259,60 +367,27 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const int kvh = dsc[1], row0 = dsc[2], nrows = dsc[3];
     const int tok0 = dsc[4], tok1 = dsc[5], nsplit = dsc[6], part = dsc[7];
     const int grp = dsc[8], part0 = dsc[9];
+    float *mbuf = reinterpret_cast<float *>(smem + C::kOffMerge + (C::kMergeBufs == 2 ? (qi & 1) * C::kMergeBytes : 0));
+    float2 *mlbuf = reinterpret_cast<float2 *>(smem + C::kOffMl + (C::kMergeBufs == 2 ? (qi & 1) * C::kMlBytes : 0));
 
     // ---- Q^T fragments (B operand): lane holds q row 8nt + gid, rows >= nrows are zero ----
-    uint32_t qb[8][NT][2];
+    uint32_t qb[kKS][NT][2];
     {
-      const T *qsm = reinterpret_cast<const T *>(smem + C::kOffQ + qs * kQSlotBytes);
       if (!KV8) {
+        const T *qsm = reinterpret_cast<const T *>(smem + C::kOffQ + qs * C::kQSlotBytes);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const bool valid = 8 * nt + gid < nrows;
-          const T *qr = qsm + (8 * nt + gid) * kD;
+          const T *qr = qsm + (8 * nt + gid) * D;
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
+          for (int ks = 0; ks < kKS; ++ks) {
             const int c = 16 * ks + 2 * q4;
             qb[ks][nt][0] = valid ? *reinterpret_cast<const uint32_t *>(qr + c) : 0u;
             qb[ks][nt][1] = valid ? *reinterpret_cast<const uint32_t *>(qr + c + 8) : 0u;
           }
         }
       } else {
-        // int8 K: k_descale is folded into Q, and inside each 16-wide group of the head dimension
-        // the contraction index is permuted so that the four bytes a lane gets from ldmatrix
-        // (d = 16ks + 4q4 .. +3) are its two A registers.  The warps convert the rows together,
-        // once per item, into fragment order: word (row tile, k-step pair, lane, 2 (ks & 1) + j)
-        // holds the fp16 pair Q[8nt + gid][16ks + 4q4 + 2j, + 1] * k_descale.
-        uint32_t *qfrag = reinterpret_cast<uint32_t *>(smem + C::kOffQFrag);
-        float *score_shift = reinterpret_cast<float *>(smem + C::kOffQFrag + NT * 4 * 32 * 16);
-        const float *ksc = p.k_descale + kvh * kD;
-        for (int u = tid; u < C::kRows * 64; u += C::kConsumerThreads) {
-          const int r = u >> 6, dp = u & 63;  // q row, index of the pair of head-dim columns
-          float e0 = 0.f, e1 = 0.f;
-          if (r < nrows) {
-            const float2 sc = __ldg(reinterpret_cast<const float2 *>(ksc + 2 * dp));
-            e0 = to_f32<T>(qsm[r * kD + 2 * dp]) * sc.x;
-            e1 = to_f32<T>(qsm[r * kD + 2 * dp + 1]) * sc.y;
-          }
-          const int ks = dp >> 3, qq = (dp >> 1) & 3, j = dp & 1;
-          const uint32_t packed = pack2<__half>(e0, e1);
-          qfrag[(((r >> 3) * 4 + (ks >> 1)) * 32 + (r & 7) * 4 + qq) * 4 + 2 * (ks & 1) + j] = packed;
-          if (p.lse != nullptr) {
-            // the K bytes enter the MMA as k + 1152 instead of k + k_offset: every score of q row r is
-            // too large by sum_d Q~[r][d] (1152 - k_offset[d]).  The softmax does not see that, the
-            // log-sum-exp does: the warp (32 column pairs of one row) adds up its half of the sum.
-            const __half2 h2 = *reinterpret_cast<const __half2 *>(&packed);
-            float o0 = 1152.f, o1 = 1152.f;
-            if (p.k_offset != nullptr) {
-              o0 -= (float)__ldg(p.k_offset + kvh * kD + 2 * dp);
-              o1 -= (float)__ldg(p.k_offset + kvh * kD + 2 * dp + 1);
-            }
-            float part = fmaf(__low2float(h2), o0, __high2float(h2) * o1);
-#pragma unroll
-            for (int sh = 16; sh > 0; sh >>= 1) part += __shfl_xor_sync(0xffffffffu, part, sh);
-            if (lane == 0) score_shift[2 * r + (dp >> 5)] = part;
-          }
-        }
-        named_bar_sync(1, C::kConsumerThreads);
+        const uint32_t *qfrag = reinterpret_cast<const uint32_t *>(smem + C::kOffQFrag + qs * C::kQFragBytes);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -323,91 +398,103 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           }
       }
     }
+    // (int8 KV: the partial score offsets of the lse correction stay in the Q slot until the merge below,
+    //  so the slot is handed back after the merge in that case)
+    const bool hold_q = KV8 && p.lse != nullptr;
     __syncwarp();
-    if (lane == 0) mbar_arrive(&qempty[qs]);
+    if (!hold_q && lane == 0) mbar_arrive(&qempty[qs]);
 
     // running state of this lane's two q rows per row tile (rows 8nt + 2q4, + 1)
     // The row sums l come from the tensor cores too: a tile of ones in place of V^T gives
     // sum_tokens P (of exactly the rounded probabilities the output is built from) in ol[nt][0..1].
     float m_run[NT][2];
     float ol[NT][4];
-    float o[8][NT][4];  // O^T: [16-wide slice of head_dim][row tile]
+    float o[kKS][NT][4];  // O^T: [16-wide slice of head_dim][row tile]
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       m_run[nt][0] = m_run[nt][1] = kNeg;
       ol[nt][0] = ol[nt][1] = ol[nt][2] = ol[nt][3] = 0.f;
     }
 #pragma unroll
-    for (int mt = 0; mt < 8; ++mt)
+    for (int mt = 0; mt < kKS; ++mt)
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) o[mt][nt][0] = o[mt][nt][1] = o[mt][nt][2] = o[mt][nt][3] = 0.f;
 
     const int ntiles = (tok1 - tok0 + kTile - 1) / kTile;
     for (int ti = 0; ti < ntiles; ++ti) {
       const int nv = min(kTile, tok1 - tok0 - ti * kTile);
-      const bool active = t0 < nv;  // warp-uniform: any of this warp's 16 tokens valid
+      const bool active = t0 < nv;  // warp-uniform: any of this warp's tokens valid
       // ---------------- S^T = K Q^T ----------------
-      float s[NT][4];
+      float s[SUBS][NT][4];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+      for (int sb = 0; sb < SUBS; ++sb)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) s[sb][nt][0] = s[sb][nt][1] = s[sb][nt][2] = s[sb][nt][3] = 0.f;
       // additive mask of this lane's (token, row) pairs, fetched before the tile is waited for;
-      // same element order as s[nt][0..3]
-      float mk[NT][4];
+      // same element order as s[sb][nt][0..3]
+      float mk[SUBS][NT][4];
       if (MASK) {
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          mk[nt][0] = mk[nt][1] = mk[nt][2] = mk[nt][3] = 0.f;
-          if (active) {
-            const int tk = tok0 + ti * kTile + t0 + gid;
+        for (int sb = 0; sb < SUBS; ++sb)
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              const int r = 8 * nt + 2 * q4 + j;
-              if (r < nrows) {
-                const int64_t base = (int64_t)b * p.mask_batch_stride +
-                                     (int64_t)(kvh * p.group + row0 + r) * p.mask_head_stride;
-                if (t0 + gid < nv) mk[nt][j] = load_mask_elem(p.mask, p.mask_dtype, base + tk);
-                if (t0 + gid + 8 < nv) mk[nt][2 + j] = load_mask_elem(p.mask, p.mask_dtype, base + tk + 8);
+          for (int nt = 0; nt < NT; ++nt) {
+            mk[sb][nt][0] = mk[sb][nt][1] = mk[sb][nt][2] = mk[sb][nt][3] = 0.f;
+            if (active) {
+              const int tw = t0 + 16 * sb + gid;  // token inside the tile
+              const int tk = tok0 + ti * kTile + tw;
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const int r = 8 * nt + 2 * q4 + j;
+                if (r < nrows) {
+                  const int64_t base = (int64_t)b * p.mask_batch_stride +
+                                       (int64_t)(kvh * p.group + row0 + r) * p.mask_head_stride;
+                  if (tw < nv) mk[sb][nt][j] = load_mask_elem(p.mask, p.mask_dtype, base + tk);
+                  if (tw + 8 < nv) mk[sb][nt][2 + j] = load_mask_elem(p.mask, p.mask_dtype, base + tk + 8);
+                }
               }
             }
           }
-        }
       }
       if (!mbar_wait(&full[st], ph, kWaitLimit)) {
         report_status(p.status, p.epoch, kStatusTimeout);
         return;
       }
       if (active) {
-        const uint32_t kbase = stage0 + st * C::kStageBytes + row_m1;
-        if (!KV8) {
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t cc = (uint32_t)(2 * (ks & 3) + (mat >> 1));
-            const uint32_t addr = kbase + (uint32_t)(ks >> 2) * (kTile * 128) + ((cc ^ (uint32_t)mr) << 4);
-            uint32_t a0, a1, a2, a3;
-            ldmatrix_x4(addr, a0, a1, a2, a3);
+        for (int sb = 0; sb < SUBS; ++sb) {
+          if (SUBS > 1 && t0 + 16 * sb >= nv) break;  // warp-uniform
+          const uint32_t kbase = stage0 + st * C::kStageBytes + row_m1 + (uint32_t)sb * (16u * 128u);
+          if (!KV8) {
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) mma16816<MT>(s[nt], a0, a1, a2, a3, qb[ks][nt][0], qb[ks][nt][1]);
-          }
-        } else {
+            for (int ks = 0; ks < kKS; ++ks) {
+              const uint32_t cc = (uint32_t)(2 * (ks & 3) + (mat >> 1));
+              const uint32_t addr = kbase + (uint32_t)(ks >> 2) * (kTile * 128) + ((cc ^ (uint32_t)mr) << 4);
+              uint32_t a0, a1, a2, a3;
+              ldmatrix_x4(addr, a0, a1, a2, a3);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint32_t cc = (uint32_t)(2 * i + (mat >> 1));
-            uint32_t r0, r1, r2, r3;  // (tokens lo, 2i) (tokens hi, 2i) (lo, 2i+1) (hi, 2i+1)
-            ldmatrix_x4(kbase + ((cc ^ (uint32_t)mr) << 4), r0, r1, r2, r3);
-            r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
-            {
-              const uint32_t a0 = bytes_to_half2_biased(r0, 0x5140u), a1 = bytes_to_half2_biased(r1, 0x5140u);
-              const uint32_t a2 = bytes_to_half2_biased(r0, 0x5342u), a3 = bytes_to_half2_biased(r1, 0x5342u);
-#pragma unroll
-              for (int nt = 0; nt < NT; ++nt)
-                mma16816<MT>(s[nt], a0, a1, a2, a3, qb[2 * i][nt][0], qb[2 * i][nt][1]);
+              for (int nt = 0; nt < NT; ++nt) mma16816<MT>(s[sb][nt], a0, a1, a2, a3, qb[ks][nt][0], qb[ks][nt][1]);
             }
-            {
-              const uint32_t a0 = bytes_to_half2_biased(r2, 0x5140u), a1 = bytes_to_half2_biased(r3, 0x5140u);
-              const uint32_t a2 = bytes_to_half2_biased(r2, 0x5342u), a3 = bytes_to_half2_biased(r3, 0x5342u);
+          } else {
 #pragma unroll
-              for (int nt = 0; nt < NT; ++nt)
-                mma16816<MT>(s[nt], a0, a1, a2, a3, qb[2 * i + 1][nt][0], qb[2 * i + 1][nt][1]);
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t cc = (uint32_t)(2 * i + (mat >> 1));
+              uint32_t r0, r1, r2, r3;  // (tokens lo, 2i) (tokens hi, 2i) (lo, 2i+1) (hi, 2i+1)
+              ldmatrix_x4(kbase + ((cc ^ (uint32_t)mr) << 4), r0, r1, r2, r3);
+              r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+              {
+                const uint32_t a0 = bytes_to_half2_biased(r0, 0x5140u), a1 = bytes_to_half2_biased(r1, 0x5140u);
+                const uint32_t a2 = bytes_to_half2_biased(r0, 0x5342u), a3 = bytes_to_half2_biased(r1, 0x5342u);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                  mma16816<MT>(s[sb][nt], a0, a1, a2, a3, qb[2 * i][nt][0], qb[2 * i][nt][1]);
+              }
+              {
+                const uint32_t a0 = bytes_to_half2_biased(r2, 0x5140u), a1 = bytes_to_half2_biased(r3, 0x5140u);
+                const uint32_t a2 = bytes_to_half2_biased(r2, 0x5342u), a3 = bytes_to_half2_biased(r3, 0x5342u);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                  mma16816<MT>(s[sb][nt], a0, a1, a2, a3, qb[2 * i + 1][nt][0], qb[2 * i + 1][nt][1]);
+              }
             }
           }
         }
@@ -417,22 +504,30 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       if (++st == C::kStages) { st = 0; ph ^= 1; }
 
       // ---------------- online softmax ----------------
-      // s[nt]: [0] (token gid, row 2q4) [1] (token gid, row 2q4+1) [2] (token gid+8, row 2q4) [3] (gid+8, 2q4+1)
-      uint32_t pb[NT][2];
+      // s[sb][nt]: [0] (token gid, row 2q4) [1] (token gid, row 2q4+1) [2] (token gid+8, row 2q4) [3] (gid+8, 2q4+1)
+      uint32_t pb[SUBS][NT][2];
       if (active) {
         const float c = p.scale_log2e;
-        const bool dead_lo = t0 + gid >= nv, dead_hi = t0 + gid + 8 >= nv;  // past the end of the range
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          float x0 = s[nt][0] * c, x1 = s[nt][1] * c, x2 = s[nt][2] * c, x3 = s[nt][3] * c;
-          if (MASK) {
-            const float l2e = 1.4426950408889634f;
-            x0 = fmaf(mk[nt][0], l2e, x0); x1 = fmaf(mk[nt][1], l2e, x1);
-            x2 = fmaf(mk[nt][2], l2e, x2); x3 = fmaf(mk[nt][3], l2e, x3);
+          float x[SUBS][4];
+          float mx0 = kNeg, mx1 = kNeg;
+#pragma unroll
+          for (int sb = 0; sb < SUBS; ++sb) {
+            const int tw = t0 + 16 * sb + gid;
+            const bool dead_lo = tw >= nv, dead_hi = tw + 8 >= nv;  // past the end of the range
+            x[sb][0] = s[sb][nt][0] * c; x[sb][1] = s[sb][nt][1] * c;
+            x[sb][2] = s[sb][nt][2] * c; x[sb][3] = s[sb][nt][3] * c;
+            if (MASK) {
+              const float l2e = 1.4426950408889634f;
+              x[sb][0] = fmaf(mk[sb][nt][0], l2e, x[sb][0]); x[sb][1] = fmaf(mk[sb][nt][1], l2e, x[sb][1]);
+              x[sb][2] = fmaf(mk[sb][nt][2], l2e, x[sb][2]); x[sb][3] = fmaf(mk[sb][nt][3], l2e, x[sb][3]);
+            }
+            if (dead_lo) x[sb][0] = x[sb][1] = kNeg;
+            if (dead_hi) x[sb][2] = x[sb][3] = kNeg;
+            mx0 = fmaxf(mx0, fmaxf(x[sb][0], x[sb][2]));
+            mx1 = fmaxf(mx1, fmaxf(x[sb][1], x[sb][3]));
           }
-          if (dead_lo) x0 = x1 = kNeg;
-          if (dead_hi) x2 = x3 = kNeg;
-          float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
 #pragma unroll
           for (int sh = 4; sh <= 16; sh <<= 1) {
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
@@ -442,19 +537,22 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           const float al0 = fast_exp2(m_run[nt][0] - mn0), al1 = fast_exp2(m_run[nt][1] - mn1);
           m_run[nt][0] = mn0;
           m_run[nt][1] = mn1;
-          x0 = fast_exp2(x0 - mn0); x2 = fast_exp2(x2 - mn0);
-          x1 = fast_exp2(x1 - mn1); x3 = fast_exp2(x3 - mn1);
           if (al0 != 1.f || al1 != 1.f) {
             ol[nt][0] *= al0; ol[nt][1] *= al1;
 #pragma unroll
-            for (int mt = 0; mt < 8; ++mt) {
+            for (int mt = 0; mt < kKS; ++mt) {
               o[mt][nt][0] *= al0; o[mt][nt][2] *= al0;
               o[mt][nt][1] *= al1; o[mt][nt][3] *= al1;
             }
           }
-          // probabilities (token-major) -> P^T fragments: (tokens 2q4, 2q4+1 | +8; row gid)
-          pb[nt][0] = movmatrix_trans(pack2<MT>(x0, x1));
-          pb[nt][1] = movmatrix_trans(pack2<MT>(x2, x3));
+#pragma unroll
+          for (int sb = 0; sb < SUBS; ++sb) {
+            const float e0 = fast_exp2(x[sb][0] - mn0), e2 = fast_exp2(x[sb][2] - mn0);
+            const float e1 = fast_exp2(x[sb][1] - mn1), e3 = fast_exp2(x[sb][3] - mn1);
+            // probabilities (token-major) -> P^T fragments: (tokens 2q4, 2q4+1 | +8; row gid)
+            pb[sb][nt][0] = movmatrix_trans(pack2<MT>(e0, e1));
+            pb[sb][nt][1] = movmatrix_trans(pack2<MT>(e2, e3));
+          }
         }
       }
 
@@ -465,57 +563,63 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       }
       if (active) {
         uint8_t *vst = smem + st * C::kStageBytes;
-        if (nv < t0 + 16) {
+        if (nv < t0 + 16 * SUBS) {
           // rows past the end of the range may hold anything (also NaN): zero them so that
           // 0 * garbage cannot reach the accumulators
           constexpr int kChunks = C::kRowBytes / 16;
-          for (int idx = lane; idx < 16 * kChunks; idx += 32) {
+          for (int idx = lane; idx < 16 * SUBS * kChunks; idx += 32) {
             const int r = idx / kChunks, ch = idx - r * kChunks;
             if (t0 + r >= nv) {
-              uint8_t *dst = KV8 ? vst + (t0 + r) * 128 + ch * 16
-                                 : vst + (ch >> 3) * (kTile * 128) + (t0 + r) * 128 + (ch & 7) * 16;
+              uint8_t *dst = vst + (ch >> 3) * (kTile * 128) + (t0 + r) * 128 + (ch & 7) * 16;
               *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
             }
           }
           fence_proxy_async();
           __syncwarp();
         }
-        {
-          const uint32_t ones = std::is_same<MT, __half>::value ? 0x3C003C00u : 0x3F803F80u;  // 1.0 twice
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) mma16816<MT>(ol[nt], ones, ones, ones, ones, pb[nt][0], pb[nt][1]);
-        }
-        if (!KV8) {
-          const uint32_t vbase = stage0 + st * C::kStageBytes + row_m2;
+        for (int sb = 0; sb < SUBS; ++sb) {
+          if (SUBS > 1 && t0 + 16 * sb >= nv) break;  // warp-uniform
+          {
+            const uint32_t ones = std::is_same<MT, __half>::value ? 0x3C003C00u : 0x3F803F80u;  // 1.0 twice
 #pragma unroll
-          for (int mt = 0; mt < 8; ++mt) {
-            const uint32_t cc = (uint32_t)(2 * (mt & 3) + (mat & 1));
-            const uint32_t addr = vbase + (uint32_t)(mt >> 2) * (kTile * 128) + ((cc ^ (uint32_t)mr) << 4);
-            uint32_t a0, a1, a2, a3;  // (d lo, tok lo) (d hi, tok lo) (d lo, tok hi) (d hi, tok hi)
-            ldmatrix_x4_trans(addr, a0, a1, a2, a3);
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) mma16816<MT>(o[mt][nt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
+            for (int nt = 0; nt < NT; ++nt)
+              mma16816<MT>(ol[nt], ones, ones, ones, ones, pb[sb][nt][0], pb[sb][nt][1]);
           }
-        } else {
-          const uint32_t vbase = stage0 + st * C::kStageBytes + row_m1;
+          if (!KV8) {
+            const uint32_t vbase = stage0 + st * C::kStageBytes + row_m2 + (uint32_t)sb * (16u * 128u);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint32_t cc = (uint32_t)(2 * i + (mat >> 1));
-            uint32_t r0, r1, r2, r3;  // (tok lo, 2i) (tok hi, 2i) (tok lo, 2i+1) (tok hi, 2i+1)
-            ldmatrix_x4_trans(vbase + ((cc ^ (uint32_t)mr) << 4), r0, r1, r2, r3);
-            r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
-            // bytes 0,2: head-dim column 16c + 2 gid (tile rows 0..7); bytes 1,3: column + 1 (rows 8..15)
-            {
-              const uint32_t a0 = bytes_to_half2_biased(r0, 0x5240u), a1 = bytes_to_half2_biased(r0, 0x5341u);
-              const uint32_t a2 = bytes_to_half2_biased(r1, 0x5240u), a3 = bytes_to_half2_biased(r1, 0x5341u);
+            for (int mt = 0; mt < kKS; ++mt) {
+              const uint32_t cc = (uint32_t)(2 * (mt & 3) + (mat & 1));
+              const uint32_t addr = vbase + (uint32_t)(mt >> 2) * (kTile * 128) + ((cc ^ (uint32_t)mr) << 4);
+              uint32_t a0, a1, a2, a3;  // (d lo, tok lo) (d hi, tok lo) (d lo, tok hi) (d hi, tok hi)
+              ldmatrix_x4_trans(addr, a0, a1, a2, a3);
 #pragma unroll
-              for (int nt = 0; nt < NT; ++nt) mma16816<MT>(o[2 * i][nt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
+              for (int nt = 0; nt < NT; ++nt) mma16816<MT>(o[mt][nt], a0, a1, a2, a3, pb[sb][nt][0], pb[sb][nt][1]);
             }
-            {
-              const uint32_t a0 = bytes_to_half2_biased(r2, 0x5240u), a1 = bytes_to_half2_biased(r2, 0x5341u);
-              const uint32_t a2 = bytes_to_half2_biased(r3, 0x5240u), a3 = bytes_to_half2_biased(r3, 0x5341u);
+          } else {
+            const uint32_t vbase = stage0 + st * C::kStageBytes + row_m1 + (uint32_t)sb * (16u * 128u);
 #pragma unroll
-              for (int nt = 0; nt < NT; ++nt) mma16816<MT>(o[2 * i + 1][nt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t cc = (uint32_t)(2 * i + (mat >> 1));
+              uint32_t r0, r1, r2, r3;  // (tok lo, 2i) (tok hi, 2i) (tok lo, 2i+1) (tok hi, 2i+1)
+              ldmatrix_x4_trans(vbase + ((cc ^ (uint32_t)mr) << 4), r0, r1, r2, r3);
+              r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+              // bytes 0,2: head-dim column 16c + 2 gid (tile rows 0..7); bytes 1,3: column + 1 (rows 8..15)
+              {
+                const uint32_t a0 = bytes_to_half2_biased(r0, 0x5240u), a1 = bytes_to_half2_biased(r0, 0x5341u);
+                const uint32_t a2 = bytes_to_half2_biased(r1, 0x5240u), a3 = bytes_to_half2_biased(r1, 0x5341u);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                  mma16816<MT>(o[2 * i][nt], a0, a1, a2, a3, pb[sb][nt][0], pb[sb][nt][1]);
+              }
+              {
+                const uint32_t a0 = bytes_to_half2_biased(r2, 0x5240u), a1 = bytes_to_half2_biased(r2, 0x5341u);
+                const uint32_t a2 = bytes_to_half2_biased(r3, 0x5240u), a3 = bytes_to_half2_biased(r3, 0x5341u);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                  mma16816<MT>(o[2 * i + 1][nt], a0, a1, a2, a3, pb[sb][nt][0], pb[sb][nt][1]);
+              }
             }
           }
         }
@@ -535,9 +639,9 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         mlbuf[warp * 16 + r0] = make_float2(m_run[nt][0], ol[nt][0]);
         mlbuf[warp * 16 + r0 + 1] = make_float2(m_run[nt][1], ol[nt][1]);
       }
-      float *w0 = mbuf + (warp * C::kRows + r0) * kMergeStride, *w1 = w0 + kMergeStride;
+      float *w0 = mbuf + (warp * C::kRows + r0) * C::kMergeStride, *w1 = w0 + C::kMergeStride;
 #pragma unroll
-      for (int mt = 0; mt < 8; ++mt) {
+      for (int mt = 0; mt < kKS; ++mt) {
         // accumulator columns: 16-bit KV  d = 16mt + gid, + 8;  int8 KV  d = 16mt + 2 gid, + 1
         const int da = KV8 ? 16 * mt + 2 * gid : 16 * mt + gid;
         const int db = KV8 ? da + 1 : da + 8;
@@ -545,17 +649,11 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         w0[db] = o[mt][nt][2]; w1[db] = o[mt][nt][3];
       }
     }
-    if (pend && tid == 0) *merge_flag = (pend_old == (unsigned)(pend_ns - 1)) ? 1 : 0;
+    merge_round_pre();
     named_bar_sync(1, C::kConsumerThreads);
-    if (pend) {
-      if (*merge_flag) {
-        __threadfence();  // the other CTAs' partials were fenced before their counter bumps
-        for (int r = warp; r < pend_nrows; r += C::kWarps) merge_row_d128<T>(p, pend_b, pend_hq0 + r, pend_ns, pend_part0, lane);
-      }
-      pend = false;
-    }
-    for (int u = tid; u < C::kRows * 32; u += C::kConsumerThreads) {
-      const int row = u >> 5, c4 = (u & 31) * 4;  // four consecutive head-dim columns of one row
+    merge_round_post();
+    for (int u = tid; u < C::kRows * (D / 4); u += C::kConsumerThreads) {
+      const int row = u / (D / 4), c4 = (u - row * (D / 4)) * 4;  // four consecutive head-dim columns of one row
       if (row < nrows) {
         float2 ml[C::kWarps];
         float M = kNeg;
@@ -570,7 +668,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         for (int w2 = 0; w2 < C::kWarps; ++w2) {
           const float f = fast_exp2(ml[w2].x - M);
           L = fmaf(ml[w2].y, f, L);
-          const float4 v = *reinterpret_cast<const float4 *>(mbuf + (w2 * C::kRows + row) * kMergeStride + c4);
+          const float4 v = *reinterpret_cast<const float4 *>(mbuf + (w2 * C::kRows + row) * C::kMergeStride + c4);
           acc.x = fmaf(v.x, f, acc.x); acc.y = fmaf(v.y, f, acc.y);
           acc.z = fmaf(v.z, f, acc.z); acc.w = fmaf(v.w, f, acc.w);
         }
@@ -580,19 +678,20 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         }
         const int hq = kvh * p.group + row0 + row;
         if (p.lse != nullptr) {
-          if (KV8) {  // back to the scores of the true K values (see the Q conversion above)
-            const float *score_shift = reinterpret_cast<const float *>(smem + C::kOffQFrag + NT * 4 * 32 * 16);
+          if (KV8) {  // back to the scores of the true K values (see the Q preparation)
+            const float *score_shift =
+                reinterpret_cast<const float *>(smem + C::kOffQFrag + qs * C::kQFragBytes + NT * 4 * 32 * 16);
             M -= (score_shift[2 * row] + score_shift[2 * row + 1]) * p.scale_log2e;
           }
-          if (nsplit == 1 && (u & 31) == 0) p.lse[(int64_t)b * p.num_q_heads + hq] = (M + log2f(L)) * kLn2;
+          if (nsplit == 1 && c4 == 0) p.lse[(int64_t)b * p.num_q_heads + hq] = (M + log2f(L)) * kLn2;
         }
         if (nsplit == 1) {
           const float inv = 1.f / L;
           float r0 = acc.x * inv, r1 = acc.y * inv, r2 = acc.z * inv, r3 = acc.w * inv;
           if (KV8) {
-            const float4 vs = __ldg(reinterpret_cast<const float4 *>(p.v_descale + kvh * kD + c4));
+            const float4 vs = __ldg(reinterpret_cast<const float4 *>(p.v_descale + kvh * D + c4));
             if (p.v_offset != nullptr) {
-              const int4 vo = __ldg(reinterpret_cast<const int4 *>(p.v_offset + kvh * kD + c4));
+              const int4 vo = __ldg(reinterpret_cast<const int4 *>(p.v_offset + kvh * D + c4));
               r0 += (float)vo.x; r1 += (float)vo.y; r2 += (float)vo.z; r3 += (float)vo.w;
             }
             r0 *= vs.x; r1 *= vs.y; r2 *= vs.z; r3 *= vs.w;
@@ -600,34 +699,33 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           uint2 pk;
           pk.x = pack2<T>(r0, r1);
           pk.y = pack2<T>(r2, r3);
-          *reinterpret_cast<uint2 *>(static_cast<T *>(p.out) + ((int64_t)b * p.num_q_heads + hq) * kD + c4) = pk;
+          *reinterpret_cast<uint2 *>(static_cast<T *>(p.out) + ((int64_t)b * p.num_q_heads + hq) * D + c4) = pk;
         } else {
           const int64_t prow = (int64_t)part * p.num_q_heads + hq;
-          *reinterpret_cast<float4 *>(p.part_o + prow * kD + c4) = acc;
-          if ((u & 31) == 0) *reinterpret_cast<float2 *>(p.part_ml + prow * 2) = make_float2(M, L);
+          *reinterpret_cast<float4 *>(p.part_o + prow * D + c4) = acc;
+          if (c4 == 0) *reinterpret_cast<float2 *>(p.part_ml + prow * 2) = make_float2(M, L);
         }
       }
     }
-    const bool bump = nsplit > 1 && p.fused_merge != 0;
-    named_bar_sync(1, C::kConsumerThreads);  // merge buffers are reused by the next item
-    if (bump) {
+    if (hold_q) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&qempty[qs]);
+    }
+    if (nsplit > 1 && p.fused_merge != 0) {
       if (tid == 0) {
-        // the barrier ordered every thread's partial stores before this fence, the fence orders them
-        // (cumulatively) before the counter moves
-        __threadfence();
-        pend_old = atomicAdd(p.sync + kSyncHeaderWords + grp, 1u);
+        volatile int *g = pinfo + (n_stored & 3) * 8;
+        g[0] = b; g[1] = kvh * p.group + row0; g[2] = nrows; g[3] = nsplit; g[4] = part0; g[5] = grp;
       }
-      pend = true;
-      pend_b = b; pend_hq0 = kvh * p.group + row0; pend_nrows = nrows; pend_ns = nsplit; pend_part0 = part0;
+      ++n_stored;
+      has_stored = true;
     }
+    if (C::kMergeBufs == 1) named_bar_sync(1, C::kConsumerThreads);  // the merge buffer is reused by the next item
   }
-  if (pend) {  // the last item of this CTA: look at the answer now
-    if (tid == 0) *merge_flag = (pend_old == (unsigned)(pend_ns - 1)) ? 1 : 0;
+  // drain the merge pipeline: up to two more rounds
+  for (int round = 0; round < 2 && (has_stored || has_bumped); ++round) {
+    merge_round_pre();
     named_bar_sync(1, C::kConsumerThreads);
-    if (*merge_flag) {
-      __threadfence();
-      for (int r = warp; r < pend_nrows; r += C::kWarps) merge_row_d128<T>(p, pend_b, pend_hq0 + r, pend_ns, pend_part0, lane);
-    }
+    merge_round_post();
   }
 }
 
@@ -652,6 +750,7 @@ EncodeTiledFn get_encode_fn() {
 // View of one cache as [tokens = num_blocks * block_size][kv heads][head_dim]; a box is one head's
 // rows of one cache block (block_size tokens) and 128 bytes of the head dimension.
 int make_cache_tmap(CUtensorMap *tm, const void *cache, const MscoPaDesc &d) {
+  const int kD = d.head_dim;
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return fail(MSCO_ERR_CUDA, "paged_attention: cuTensorMapEncodeTiled is not available");
   const bool kv8 = d.kv_dtype == MSCO_DTYPE_I8;
@@ -671,12 +770,12 @@ int make_cache_tmap(CUtensorMap *tm, const void *cache, const MscoPaDesc &d) {
   return MSCO_OK;
 }
 
-template <typename T, bool KV8, int NT, bool MASK>
+template <typename T, int D, bool KV8, int NT, bool MASK, int SUBS>
 int launch_one(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, const CUtensorMap &tk,
                const CUtensorMap &tv, cudaStream_t stream, bool after_kernel) {
-  using C = Cfg<KV8, NT>;
+  using C = Cfg<D, KV8, NT, SUBS>;
   static_assert(C::kDynSmem <= 232448, "shared memory budget of one SM exceeded");
-  auto kfn = pa_tma_kernel<T, KV8, NT, MASK>;
+  auto kfn = pa_tma_kernel<T, D, KV8, NT, MASK, SUBS>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [&] {
@@ -700,10 +799,24 @@ int launch_one(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, c
 
 }  // namespace
 
+// Tokens per tile of the kernel variant that serves `d`: a tile holds whole cache blocks.
+static int tile_tokens(const MscoPaDesc &d) {
+  if (d.head_dim == 256) return 64;
+  if (d.kv_dtype == MSCO_DTYPE_I8 && d.num_q_heads / d.num_kv_heads <= 8) return 256;
+  return 128;
+}
+
 bool pa_tma_supported(const MscoPaDesc &d) {
   const int bs = d.block_size;
-  const bool bs_ok = bs == 16 || bs == 32 || bs == 64 || bs == 128;
-  return d.head_dim == kD && bs_ok && d.num_blocks * (int64_t)bs < (1ll << 31);
+  const bool bs_ok = (bs == 16 || bs == 32 || bs == 64 || bs == 128) && bs <= tile_tokens(d);
+  const bool kv8 = d.kv_dtype == MSCO_DTYPE_I8;
+  const bool d_ok = d.head_dim == 128 || (!kv8 && (d.head_dim == 64 || d.head_dim == 256));
+  return d_ok && bs_ok && d.num_blocks * (int64_t)bs < (1ll << 31);
+}
+
+int pa_tma_rows_per_item(const MscoPaDesc &d) {
+  const int g = d.num_q_heads / d.num_kv_heads;
+  return (g > 8 && d.head_dim != 256) ? 16 : 8;
 }
 
 int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream,
@@ -732,18 +845,28 @@ int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp
   const bool g16 = plan->rows_per_item == 16;
   const bool f16 = plan->desc.q_dtype == MSCO_DTYPE_F16;
   const bool masked = plan->desc.mask_type != 0;
-#define MSCO_GO(T, A, B)                                                   \
-  do {                                                                     \
-    if (masked) return launch_one<T, A, B, true>(plan, p, pp, tk, tv, stream, after_kernel); \
-    return launch_one<T, A, B, false>(plan, p, pp, tk, tv, stream, after_kernel);            \
+  const int hd = plan->desc.head_dim;
+  const bool subs2 = kv8 && !g16 && plan->int8_subs == 2;
+#define MSCO_GO(T, D, A, B, S)                                                                      \
+  do {                                                                                              \
+    if (masked) return launch_one<T, D, A, B, true, S>(plan, p, pp, tk, tv, stream, after_kernel);  \
+    return launch_one<T, D, A, B, false, S>(plan, p, pp, tk, tv, stream, after_kernel);             \
   } while (0)
-  if (f16) {
-    if (kv8) { if (g16) MSCO_GO(__half, true, 2); else MSCO_GO(__half, true, 1); }
-    else     { if (g16) MSCO_GO(__half, false, 2); else MSCO_GO(__half, false, 1); }
-  } else {
-    if (kv8) { if (g16) MSCO_GO(__nv_bfloat16, true, 2); else MSCO_GO(__nv_bfloat16, true, 1); }
-    else     { if (g16) MSCO_GO(__nv_bfloat16, false, 2); else MSCO_GO(__nv_bfloat16, false, 1); }
-  }
+#define MSCO_GO_T(T)                                                      \
+  do {                                                                    \
+    if (hd == 64) { if (g16) MSCO_GO(T, 64, false, 2, 1); else MSCO_GO(T, 64, false, 1, 1); } \
+    if (hd == 256) MSCO_GO(T, 256, false, 1, 1);                          \
+    if (kv8) {                                                            \
+      if (g16) MSCO_GO(T, 128, true, 2, 1);                               \
+      if (subs2) MSCO_GO(T, 128, true, 1, 2);                             \
+      MSCO_GO(T, 128, true, 1, 1);                                        \
+    }                                                                     \
+    if (g16) MSCO_GO(T, 128, false, 2, 1);                                \
+    MSCO_GO(T, 128, false, 1, 1);                                         \
+  } while (0)
+  if (f16) MSCO_GO_T(__half);
+  MSCO_GO_T(__nv_bfloat16);
+#undef MSCO_GO_T
 #undef MSCO_GO
 }
 

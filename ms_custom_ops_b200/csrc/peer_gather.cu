@@ -30,6 +30,7 @@ struct GatherArgs {
   uint32_t *flags[MSCO_MAX_PEERS];  // rank r's flag array (uint32[world]) as mapped into this process
   int64_t slice_bytes;
   int world, rank;
+  uint32_t wait_limit;
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
@@ -73,7 +74,7 @@ peer_gather_kernel(GatherArgs a, const uint4 *__restrict__ local, uint32_t step,
     st_release_sys(a.flags[r] + a.rank, step);  // "rank's slice of step `step` is in your buffer"
     const uint32_t *mine = a.flags[a.rank] + r; // peer r's announcement in my own flag array
     bool ok = false;
-    for (uint32_t it = 0; it < kPeerWaitLimit; ++it) {
+    for (uint32_t it = 0; it < a.wait_limit; ++it) {
       if ((int32_t)(ld_acquire_sys(mine) - step) >= 0) { ok = true; break; }
       __nanosleep(100);
     }
@@ -147,6 +148,7 @@ extern "C" int msco_peer_allgather(const MscoGatherDesc *desc, const void *local
   a.slice_bytes = desc->slice_bytes;
   a.world = desc->world;
   a.rank = desc->rank;
+  a.wait_limit = desc->wait_polls != 0 ? desc->wait_polls : kPeerWaitLimit;
   const int64_t n16 = desc->slice_bytes / 16;
   int blocks = (int)((n16 + kPushThreads - 1) / kPushThreads);
   blocks = blocks < 1 ? 1 : (blocks > kPushMaxBlocks ? kPushMaxBlocks : blocks);

@@ -4,18 +4,12 @@ No dataset is involved anywhere on this path: every input is drawn from a
 seeded generator with the shapes, sizes and value distributions of the
 benchmark configurations (C1..C5 below) or of the reference's system tests.
 
-Two families:
-
-* ``st_style_case``  -- inputs distributed like the reference's system tests
-  (tests/st/test_custom_paged_attention.py:104-340: uniform(-1, 1) query and
-  caches, int8 caches as clip(rint(u * 127 / 4)), i.i.d. random block tables,
-  integer de-quantisation scales in {-1, 0, 1} and offsets in [-20, 20)),
-  drawn in the same order from the same generators so that a given seed
-  reproduces the reference test's inputs.
-* ``decode_case`` / ``config_case`` -- the benchmark configurations: N(0, 1)
-  query / cache / new rows, block tables that are a shuffled assignment of a
-  block pool, one new token per sequence written by reshape_and_cache at the
-  last position, per-channel int8 scales uniform in [0.01, 0.05].
+``decode_case`` / ``config_spec`` -- the benchmark configurations: N(0, 1)
+query / cache / new rows, block tables that are a shuffled assignment of a
+block pool, one new token per sequence written by reshape_and_cache at the
+last position, per-channel int8 scales uniform in [0.01, 0.05].
+(The generator that reproduces the inputs of the reference's own system tests
+is test infrastructure and lives beside the golden fixtures, tests/golden/st_inputs.py.)
 
 Host arrays are numpy (bf16 as ``ml_dtypes.bfloat16``).  ``decode_case_device``
 builds the same kind of case directly in GPU memory for the full-size
@@ -24,7 +18,6 @@ benchmark configurations, where host generation would take minutes.
 from __future__ import annotations
 
 import math
-import random
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -38,100 +31,6 @@ NP_DTYPES = {"float16": np.float16, "bfloat16": bfloat16, "int8": np.int8}
 
 def _round_to(a32: np.ndarray, dtype: str) -> np.ndarray:
     return a32.astype(NP_DTYPES[dtype])
-
-
-# --------------------------------------------------------------------------
-# reference system-test style
-# --------------------------------------------------------------------------
-def st_style_case(seed, num_heads, kv_heads, head_size, block_size, num_blocks, context_lens,
-                  q_dtype="float16", kv_dtype=None, quant_type=0, has_quant_offset=False,
-                  mask_type=0, qk_scale=None, q_seq_lens=None):
-    """Inputs of one reference-style decode test (one query token per sequence; with `q_seq_lens`
-    several per sequence, the multi-token / speculative form with the SPEC mask, mask_type 3).
-
-    Draw order and distributions follow the reference generator
-    (tests/st/test_custom_paged_attention.py:87-92,176-190,196-246,280-299):
-    numpy ``default_rng(seed)`` for tensors, Python ``random`` (same seed) for
-    the block tables.  bf16 tensors are float32 draws rounded to bf16.
-    """
-    kv_dtype = kv_dtype or q_dtype
-    rng = np.random.default_rng(seed)
-    random.seed(seed)
-    batch = len(context_lens)
-    num_tokens = batch if q_seq_lens is None else int(sum(q_seq_lens))
-    q32 = rng.uniform(-1.0, 1.0, (num_tokens, num_heads, head_size))
-    if q_dtype == "float16":
-        query = q32.astype(np.float16)
-    else:
-        query = q32.astype(np.float32).astype(bfloat16)
-    shape = (num_blocks, block_size, kv_heads, head_size)
-    if kv_dtype == "int8":
-        kc = np.clip(np.rint(rng.uniform(-4.0, 4.0, shape).astype(np.float32) * 127.0 / 4.0), -127, 127).astype(np.int8)
-        vc = np.clip(np.rint(rng.uniform(-4.0, 4.0, shape).astype(np.float32) * 127.0 / 4.0), -127, 127).astype(np.int8)
-    elif kv_dtype == "float16":
-        kc = rng.uniform(-1.0, 1.0, shape).astype(np.float16)
-        vc = rng.uniform(-1.0, 1.0, shape).astype(np.float16)
-    else:  # the reference keeps bf16 caches as raw float32 draws; the operator sees them rounded
-        kc = rng.uniform(-1.0, 1.0, shape).astype(np.float32)
-        vc = rng.uniform(-1.0, 1.0, shape).astype(np.float32)
-    max_blocks = (max(context_lens) + block_size - 1) // block_size
-    tables = np.array([[random.randint(0, num_blocks - 1) for _ in range(max_blocks)] for _ in range(batch)],
-                      dtype=np.int32).reshape(batch, max_blocks)
-    mask = None
-    if mask_type == 1:  # NORM decode mask (:430-447)
-        mask = np.zeros((batch, 1, max(context_lens)), dtype=np.float32)
-        for i in range(1, batch):
-            mask[i, :, :i] = -10000.0
-    elif mask_type == 2:  # ALIBI (:465-507, slopes :340-368)
-        p2 = 2 ** int(np.floor(np.log2(num_heads)))
-        m0 = 2.0 ** (-8.0 / p2)
-        slopes = np.array([m0 ** i for i in range(1, p2 + 1)], dtype=np.float32)
-        if p2 < num_heads:
-            m1 = 2.0 ** (-4.0 / p2)
-            extra = np.array([m1 ** i for i in range(1, 1 + 2 * (num_heads - p2), 2)], dtype=np.float32)
-            slopes = np.concatenate([slopes, extra])
-        mask = np.zeros((batch, num_heads, 1, max(context_lens)), dtype=np.float32)
-        for i, kl in enumerate(context_lens):
-            if kl:
-                bias = (np.arange(kl, dtype=np.int32) - kl + 1).astype(np.float32)
-                mask[i, :, :, :kl] = slopes.reshape(-1, 1, 1) * bias.reshape(1, 1, -1)
-    elif mask_type == 3:  # SPEC (:509-524): causal inside the window of the last q_len context positions
-        ql_all = [1] * batch if q_seq_lens is None else list(q_seq_lens)
-        mask = np.zeros((num_tokens, max(context_lens)), dtype=np.float32)
-        pre = 0
-        for ql, kl in zip(ql_all, context_lens):
-            if ql and kl:
-                start = max(0, kl - ql)
-                mask[pre:pre + ql, start:kl] = np.triu(np.ones((ql, ql), dtype=np.float32), 1) * -10000.0
-            pre += ql
-    k_descale = v_descale = k_offset = v_offset = None
-    if quant_type == 1:
-        k_descale = rng.integers(-1, 2, size=(kv_heads * head_size,)).astype(np.float32)
-        v_descale = rng.integers(-1, 2, size=(kv_heads * head_size,)).astype(np.float32)
-        if has_quant_offset:
-            k_offset = rng.integers(-20, 20, size=(kv_heads * head_size,)).astype(np.int32)
-            v_offset = rng.integers(-20, 20, size=(kv_heads * head_size,)).astype(np.int32)
-    return {
-        "query": query, "key_cache": kc, "value_cache": vc, "block_tables": tables,
-        "context_lens": np.array(context_lens, dtype=np.int32), "mask": mask, "mask_type": mask_type,
-        "q_seq_lens": None if q_seq_lens is None else np.array(q_seq_lens, dtype=np.int32),
-        "k_descale": k_descale, "v_descale": v_descale, "k_offset": k_offset, "v_offset": v_offset,
-        "q_dtype": q_dtype, "kv_dtype": kv_dtype, "quant_type": quant_type,
-        "has_quant_offset": has_quant_offset,
-        "qk_scale": (1.0 / math.sqrt(head_size)) if qk_scale is None else qk_scale,
-        "num_heads": num_heads, "kv_heads": kv_heads, "head_size": head_size, "block_size": block_size,
-    }
-
-
-def operator_view(case):
-    """The tensors as the operator receives them (bf16 caches rounded to bf16)."""
-    out = dict(case)
-    if case["kv_dtype"] == "bfloat16" and case["key_cache"].dtype == np.float32:
-        out["key_cache"] = case["key_cache"].astype(bfloat16)
-        out["value_cache"] = case["value_cache"].astype(bfloat16)
-    if case["mask"] is not None:
-        out["mask"] = case["mask"].astype(NP_DTYPES[case["q_dtype"]])
-    return out
 
 
 # --------------------------------------------------------------------------
@@ -205,6 +104,39 @@ def layout(spec: DecodeSpec, lens: np.ndarray, rng):
     slots = np.where(lens > 0, tables[np.arange(spec.batch), np.maximum(last, 0) // bs].astype(np.int64) * bs
                      + np.maximum(last, 0) % bs, -1).astype(np.int32)
     return nb, tables, slots
+
+
+def slots_of_last_token(tables, lens, block_size):
+    """slot_mapping of a decode step: the cache slot of every sequence's newest token (position
+    len - 1), -1 for an empty sequence."""
+    tables = np.asarray(tables)
+    lens = np.asarray(lens).astype(np.int64)
+    last = np.maximum(lens - 1, 0)
+    rows = np.arange(len(lens))
+    return np.where(lens > 0, tables[rows, last // block_size].astype(np.int64) * block_size + last % block_size,
+                    -1).astype(np.int32)
+
+
+def grow_tables(tables, lens, num_blocks, block_size, steps):
+    """Room for `steps` more tokens per sequence: a decode loop appends one token to every sequence
+    per step and needs a fresh cache block whenever a sequence crosses a block boundary.  The blocks
+    the sequences will need are taken from new ids appended to the pool ([num_blocks, num_blocks +
+    extra)) and entered into wider block tables up front -- a block allocator that reserves ahead; an
+    attention launch only ever reads the first ceil(len / block_size) columns of a row.
+    Returns (tables, num_blocks) after growth."""
+    tables = np.asarray(tables)
+    lens = np.asarray(lens).astype(np.int64)
+    now = (lens + block_size - 1) // block_size
+    later = (lens + steps + block_size - 1) // block_size
+    width = max(int(later.max()) if len(lens) else 1, tables.shape[1])
+    out = np.zeros((tables.shape[0], width), dtype=np.int32)
+    out[:, :tables.shape[1]] = tables
+    nxt = int(num_blocks)
+    for b in range(len(lens)):
+        n = int(later[b] - now[b])
+        out[b, now[b]:now[b] + n] = np.arange(nxt, nxt + n, dtype=np.int32)
+        nxt += n
+    return out, nxt
 
 
 def quantize_per_channel(x32: np.ndarray, descale: np.ndarray) -> np.ndarray:
@@ -298,7 +230,7 @@ def algorithmic_bytes_scatter(slots, row_elems, in_bytes, cache_bytes, quant=Fal
 # --------------------------------------------------------------------------
 # full-size cases generated directly in GPU memory
 # --------------------------------------------------------------------------
-def decode_case_device(spec: DecodeSpec, device="cuda", kv_head_range=None):
+def decode_case_device(spec: DecodeSpec, device="cuda", kv_head_range=None, growth_steps=0):
     """Same kind of case as `decode_case`, built on the GPU with torch's seeded generator.
 
     Lengths, block tables and slots come from the same numpy draws as the host
@@ -309,19 +241,23 @@ def decode_case_device(spec: DecodeSpec, device="cuda", kv_head_range=None):
     matching q heads): the shard one GPU owns when the cache is partitioned by
     kv head.  Each head's values depend on (seed, head) only, so a shard holds
     exactly the values the same heads have in the unsharded case.
+    `growth_steps` > 0 reserves cache blocks and block-table columns for that many further decode
+    steps (see grow_tables); "block_tables_host" is the host copy of the tables.
     """
     import torch
 
     rng = np.random.default_rng(spec.seed)
     lens = draw_lens(spec, rng)
     nb, tables, slots = layout(spec, lens, rng)
+    if growth_steps > 0:
+        tables, nb = grow_tables(tables, lens, nb, spec.block_size, growth_steps)
     tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[spec.dtype]
     h0, h1 = kv_head_range if kv_head_range is not None else (0, spec.kv_heads)
     nh = h1 - h0
     g = spec.num_heads // spec.kv_heads
     d = spec.head_size
     out = {"spec": spec, "context_lens": lens, "num_blocks": nb, "qk_scale": spec.qk_scale,
-           "kv_head_range": (h0, h1),
+           "kv_head_range": (h0, h1), "block_tables_host": tables,
            "block_tables": torch.from_numpy(tables).to(device),
            "slot_mapping": torch.from_numpy(slots).to(device),
            "k_descale": None, "v_descale": None}

@@ -72,15 +72,15 @@ MTP_CASES = {
 
 
 def mtp_case(name):
-    from ms_custom_ops_b200 import workloads
+    from tests.golden import st_inputs
     seed, h, kvh, hd, bs, nb, qlens, lens, dt, scale = MTP_CASES[name]
-    return workloads.st_style_case(seed, h, kvh, hd, bs, nb, lens, dt, None, 0, False, 3, scale, q_seq_lens=qlens)
+    return st_inputs.st_style_case(seed, h, kvh, hd, bs, nb, lens, dt, None, 0, False, 3, scale, q_seq_lens=qlens)
 
 
 def st_case(name, mask_free=False):
-    from ms_custom_ops_b200 import workloads
+    from tests.golden import st_inputs
     seed, h, kvh, hd, bs, nb, lens, qd, kvd, quant, off, scale, mask = ST_CASES[name]
-    return workloads.st_style_case(seed, h, kvh, hd, bs, nb, lens, qd, kvd, quant, off, 0 if mask_free else mask,
+    return st_inputs.st_style_case(seed, h, kvh, hd, bs, nb, lens, qd, kvd, quant, off, 0 if mask_free else mask,
                                    scale)
 
 

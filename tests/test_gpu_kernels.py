@@ -13,7 +13,7 @@ import torch
 
 from ms_custom_ops_b200 import _abi, kernels, workloads
 from oracle import paged_kv_numpy as oracle
-from tests.golden import cases
+from tests.golden import cases, st_inputs
 from tests.helpers import BF16, assert_close, to_dev, to_np, tol_for
 
 pytestmark = pytest.mark.gpu
@@ -132,7 +132,7 @@ def test_rac_quant_bit_exact(dtype, offsets):
 # paged attention
 # ----------------------------------------------------------------------------
 def _run_pa(case, kernel=_abi.KERNEL_AUTO):
-    v = workloads.operator_view(case)
+    v = st_inputs.operator_view(case)
     out, info = kernels.paged_attention_raw(
         to_dev(v["query"]), to_dev(v["key_cache"]), to_dev(v["value_cache"]), to_dev(v["block_tables"]),
         [int(x) for x in v["context_lens"]], v["qk_scale"], v["quant_type"],
@@ -158,7 +158,7 @@ def _check(case, out, what):
     assert ok, (what, detail)
     # (2) the decode path's tolerance against the float32 golden of the tensors the operator
     #     actually received (bf16 caches and masks rounded to bf16)
-    g = _golden(workloads.operator_view(case))
+    g = _golden(st_inputs.operator_view(case))
     assert_close(out, g, tol_for(case["q_dtype"], quant), what)
     rel_max, rel_l2 = oracle.scale_free_error(out, g)
     assert rel_l2 < 1e-2, (what, rel_max, rel_l2)
@@ -350,7 +350,7 @@ def test_fused_decode_step_equals_separate_calls(n, scale):
 
 def test_pa_out_of_range_block_id_is_reported_not_faulted():
     case = _st_case("gqa_32to8_alibi", mask_free=True)
-    v = workloads.operator_view(case)
+    v = st_inputs.operator_view(case)
     tables = v["block_tables"].copy()
     tables[2, 0] = 10 ** 6
     for kernel in (_abi.KERNEL_GENERIC, _abi.KERNEL_TMA):
@@ -358,3 +358,173 @@ def test_pa_out_of_range_block_id_is_reported_not_faulted():
             kernels.paged_attention_raw(to_dev(v["query"]), to_dev(v["key_cache"]), to_dev(v["value_cache"]),
                                         to_dev(tables), list(v["context_lens"]), v["qk_scale"], kernel=kernel)
         assert e.value.code == _abi.ERR_OOB
+
+
+# ----------------------------------------------------------------------------
+# the benchmark configurations at FULL size (caches generated on the device, the C / OpenMP
+# restatement of the reference golden as the checker)
+# ----------------------------------------------------------------------------
+def _host_case(c, lens, slots):
+    kd, vd = c["k_descale"], c["v_descale"]
+    return {"query": to_np(c["query"]), "key": to_np(c["key"]), "value": to_np(c["value"]),
+            "key_cache": to_np(c["key_cache"]), "value_cache": to_np(c["value_cache"]),
+            "block_tables": c["block_tables_host"], "slot_mapping": slots, "context_lens": lens,
+            "k_descale": None if kd is None else kd.cpu().numpy(), "v_descale": None if vd is None else vd.cpu().numpy()}
+
+
+@pytest.mark.parametrize("n", [2, 3, 4, 5])
+def test_pa_benchmark_configs_full_size(n):
+    # C2 (bf16, batch 64), C3 (int8 KV, batch 128, 64 q heads), C4 (log-uniform lengths up to 131072
+    # tokens, 2048-token splits, batch 32) and C5's decode (batch 256): one real decode step through
+    # msco_decode_step on caches of the full size, every sequence checked against the C oracle
+    from oracle import c_oracle
+    spec = workloads.config_spec(n)
+    c = workloads.decode_case_device(spec, "cuda", growth_steps=2)
+    lens = np.asarray(c["context_lens"], dtype=np.int32)
+    if n == 4:
+        assert lens.max() > 65536, "the drawn lengths must reach the 2048-token split rule"
+    quant = 1 if spec.kv_int8 else 0
+    desc = kernels.make_pa_desc(c["query"], c["key_cache"], c["block_tables"], c["qk_scale"], quant)
+    plan = _abi.PaPlan(desc, [int(x) for x in lens])
+    info = plan.info()
+    assert info.kernel == 2 and info.partials > 0
+    ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device="cuda")
+    out = torch.empty_like(c["query"])
+    slots = workloads.slots_of_last_token(c["block_tables_host"], lens, spec.block_size)
+    kernels.decode_step(plan, c["key"], c["value"], c["key_cache"], c["value_cache"], to_dev(slots), c["query"],
+                        c["block_tables"], out, ws, c["k_descale"], None, c["v_descale"], None)
+    kernels.pa_status(plan, ws)
+    h = _host_case(c, lens, slots)  # the caches as the step left them: the scatter is idempotent
+    if quant:
+        gk, gv = c_oracle.reshape_and_cache_quant(h["key"], h["value"], h["key_cache"], h["value_cache"], slots,
+                                                  h["k_descale"], h["v_descale"], inplace=False)
+    else:
+        gk, gv = c_oracle.reshape_and_cache(h["key"], h["value"], h["key_cache"], h["value_cache"], slots, inplace=False)
+    # bit-exact scatter: the rows the step wrote are what the oracle writes
+    assert np.array_equal(gk.view(np.uint8), h["key_cache"].view(np.uint8))
+    assert np.array_equal(gv.view(np.uint8), h["value_cache"].view(np.uint8))
+    g = c_oracle.paged_attention(h["query"], gk, gv, h["block_tables"], lens, c["qk_scale"], h["k_descale"],
+                                 h["v_descale"])
+    o = to_np(out)
+    assert_close(o, g, tol_for(spec.dtype, spec.kv_int8), spec.name)
+    rel_max, rel_l2 = oracle.scale_free_error(o, g)
+    assert rel_l2 < 1e-2 and rel_max < 3e-2, (spec.name, rel_max, rel_l2)
+    plan.close()
+
+
+@pytest.mark.parametrize("quant", [False, True])
+def test_rac_prefill_config5_full_size_bit_exact(quant):
+    # 16384 tokens x (8 kv heads x 128) through an injective random slot map into 4096 blocks of 128
+    # with 5 % of the slots -1.  The oracle runs on a compact cache (one row per token); the device
+    # cache has the full 4096 x 128 slots: written rows must equal the oracle's bit for bit and no
+    # other byte may change.
+    tokens, blocks, bs, c = 16384, 4096, 128, 1024
+    rng = np.random.default_rng(5)
+    slots = rng.permutation(blocks * bs)[:tokens].astype(np.int32)
+    slots[rng.random(tokens) < 0.05] = -1
+    key = rng.standard_normal((tokens, c), dtype=np.float32).astype(BF16)
+    val = rng.standard_normal((tokens, c), dtype=np.float32).astype(BF16)
+    cdt = torch.int8 if quant else torch.bfloat16
+    fill = 7 if quant else 1.5
+    kc = torch.full((blocks, bs, 8, 128), fill, dtype=cdt, device="cuda")
+    vc = torch.full((blocks, bs, 8, 128), fill, dtype=cdt, device="cuda")
+    compact = np.where(slots >= 0, np.arange(tokens), -1).astype(np.int32)
+    if quant:
+        kd = rng.uniform(0.01, 0.05, c).astype(np.float32)
+        vd = rng.uniform(0.01, 0.05, c).astype(np.float32)
+        z = np.full((tokens, 1, 8, 128), fill, dtype=np.int8)
+        gk, gv = oracle.reshape_and_cache_quant_golden(key, val, z, z.copy(), compact, kd, vd)
+        kernels.rac_scatter_quant(to_dev(key), to_dev(val), kc, vc, to_dev(slots), to_dev(kd), to_dev(vd))
+    else:
+        z = np.full((tokens, 1, 8, 128), fill, dtype=np.float32).astype(BF16)
+        gk, gv = oracle.reshape_and_cache_golden(key, val, z, z.copy(), compact)
+        kernels.rac_scatter(to_dev(key), to_dev(val), kc, vc, to_dev(slots))
+    torch.cuda.synchronize()
+    valid = slots >= 0
+    idx = torch.from_numpy(slots[valid].astype(np.int64)).cuda()
+    for cache, g in ((kc, gk), (vc, gv)):
+        flat = cache.view(blocks * bs, c)
+        rows = to_np(flat[idx])
+        assert np.array_equal(rows.view(np.uint8), g.reshape(tokens, c)[valid].view(np.uint8))
+        untouched = torch.ones(blocks * bs, dtype=torch.bool, device="cuda")
+        untouched[idx] = False
+        assert bool((flat[untouched] == fill).all()), "a slot outside the map was written"
+
+
+def test_replanned_decode_steps_equal_freshly_planned_ones():
+    # a decode loop: lengths grow by one per step, the plan object is re-planned in place; every
+    # step's output must equal, bit for bit, the output of a freshly built plan
+    spec = workloads.config_spec(2, 0.12)
+    c = workloads.decode_case_device(spec, "cuda", growth_steps=140)
+    lens0 = np.asarray(c["context_lens"], dtype=np.int32)
+    desc = kernels.make_pa_desc(c["query"], c["key_cache"], c["block_tables"], c["qk_scale"], 0)
+    plan = _abi.PaPlan(desc, [int(x) for x in lens0])
+    ws = torch.empty(max(_abi.PaPlan(desc, [int(x) + 140 for x in lens0]).workspace_bytes, 256), dtype=torch.uint8,
+                     device="cuda")
+    a0 = _abi.plan_arena_stats()
+    for i in (1, 2, 3, 64, 129, 130):  # across a block boundary for every sequence
+        lens = lens0 + np.int32(i)
+        slots = to_dev(workloads.slots_of_last_token(c["block_tables_host"], lens, spec.block_size))
+        plan.replan(lens)
+        out = torch.empty_like(c["query"])
+        kernels.decode_step(plan, c["key"], c["value"], c["key_cache"], c["value_cache"], slots, c["query"],
+                            c["block_tables"], out, ws)
+        kernels.pa_status(plan, ws)
+        fresh, _ = kernels.paged_attention_raw(c["query"], c["key_cache"], c["value_cache"], c["block_tables"],
+                                               [int(x) for x in lens], c["qk_scale"])
+        assert np.array_equal(to_np(out).view(np.uint16), to_np(fresh).view(np.uint16)), f"step {i}"
+    a1 = _abi.plan_arena_stats()
+    assert a1["slabs"] == a0["slabs"], "re-planning must not add pinned slabs"
+    plan.close()
+
+
+@pytest.mark.parametrize("kv8", [False, True])
+def test_pa_batch_invariance_at_batch_256(kv8):
+    # the reference's property test (tests/st/test_custom_paged_attention_batch_invariant.py:231-317)
+    # at batch 256 with lengths around the split boundaries, GQA 32 / 8
+    base = [255, 256, 257, 511, 512, 513, 2048, 4096, 8192]
+    lens_all = (base * 29)[:256]
+    spec = workloads.DecodeSpec("binv256", 256, 32, dtype="bfloat16", kv_int8=kv8, seed=34, len_lo=1, len_hi=1)
+    rng = np.random.default_rng(6)
+    nb, tables, _ = workloads.layout(spec, np.array(lens_all, dtype=np.int32), rng)
+    spec.num_blocks = nb
+    spec.len_lo, spec.len_hi = 1, 1
+    c = workloads.decode_case_device(spec, "cuda")
+    q, kc, vc, kd, vd = c["query"], c["key_cache"], c["value_cache"], c["k_descale"], c["v_descale"]
+    dt = to_dev(tables)
+    full, info = kernels.paged_attention_raw(q, kc, vc, dt, lens_all, c["qk_scale"], int(kv8), kd, None, vd, None)
+    assert info.kernel == 2
+    full = to_np(full).view(np.uint16)
+    for i in (0, 1, 2, 3, 4, 5, 6, 7, 8, 100, 255):
+        one, _ = kernels.paged_attention_raw(q[i:i + 1].contiguous(), kc, vc, dt[i:i + 1].contiguous(),
+                                             [lens_all[i]], c["qk_scale"], int(kv8), kd, None, vd, None)
+        assert np.array_equal(to_np(one).view(np.uint16)[0], full[i]), f"request {i} (length {lens_all[i]}) changed"
+
+
+@pytest.mark.parametrize("hd,bs,hq,hkv,dtype", [(64, 128, 32, 8, "bfloat16"), (64, 16, 24, 2, "float16"),
+                                                (256, 64, 16, 4, "bfloat16"), (256, 16, 8, 8, "float16"),
+                                                (256, 32, 24, 2, "bfloat16")])
+def test_pa_head_dims_64_and_256_in_the_tma_kernel(hd, bs, hq, hkv, dtype):
+    # the reference's head-size sweeps (tests/st/test_custom_paged_attention.py:1826-1871, 2211-2286):
+    # head_dim 64 and 256 run in the TMA kernel too; both kernels against the oracle, several splits
+    lens = [1, 17, 500, 513, 1300, 2049, 0, 4100]
+    spec = workloads.DecodeSpec("hd", len(lens), hq, kv_heads=hkv, head_size=hd, block_size=bs, dtype=dtype, seed=hd + bs,
+                                len_lo=1, len_hi=1)
+    rng = np.random.default_rng(7)
+    nb, tables, _ = workloads.layout(spec, np.array(lens, dtype=np.int32), rng)
+    spec.num_blocks = nb
+    case = workloads.decode_case(spec)
+    q, kc, vc, dt = to_dev(case["query"]), to_dev(case["key_cache"]), to_dev(case["value_cache"]), to_dev(tables)
+    g = oracle.paged_attention_golden(case["query"], case["key_cache"], case["value_cache"], tables,
+                                      np.array(lens, dtype=np.int32), case["qk_scale"])
+    outs = {}
+    for kernel in (_abi.KERNEL_GENERIC, _abi.KERNEL_TMA, _abi.KERNEL_AUTO):
+        out, info = kernels.paged_attention_raw(q, kc, vc, dt, lens, case["qk_scale"], kernel=kernel)
+        assert info.kernel == (1 if kernel == _abi.KERNEL_GENERIC else 2)
+        o = to_np(out).astype(np.float32)
+        assert np.all(o[6] == 0)
+        assert_close(o, g, tol_for(dtype, False), f"head_dim {hd} kernel={kernel}")
+        rel_max, rel_l2 = oracle.scale_free_error(o, g)
+        assert rel_l2 < 1e-2, (kernel, rel_max, rel_l2)
+        outs[kernel] = to_np(out).view(np.uint16)
+    assert np.array_equal(outs[_abi.KERNEL_TMA], outs[_abi.KERNEL_AUTO])

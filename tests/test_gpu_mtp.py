@@ -9,7 +9,7 @@ import torch
 import ms_custom_ops_b200 as ops
 from ms_custom_ops_b200 import workloads
 from oracle import paged_kv_numpy as oracle
-from tests.golden import cases
+from tests.golden import cases, st_inputs
 from tests.helpers import assert_close, to_dev, to_np, tol_for
 
 pytestmark = pytest.mark.gpu
@@ -17,7 +17,7 @@ GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
 def _run(c, with_mask=True):
-    v = workloads.operator_view(c)
+    v = st_inputs.operator_view(c)
     kw = dict(q_head_num=c["num_heads"], kv_head_num=c["kv_heads"], qk_scale=c["qk_scale"], calc_type=1,
               q_seq_lens=torch.from_numpy(c["q_seq_lens"]))
     if with_mask:
@@ -46,7 +46,7 @@ def test_multi_token_queries_match_reference_golden(name):
 
 def test_multi_token_queries_without_mask_and_with_empty_sequences():
     # no mask: every token of a sequence sees the whole context; q_len 0 and context 0 are legal
-    c = workloads.st_style_case(77, 8, 2, 128, 16, 64, [40, 0, 130, 17], "bfloat16", None, 0, False, 0, None,
+    c = st_inputs.st_style_case(77, 8, 2, 128, 16, 64, [40, 0, 130, 17], "bfloat16", None, 0, False, 0, None,
                                 q_seq_lens=[3, 2, 0, 4])
     v, out = _run(c, with_mask=False)
     g = oracle.paged_attention_golden(v["query"], v["key_cache"], v["value_cache"], v["block_tables"],
@@ -55,7 +55,7 @@ def test_multi_token_queries_without_mask_and_with_empty_sequences():
     assert_close(out, g, 1e-2, "mask-free multi-token")
     assert not out[3:5].any()  # the sequence with an empty context
     # one token per sequence is plain decode
-    c1 = workloads.st_style_case(78, 8, 2, 128, 16, 64, [40, 9, 130], "float16", None, 0, False, 0, None,
+    c1 = st_inputs.st_style_case(78, 8, 2, 128, 16, 64, [40, 9, 130], "float16", None, 0, False, 0, None,
                                  q_seq_lens=[1, 1, 1])
     v1, out1 = _run(c1, with_mask=False)
     plain = ops.paged_attention(to_dev(v1["query"]), to_dev(v1["key_cache"]), to_dev(v1["value_cache"]),

@@ -9,7 +9,7 @@ import ms_custom_ops_b200 as ops
 from ms_custom_ops_b200 import workloads
 from oracle import c_oracle
 from oracle import paged_kv_numpy as oracle
-from tests.golden import cases
+from tests.golden import cases, st_inputs
 from tests.helpers import assert_close, to_dev, to_np, tol_for
 
 pytestmark = pytest.mark.gpu
@@ -61,7 +61,7 @@ def test_reshape_and_cache_key_only_keyword_form():
                                   "int8_kv_offset", "gqa_int8_bf16", "bf16_int8_head33", "head_256_block_16"])
 def test_paged_attention_operator_on_reference_cases(name):
     case = cases.st_case(name)
-    v = workloads.operator_view(case)
+    v = st_inputs.operator_view(case)
     out = ops.paged_attention(
         to_dev(v["query"]), to_dev(v["key_cache"]), to_dev(v["value_cache"]), to_dev(v["block_tables"]),
         v["context_lens"], to_dev(v["mask"]), None, to_dev(v["k_descale"]), to_dev(v["k_offset"]),

@@ -64,3 +64,39 @@ def test_peer_store_allgather_matches_nccl():
             p.kill()
         assert p.exitcode == 0, "a rank failed or timed out"
     assert dict(ret) == {0: True, 1: True}
+
+
+def test_bounded_wait_for_a_peer_runs_out_and_reports_timeout():
+    """One GPU stands in for rank 0 of a two-rank gather whose second rank never shows up: nobody
+    ever writes the second flag word.  The wait is bounded (shortened here through the descriptor),
+    so the kernel gives up, leaves MSCO_ERR_TIMEOUT in the status word and returns; the context
+    stays usable.  Nothing faults, nothing hangs."""
+    import ctypes as C
+
+    from ms_custom_ops_b200 import _abi
+    dev = torch.device("cuda", 0)
+    slice_bytes = 4096
+    gathered = [torch.zeros(2 * slice_bytes, dtype=torch.uint8, device=dev) for _ in range(2)]
+    flags = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in range(2)]
+    words = torch.zeros(2, dtype=torch.int32, device=dev)  # ticket, status
+    local = torch.arange(slice_bytes, dtype=torch.int32, device=dev).to(torch.uint8)
+    d = _abi.MscoGatherDesc()
+    d.world, d.rank, d.slice_bytes = 2, 0, slice_bytes
+    d.ticket, d.status = words.data_ptr(), words.data_ptr() + 4
+    d.wait_polls = 20000   # a few milliseconds
+    for r in range(2):
+        d.gathered[r], d.flags[r] = gathered[r].data_ptr(), flags[r].data_ptr()
+    _abi.check(_abi.lib().msco_peer_allgather(C.byref(d), C.c_void_p(local.data_ptr()), C.c_uint32(1),
+                                              C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    assert int(words[1].item()) == _abi.ERR_TIMEOUT
+    # the local push happened, the flag of this rank was published to both "ranks"
+    assert torch.equal(gathered[0][:slice_bytes], local) and torch.equal(gathered[1][:slice_bytes], local)
+    assert int(flags[0][0].item()) == 1 and int(flags[1][0].item()) == 1 and int(flags[0][1].item()) == 0
+    # the context is alive: the same launch with the missing flag provided completes cleanly
+    words.zero_()
+    flags[0][1] = 2
+    _abi.check(_abi.lib().msco_peer_allgather(C.byref(d), C.c_void_p(local.data_ptr()), C.c_uint32(2),
+                                              C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    assert int(words[1].item()) == 0

@@ -8,7 +8,7 @@ import torch
 import ms_custom_ops_b200 as ops
 from ms_custom_ops_b200 import _abi, kernels, sharding, workloads
 from oracle import paged_kv_numpy as oracle
-from tests.golden import cases
+from tests.golden import cases, st_inputs
 from tests.helpers import assert_close, to_dev, to_np, tol_for
 
 pytestmark = pytest.mark.gpu
@@ -26,7 +26,7 @@ def _golden_with_lse(v):
                                   "int8_kv_offset", "gqa_int8_bf16", "bf16_int8_gqa_24to2", "bf16_int8_len1025",
                                   "large_seqlen_bf16"])
 def test_lse_output_matches_oracle(name, kernel):
-    v = workloads.operator_view(cases.st_case(name))
+    v = st_inputs.operator_view(cases.st_case(name))
     q = to_dev(v["query"])
     lse = torch.full(q.shape[:2], 12345.0, dtype=torch.float32, device="cuda")
     try:

@@ -284,13 +284,18 @@ def test_kernel_selection_and_workspace():
     assert _plan([100], hq=128, hkv=8).info().rows_per_item == 16
     wide = _plan([100], hq=24 * 8, hkv=8).info()      # 24 q rows per kv head -> two 16-row items
     assert wide.rows_per_item == 16 and wide.work_items == 16
-    assert _plan([100], d=64).info().kernel == 1       # head_dim 64 -> general kernel
+    assert _plan([100], d=64).info().kernel == 2       # head_dim 64 / 128 / 256 (16-bit cache): TMA kernel
+    assert _plan([100], d=256, bs=64).info().kernel == 2
+    assert _plan([100], d=256, bs=64, hq=128).info().rows_per_item == 8   # head_dim 256: 8 q rows per item
+    assert _plan([100], d=256, bs=128).info().kernel == 1   # a tile of the head_dim 256 variant holds 64 tokens
+    assert _plan([100], d=32).info().kernel == 1       # every other head_dim -> general kernel
+    assert _plan([100], d=64, kv="int8").info().kernel == 1   # int8 cache: head_dim 128 only
     assert _plan([100], bs=48).info().kernel == 1
     assert _plan([100], mask=1).info().kernel == 2      # additive masks run in the TMA kernel too
-    assert _plan([100], d=64, mask=2).info().kernel == 1
+    assert _plan([100], d=64, mask=2).info().kernel == 2
     assert _plan([100], kv="int8").info().kernel == 2
     with pytest.raises(_abi.MscoError):
-        _plan([100], d=64, kernel=2)
+        _plan([100], d=32, kernel=2)
     p = _plan([1000, 3000])
     parts = 2 + 6
     assert p.workspace_bytes >= parts * 32 * (128 + 2) * 4

@@ -16,7 +16,8 @@ import pytest
 import torch
 
 from ms_custom_ops_b200 import _abi, kernels, workloads
-from tests.helpers import to_dev, to_np
+from oracle import paged_kv_numpy as oracle
+from tests.helpers import assert_close, to_dev, to_np
 
 pytestmark = pytest.mark.gpu
 
@@ -70,6 +71,10 @@ def test_static_scratch_launch_matches_workspace_launch_twice(n, scale):
         assert np.all(np.abs(a - b) <= tol + tol * np.abs(b))
         # same kernels, same plan, same split order: the two results are in fact identical
         assert np.array_equal(to_np(out).view(np.uint16), to_np(ref).view(np.uint16))
+        # and, directly, against the oracle of the reference's golden
+        g = oracle.paged_attention_golden(c["query"], c["key_cache"], c["value_cache"], c["block_tables"],
+                                          c["context_lens"], c["qk_scale"], c["k_descale"], c["v_descale"])
+        assert_close(a, g, tol, f"static-scratch launch, {spec.name}")
         results.append(a)
         plan.close()
     assert not np.array_equal(results[0], results[1])
