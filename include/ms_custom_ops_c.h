@@ -19,6 +19,9 @@
  *                    is_seq_lens_cumsum_type, has_seq_starts) -> (key_out, value_out)
  *       reference: ops/c_api/paged_cache_load/paged_cache_load_op.yaml:2-28,
  *                  pybind definition ops/c_api/paged_cache_load/paged_cache_load_pynative.cc:129-134
+ *   reshape_and_cache_npd(key, value, key_cache, value_cache, slot_mapping, actual_seq_qlen,
+ *                         actual_seq_kvlen, block_tbl, kv_cache_layout, key_value_layout) -> (out_key, out_value)
+ *       reference: ops/ascendc/ms_glue/reshape_and_cache_npd/reshape_and_cache_npd_op.yaml
  *   fa_update(lse, local_out, fa_update_type, sp) -> output
  *       reference: ops/c_api/fa_update/fa_update_op.yaml:2-16,
  *                  pybind definition ops/c_api/fa_update/fa_update_pynative.cc:85-88
@@ -79,6 +82,26 @@ int ms_custom_ops_reshape_and_cache_infer(const MsTensorDesc *key, const MsTenso
                                           const MsTensorDesc *slot_mapping, int64_t cache_mode, int64_t head_num,
                                           int32_t *out_dtype, int32_t *out_ndim,
                                           int64_t *out_shape /* [MS_MAX_DIMS] */);
+
+/* reshape_and_cache_npd (reference: ops/ascendc/ms_glue/reshape_and_cache_npd/reshape_and_cache_npd_op.yaml,
+ * argument meaning reshape_and_cache_npd.md:11-34): the cache write in either block layout,
+ * kv_cache_layout "BSND" (num_blocks, block_size, heads, head_dim) or "BNSD" (num_blocks, heads, block_size,
+ * head_dim), with the current key / value returned in the "TH" layout (tokens, heads * head_dim): out_key /
+ * out_value are caller-allocated with key's / value's shape and dtype and receive copies (NULL: no output).
+ * key_value_layout "NPD" (re-blocked outputs with the cached history, an input format of the Ascend attention
+ * kernels) fails with MSCO_ERR_UNSUPPORTED.  actual_seq_qlen / actual_seq_kvlen / block_tbl only serve
+ * that layout; they are type-checked when given and otherwise unused. */
+int ms_custom_ops_reshape_and_cache_npd_infer(
+    const MsTensorDesc *key, const MsTensorDesc *value, const MsTensorDesc *key_cache, const MsTensorDesc *value_cache,
+    const MsTensorDesc *slot_mapping, const MsTensorDesc *actual_seq_qlen, const MsTensorDesc *actual_seq_kvlen,
+    const MsTensorDesc *block_tbl, const char *kv_cache_layout, const char *key_value_layout, int32_t *out_key_dtype,
+    int32_t *out_value_dtype, int32_t *out_ndim, int64_t *out_key_shape /* [MS_MAX_DIMS] */,
+    int64_t *out_value_shape /* [MS_MAX_DIMS] */);
+int ms_custom_ops_reshape_and_cache_npd(
+    const MsTensorDesc *key, const MsTensorDesc *value, const MsTensorDesc *key_cache, const MsTensorDesc *value_cache,
+    const MsTensorDesc *slot_mapping, const MsTensorDesc *actual_seq_qlen, const MsTensorDesc *actual_seq_kvlen,
+    const MsTensorDesc *block_tbl, const char *kv_cache_layout, const char *key_value_layout,
+    const MsTensorDesc *out_key, const MsTensorDesc *out_value, void *stream);
 
 /* Extension (no reference counterpart): quantise fp16/bf16 rows to the int8
  * cache on the way in; inverse of paged_attention's quant_type = 1 formula. */

@@ -77,6 +77,22 @@ int msco_reshape_and_cache(const void *key, const void *value, void *key_cache, 
                            const int32_t *slot_mapping, int64_t num_tokens, int64_t k_row_bytes,
                            int64_t v_row_bytes, int64_t num_slots, int32_t *oob_count, void *stream);
 
+/* The same scatter into head-major cache blocks, [num_blocks, num_heads, block_size, head_dim] -- the
+ * "BNSD" cache layout of the reference's reshape_and_cache_npd (cache shapes
+ * ops/ascendc/ms_glue/reshape_and_cache_npd/reshape_and_cache_npd.md:24-25, addressing
+ * ops/ascendc/aclnn_src/reshape_and_cache_npd/op_kernel/reshape_and_cache_npd.cpp:167-173): head h of
+ * token i goes to key_cache + ((s / block_size * num_heads + h) * block_size + s % block_size) * k_head_bytes
+ * for s = slot_mapping[i] >= 0.  key [num_tokens, num_heads * k_head_bytes], value likewise (may be NULL
+ * together with value_cache). */
+int msco_reshape_and_cache_bnsd(const void *key, const void *value, void *key_cache, void *value_cache,
+                                const int32_t *slot_mapping, int64_t num_tokens, int32_t num_heads,
+                                int64_t k_head_bytes, int64_t v_head_bytes, int32_t block_size,
+                                int64_t num_slots, int32_t *oob_count, void *stream);
+
+/* Asynchronous device-to-device copy on `stream` (the pass-through outputs of reshape_and_cache_npd;
+ * lets the operator layer stay free of the CUDA runtime). */
+int msco_copy_device(void *dst, const void *src, size_t bytes, void *stream);
+
 /* ------------------------------------------------------------------------
  * Quantising variant (extension; the reference operator has no such mode).
  * Rows arrive in fp16/bf16 (in_dtype), the caches are int8, and per channel
@@ -171,7 +187,8 @@ typedef struct MscoPaDesc {
   int64_t mask_batch_stride;  /* elements between sequences in attn_mask                        */
   int64_t mask_head_stride;   /* elements between q heads (0 for NORM)                          */
   int32_t kernel;             /* 0 = auto, 1 = force the generic kernel, 2 = require the TMA kernel */
-  int32_t reserved;
+  int32_t cache_layout;       /* 0 = [num_blocks, block_size, kv_heads, head_dim] (the operator's input_layout 0,
+                                 "BSND"); 1 = [num_blocks, kv_heads, block_size, head_dim] (input_layout 1, "BNSD") */
 } MscoPaDesc;
 
 typedef struct MscoPaPlan MscoPaPlan;
@@ -219,6 +236,7 @@ void msco_paged_attention_plan_destroy(MscoPaPlan *plan);
 /* Launch.  Layouts (all contiguous):
  *   query        [batch, num_q_heads, head_dim]                      q_dtype
  *   key_cache    [num_blocks, block_size, num_kv_heads, head_dim]    kv_dtype
+ *                ([num_blocks, num_kv_heads, block_size, head_dim] when desc.cache_layout == 1)
  *   value_cache  same shape as key_cache
  *   block_tables [batch, max_blocks_per_seq] int32 (device)
  *   k_descale / v_descale [num_kv_heads * head_dim] float32, k_offset / v_offset int32

@@ -29,7 +29,8 @@ from ._abi import MscoError  # noqa: F401
 from ._host import (UnsupportedOnB200, plan_arena_stats, plan_cache_clear, plan_cache_stats,  # noqa: F401
                     registered_ops)
 
-__all__ = ["reshape_and_cache", "reshape_and_cache_infer", "reshape_and_cache_quant", "paged_attention",
+__all__ = ["reshape_and_cache", "reshape_and_cache_infer", "reshape_and_cache_npd", "reshape_and_cache_npd_infer",
+           "reshape_and_cache_quant", "paged_attention",
            "paged_attention_infer", "plan_arena_stats",
            "paged_cache_load", "paged_cache_load_infer", "fa_update", "fa_update_infer", "paged_attention_with_lse",
            "paged_attention_workspace_size", "paged_attention_check_status", "TensorSpec", "MscoError",
@@ -158,6 +159,45 @@ def reshape_and_cache_infer(key, value=None, key_cache=None, value_cache=None, s
     return tuple(shp[i] for i in range(nd.value)), _DT_NAMES[dt.value]
 
 
+def reshape_and_cache_npd(key, value, key_cache, value_cache, slot_mapping, actual_seq_qlen, actual_seq_kvlen,
+                          block_tbl, kv_cache_layout='BNSD', key_value_layout='NPD'):
+    """Cache write in either block layout; returns ``(out_key, out_value)``.
+
+    key / value   [tokens, heads * head_dim] (or [batch, seq, heads * head_dim]); fp16 / bf16 / int8
+    key_cache / value_cache  kv_cache_layout 'BNSD': [num_blocks, heads, block_size, head_dim] (head-major, the
+                  layout ``paged_attention(input_layout=1)`` reads); 'BSND': [num_blocks, block_size, heads, head_dim]
+    slot_mapping  int32 [tokens]; negative slots are skipped
+    key_value_layout  'TH': the outputs are the current key / value, (tokens, heads * head_dim).  The default
+                  'NPD' (outputs re-blocked per page together with the cached history, an input format of the
+                  Ascend attention kernels) raises UnsupportedOnB200; so does nothing else of the argument list.
+    actual_seq_qlen / actual_seq_kvlen / block_tbl only serve the 'NPD' outputs and may be None.
+    """
+    import torch
+    D = _Descs()
+    out_key, out_value = torch.empty_like(key), torch.empty_like(value)
+    rc = _host.lib().ms_custom_ops_reshape_and_cache_npd(
+        D(key), D(value), D(key_cache), D(value_cache), D(slot_mapping), D(actual_seq_qlen, host_ok=True),
+        D(actual_seq_kvlen, host_ok=True), D(block_tbl), str(kv_cache_layout).encode(), str(key_value_layout).encode(),
+        D(out_key), D(out_value), _stream())
+    if rc:
+        _host.check(rc)
+    return out_key, out_value
+
+
+def reshape_and_cache_npd_infer(key, value, key_cache, value_cache, slot_mapping, actual_seq_qlen=None,
+                                actual_seq_kvlen=None, block_tbl=None, kv_cache_layout='BNSD', key_value_layout='NPD'):
+    """Shapes and dtypes of (out_key, out_value) after the operator's checks; TensorSpec or real tensors."""
+    D = _Descs()
+    kd, vd, nd = C.c_int32(), C.c_int32(), C.c_int32()
+    ks, vs = (C.c_int64 * _host.MS_MAX_DIMS)(), (C.c_int64 * _host.MS_MAX_DIMS)()
+    _host.check(_host.lib().ms_custom_ops_reshape_and_cache_npd_infer(
+        D(key), D(value), D(key_cache), D(value_cache), D(slot_mapping), D(actual_seq_qlen, host_ok=True),
+        D(actual_seq_kvlen, host_ok=True), D(block_tbl), str(kv_cache_layout).encode(), str(key_value_layout).encode(),
+        C.byref(kd), C.byref(vd), C.byref(nd), ks, vs))
+    return ((tuple(ks[i] for i in range(nd.value)), _DT_NAMES[kd.value]),
+            (tuple(vs[i] for i in range(nd.value)), _DT_NAMES[vd.value]))
+
+
 def reshape_and_cache_quant(key, value, key_cache, value_cache, slot_mapping, k_descale, v_descale,
                             k_offset=None, v_offset=None):
     """Extension: quantise fp16 / bf16 rows to the int8 caches while scattering them.
@@ -233,7 +273,8 @@ def paged_attention(query, key_cache, value_cache, block_tables, context_lens, a
 
     query        [batch, q_head_num, head_dim] fp16 / bf16 (one token per sequence)
     key_cache / value_cache  [num_blocks, block_size, kv_heads, head_dim]; query's dtype, or int8
-                 with quant_type = 1
+                 with quant_type = 1.  With input_layout = 1 (BNSD) the caches are head-major,
+                 [num_blocks, kv_heads, block_size, head_dim], as reshape_and_cache_npd writes them
     block_tables int32 [batch, max_blocks]; context_lens int32 [batch] on the HOST
     attn_mask    additive: mask_type 1 (NORM) [batch, 1, max_ctx], 2 (ALIBI) [batch, heads, 1, max_ctx]
     k_descale / v_descale float32, k_offset / v_offset int32, [kv_heads * head_dim] (quant_type = 1):

@@ -23,7 +23,7 @@ class MscoPaDesc(C.Structure):
         ("num_blocks", C.c_int64), ("max_blocks_per_seq", C.c_int32), ("qk_scale", C.c_float),
         ("quant_type", C.c_int32), ("has_quant_offset", C.c_int32), ("mask_type", C.c_int32),
         ("mask_dtype", C.c_int32), ("mask_batch_stride", C.c_int64), ("mask_head_stride", C.c_int64),
-        ("kernel", C.c_int32), ("reserved", C.c_int32),
+        ("kernel", C.c_int32), ("cache_layout", C.c_int32),
     ]
 
 
@@ -62,7 +62,8 @@ EXPORTS = (
     "msco_paged_attention_status", "msco_paged_attention_profile_enable", "msco_paged_attention_profile_read",
     "msco_paged_attention_launch_static", "msco_paged_attention_status_static",
     "msco_ipc_export", "msco_ipc_import", "msco_ipc_release", "msco_peer_allgather", "msco_decode_step",
-    "msco_paged_attention_launch_lse", "msco_expand_rows_i32", "msco_paged_attention_replan", "msco_plan_arena_stats", "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update", "msco_fa_update_strided",
+    "msco_paged_attention_launch_lse", "msco_expand_rows_i32", "msco_paged_attention_replan", "msco_plan_arena_stats",
+    "msco_reshape_and_cache_bnsd", "msco_copy_device", "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update", "msco_fa_update_strided",
 )
 
 
@@ -83,6 +84,10 @@ def lib():
     L.msco_reshape_and_cache.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, vp]
     L.msco_reshape_and_cache_quant.restype = C.c_int
     L.msco_reshape_and_cache_quant.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32, vp, vp, vp, vp, i64, vp, vp]
+    L.msco_reshape_and_cache_bnsd.restype = C.c_int
+    L.msco_reshape_and_cache_bnsd.argtypes = [vp, vp, vp, vp, vp, i64, i32, i64, i64, i32, i64, vp, vp]
+    L.msco_copy_device.restype = C.c_int
+    L.msco_copy_device.argtypes = [vp, vp, sz, vp]
     L.msco_paged_cache_load_workspace_bytes.restype = sz
     L.msco_paged_cache_load_workspace_bytes.argtypes = [i32, i32]
     L.msco_paged_cache_load.restype = C.c_int

@@ -44,6 +44,7 @@ EXPORTS = (
     "ms_custom_ops_paged_cache_load", "ms_custom_ops_fa_update_infer", "ms_custom_ops_fa_update",
     "ms_custom_ops_paged_attention_with_lse", "ms_custom_ops_reshape_and_cache_infer",
     "ms_custom_ops_plan_cache_miss_stats", "ms_custom_ops_plan_arena_stats",
+    "ms_custom_ops_reshape_and_cache_npd_infer", "ms_custom_ops_reshape_and_cache_npd",
 )
 
 
@@ -70,6 +71,11 @@ def lib():
     L.ms_custom_ops_reshape_and_cache_infer.restype = C.c_int
     L.ms_custom_ops_reshape_and_cache_infer.argtypes = [_TP] * 5 + [i64, i64, C.POINTER(C.c_int32),
                                                         C.POINTER(C.c_int32), C.POINTER(i64)]
+    L.ms_custom_ops_reshape_and_cache_npd_infer.restype = C.c_int
+    L.ms_custom_ops_reshape_and_cache_npd_infer.argtypes = [_TP] * 8 + [C.c_char_p, C.c_char_p] + [
+        C.POINTER(C.c_int32)] * 3 + [C.POINTER(i64)] * 2
+    L.ms_custom_ops_reshape_and_cache_npd.restype = C.c_int
+    L.ms_custom_ops_reshape_and_cache_npd.argtypes = [_TP] * 8 + [C.c_char_p, C.c_char_p, _TP, _TP, vp]
     L.ms_custom_ops_plan_cache_miss_stats.restype = None
     L.ms_custom_ops_plan_cache_miss_stats.argtypes = [C.POINTER(i64)] * 2
     L.ms_custom_ops_plan_arena_stats.restype = None

@@ -47,6 +47,8 @@ extern "C" const char *msco_last_error(void) { return g_err; }
 extern "C" int32_t msco_paged_attention_split_tokens(int32_t context_len, int32_t kv_dtype) {
   if (context_len > 65536) return 2048;
   if (context_len > 16384) return 1024;
+  static const int tune8 = getenv("MSCO_TUNE_INT8_SPLIT") ? atoi(getenv("MSCO_TUNE_INT8_SPLIT")) : 0;  // TUNING ONLY
+  if (tune8 > 0 && kv_dtype == MSCO_DTYPE_I8) return tune8;
   return kv_dtype == MSCO_DTYPE_I8 ? 1024 : 512;
 }
 
@@ -69,6 +71,11 @@ static int validate_desc(const MscoPaDesc &d) {
     return fail(MSCO_ERR_INVALID_ARG, "paged_attention: head_dim must be in (0, 256], got %d", d.head_dim);
   if (d.block_size <= 0 || d.num_blocks <= 0 || d.max_blocks_per_seq < 0)
     return fail(MSCO_ERR_INVALID_ARG, "paged_attention: bad cache geometry");
+  if (d.cache_layout != 0 && d.cache_layout != 1)
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention: cache_layout must be 0 (block_size major) or 1 (head major)");
+  if (d.cache_layout == 1 && d.quant_type != 0)
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention: the head-major cache layout takes no quantised cache "
+                                      "(the reference requires quant_type 0 with input_layout 1)");
   if (d.mask_type < 0 || d.mask_type > 2)
     return fail(MSCO_ERR_UNSUPPORTED, "paged_attention: mask_type %d is not built (0, 1, 2 are)", d.mask_type);
   if (d.mask_type != 0 && d.mask_dtype != MSCO_DTYPE_F16 && d.mask_dtype != MSCO_DTYPE_BF16 &&
@@ -173,11 +180,13 @@ int fill_plan(MscoPaPlan *pl, const int32_t *host_context_lens, int32_t batch) {
   // the TMA kernel merges its split partials itself (the CTA that stores the last partial of a group
   // does it); the reduce kernel is then only needed to zero the rows of empty sequences
   pl->fused_merge = pl->kernel == kKernelTma;
+  if (const char *e = getenv("MSCO_TUNE_FUSED_MERGE")) pl->fused_merge = pl->fused_merge && atoi(e) != 0;  // TUNING ONLY
   pl->need_reduce = pl->fused_merge ? nseq < batch : (parts > 0 || nseq < batch);
   pl->grid = pl->kernel == kKernelTma ? (int)std::min<int64_t>(items, pl->num_sms) : (int)items;
   pl->num_groups = pl->fused_merge ? nseq * items_per_split : 0;
   pl->sync_offset = align_up(kPlanRegionOffset + pl->plan_bytes, 256);
-  pl->sync_bytes = pl->fused_merge ? align_up((size_t)(kSyncHeaderWords + pl->num_groups) * 4, 256) : 0;
+  // the TMA kernel always takes its work items by the ticket in the first scheduling word
+  pl->sync_bytes = pl->kernel == kKernelTma ? align_up((size_t)(kSyncHeaderWords + pl->num_groups) * 4, 256) : 0;
   pl->part_o_offset = pl->sync_offset + pl->sync_bytes;
   const size_t part_o_bytes = (size_t)parts * d.num_q_heads * d.head_dim * 4;
   pl->part_ml_offset = align_up(pl->part_o_offset + part_o_bytes, 256);
@@ -361,6 +370,7 @@ int pa_launch_impl(const MscoPaPlan *plan, const void *query, const void *key_ca
   p.block_size = d.block_size; p.group = d.num_q_heads / d.num_kv_heads;
   p.rows_per_item = plan->rows_per_item; p.max_blocks_per_seq = d.max_blocks_per_seq;
   p.mask_type = d.mask_type; p.mask_dtype = d.mask_dtype;
+  p.cache_layout = d.cache_layout;
   p.scale = d.qk_scale;
   p.scale_log2e = d.qk_scale * 1.4426950408889634f;
   p.epoch = g_epoch.fetch_add(2u);
@@ -500,6 +510,10 @@ extern "C" int msco_decode_step(const MscoPaPlan *plan, const void *key, const v
                           slot_mapping, num_tokens, row, row, d.q_dtype, k_descale,
                           d.has_quant_offset ? k_offset : nullptr, v_descale,
                           d.has_quant_offset ? v_offset : nullptr, slots, nullptr, st, clear, clear_words, &cleared);
+  } else if (d.cache_layout == 1) {
+    rc = msco_reshape_and_cache_bnsd(key, value, key_cache, value_cache, slot_mapping, num_tokens, d.num_kv_heads,
+                                     (int64_t)d.head_dim * 2, (int64_t)d.head_dim * 2, d.block_size, slots, nullptr,
+                                     stream);
   } else {
     rc = launch_rac(key, value, key_cache, value_cache, slot_mapping, num_tokens, row * 2, row * 2, slots, nullptr, st,
                     clear, clear_words, &cleared);

@@ -101,7 +101,9 @@ __global__ void __launch_bounds__(kGenThreads) pa_generic_kernel(PaParams p, con
         report_status(p.status, p.epoch, kStatusOob);
         valid = false;
       } else {
-        row_off = ((int64_t)blk * p.block_size + tok % p.block_size) * tok_stride + (int64_t)w.kvh * D;
+        row_off = p.cache_layout == 0
+                      ? ((int64_t)blk * p.block_size + tok % p.block_size) * tok_stride + (int64_t)w.kvh * D
+                      : (((int64_t)blk * p.num_kv_heads + w.kvh) * p.block_size + tok % p.block_size) * D;
       }
     }
     // scores of this lane's token against every q row

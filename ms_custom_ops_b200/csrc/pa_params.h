@@ -40,6 +40,7 @@ struct PaParams {
   int64_t mask_batch_stride, mask_head_stride;
   int num_q_heads, num_kv_heads, head_dim, block_size, group, rows_per_item, max_blocks_per_seq;
   int mask_type, mask_dtype;
+  int cache_layout;   // 0: [blocks, block_size, kv_heads, head_dim]; 1: [blocks, kv_heads, block_size, head_dim]
   float scale;        // qk_scale
   float scale_log2e;  // qk_scale * log2(e)
 };

@@ -55,7 +55,8 @@ template <int D, bool KV8, int NT, int SUBS> struct Cfg {
   static constexpr int kWarps = D == 256 ? 4 : ((KV8 && NT == 1 && SUBS == 1) ? 16 : 8);  // consumer warps
   static constexpr int kTile = kWarps * 16 * SUBS;          // tokens per tile
   static constexpr int kAux = KV8 ? 1 : 0;                  // helper warp that prepares Q (int8 KV)
-  static constexpr int kThreads = (kWarps + 1 + kAux) * 32;
+  // warps: consumers, the producer, the warp that counts stored partials, (int8 KV) the Q-preparation warp
+  static constexpr int kThreads = (kWarps + 2 + kAux) * 32;
   static constexpr int kConsumerThreads = kWarps * 32;
   static constexpr int kRowBytes = KV8 ? D : 2 * D;         // one token row of one head
   static constexpr int kBoxes = kRowBytes / 128;            // 128-byte TMA boxes per token row
@@ -74,10 +75,10 @@ template <int D, bool KV8, int NT, int SUBS> struct Cfg {
                                                                          // 2 partial score offsets per q row (lse)
   static constexpr int kOffMerge = kOffQFrag + 2 * kQFragBytes;
   static constexpr int kOffMl = kOffMerge + kMergeBufs * kMergeBytes;
-  static constexpr int kOffDesc = kOffMl + kMergeBufs * kMlBytes;   // 2 x kDescInts ints, 2 merge flags (+ pad),
+  static constexpr int kOffDesc = kOffMl + kMergeBufs * kMlBytes;   // 2 x kDescInts ints, 4 spare ints,
                                                                     // 4 x 8 ints: groups awaiting their merge
   static constexpr int kOffBar = kOffDesc + 2 * kDescInts * 4 + 16 + 4 * 8 * 4;  // mbarriers
-  static constexpr int kNumBars = 2 * kStages + 6;
+  static constexpr int kNumBars = 2 * kStages + 8;
   static constexpr int kOffItemBase = kOffBar + kNumBars * 8 + 16;  // copy of the plan's item_base[]
   static constexpr int kItemBaseCap = 1024;                          // sequences (+1) that fit
   static constexpr int kSmemBytes = kOffItemBase + kItemBaseCap * 4;
@@ -118,6 +119,10 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + C::kOffBar);
   uint64_t *full = bars, *empty = bars + C::kStages;
   uint64_t *qfull = bars + 2 * C::kStages, *qempty = qfull + 2, *qready = qfull + 4;
+  uint64_t *pstored = qfull + 6, *pdone = qfull + 7;
+  // [slot][b, first q head, rows, splits, first partial, counter index, last-arriver flag]: groups whose
+  // partial this CTA has stored and whose arrival counter has yet to be looked at
+  volatile int *pinfo = reinterpret_cast<volatile int *>(smem + C::kOffDesc) + 2 * kDescInts + 4;
   int *desc = reinterpret_cast<int *>(smem + C::kOffDesc);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,6 +139,8 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       mbar_init(&qempty[i], C::kWarps);
       mbar_init(&qready[i], 1);
     }
+    mbar_init(pstored, C::kWarps);
+    mbar_init(pdone, 1);
     fence_barrier_init();
   }
   __syncthreads();
@@ -225,12 +232,17 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
               const int id = __shfl_sync(0xffffffffu, my_id, jb + j);
               if (lane == 0) {
                 const CUtensorMap *tm = op == 0 ? &tm_k : &tm_v;
-                const int z = id * bs;
+                // block-size-major cache: view [tokens][kv heads][head_dim], box {128 B, 1 head, block_size
+                // tokens} at (x, head, first token of the block); head-major cache: view
+                // [blocks x kv heads][block_size][head_dim], box {128 B, block_size tokens, 1} at
+                // (x, 0, block x heads + head).  Either way the box lands as block_size rows of 128 bytes.
+                const int y = p.cache_layout == 0 ? w.kvh : 0;
+                const int z = p.cache_layout == 0 ? id * bs : id * p.num_kv_heads + w.kvh;
                 // one 128-byte box per 64 elements (16-bit) / 128 elements (int8) of the head dimension;
                 // x is a multiple of 64 elements = 128 bytes: TMA's 16-byte rule holds by construction
 #pragma unroll
                 for (int bx = 0; bx < C::kBoxes; ++bx)
-                  tma_load_3d(dst + bx * (kTile * 128) + j * bs * 128, tm, bx * (KV8 ? 128 : 64), w.kvh, z, &full[st]);
+                  tma_load_3d(dst + bx * (kTile * 128) + j * bs * 128, tm, bx * (KV8 ? 128 : 64), y, z, &full[st]);
               }
             }
             if (++st == C::kStages) { st = 0; ph ^= 1; }
@@ -242,7 +254,32 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     return;
   }
 
-  if (C::kAux && warp == C::kWarps + 1) {
+  if (warp == C::kWarps + 1) {
+    // ======================= arrival-counter warp =======================
+    // Split partials are merged by the CTA that stores the LAST partial of a (sequence, kv head,
+    // q-row block) group.  Finding that out takes a device-scope fence (the CTA's partial stores before
+    // the counter) and an atomic on the group's counter: about two microseconds of latency that this
+    // warp absorbs, so the consumer warps never wait for either.  The consumers announce a stored
+    // partial on `pstored`, this warp answers on `pdone` with the flag in the group's slot.
+    for (int k = 0;; ++k) {
+      if (!mbar_wait(pstored, (uint32_t)(k & 1), kWaitLimit)) {
+        report_status(p.status, p.epoch, kStatusTimeout);
+        return;
+      }
+      volatile int *g = pinfo + (k & 3) * 8;
+      if (g[0] < 0) return;  // the consumers are done
+      if (lane == 0) {
+        __threadfence();  // every consumer warp's partial stores (ordered before its arrival) precede the count
+        const unsigned old = atomicAdd(p.sync + kSyncHeaderWords + g[5], 1u);
+        __threadfence();  // ... and the other CTAs' partials precede whatever follows the answer
+        g[6] = (old == (unsigned)(g[3] - 1)) ? 1 : 0;
+        mbar_arrive(pdone);
+      }
+      __syncwarp();
+    }
+  }
+
+  if (C::kAux && warp == C::kWarps + 2) {
     // ======================= Q-preparation warp (int8 KV) =======================
     // k_descale is folded into Q, and inside each 16-wide group of the head dimension the
     // contraction index is permuted so that the four bytes a lane gets from ldmatrix
@@ -311,47 +348,20 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   const int tid = threadIdx.x;
 
   uint32_t st = 0, ph = 0;
-  // Merge of split partials, two steps behind.  When an item of a multi-split group has stored its
-  // partial ("stored"), one thread bumps the group's arrival counter at the next item's barrier
-  // (every thread's stores are ordered before it by then) -- "bumped"; the answer is looked at one
-  // item later still, so neither the fence nor the atomic's latency is ever waited for, and if this
-  // CTA was the last arriver all warps merge the group then.
-  volatile int *merge_flag = reinterpret_cast<volatile int *>(desc + 2 * kDescInts);
-  // [slot][b, first q head, rows, splits, first partial, counter index]: written by thread 0 when an item
-  // has stored its partial, read by everybody one and two barriers later
-  volatile int *pinfo = reinterpret_cast<volatile int *>(desc + 2 * kDescInts + 4);
-  int n_stored = 0;                              // multi-split items finished so far (uniform)
-  bool has_stored = false, has_bumped = false;   // uniform over the consumer threads
-  unsigned bumped_old = 0;                       // the counter's answer (thread 0 only)
-  int nround = 0;                                // rounds so far: the flag words alternate
-  // one round of that pipeline: `pre` before a barrier of the consumer threads, `post` after it
-  auto merge_round_pre = [&]() {
-    if (has_bumped && tid == 0) {
-      const int ns = pinfo[((n_stored - (has_stored ? 2 : 1)) & 3) * 8 + 3];
-      merge_flag[nround & 1] = (bumped_old == (unsigned)(ns - 1)) ? 1 : 0;
+  // Merge of split partials.  When an item of a multi-split group has stored its partial, the warps
+  // announce it to the arrival-counter warp; at the next item's barrier they pick up the answer and, if
+  // this CTA stored the group's last partial, all warps merge the group (in split order).
+  int n_stored = 0, n_checked = 0;  // groups announced / answers picked up (uniform)
+  auto merge_if_last = [&]() -> bool {  // run by all consumer threads, after a barrier
+    if (n_checked == n_stored) return true;
+    if (!mbar_wait(pdone, (uint32_t)(n_checked & 1), kWaitLimit)) return false;
+    const volatile int *g = pinfo + (n_checked & 3) * 8;
+    if (g[6]) {
+      const int gb = g[0], ghq0 = g[1], gnrows = g[2], gns = g[3], gpart0 = g[4];
+      for (int r = warp; r < gnrows; r += C::kWarps) merge_row<T, D>(p, gb, ghq0 + r, gns, gpart0, lane);
     }
-  };
-  auto merge_round_post = [&]() {
-    if (has_bumped) {
-      if (merge_flag[nround & 1]) {
-        const volatile int *g = pinfo + ((n_stored - (has_stored ? 2 : 1)) & 3) * 8;
-        const int gb = g[0], ghq0 = g[1], gnrows = g[2], gns = g[3], gpart0 = g[4];
-        __threadfence();  // the other CTAs' partials were fenced before their counter bumps
-        for (int r = warp; r < gnrows; r += C::kWarps) merge_row<T, D>(p, gb, ghq0 + r, gns, gpart0, lane);
-      }
-      has_bumped = false;
-    }
-    if (has_stored) {
-      if (tid == 0) {
-        // the barrier ordered every thread's partial stores before this fence, the fence orders them
-        // (cumulatively) before the counter moves
-        __threadfence();
-        bumped_old = atomicAdd(p.sync + kSyncHeaderWords + pinfo[((n_stored - 1) & 3) * 8 + 5], 1u);
-      }
-      has_bumped = true;
-      has_stored = false;
-    }
-    ++nround;
+    ++n_checked;
+    return true;
   };
 
   for (int qi = 0;; ++qi) {
@@ -649,9 +659,11 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         w0[db] = o[mt][nt][2]; w1[db] = o[mt][nt][3];
       }
     }
-    merge_round_pre();
     named_bar_sync(1, C::kConsumerThreads);
-    merge_round_post();
+    if (!merge_if_last()) {
+      report_status(p.status, p.epoch, kStatusTimeout);
+      return;
+    }
     for (int u = tid; u < C::kRows * (D / 4); u += C::kConsumerThreads) {
       const int row = u / (D / 4), c4 = (u - row * (D / 4)) * 4;  // four consecutive head-dim columns of one row
       if (row < nrows) {
@@ -716,17 +728,18 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         volatile int *g = pinfo + (n_stored & 3) * 8;
         g[0] = b; g[1] = kvh * p.group + row0; g[2] = nrows; g[3] = nsplit; g[4] = part0; g[5] = grp;
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pstored);  // release: this warp's partial stores are ordered before it
       ++n_stored;
-      has_stored = true;
     }
     if (C::kMergeBufs == 1) named_bar_sync(1, C::kConsumerThreads);  // the merge buffer is reused by the next item
   }
-  // drain the merge pipeline: up to two more rounds
-  for (int round = 0; round < 2 && (has_stored || has_bumped); ++round) {
-    merge_round_pre();
-    named_bar_sync(1, C::kConsumerThreads);
-    merge_round_post();
-  }
+  // the last group this CTA stored, then the arrival-counter warp is told to leave
+  const bool ok = merge_if_last();
+  if (tid == 0) pinfo[(n_stored & 3) * 8] = -1;
+  __syncwarp();
+  if (lane == 0) mbar_arrive(pstored);
+  if (!ok) report_status(p.status, p.epoch, kStatusTimeout);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -755,10 +768,14 @@ int make_cache_tmap(CUtensorMap *tm, const void *cache, const MscoPaDesc &d) {
   if (enc == nullptr) return fail(MSCO_ERR_CUDA, "paged_attention: cuTensorMapEncodeTiled is not available");
   const bool kv8 = d.kv_dtype == MSCO_DTYPE_I8;
   const int es = kv8 ? 1 : 2;
-  const cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)d.num_kv_heads,
-                              (cuuint64_t)d.num_blocks * (cuuint64_t)d.block_size};
-  const cuuint64_t strides[2] = {(cuuint64_t)kD * es, (cuuint64_t)d.num_kv_heads * kD * es};
-  const cuuint32_t box[3] = {(cuuint32_t)(kv8 ? 128 : 64), 1u, (cuuint32_t)d.block_size};
+  const bool head_major = d.cache_layout == 1;
+  const cuuint64_t dims[3] = {(cuuint64_t)kD, head_major ? (cuuint64_t)d.block_size : (cuuint64_t)d.num_kv_heads,
+                              head_major ? (cuuint64_t)d.num_blocks * (cuuint64_t)d.num_kv_heads
+                                         : (cuuint64_t)d.num_blocks * (cuuint64_t)d.block_size};
+  const cuuint64_t strides[2] = {(cuuint64_t)kD * es, head_major ? (cuuint64_t)d.block_size * kD * es
+                                                                 : (cuuint64_t)d.num_kv_heads * kD * es};
+  const cuuint32_t box[3] = {(cuuint32_t)(kv8 ? 128 : 64), head_major ? (cuuint32_t)d.block_size : 1u,
+                             head_major ? 1u : (cuuint32_t)d.block_size};
   const cuuint32_t estr[3] = {1u, 1u, 1u};
   const CUtensorMapDataType dt = kv8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                      : (d.kv_dtype == MSCO_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
@@ -811,7 +828,8 @@ bool pa_tma_supported(const MscoPaDesc &d) {
   const bool bs_ok = (bs == 16 || bs == 32 || bs == 64 || bs == 128) && bs <= tile_tokens(d);
   const bool kv8 = d.kv_dtype == MSCO_DTYPE_I8;
   const bool d_ok = d.head_dim == 128 || (!kv8 && (d.head_dim == 64 || d.head_dim == 256));
-  return d_ok && bs_ok && d.num_blocks * (int64_t)bs < (1ll << 31);
+  return d_ok && bs_ok && d.num_blocks * (int64_t)bs < (1ll << 31) &&
+         d.num_blocks * (int64_t)d.num_kv_heads < (1ll << 31);
 }
 
 int pa_tma_rows_per_item(const MscoPaDesc &d) {

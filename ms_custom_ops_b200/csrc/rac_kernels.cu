@@ -112,6 +112,53 @@ rac_scatter1_kernel(const uint8_t *__restrict__ key, const uint8_t *__restrict__
   for (int c = lane; c < v1; c += 32) value_cache[slot * v1 + c] = value[tok * v1 + c];
 }
 
+// ---- head-major cache blocks ("BNSD": [num_blocks, heads, block_size, head_dim]) --------------------
+// The layout of the reference's reshape_and_cache_npd (cache shapes
+// ops/ascendc/ms_glue/reshape_and_cache_npd/reshape_and_cache_npd.md:24-25; addressing
+// ops/ascendc/aclnn_src/reshape_and_cache_npd/op_kernel/reshape_and_cache_npd.cpp:167-173): the rows of
+// one head of one block are contiguous, so the token row is split by head and head h of slot s lands at
+// ((s / block_size * heads + h) * block_size + s % block_size) * head_bytes.  G = bytes per copy granule.
+template <typename G, int UNROLL>
+__global__ void __launch_bounds__(kRacThreads)
+rac_scatter_bnsd_kernel(const G *__restrict__ key, const G *__restrict__ value, G *__restrict__ key_cache,
+                        G *__restrict__ value_cache, const int32_t *__restrict__ slot_mapping, int64_t num_tokens,
+                        int heads, int kg, int vg, int block_size, int64_t num_slots, int32_t *oob_count) {
+  // kg / vg: granules per head row of K / V (vg == 0: key only)
+  const int lane = threadIdx.x & 31;
+  const int64_t nwarps = (int64_t)gridDim.x * kRacWarps;
+  const int ktot = heads * kg, total = heads * (kg + vg);
+  for (int64_t tok = (int64_t)blockIdx.x * kRacWarps + (threadIdx.x >> 5); tok < num_tokens; tok += nwarps) {
+    const int64_t slot = __ldg(slot_mapping + tok);
+    if (slot < 0) continue;  // padding token: nothing is written
+    if (slot >= num_slots) {
+      if (lane == 0 && oob_count != nullptr) atomicAdd(oob_count, 1);
+      continue;
+    }
+    const int64_t blk = slot / block_size, off = slot - blk * block_size;
+    const G *ks = key + tok * (int64_t)ktot;
+    const G *vs = value + tok * (int64_t)(heads * vg);
+    for (int c0 = lane; c0 < total; c0 += 32 * UNROLL) {
+      G r[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = c0 + 32 * u;
+        if (c < total) r[u] = (c < ktot) ? ks[c] : vs[c - ktot];
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = c0 + 32 * u;
+        if (c < total) {
+          const bool is_k = c < ktot;
+          const int cc = is_k ? c : c - ktot, per = is_k ? kg : vg;
+          const int h = cc / per, g = cc - h * per;
+          G *dst = (is_k ? key_cache : value_cache) + ((blk * heads + h) * block_size + off) * per + g;
+          *dst = r[u];
+        }
+      }
+    }
+  }
+}
+
 // ---- quantising scatter ------------------------------------------------------
 // q = saturate_int8(rint(float(x) / descale[c]) - offset[c]); IEEE division,
 // round-half-to-even, NaN -> 0: bit-identical to float32 numpy arithmetic.
@@ -245,7 +292,7 @@ __device__ __forceinline__ uint32_t pack_low_bytes(uint32_t w0, uint32_t w1, uin
 // is sized to what is resident at once, so the per-warp set-up (reciprocal scales, offsets) is paid
 // once and the loop runs at the rate of the conversion units.
 template <typename T, bool HAS_OFF>
-__global__ void __launch_bounds__(kRacThreads)
+__global__ void __launch_bounds__(kRacThreads, 2)
 rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ value,
                               int8_t *__restrict__ key_cache, int8_t *__restrict__ value_cache,
                               const int32_t *__restrict__ slot_mapping, int64_t num_tokens, int elems,
@@ -289,8 +336,10 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
   const T *src_base = is_v ? value : key;
   int8_t *dst_base = is_v ? value_cache : key_cache;
 
-  uint4 cur[4], nxt[4];
-  int64_t slot_cur = -1, slot_nxt = -1;
+  // three token rows per warp: one being converted, two in flight (a resident SM then keeps about
+  // 64 KB of loads outstanding, what the memory latency needs at full bandwidth)
+  uint4 cur[4], nxt[4], nx2[4];
+  int64_t slot_cur = -1, slot_nxt = -1, slot_nx2 = -1;
   auto fetch = [&](int64_t tok, int64_t &slot, uint4 (&raw)[4]) {
     slot = -1;
     if (tok < num_tokens) {
@@ -308,8 +357,9 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
     }
   };
   fetch(first, slot_cur, cur);
+  fetch(first + stride, slot_nxt, nxt);
   for (int64_t tok = first; tok < num_tokens; tok += stride) {
-    fetch(tok + stride, slot_nxt, nxt);
+    fetch(tok + 2 * stride, slot_nx2, nx2);
     if (slot_cur >= 0) {
       int8_t *dst = dst_base + slot_cur * elems + lane * 8;
 #pragma unroll
@@ -327,8 +377,12 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
       }
     }
     slot_cur = slot_nxt;
+    slot_nxt = slot_nx2;
 #pragma unroll
-    for (int it = 0; it < 4; ++it) cur[it] = nxt[it];
+    for (int it = 0; it < 4; ++it) {
+      cur[it] = nxt[it];
+      nxt[it] = nx2[it];
+    }
   }
 }
 
@@ -420,6 +474,54 @@ extern "C" int msco_reshape_and_cache_quant(const void *key, const void *value, 
   return launch_rac_quant(key, value, key_cache, value_cache, slot_mapping, num_tokens, k_row_elems, v_row_elems,
                           in_dtype, k_descale, k_offset, v_descale, v_offset, num_slots, oob_count,
                           static_cast<cudaStream_t>(stream), nullptr, 0, &cleared);
+}
+
+extern "C" int msco_copy_device(void *dst, const void *src, size_t bytes, void *stream) {
+  if (bytes == 0) return MSCO_OK;
+  if (dst == nullptr || src == nullptr) return fail(MSCO_ERR_INVALID_ARG, "copy_device: NULL argument");
+  MSCO_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+  return MSCO_OK;
+}
+
+extern "C" int msco_reshape_and_cache_bnsd(const void *key, const void *value, void *key_cache, void *value_cache,
+                                           const int32_t *slot_mapping, int64_t num_tokens, int32_t num_heads,
+                                           int64_t k_head_bytes, int64_t v_head_bytes, int32_t block_size,
+                                           int64_t num_slots, int32_t *oob_count, void *stream) {
+  if (num_tokens < 0 || num_heads < 0 || k_head_bytes < 0 || v_head_bytes < 0 || block_size < 0 || num_slots < 0)
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_bnsd: negative size");
+  if (num_tokens == 0 || num_heads == 0 || k_head_bytes == 0 || num_slots == 0) return MSCO_OK;
+  if (block_size == 0) return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_bnsd: block_size must be positive");
+  const bool has_v = (value != nullptr) || (value_cache != nullptr);
+  if (has_v && (value == nullptr || value_cache == nullptr))
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_bnsd: value and value_cache must be given together");
+  if (!has_v) v_head_bytes = 0;
+  if (key == nullptr || key_cache == nullptr || slot_mapping == nullptr)
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_bnsd: key, key_cache and slot_mapping must not be NULL");
+  if ((k_head_bytes + v_head_bytes) * num_heads > (int64_t)INT32_MAX)
+    return fail(MSCO_ERR_INVALID_ARG, "reshape_and_cache_bnsd: row too large");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t blocks64 = (num_tokens + kRacWarps - 1) / kRacWarps;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    sms = 148;
+  const dim3 grid((unsigned)std::min<int64_t>(blocks64, (int64_t)sms * 16)), block(kRacThreads);
+  const uintptr_t all = (uintptr_t)key | (uintptr_t)key_cache | (uintptr_t)value | (uintptr_t)value_cache;
+  if (k_head_bytes % 16 == 0 && v_head_bytes % 16 == 0 && (all & 15) == 0) {
+    rac_scatter_bnsd_kernel<uint4, 4><<<grid, block, 0, st>>>(
+        (const uint4 *)key, (const uint4 *)value, (uint4 *)key_cache, (uint4 *)value_cache, slot_mapping, num_tokens,
+        num_heads, (int)(k_head_bytes / 16), (int)(v_head_bytes / 16), block_size, num_slots, oob_count);
+  } else if (k_head_bytes % 2 == 0 && v_head_bytes % 2 == 0 && (all & 1) == 0) {
+    rac_scatter_bnsd_kernel<uint16_t, 4><<<grid, block, 0, st>>>(
+        (const uint16_t *)key, (const uint16_t *)value, (uint16_t *)key_cache, (uint16_t *)value_cache, slot_mapping,
+        num_tokens, num_heads, (int)(k_head_bytes / 2), (int)(v_head_bytes / 2), block_size, num_slots, oob_count);
+  } else {
+    rac_scatter_bnsd_kernel<uint8_t, 4><<<grid, block, 0, st>>>(
+        (const uint8_t *)key, (const uint8_t *)value, (uint8_t *)key_cache, (uint8_t *)value_cache, slot_mapping,
+        num_tokens, num_heads, (int)k_head_bytes, (int)v_head_bytes, block_size, num_slots, oob_count);
+  }
+  MSCO_CUDA_CHECK(cudaGetLastError());
+  return MSCO_OK;
 }
 
 int msco::launch_rac_quant(const void *key, const void *value, int8_t *key_cache, int8_t *value_cache,

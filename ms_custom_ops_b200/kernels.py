@@ -40,6 +40,17 @@ def rac_scatter(key, value, key_cache, value_cache, slot_mapping, oob_count=None
         _ptr(oob_count), _stream()))
 
 
+def rac_scatter_bnsd(key, value, key_cache, value_cache, slot_mapping, oob_count=None):
+    """msco_reshape_and_cache_bnsd on the current stream: caches are [num_blocks, heads, block_size, head_dim]."""
+    t = slot_mapping.numel()
+    nb, heads, bs, kd = key_cache.shape
+    vd = 0 if value_cache is None else value_cache.shape[3]
+    _abi.check(_abi.lib().msco_reshape_and_cache_bnsd(
+        _ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache), _ptr(slot_mapping), t, heads,
+        kd * key.element_size(), 0 if value is None else vd * value.element_size(), bs, nb * bs, _ptr(oob_count),
+        _stream()))
+
+
 def rac_scatter_quant(key, value, key_cache, value_cache, slot_mapping, k_descale, v_descale,
                       k_offset=None, v_offset=None, oob_count=None):
     """msco_reshape_and_cache_quant on the current stream (fp16/bf16 rows -> int8 cache)."""
@@ -85,14 +96,16 @@ def merge_partials_strided(lse, lse_stride, local_out, local_out_stride, out, sp
 
 
 def make_pa_desc(query, key_cache, block_tables, qk_scale, quant_type=0, has_quant_offset=False,
-                 mask=None, mask_type=0, kernel=_abi.KERNEL_AUTO) -> _abi.MscoPaDesc:
+                 mask=None, mask_type=0, kernel=_abi.KERNEL_AUTO, cache_layout=0) -> _abi.MscoPaDesc:
+    """`cache_layout` 0: caches [num_blocks, block_size, kv_heads, head_dim]; 1: [num_blocks, kv_heads, block_size, head_dim]."""
     d = _abi.MscoPaDesc()
     d.q_dtype = msco_dtype(query.dtype)
     d.kv_dtype = msco_dtype(key_cache.dtype)
     d.num_q_heads = query.shape[1]
-    d.num_kv_heads = key_cache.shape[2]
+    d.num_kv_heads = key_cache.shape[1 if cache_layout else 2]
     d.head_dim = query.shape[2]
-    d.block_size = key_cache.shape[1]
+    d.block_size = key_cache.shape[2 if cache_layout else 1]
+    d.cache_layout = int(cache_layout)
     d.num_blocks = key_cache.shape[0]
     d.max_blocks_per_seq = block_tables.shape[1]
     d.qk_scale = float(qk_scale)
@@ -141,11 +154,11 @@ def pa_status(plan: _abi.PaPlan, workspace) -> int:
 
 def paged_attention_raw(query, key_cache, value_cache, block_tables, context_lens, qk_scale, quant_type=0,
                         k_descale=None, k_offset=None, v_descale=None, v_offset=None, mask=None, mask_type=0,
-                        kernel=_abi.KERNEL_AUTO, check_status=True, lse=None):
+                        kernel=_abi.KERNEL_AUTO, check_status=True, lse=None, cache_layout=0):
     """Plan + launch + (optionally) status check in one call; returns (out, plan info).
     `lse`: optional float32 [batch, q_heads] tensor that receives the log-sum-exp of the scores."""
     desc = make_pa_desc(query, key_cache, block_tables, qk_scale, quant_type,
-                        k_offset is not None, mask, mask_type, kernel)
+                        k_offset is not None, mask, mask_type, kernel, cache_layout)
     plan = _abi.PaPlan(desc, [int(x) for x in context_lens])
     ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device=query.device)
     out = torch.empty_like(query)

@@ -194,9 +194,14 @@ void CheckShapes(const PaInputs &in) {
     MS_VALUE_ERROR << "For PagedAttention the rank of context len must be " << kPaContextLenRank << ", but got "
                    << in.context_lens.rank() << ".";
   if (nz) return;
-  const int64_t nbk = in.key_cache.dim(0), bsk = in.key_cache.dim(1), hk = in.key_cache.dim(2),
+  // input_layout 0 (BSND): caches are (num_blocks, block_size, kv_heads, head_size); input_layout 1 (BNSD):
+  // (num_blocks, kv_heads, block_size, head_size), the cache layout reshape_and_cache_npd writes
+  // (ops/ascendc/ms_glue/reshape_and_cache_npd/reshape_and_cache_npd.md:24-25)
+  const bool bnsd = a.input_layout == kLayoutBNSD;
+  const int bs_dim = bnsd ? 2 : 1, h_dim = bnsd ? 1 : 2;
+  const int64_t nbk = in.key_cache.dim(0), bsk = in.key_cache.dim(bs_dim), hk = in.key_cache.dim(h_dim),
                 dk = in.key_cache.dim(3);
-  const int64_t nbv = in.value_cache.dim(0), bsv = in.value_cache.dim(1), hv = in.value_cache.dim(2),
+  const int64_t nbv = in.value_cache.dim(0), bsv = in.value_cache.dim(bs_dim), hv = in.value_cache.dim(h_dim),
                 dv = in.value_cache.dim(3);
   if (a.mla_v_dim == 0) {
     if (nbk != nbv)
@@ -287,8 +292,6 @@ void CheckBuiltForB200(const PaInputs &in) {
     MS_UNSUPPORTED << "For PagedAttention, compress_type=" << a.compress_type << " is not built for B200.";
   if (a.scale_type != kScaleTor)
     MS_UNSUPPORTED << "For PagedAttention, scale_type=1 (LogN) is not built for B200.";
-  if (a.input_layout != kLayoutBSND)
-    MS_UNSUPPORTED << "For PagedAttention, input_layout=1 (BNSD) is not built for B200.";
   if (a.mla_v_dim != 0)
     MS_UNSUPPORTED << "For PagedAttention, mla_v_dim>0 (MLA mode) is not built for B200.";
   if (a.batch_run_status_enable)
@@ -350,7 +353,8 @@ Prepared Prepare(const PaInputs &in) {
     p.multi_token = true;
   }
   const int64_t hq = in.query.dim(1), d = in.query.dim(2);
-  const int64_t hkv = in.key_cache.dim(2);
+  const bool bnsd = a.input_layout == kLayoutBNSD;
+  const int64_t hkv = in.key_cache.dim(bnsd ? 1 : 2);
   if (hq != a.q_head_num)
     MS_VALUE_ERROR << "For PagedAttention the q_head_num (" << a.q_head_num << ") must equal query's head dimension ("
                    << hq << ").";
@@ -391,7 +395,8 @@ Prepared Prepare(const PaInputs &in) {
   ds.num_q_heads = static_cast<int32_t>(hq);
   ds.num_kv_heads = static_cast<int32_t>(hkv);
   ds.head_dim = static_cast<int32_t>(d);
-  ds.block_size = static_cast<int32_t>(in.key_cache.dim(1));
+  ds.block_size = static_cast<int32_t>(in.key_cache.dim(bnsd ? 2 : 1));
+  ds.cache_layout = bnsd ? 1 : 0;
   ds.num_blocks = in.key_cache.dim(0);
   ds.max_blocks_per_seq = static_cast<int32_t>(in.block_tables.dim(1));
   ds.qk_scale = static_cast<float>(a.qk_scale);

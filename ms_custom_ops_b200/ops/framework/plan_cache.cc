@@ -34,14 +34,14 @@ uint64_t HashBytes(const void *data, size_t len, uint64_t seed) {
 namespace {
 // field by field: the struct has padding bytes that must not enter a key
 struct DescFields {
-  int64_t f[16];
+  int64_t f[17];
   uint32_t scale_bits;
 };
 DescFields FieldsOf(const MscoPaDesc &desc) {
   DescFields d = {{desc.q_dtype, desc.kv_dtype, desc.num_q_heads, desc.num_kv_heads, desc.head_dim,
                    desc.block_size, desc.num_blocks, desc.max_blocks_per_seq, desc.quant_type,
                    desc.has_quant_offset, desc.mask_type, desc.mask_dtype, desc.mask_batch_stride,
-                   desc.mask_head_stride, desc.kernel, desc.reserved},
+                   desc.mask_head_stride, desc.kernel, desc.cache_layout, 0},
                   0};
   memcpy(&d.scale_bits, &desc.qk_scale, 4);
   return d;
@@ -55,7 +55,7 @@ uint64_t MakeDescHash(const MscoPaDesc &desc) {
 
 PlanKey MakePlanKey(const MscoPaDesc &desc, const std::vector<int32_t> &lens) {
   DescFields d = FieldsOf(desc);
-  d.f[15] = static_cast<int64_t>(lens.size());
+  d.f[16] = static_cast<int64_t>(lens.size());
   PlanKey k;
   k.h1 = HashBytes(d.f, sizeof(d.f), 0x243f6a8885a308d3ull ^ d.scale_bits);
   k.h2 = HashBytes(d.f, sizeof(d.f), 0x13198a2e03707344ull + d.scale_bits);

@@ -29,6 +29,34 @@ except Exception:  # pragma: no cover - ml_dtypes ships with the image
 # --------------------------------------------------------------------------
 # reshape_and_cache
 # --------------------------------------------------------------------------
+def reshape_and_cache_bnsd_golden(key, value, key_cache, value_cache, slot_mapping):
+    """The same scatter into head-major cache blocks [num_blocks, heads, block_size, head_dim].
+
+    Follows tests/st/test_custom_reshape_and_cache_npd.py:487-515 (`npd_cache_inference`):
+    ``cache[slot // block_size][h][slot % block_size] = row.reshape(heads, head_dim)[h]``; device twin
+    ops/ascendc/aclnn_src/reshape_and_cache_npd/op_kernel/reshape_and_cache_npd.cpp:167-173.  Negative slots
+    are skipped (:149-150 of the device twin).  Returns new arrays.
+    """
+    slot = np.asarray(slot_mapping).reshape(-1).astype(np.int64)
+    out = []
+    for rows, cache in ((key, key_cache), (value, value_cache)):
+        if rows is None or cache is None:
+            out.append(None)
+            continue
+        c = np.array(cache, copy=True)
+        bs = c.shape[2]
+        r = np.asarray(rows).reshape(-1, c.shape[1], c.shape[3])
+        for i in np.flatnonzero(slot >= 0):
+            c[slot[i] // bs, :, slot[i] % bs] = r[i]
+        out.append(c)
+    return out[0], out[1]
+
+
+def bnsd_to_bsnd(cache):
+    """[num_blocks, heads, block_size, head_dim] -> [num_blocks, block_size, heads, head_dim] (a copy)."""
+    return np.ascontiguousarray(np.transpose(np.asarray(cache), (0, 2, 1, 3)))
+
+
 def reshape_and_cache_golden(key, value, key_cache, value_cache, slot_mapping):
     """Scatter rows of `key`/`value` into copies of the paged caches.
 

@@ -104,6 +104,35 @@ def rac_case(name):
             "slot_mapping": rng.permutation(t).astype(np.int32)}
 
 
+# reshape_and_cache_npd cases, head-major ("BNSD") cache: (dtype, heads, head_dim, batch, seed); geometry of
+# tests/st/test_custom_reshape_and_cache_npd.py:51-58, 620-626 (16 tokens per sequence, pages of 16 slots)
+RACNPD_CASES = {
+    "fp16_h32_d128_b13": ("float16", 32, 128, 13, 201),
+    "bf16_h8_d256_b2": ("bfloat16", 8, 256, 2, 202),
+    "int8_h4_d32_b16": ("int8", 4, 32, 16, 203),
+    "fp16_h8_d128_b8_pad": ("float16", 8, 128, 8, 204),   # with -1 slots (padding tokens)
+}
+
+
+def racnpd_case(name):
+    import ml_dtypes
+    dtype, heads, hd, batch, seed = RACNPD_CASES[name]
+    rng = np.random.default_rng(seed)
+    seq = slot_size = 16
+    t, pages = batch * seq, batch
+    npdt = {"float16": np.float16, "bfloat16": ml_dtypes.bfloat16, "int8": np.int8}[dtype]
+
+    def rnd(shape):
+        if dtype == "int8":
+            return rng.integers(-128, 127, shape, dtype=np.int8)
+        return rng.random(shape, dtype=np.float32).astype(npdt)
+    slots = rng.permutation(pages * slot_size)[:t].astype(np.int32)
+    if name.endswith("_pad"):
+        slots[rng.random(t) < 0.2] = -1
+    return {"key": rnd((t, heads * hd)), "value": rnd((t, heads * hd)), "key_cache": rnd((pages, heads, slot_size, hd)),
+            "value_cache": rnd((pages, heads, slot_size, hd)), "slot_mapping": slots}
+
+
 # paged_cache_load cases: (key dtype, value dtype, cumulative lengths + seq_starts, seed,
 #   (num_blocks, block_size, heads, head_size_k, head_size_v, batch, max_len)).
 # "ref" geometry = tests/st/test_custom_paged_cache_load.py:268 ([128, 128, 16, 144, 128, 16, 1], lengths 1..1024)

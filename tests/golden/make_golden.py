@@ -22,6 +22,8 @@ Written files (tests/golden/):
   config1.npz         benchmark configuration 1: cache digests after the scatter + attention output
   pcl_<case>.npz      sha256 of the gathered K / V (and of the input caches)
   fa_<case>.npz       golden output of the partial-output merge
+  racnpd_<case>.npz   sha256 of the golden head-major caches of `npd_cache_inference`
+                      (tests/st/test_custom_reshape_and_cache_npd.py:487-515)
 """
 import math
 import os
@@ -90,6 +92,24 @@ def main(ref_root):
                             sha_in_key=np.array(cases.digest(c["key"])),
                             sha_in_key_cache=np.array(cases.digest(c["key_cache"])))
         print("rac", name)
+
+    # head-major ("BNSD") cache scatter: the golden of the reference's reshape_and_cache_npd test.  Its loop
+    # has no skip for negative slots (its inputs have none); for the padded case the reference golden is
+    # run on the valid tokens only, which is what the device code does (reshape_and_cache_npd.cpp:149-150).
+    import test_custom_reshape_and_cache_npd as tnpd
+    from oracle import paged_kv_numpy as restated_npd
+    for name in cases.RACNPD_CASES:
+        c = cases.racnpd_case(name)
+        valid = c["slot_mapping"] >= 0
+        gk, gv = tnpd.npd_cache_inference(c["key"][valid], c["value"][valid], c["key_cache"], c["value_cache"],
+                                          c["slot_mapping"][valid])
+        ok, ov = restated_npd.reshape_and_cache_bnsd_golden(c["key"], c["value"], c["key_cache"], c["value_cache"],
+                                                            c["slot_mapping"])
+        assert cases.digest(ok) == cases.digest(gk) and cases.digest(ov) == cases.digest(gv), name
+        np.savez_compressed(os.path.join(HERE, f"racnpd_{name}.npz"), sha_key_cache=np.array(cases.digest(gk)),
+                            sha_value_cache=np.array(cases.digest(gv)), sha_in_key=np.array(cases.digest(c["key"])),
+                            sha_in_key_cache=np.array(cases.digest(c["key_cache"])))
+        print("racnpd", name)
 
     import test_custom_paged_cache_load as tpcl
     import test_asd_faupdate as tfa

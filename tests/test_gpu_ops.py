@@ -142,3 +142,54 @@ def test_plan_cache_and_length_change_between_steps():
     g = oracle.paged_attention_golden(c["query"], c["key_cache"], c["value_cache"], c["block_tables"], lens,
                                       c["qk_scale"])
     assert_close(outs[2], g, 1e-2, "after length change")
+
+
+# ----------------------------------------------------------------------------
+# head-major ("BNSD") cache blocks: reshape_and_cache_npd writes them, paged_attention(input_layout=1) reads them
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("name", sorted(cases.RACNPD_CASES))
+def test_reshape_and_cache_npd_bit_exact(name):
+    c = cases.racnpd_case(name)
+    fx = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", f"racnpd_{name}.npz"))
+    kc, vc = to_dev(c["key_cache"]), to_dev(c["value_cache"])
+    ok, ov = ops.reshape_and_cache_npd(to_dev(c["key"]), to_dev(c["value"]), kc, vc, to_dev(c["slot_mapping"]), None,
+                                       None, None, kv_cache_layout="BNSD", key_value_layout="TH")
+    assert cases.digest(to_np(kc)) == str(fx["sha_key_cache"]) and cases.digest(to_np(vc)) == str(fx["sha_value_cache"])
+    assert np.array_equal(to_np(ok).view(np.uint8), c["key"].view(np.uint8))       # "TH" outputs: key / value
+    assert np.array_equal(to_np(ov).view(np.uint8), c["value"].view(np.uint8))
+    # the other block layout through the same operator equals reshape_and_cache
+    bk, bv = oracle.reshape_and_cache_golden(c["key"], c["value"], oracle.bnsd_to_bsnd(c["key_cache"]),
+                                             oracle.bnsd_to_bsnd(c["value_cache"]), c["slot_mapping"])
+    kc2, vc2 = to_dev(oracle.bnsd_to_bsnd(c["key_cache"])), to_dev(oracle.bnsd_to_bsnd(c["value_cache"]))
+    ops.reshape_and_cache_npd(to_dev(c["key"]), to_dev(c["value"]), kc2, vc2, to_dev(c["slot_mapping"]), None, None,
+                              None, kv_cache_layout="BSND", key_value_layout="TH")
+    assert np.array_equal(to_np(kc2).view(np.uint8), bk.view(np.uint8))
+    assert np.array_equal(to_np(vc2).view(np.uint8), bv.view(np.uint8))
+    with pytest.raises(ops.UnsupportedOnB200):
+        ops.reshape_and_cache_npd(to_dev(c["key"]), to_dev(c["value"]), kc, vc, to_dev(c["slot_mapping"]), None, None, None)
+
+
+@pytest.mark.parametrize("n,scale,hd,bs", [(2, 0.1, 128, 128), (1, 1.0, 128, 128), (4, 0.05, 128, 128),
+                                           (2, 0.1, 64, 32), (2, 0.05, 256, 64), (2, 0.05, 80, 16)])
+def test_decode_over_head_major_caches(n, scale, hd, bs):
+    # one decode step on head-major caches: reshape_and_cache_npd('BNSD') then paged_attention(input_layout=1);
+    # the output must equal, bit for bit, the step on the same data in the block-size-major layout
+    spec = workloads.config_spec(n, scale)
+    spec.head_size, spec.block_size = hd, bs
+    c = workloads.decode_case(spec)
+    kw = dict(q_head_num=spec.num_heads, kv_head_num=spec.kv_heads, qk_scale=c["qk_scale"])
+    q, key, val = to_dev(c["query"]), to_dev(c["key"]), to_dev(c["value"])
+    bt, slot = to_dev(c["block_tables"]), to_dev(c["slot_mapping"])
+    kc, vc = to_dev(c["key_cache"]), to_dev(c["value_cache"])
+    ops.reshape_and_cache(key, val, kc, vc, slot)
+    ref = ops.paged_attention(q, kc, vc, bt, c["context_lens"], **kw)
+    hk = to_dev(np.ascontiguousarray(np.transpose(c["key_cache"], (0, 2, 1, 3))))
+    hv = to_dev(np.ascontiguousarray(np.transpose(c["value_cache"], (0, 2, 1, 3))))
+    ops.reshape_and_cache_npd(key, val, hk, hv, slot, None, None, None, kv_cache_layout="BNSD", key_value_layout="TH")
+    out = ops.paged_attention(q, hk, hv, bt, c["context_lens"], input_layout=1, **kw)
+    ops.paged_attention_check_status()
+    assert torch.equal(hk.permute(0, 2, 1, 3), kc) and torch.equal(hv.permute(0, 2, 1, 3), vc)
+    assert np.array_equal(to_np(out).view(np.uint16), to_np(ref).view(np.uint16))
+    gk, gv = oracle.reshape_and_cache_golden(c["key"], c["value"], c["key_cache"], c["value_cache"], c["slot_mapping"])
+    g = oracle.paged_attention_golden(c["query"], gk, gv, c["block_tables"], c["context_lens"], c["qk_scale"])
+    assert_close(to_np(out), g, tol_for(spec.dtype, False), f"{spec.name} head-major")

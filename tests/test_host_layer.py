@@ -35,7 +35,8 @@ def test_library_exports_every_declared_symbol(header, loader, listed):
 def test_registered_signatures_match_the_yaml_definitions():
     reg = ops.registered_ops()
     for op, sub in (("reshape_and_cache", "reshape_and_cache"), ("paged_attention", "paged_attention"),
-                    ("paged_cache_load", "paged_cache_load"), ("fa_update", "fa_update")):
+                    ("paged_cache_load", "paged_cache_load"), ("fa_update", "fa_update"),
+                    ("reshape_and_cache_npd", "reshape_and_cache_npd")):
         y = yaml.safe_load(open(os.path.join(ROOT, "ms_custom_ops_b200", "ops", "c_api", sub, op + "_op.yaml")))
         parts = []
         for name, spec in y[op]["args"].items():
@@ -45,9 +46,11 @@ def test_registered_signatures_match_the_yaml_definitions():
         assert reg[op] == f"{op}({', '.join(parts)})"
     # and the Python functions expose the same names, order and defaults
     import inspect
-    for op in ("reshape_and_cache", "paged_attention", "paged_cache_load", "fa_update"):
+    for op in ("reshape_and_cache", "paged_attention", "paged_cache_load", "fa_update", "reshape_and_cache_npd"):
         sig = inspect.signature(getattr(ops, op))
-        got = ", ".join(n if p.default is inspect._empty else f"{n}={p.default}" for n, p in sig.parameters.items())
+        got = ", ".join(n if p.default is inspect._empty else
+                        f"{n}={p.default!r}" if isinstance(p.default, str) else f"{n}={p.default}"
+                        for n, p in sig.parameters.items())
         assert reg[op] == f"{op}({got})"
 
 
@@ -95,7 +98,7 @@ def test_infer_returns_query_shape_and_dtype():
           attn_mask=T((4, 1, 1024), "float16")), ops.UnsupportedOnB200, "prefill-shaped"),
     (dict(q_head_num=32, kv_head_num=8, mask_type=3), ops.UnsupportedOnB200, "mask_type=3"),
     (dict(q_head_num=32, kv_head_num=8, scale_type=1), ops.UnsupportedOnB200, "LogN"),
-    (dict(q_head_num=32, kv_head_num=8, input_layout=1), ops.UnsupportedOnB200, "BNSD"),
+    (dict(q_head_num=32, kv_head_num=8, input_layout=1, quant_type=1), ValueError, "BNSD"),
     (dict(q_head_num=32, kv_head_num=8, compress_type=1), ops.UnsupportedOnB200, "compress_type"),
     (dict(q_head_num=32, kv_head_num=8, batch_run_status_enable=True), ops.UnsupportedOnB200, "batch_run_status"),
 ])
@@ -395,3 +398,32 @@ def test_reshape_and_cache_infer_returns_the_placeholder_of_the_reference():
         ops.reshape_and_cache_infer(k2, k2, c, c, T((4,), "int32"), cache_mode=1)
     with pytest.raises(ValueError):
         ops.reshape_and_cache_infer(k2, k2, c, c, T((5,), "int32"))
+
+
+def test_bnsd_layout_is_accepted_under_the_reference_rules():
+    # input_layout = 1: caches are (num_blocks, kv_heads, block_size, head_size); same checks on the same
+    # quantities (reference: paged_attention_pynative.cc:119-145 for what may be combined with it)
+    kc = T((64, 8, 128, 128), "float16")
+    assert ops.paged_attention_infer(Q, kc, kc, BT, LENS, input_layout=1, **OKW) == ((4, 32, 128), "float16")
+    assert ops.paged_attention_workspace_size(Q, kc, kc, BT, LENS, input_layout=1, **OKW) > 0
+    with pytest.raises(ValueError, match="kv_head_num"):   # read as BNSD, a BSND-shaped cache has 128 heads
+        ops.paged_attention_infer(Q, KC, KC, BT, LENS, input_layout=1, **OKW)
+    for kw in (dict(calc_type=1), dict(compress_type=1), dict(scale_type=1)):
+        with pytest.raises(ValueError, match="BNSD"):
+            ops.paged_attention_infer(Q, kc, kc, BT, LENS, input_layout=1, **OKW, **kw)
+
+
+def test_reshape_and_cache_npd_checks():
+    k, c = T((32, 1024), "float16"), T((4, 8, 16, 128), "float16")
+    sm = T((32,), "int32")
+    assert ops.reshape_and_cache_npd_infer(k, k, c, c, sm, key_value_layout="TH") == (((32, 1024), "float16"),) * 2
+    cb = T((4, 16, 8, 128), "float16")
+    assert ops.reshape_and_cache_npd_infer(k, k, cb, cb, sm, kv_cache_layout="BSND", key_value_layout="TH")[0][0] == (32, 1024)
+    with pytest.raises(ops.UnsupportedOnB200, match="NPD"):
+        ops.reshape_and_cache_npd_infer(k, k, c, c, sm)    # the reference's default output layout
+    with pytest.raises(ValueError, match="kv_cache_layout"):
+        ops.reshape_and_cache_npd_infer(k, k, c, c, sm, kv_cache_layout="NHWC", key_value_layout="TH")
+    with pytest.raises(ValueError, match="hidden sizes"):
+        ops.reshape_and_cache_npd_infer(k, k, cb, cb, sm, key_value_layout="TH")  # BSND-shaped cache read as BNSD
+    with pytest.raises(TypeError):
+        ops.reshape_and_cache_npd_infer(k, k, c, c, T((32,), "int64"), key_value_layout="TH")

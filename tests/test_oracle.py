@@ -204,3 +204,17 @@ def test_split_merge_equals_unsplit_attention():
         lses.append((m + np.log(e.sum(-1, keepdims=True)))[:, 0])
     merged = oracle.fa_update_golden(np.stack(lses), np.stack(outs))
     assert np.allclose(merged, full[b], atol=2e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("name", sorted(cases.RACNPD_CASES))
+def test_head_major_scatter_oracle_matches_reference_golden(name):
+    # digests of the reference's npd_cache_inference (tests/st/test_custom_reshape_and_cache_npd.py:487-515)
+    c = cases.racnpd_case(name)
+    fx = np.load(os.path.join(GOLDEN_DIR, f"racnpd_{name}.npz"))
+    assert str(fx["sha_in_key"]) == cases.digest(c["key"]) and str(fx["sha_in_key_cache"]) == cases.digest(c["key_cache"])
+    gk, gv = oracle.reshape_and_cache_bnsd_golden(c["key"], c["value"], c["key_cache"], c["value_cache"], c["slot_mapping"])
+    assert cases.digest(gk) == str(fx["sha_key_cache"]) and cases.digest(gv) == str(fx["sha_value_cache"])
+    # the same rows in the other block layout: transposing the blocks commutes with the scatter
+    bk, bv = oracle.reshape_and_cache_golden(c["key"], c["value"], oracle.bnsd_to_bsnd(c["key_cache"]),
+                                             oracle.bnsd_to_bsnd(c["value_cache"]), c["slot_mapping"])
+    assert np.array_equal(oracle.bnsd_to_bsnd(gk), bk) and np.array_equal(oracle.bnsd_to_bsnd(gv), bv)
