@@ -209,6 +209,10 @@ typedef struct MscoPaPlanInfo {
  * request's result is bitwise independent of what it is batched with. */
 int32_t msco_paged_attention_split_tokens(int32_t context_len, int32_t kv_dtype);
 
+/* 1 when the TMA + tensor-core kernel serves this descriptor (head_dim 128, or 64 / 256 with a 16-bit
+ * cache; block_size 16 / 32 / 64 / 128, at most 64 for head_dim 256), 0 when the general kernel does. */
+int32_t msco_paged_attention_tma_supported(const MscoPaDesc *desc);
+
 /* Build the launch plan from the host copy of context_lens (the reference
  * reads the same host values into its param: paged_attention_graph.cc:773-776,
  * paged_attention_pynative.cc:686-692).  Pure host work.  The plan words live in
@@ -226,6 +230,18 @@ int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *host_contex
  * pending upload).  Not thread-safe against launches of the same plan object.  On failure the plan
  * must not be launched again before a successful re-plan. */
 int msco_paged_attention_replan(MscoPaPlan *plan, const int32_t *host_context_lens, int32_t batch);
+/* Multi-token (speculative) queries, calc_type = 1 of the operator (q_seq_len of
+ * CustomASDPagedAttentionParam, paged_attention_graph.cc:758-762), planned so that the context is read ONCE
+ * for all query tokens of a sequence: sequence b has host_q_seq_lens[b] consecutive rows in `query` / `out`
+ * (sum of them rows in total) and ONE row of block_tables.  Runs of up to 16 / (q heads per kv head)
+ * consecutive tokens (8 / ... for head_dim 256) are stacked into the q rows of one work item.  The launch
+ * entry points are the same; attn_mask, when given, has one row per query token (mask_type 1 with
+ * mask_batch_stride = the row length: the operator's SPEC mask).  Needs the TMA kernel (MSCO_ERR_UNSUPPORTED
+ * otherwise: plan one decode row per token with msco_paged_attention_plan + msco_expand_rows_i32 instead). */
+int msco_paged_attention_plan_tokens(const MscoPaDesc *desc, const int32_t *host_context_lens,
+                                     const int32_t *host_q_seq_lens, int32_t num_seqs, MscoPaPlan **plan);
+int msco_paged_attention_replan_tokens(MscoPaPlan *plan, const int32_t *host_context_lens,
+                                       const int32_t *host_q_seq_lens, int32_t num_seqs);
 /* Counters of the plan arena: [0] slabs obtained (cudaHostAlloc calls), [1] their bytes, [2] blocks
  * in use, [3] block requests served, [4] requests larger than a slab, [5] 1 if page-locked. */
 void msco_plan_arena_stats(int64_t *stats /* [6] */);

@@ -63,7 +63,8 @@ EXPORTS = (
     "msco_paged_attention_launch_static", "msco_paged_attention_status_static",
     "msco_ipc_export", "msco_ipc_import", "msco_ipc_release", "msco_peer_allgather", "msco_decode_step",
     "msco_paged_attention_launch_lse", "msco_expand_rows_i32", "msco_paged_attention_replan", "msco_plan_arena_stats",
-    "msco_reshape_and_cache_bnsd", "msco_copy_device", "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update", "msco_fa_update_strided",
+    "msco_reshape_and_cache_bnsd", "msco_copy_device", "msco_paged_attention_plan_tokens",
+    "msco_paged_attention_replan_tokens", "msco_paged_attention_tma_supported", "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update", "msco_fa_update_strided",
 )
 
 
@@ -102,6 +103,12 @@ def lib():
     L.msco_paged_attention_plan.argtypes = [C.POINTER(MscoPaDesc), C.POINTER(i32), i32, C.POINTER(vp)]
     L.msco_paged_attention_replan.restype = C.c_int
     L.msco_paged_attention_replan.argtypes = [vp, C.POINTER(i32), i32]
+    L.msco_paged_attention_plan_tokens.restype = C.c_int
+    L.msco_paged_attention_plan_tokens.argtypes = [C.POINTER(MscoPaDesc), C.POINTER(i32), C.POINTER(i32), i32, C.POINTER(vp)]
+    L.msco_paged_attention_replan_tokens.restype = C.c_int
+    L.msco_paged_attention_replan_tokens.argtypes = [vp, C.POINTER(i32), C.POINTER(i32), i32]
+    L.msco_paged_attention_tma_supported.restype = i32
+    L.msco_paged_attention_tma_supported.argtypes = [C.POINTER(MscoPaDesc)]
     L.msco_plan_arena_stats.restype = None
     L.msco_plan_arena_stats.argtypes = [C.POINTER(i64)]
     L.msco_paged_attention_workspace_bytes.restype = sz
@@ -156,11 +163,16 @@ def plan_arena_stats():
 class PaPlan:
     """Owner of one MscoPaPlan (host-side launch plan for a vector of context lengths)."""
 
-    def __init__(self, desc: MscoPaDesc, context_lens):
+    def __init__(self, desc: MscoPaDesc, context_lens, q_seq_lens=None):
+        """`q_seq_lens` (one entry per sequence): multi-token queries, stacked into the q rows of the items."""
         L = lib()
         lens = (C.c_int32 * len(context_lens))(*[int(x) for x in context_lens])
         h = C.c_void_p()
-        check(L.msco_paged_attention_plan(C.byref(desc), lens, len(context_lens), C.byref(h)))
+        if q_seq_lens is None:
+            check(L.msco_paged_attention_plan(C.byref(desc), lens, len(context_lens), C.byref(h)))
+        else:
+            ql = (C.c_int32 * len(q_seq_lens))(*[int(x) for x in q_seq_lens])
+            check(L.msco_paged_attention_plan_tokens(C.byref(desc), lens, ql, len(context_lens), C.byref(h)))
         self._h = h
         self.desc = desc
         self.batch = len(context_lens)

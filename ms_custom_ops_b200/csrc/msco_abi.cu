@@ -110,10 +110,16 @@ int current_sm_count() {
 // Fills `pl` (descriptor already set) for one vector of context lengths.  The plan words live in a
 // block of the pinned arena that the plan keeps across calls: a re-plan with a batch of the same size
 // class touches no allocator at all.
-int fill_plan(MscoPaPlan *pl, const int32_t *host_context_lens, int32_t batch) {
+// `q_lens` (NULL for a decode batch: one query token per sequence) gives the number of query tokens of
+// every sequence (multi-token / speculative queries); `num` is the number of sequences.  Runs of up to
+// rows / group consecutive tokens of a sequence become one plan entry whose q rows are stacked into one
+// work item, so the context is read once for all of them.
+int fill_plan(MscoPaPlan *pl, const int32_t *host_context_lens, const int32_t *q_lens, int32_t num) {
   const MscoPaDesc &d = pl->desc;
   const int64_t cap = (int64_t)d.max_blocks_per_seq * d.block_size;
-  for (int b = 0; b < batch; ++b) {
+  int64_t tokens = 0;
+  int max_q = 1;
+  for (int b = 0; b < num; ++b) {
     if (host_context_lens[b] < 0)
       return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: context_lens[%d] = %d is negative", b,
                   host_context_lens[b]);
@@ -121,23 +127,48 @@ int fill_plan(MscoPaPlan *pl, const int32_t *host_context_lens, int32_t batch) {
       return fail(MSCO_ERR_INVALID_ARG,
                   "paged_attention_plan: context_lens[%d] = %d exceeds the block table (%d blocks of %d)", b,
                   host_context_lens[b], d.max_blocks_per_seq, d.block_size);
+    if (q_lens != nullptr) {
+      if (q_lens[b] < 0) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: q_seq_lens[%d] = %d is negative", b, q_lens[b]);
+      tokens += q_lens[b];
+      max_q = std::max(max_q, q_lens[b]);
+    }
   }
+  if (tokens > 0x7fffffffLL) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: too many query tokens");
+  const bool mt = q_lens != nullptr;
+  const int batch = mt ? (int)tokens : num;  // rows of query / out
   pl->batch = batch;
+  pl->multi_token = mt;
   const int g = d.num_q_heads / d.num_kv_heads;
+  // query tokens stacked into one item: as many as the item's q rows hold
+  int tpi = 1;
+  pl->rows_per_item = pl->kernel == kKernelTma ? pa_tma_rows_per_item(d) : 8;
+  if (mt && pl->kernel == kKernelTma) {
+    const int rows_max = d.head_dim == 256 ? 8 : 16;
+    tpi = std::max(1, std::min(max_q, rows_max / g));
+    if (tpi > 1) pl->rows_per_item = tpi * g > 8 ? 16 : 8;
+  }
   const int nqb = (g + pl->rows_per_item - 1) / pl->rows_per_item;
   const int items_per_split = d.num_kv_heads * nqb;
   pl->num_sms = current_sm_count();
 
-  // sequences with tokens, longest first (stable), so that the big items lead the work list
-  static thread_local std::vector<int> order;
-  order.clear();
-  for (int b = 0; b < batch; ++b)
-    if (host_context_lens[b] > 0) order.push_back(b);
-  std::stable_sort(order.begin(), order.end(),
-                   [&](int a, int b) { return host_context_lens[a] > host_context_lens[b]; });
-  const int nseq = (int)order.size();
+  // entries with work, longest first (stable), so that the big items lead the work list
+  struct Entry { int b, len, qtok0, ntok; };
+  static thread_local std::vector<Entry> entries;
+  entries.clear();
+  int qbase = 0, empty_rows = 0;
+  for (int b = 0; b < num; ++b) {
+    const int ql = mt ? q_lens[b] : 1;
+    if (host_context_lens[b] > 0) {
+      for (int t0 = 0; t0 < ql; t0 += tpi) entries.push_back({b, host_context_lens[b], mt ? qbase + t0 : b, std::min(tpi, ql - t0)});
+    } else {
+      empty_rows += ql;
+    }
+    qbase += ql;
+  }
+  std::stable_sort(entries.begin(), entries.end(), [](const Entry &a, const Entry &b) { return a.len > b.len; });
+  const int nseq = (int)entries.size();
   pl->nseq = nseq;
-  pl->plan_words = kPlanHeaderWords + (size_t)(nseq + 1) + 5 * (size_t)nseq + 2 * (size_t)batch;
+  pl->plan_words = kPlanHeaderWords + (size_t)(nseq + 1) + 5 * (size_t)nseq + 2 * (size_t)batch + (mt ? 2 * (size_t)nseq : 0);
   pl->plan_bytes = pl->plan_words * 4;
   if (pl->upload_pending) {  // an async copy out of the old words may still be queued
     MSCO_CUDA_CHECK(cudaEventSynchronize(pl->upload_done));
@@ -155,33 +186,44 @@ int fill_plan(MscoPaPlan *pl, const int32_t *host_context_lens, int32_t batch) {
   int32_t *seq_idx = item_base + nseq + 1, *seq_len = seq_idx + nseq, *chunk = seq_len + nseq;
   int32_t *nsplit = chunk + nseq, *part_base = nsplit + nseq;
   int32_t *b_nsplit = part_base + nseq, *b_part_base = b_nsplit + batch;
+  int32_t *qtok0 = b_part_base + batch, *qntok = qtok0 + nseq;
   int64_t items = 0, parts = 0, kv_tokens = 0;
   int max_splits = 0;
+  const bool fused = pl->kernel == kKernelTma && pl->fused_merge_wanted;
   for (int s = 0; s < nseq; ++s) {
-    const int b = order[s], len = host_context_lens[b];
-    const int c = msco_paged_attention_split_tokens(len, d.kv_dtype);
-    const int ns = (len + c - 1) / c;
+    const Entry &e = entries[s];
+    const int c = msco_paged_attention_split_tokens(e.len, d.kv_dtype);
+    const int ns = (e.len + c - 1) / c;
     item_base[s] = (int32_t)items;
-    seq_idx[s] = b; seq_len[s] = len; chunk[s] = c; nsplit[s] = ns;
+    seq_idx[s] = e.b; seq_len[s] = e.len; chunk[s] = c; nsplit[s] = ns;
     part_base[s] = (int32_t)parts;
-    b_nsplit[b] = ns; b_part_base[b] = (int32_t)parts;
+    if (mt) { qtok0[s] = e.qtok0; qntok[s] = e.ntok; }
+    // per output row (the reduce kernel's view): splits and first partial.  When the attention kernel
+    // merges its partials itself the reduce kernel only zero-fills the rows of empty sequences, so every
+    // other row is marked as written.
+    for (int t = 0; t < e.ntok; ++t) {
+      b_nsplit[e.qtok0 + t] = fused ? 1 : ns;
+      b_part_base[e.qtok0 + t] = (int32_t)parts;
+    }
     items += (int64_t)ns * items_per_split;
-    if (ns > 1) parts += ns;
+    if (ns > 1) parts += (int64_t)ns * e.ntok;
     max_splits = std::max(max_splits, ns);
-    kv_tokens += len;
-    if (items > 0x7fffffffLL) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: too many work items");
+    kv_tokens += e.len;
+    if (items > 0x7fffffffLL || parts > 0x7fffffffLL)
+      return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: too many work items");
   }
   item_base[nseq] = (int32_t)items;
   w[0] = 0; w[1] = nseq; w[2] = (int32_t)items; w[3] = (int32_t)parts; w[4] = batch; w[5] = items_per_split;
+  w[6] = mt ? 1 : 0;
   pl->total_items = (int)items;
   pl->total_parts = (int)parts;
   pl->max_splits = max_splits;
   pl->kv_tokens = kv_tokens;
   // the TMA kernel merges its split partials itself (the CTA that stores the last partial of a group
   // does it); the reduce kernel is then only needed to zero the rows of empty sequences
-  pl->fused_merge = pl->kernel == kKernelTma;
-  if (const char *e = getenv("MSCO_TUNE_FUSED_MERGE")) pl->fused_merge = pl->fused_merge && atoi(e) != 0;  // TUNING ONLY
-  pl->need_reduce = pl->fused_merge ? nseq < batch : (parts > 0 || nseq < batch);
+  pl->fused_merge = fused;
+  const bool has_empty = mt ? empty_rows > 0 : nseq < batch;
+  pl->need_reduce = pl->fused_merge ? has_empty : (parts > 0 || has_empty);
   pl->grid = pl->kernel == kKernelTma ? (int)std::min<int64_t>(items, pl->num_sms) : (int)items;
   pl->num_groups = pl->fused_merge ? nseq * items_per_split : 0;
   pl->sync_offset = align_up(kPlanRegionOffset + pl->plan_bytes, 256);
@@ -194,11 +236,8 @@ int fill_plan(MscoPaPlan *pl, const int32_t *host_context_lens, int32_t batch) {
   return MSCO_OK;
 }
 
-}  // namespace
-
-extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *host_context_lens,
-                                         int32_t batch, MscoPaPlan **out_plan) {
-  if (desc == nullptr || out_plan == nullptr || batch < 0 || (batch > 0 && host_context_lens == nullptr))
+int new_plan(const MscoPaDesc *desc, const int32_t *lens, const int32_t *q_lens, int32_t num, MscoPaPlan **out_plan) {
+  if (desc == nullptr || out_plan == nullptr || num < 0 || (num > 0 && lens == nullptr))
     return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan: NULL argument");
   *out_plan = nullptr;
   int rc = validate_desc(*desc);
@@ -209,15 +248,21 @@ extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *
     return fail(MSCO_ERR_UNSUPPORTED,
                 "paged_attention_plan: the TMA kernel needs head_dim 128 (or 64 / 256 with a 16-bit cache) and "
                 "block_size 16/32/64/128 (at most 64 for head_dim 256)");
+  const int kernel = (d.kernel == kKernelGeneric || !tma_ok) ? kKernelGeneric : kKernelTma;
+  if (q_lens != nullptr && kernel != kKernelTma)
+    return fail(MSCO_ERR_UNSUPPORTED,
+                "paged_attention_plan_tokens: stacked query tokens need the TMA kernel; for this shape plan one decode "
+                "row per query token instead (msco_paged_attention_plan + msco_expand_rows_i32)");
   MscoPaPlan *pl = new (std::nothrow) MscoPaPlan();
   if (pl == nullptr) return fail(MSCO_ERR_INTERNAL, "paged_attention_plan: out of host memory");
   pl->desc = d;
-  const int g = d.num_q_heads / d.num_kv_heads;
-  pl->kernel = (d.kernel == kKernelGeneric || !tma_ok) ? kKernelGeneric : kKernelTma;
-  pl->rows_per_item = pl->kernel == kKernelTma ? pa_tma_rows_per_item(d) : 8;
-  (void)g;
-  if (const char *e = getenv("MSCO_PA_INT8_SUBS")) pl->int8_subs = atoi(e) == 2 ? 2 : 1;
-  rc = fill_plan(pl, host_context_lens, batch);
+  pl->kernel = kernel;
+  if (const char *e = getenv("MSCO_PA_INT8_SUBS")) pl->int8_subs = atoi(e) == 1 ? 1 : 2;   // TUNING ONLY
+  // MSCO_PA_FUSED_MERGE=1: the attention kernel merges its split partials itself (the CTA that stores a
+  // group's last partial does it) instead of leaving them to the reduce kernel: one launch less per step,
+  // paid for with a device-scope fence and an atomic per multi-split item
+  if (const char *e = getenv("MSCO_PA_FUSED_MERGE")) pl->fused_merge_wanted = atoi(e) != 0;
+  rc = fill_plan(pl, lens, q_lens, num);
   if (rc != MSCO_OK) {
     msco_paged_attention_plan_destroy(pl);
     return rc;
@@ -226,10 +271,41 @@ extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *
   return MSCO_OK;
 }
 
+}  // namespace
+
+extern "C" int32_t msco_paged_attention_tma_supported(const MscoPaDesc *desc) {
+  return (desc != nullptr && validate_desc(*desc) == MSCO_OK && desc->kernel != kKernelGeneric &&
+          pa_tma_supported(*desc)) ? 1 : 0;
+}
+
+extern "C" int msco_paged_attention_plan(const MscoPaDesc *desc, const int32_t *host_context_lens,
+                                         int32_t batch, MscoPaPlan **out_plan) {
+  return new_plan(desc, host_context_lens, nullptr, batch, out_plan);
+}
+
+extern "C" int msco_paged_attention_plan_tokens(const MscoPaDesc *desc, const int32_t *host_context_lens,
+                                                const int32_t *host_q_seq_lens, int32_t num_seqs,
+                                                MscoPaPlan **out_plan) {
+  if (num_seqs > 0 && host_q_seq_lens == nullptr)
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention_plan_tokens: NULL q_seq_lens");
+  static const int32_t none = 0;
+  return new_plan(desc, host_context_lens, host_q_seq_lens != nullptr ? host_q_seq_lens : &none, num_seqs, out_plan);
+}
+
 extern "C" int msco_paged_attention_replan(MscoPaPlan *plan, const int32_t *host_context_lens, int32_t batch) {
   if (plan == nullptr || batch < 0 || (batch > 0 && host_context_lens == nullptr))
     return fail(MSCO_ERR_INVALID_ARG, "paged_attention_replan: NULL argument");
-  return fill_plan(plan, host_context_lens, batch);
+  return fill_plan(plan, host_context_lens, nullptr, batch);
+}
+
+extern "C" int msco_paged_attention_replan_tokens(MscoPaPlan *plan, const int32_t *host_context_lens,
+                                                  const int32_t *host_q_seq_lens, int32_t num_seqs) {
+  if (plan == nullptr || num_seqs < 0 || (num_seqs > 0 && (host_context_lens == nullptr || host_q_seq_lens == nullptr)))
+    return fail(MSCO_ERR_INVALID_ARG, "paged_attention_replan_tokens: NULL argument");
+  if (plan->kernel != kKernelTma)
+    return fail(MSCO_ERR_UNSUPPORTED, "paged_attention_replan_tokens: stacked query tokens need the TMA kernel");
+  static const int32_t none = 0;
+  return fill_plan(plan, host_context_lens, num_seqs > 0 ? host_q_seq_lens : &none, num_seqs);
 }
 
 extern "C" void msco_plan_arena_stats(int64_t *stats /* [6] */) {

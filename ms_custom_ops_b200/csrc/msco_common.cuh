@@ -39,17 +39,21 @@ inline int dtype_size(int dt) {
 }
 
 // ---- device plan layout (int32 words at the start of the PA workspace) ----
-// [0] unused  [1] nseq  [2] total_items  [3] total_parts  [4] batch  [5] items_per_split  [6..7] pad
+// [0] unused  [1] nseq  [2] total_items  [3] total_parts  [4] batch  [5] items_per_split
+// [6] 1 when the entries carry query-token ranges (multi-token queries)  [7] pad
 // then: item_base[nseq+1], seq_idx[nseq], seq_len[nseq], chunk[nseq], nsplit[nseq], part_base[nseq],
-//       b_nsplit[batch], b_part_base[batch]
+//       b_nsplit[batch], b_part_base[batch], and with [6] set: qtok0[nseq], qntok[nseq]
+// An "entry" (nseq of them) is one sequence of a decode batch, or -- multi-token queries -- a run of up to
+// rows_per_item / group consecutive query tokens of one sequence, whose q rows are stacked into one item.
 constexpr int kPlanHeaderWords = 8;
 constexpr int kStatusTimeout = MSCO_ERR_TIMEOUT;
 constexpr int kStatusOob = MSCO_ERR_OOB;
 
 struct PlanView {
   const int32_t *base;
-  int nseq, total_items, total_parts, batch;
+  int nseq, total_items, total_parts, batch, multi_token;
   const int32_t *item_base, *seq_idx, *seq_len, *chunk, *nsplit, *part_base, *b_nsplit, *b_part_base;
+  const int32_t *qtok0, *qntok;  // multi-token queries only
 };
 
 __host__ __device__ inline PlanView make_plan_view(const int32_t *w) {
@@ -59,6 +63,7 @@ __host__ __device__ inline PlanView make_plan_view(const int32_t *w) {
   v.total_items = w[2];
   v.total_parts = w[3];
   v.batch = w[4];
+  v.multi_token = w[6];
   const int32_t *p = w + kPlanHeaderWords;
   v.item_base = p; p += v.nseq + 1;
   v.seq_idx = p; p += v.nseq;
@@ -67,7 +72,9 @@ __host__ __device__ inline PlanView make_plan_view(const int32_t *w) {
   v.nsplit = p; p += v.nseq;
   v.part_base = p; p += v.nseq;
   v.b_nsplit = p; p += v.batch;
-  v.b_part_base = p;
+  v.b_part_base = p; p += v.batch;
+  v.qtok0 = p; p += v.nseq;
+  v.qntok = p;
   return v;
 }
 
@@ -76,7 +83,9 @@ __host__ __device__ inline PlanView make_plan_view(const int32_t *w) {
 struct WorkItem {
   int b, kvh, row0, nrows, tok0, tok1, nsplit, part;
   int grp;    // index of the (sequence, kv head, q-row block) group: one arrival counter per group
-  int part0;  // partial row of the group's first split (part = part0 + split)
+  int part0;  // partial row of the group's first split and first token: part = part0 + split * ntok + token
+  int qtok0;  // first query token (row of query / out) of the item; the sequence index b for a decode batch
+  int ntok;   // query tokens stacked into the item (1 for a decode batch): q row r is token r / group
 };
 
 #ifdef __CUDACC__
@@ -142,8 +151,15 @@ __device__ __forceinline__ WorkItem decode_item(const PlanView &pv, int t, int n
   w.tok0 = split * c;
   w.tok1 = min(len, w.tok0 + c);
   w.part0 = __ldg(pv.part_base + s);
-  w.part = w.part0 + split;
   w.grp = s * nps + hh;
+  w.qtok0 = w.b;
+  w.ntok = 1;
+  if (pv.multi_token) {
+    w.qtok0 = __ldg(pv.qtok0 + s);
+    w.ntok = __ldg(pv.qntok + s);
+    if (w.ntok > 1) w.nrows = w.ntok * g;  // one row block holds the whole run (the planner sees to it)
+  }
+  w.part = w.part0 + split * w.ntok;
   return w;
 }
 

@@ -77,7 +77,8 @@ template <int D, bool KV8, int NT, int SUBS> struct Cfg {
   static constexpr int kOffMl = kOffMerge + kMergeBufs * kMergeBytes;
   static constexpr int kOffDesc = kOffMl + kMergeBufs * kMlBytes;   // 2 x kDescInts ints, 4 spare ints,
                                                                     // 4 x 8 ints: groups awaiting their merge
-  static constexpr int kOffBar = kOffDesc + 2 * kDescInts * 4 + 16 + 4 * 8 * 4;  // mbarriers
+  static constexpr int kOffShift = kOffDesc + 2 * kDescInts * 4 + 16 + 4 * 8 * 4;  // 2 x 32 floats (lse, int8 KV)
+  static constexpr int kOffBar = kOffShift + 2 * 32 * 4;            // mbarriers
   static constexpr int kNumBars = 2 * kStages + 8;
   static constexpr int kOffItemBase = kOffBar + kNumBars * 8 + 16;  // copy of the plan's item_base[]
   static constexpr int kItemBaseCap = 1024;                          // sequences (+1) that fit
@@ -169,38 +170,50 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     uint32_t st = 0, ph = 0;
     const int bs = p.block_size;
     const int bpt = kTile / bs;  // cache blocks per tile (divides 32)
-    // Work items are handed out by a ticket (the list is longest-first): the first item of a CTA is
-    // its own index, every further one comes from an atomic counter in the workspace that is zero
-    // when the kernel starts.  Which CTA computes an item has no influence on the item's bits.
-    int t = blockIdx.x;
+    // Work items are handed out by a ticket (the list is longest-first): the first two items of a CTA
+    // are fixed (its own index, and that plus the grid size), every further one comes from an atomic
+    // counter in the workspace that is zero when the kernel starts.  Which CTA computes an item has no
+    // influence on the item's bits.  The descriptor and the q rows of item i + 1 are published BEFORE
+    // the tiles of item i are issued, so they are in shared memory (and, for an int8 cache, converted
+    // by the helper warp) a whole item ahead of their use.
+    auto publish = [&](const WorkItem &w, int qs) {  // lane 0: descriptor + q rows into slot qs
+      int *d = desc + qs * kDescInts;
+      d[0] = w.b; d[1] = w.kvh; d[2] = w.row0; d[3] = w.nrows;
+      d[4] = w.tok0; d[5] = w.tok1; d[6] = w.nsplit; d[7] = w.part;
+      d[8] = w.grp; d[9] = w.part0; d[10] = w.qtok0; d[11] = w.ntok;
+      // q rows of the item: for a decode batch one contiguous run (rows row0 .. row0 + nrows of the kv
+      // head's group); for stacked query tokens the group's rows of every token, one run per token
+      const uint32_t qbytes = (uint32_t)w.nrows * D * 2;
+      mbar_arrive_expect_tx(&qfull[qs], qbytes);
+      const uint32_t run = qbytes / (uint32_t)w.ntok;
+      for (int tq = 0; tq < w.ntok; ++tq) {
+        const char *qsrc = static_cast<const char *>(p.q) +
+                           ((int64_t)(w.qtok0 + tq) * p.num_q_heads + w.kvh * p.group + w.row0) * (D * 2);
+        bulk_load(smem + C::kOffQ + qs * C::kQSlotBytes + tq * run, qsrc, run, &qfull[qs]);
+      }
+    };
+    int t_nxt = (int)blockIdx.x + (int)gridDim.x;
+    WorkItem w = decode_item(pv, blockIdx.x, p.num_kv_heads, p.group, C::kRows, ibs);  // grid <= items
+    if (lane == 0) publish(w, 0);  // slot 0 is free at the start
     for (int qi = 0;; ++qi) {
-      const int qs = qi & 1;
-      const uint32_t qph = (qi >> 1) & 1;
-      if (!mbar_wait(&qempty[qs], qph ^ 1, kWaitLimit)) {
+      // next-but-one ticket: its latency hides behind this item's loads
+      int t_nn = 0;
+      if (lane == 0) t_nn = 2 * (int)gridDim.x + (int)atomicAdd(p.sync, 1u);
+      // item qi + 1 (or the end marker) into the other slot, once the consumers have let go of it
+      const int ns = (qi + 1) & 1;
+      const uint32_t nph = ((qi + 1) >> 1) & 1;
+      if (!mbar_wait(&qempty[ns], nph ^ 1, kWaitLimit)) {
         report_status(p.status, p.epoch, kStatusTimeout);
         return;
       }
-      if (t >= total) {  // no work left: tell the consumers
-        if (lane == 0) {
-          desc[qs * kDescInts] = -1;
-          mbar_arrive(&qfull[qs]);
-        }
-        break;
-      }
-      const WorkItem w = decode_item(pv, t, p.num_kv_heads, p.group, C::kRows, ibs);
-      // next ticket: its latency hides behind this item's loads
-      int t_next = 0;
-      if (lane == 0) t_next = (int)gridDim.x + (int)atomicAdd(p.sync, 1u);
-      if (lane == 0) {
-        int *d = desc + qs * kDescInts;
-        d[0] = w.b; d[1] = w.kvh; d[2] = w.row0; d[3] = w.nrows;
-        d[4] = w.tok0; d[5] = w.tok1; d[6] = w.nsplit; d[7] = w.part;
-        d[8] = w.grp; d[9] = w.part0;
-        const uint32_t qbytes = (uint32_t)w.nrows * D * 2;
-        mbar_arrive_expect_tx(&qfull[qs], qbytes);
-        const char *qsrc = static_cast<const char *>(p.q) +
-                           ((int64_t)w.b * p.num_q_heads + w.kvh * p.group + w.row0) * (D * 2);
-        bulk_load(smem + C::kOffQ + qs * C::kQSlotBytes, qsrc, qbytes, &qfull[qs]);
+      const bool more = t_nxt < total;
+      WorkItem w_nxt = w;
+      if (more) {
+        w_nxt = decode_item(pv, t_nxt, p.num_kv_heads, p.group, C::kRows, ibs);
+        if (lane == 0) publish(w_nxt, ns);
+      } else if (lane == 0) {  // no work left: tell the consumers
+        desc[ns * kDescInts] = -1;
+        mbar_arrive(&qfull[ns]);
       }
       const int ntok = w.tok1 - w.tok0;
       const int nblk_item = (ntok + bs - 1) / bs;
@@ -249,7 +262,9 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           }
         }
       }
-      t = __shfl_sync(0xffffffffu, t_next, 0);
+      if (!more) break;
+      w = w_nxt;
+      t_nxt = __shfl_sync(0xffffffffu, t_nn, 0);
     }
     return;
   }
@@ -357,8 +372,12 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     if (!mbar_wait(pdone, (uint32_t)(n_checked & 1), kWaitLimit)) return false;
     const volatile int *g = pinfo + (n_checked & 3) * 8;
     if (g[6]) {
-      const int gb = g[0], ghq0 = g[1], gnrows = g[2], gns = g[3], gpart0 = g[4];
-      for (int r = warp; r < gnrows; r += C::kWarps) merge_row<T, D>(p, gb, ghq0 + r, gns, gpart0, lane);
+      const int gq0 = g[0], ghq0 = g[1], gnrows = g[2], gns = g[3], gpart0 = g[4], gntok = g[7];
+      const int gt = gntok > 1 ? p.group : 16;  // q rows per stacked token (a decode item is one token)
+      for (int r = warp; r < gnrows; r += C::kWarps) {
+        const int tq = r / gt, j = r - tq * gt;
+        merge_row<T, D>(p, (int64_t)(gq0 + tq) * p.num_q_heads + ghq0 + j, ghq0 + j, gns, gpart0 + tq, gntok, lane);
+      }
     }
     ++n_checked;
     return true;
@@ -376,7 +395,8 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     if (b < 0) break;  // the producer found no further work item
     const int kvh = dsc[1], row0 = dsc[2], nrows = dsc[3];
     const int tok0 = dsc[4], tok1 = dsc[5], nsplit = dsc[6], part = dsc[7];
-    const int grp = dsc[8], part0 = dsc[9];
+    const int grp = dsc[8], part0 = dsc[9], qtok0 = dsc[10], ntok = dsc[11];
+    const int gt = ntok > 1 ? p.group : 16;  // q rows per stacked query token: row r belongs to token r / gt
     float *mbuf = reinterpret_cast<float *>(smem + C::kOffMerge + (C::kMergeBufs == 2 ? (qi & 1) * C::kMergeBytes : 0));
     float2 *mlbuf = reinterpret_cast<float2 *>(smem + C::kOffMl + (C::kMergeBufs == 2 ? (qi & 1) * C::kMlBytes : 0));
 
@@ -408,11 +428,13 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           }
       }
     }
-    // (int8 KV: the partial score offsets of the lse correction stay in the Q slot until the merge below,
-    //  so the slot is handed back after the merge in that case)
-    const bool hold_q = KV8 && p.lse != nullptr;
+    // int8 KV with the lse output: the partial score offsets of the lse correction are needed at the merge
+    // below; warp 0 takes a copy so that the slot can be handed back right away
+    float *shift_copy = reinterpret_cast<float *>(smem + C::kOffShift) + (qi & 1) * 32;
+    if (KV8 && p.lse != nullptr && tid < 2 * C::kRows)
+      shift_copy[tid] = reinterpret_cast<const float *>(smem + C::kOffQFrag + qs * C::kQFragBytes + NT * 4 * 32 * 16)[tid];
     __syncwarp();
-    if (!hold_q && lane == 0) mbar_arrive(&qempty[qs]);
+    if (lane == 0) mbar_arrive(&qempty[qs]);
 
     // running state of this lane's two q rows per row tile (rows 8nt + 2q4, + 1)
     // The row sums l come from the tensor cores too: a tile of ones in place of V^T gives
@@ -456,8 +478,9 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
               for (int j = 0; j < 2; ++j) {
                 const int r = 8 * nt + 2 * q4 + j;
                 if (r < nrows) {
-                  const int64_t base = (int64_t)b * p.mask_batch_stride +
-                                       (int64_t)(kvh * p.group + row0 + r) * p.mask_head_stride;
+                  const int tq = r / gt;
+                  const int64_t base = (int64_t)(qtok0 + tq) * p.mask_batch_stride +
+                                       (int64_t)(kvh * p.group + row0 + r - tq * gt) * p.mask_head_stride;
                   if (tw < nv) mk[sb][nt][j] = load_mask_elem(p.mask, p.mask_dtype, base + tk);
                   if (tw + 8 < nv) mk[sb][nt][2 + j] = load_mask_elem(p.mask, p.mask_dtype, base + tk + 8);
                 }
@@ -688,14 +711,13 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           acc.x = fmaf(-1152.f, L, acc.x); acc.y = fmaf(-1152.f, L, acc.y);
           acc.z = fmaf(-1152.f, L, acc.z); acc.w = fmaf(-1152.f, L, acc.w);
         }
-        const int hq = kvh * p.group + row0 + row;
+        const int tq = row / gt;
+        const int hq = kvh * p.group + row0 + row - tq * gt;
+        const int64_t orow = (int64_t)(qtok0 + tq) * p.num_q_heads + hq;  // row of query / out / lse
         if (p.lse != nullptr) {
-          if (KV8) {  // back to the scores of the true K values (see the Q preparation)
-            const float *score_shift =
-                reinterpret_cast<const float *>(smem + C::kOffQFrag + qs * C::kQFragBytes + NT * 4 * 32 * 16);
-            M -= (score_shift[2 * row] + score_shift[2 * row + 1]) * p.scale_log2e;
-          }
-          if (nsplit == 1 && c4 == 0) p.lse[(int64_t)b * p.num_q_heads + hq] = (M + log2f(L)) * kLn2;
+          if (KV8)  // back to the scores of the true K values (see the Q preparation)
+            M -= (shift_copy[2 * row] + shift_copy[2 * row + 1]) * p.scale_log2e;
+          if (nsplit == 1 && c4 == 0) p.lse[orow] = (M + log2f(L)) * kLn2;
         }
         if (nsplit == 1) {
           const float inv = 1.f / L;
@@ -711,22 +733,19 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           uint2 pk;
           pk.x = pack2<T>(r0, r1);
           pk.y = pack2<T>(r2, r3);
-          *reinterpret_cast<uint2 *>(static_cast<T *>(p.out) + ((int64_t)b * p.num_q_heads + hq) * D + c4) = pk;
+          *reinterpret_cast<uint2 *>(static_cast<T *>(p.out) + orow * D + c4) = pk;
         } else {
-          const int64_t prow = (int64_t)part * p.num_q_heads + hq;
+          const int64_t prow = (int64_t)(part + tq) * p.num_q_heads + hq;
           *reinterpret_cast<float4 *>(p.part_o + prow * D + c4) = acc;
           if (c4 == 0) *reinterpret_cast<float2 *>(p.part_ml + prow * 2) = make_float2(M, L);
         }
       }
     }
-    if (hold_q) {
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&qempty[qs]);
-    }
     if (nsplit > 1 && p.fused_merge != 0) {
       if (tid == 0) {
         volatile int *g = pinfo + (n_stored & 3) * 8;
-        g[0] = b; g[1] = kvh * p.group + row0; g[2] = nrows; g[3] = nsplit; g[4] = part0; g[5] = grp;
+        g[0] = qtok0; g[1] = kvh * p.group + row0; g[2] = nrows; g[3] = nsplit; g[4] = part0; g[5] = grp;
+        g[7] = ntok;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(pstored);  // release: this warp's partial stores are ordered before it

@@ -17,7 +17,6 @@
 
 #include "ms_custom_ops_c.h"
 #include "ops/c_api/paged_attention/paged_attention_common.h"
-#include "ops/c_api/utils/attention_utils.h"
 #include "ops/framework/module.h"
 #include "ops/framework/plan_cache.h"
 #include "ops/framework/tensor.h"
@@ -306,11 +305,15 @@ struct Prepared {
   // the block table and the context length of its sequence (paged_attention_graph.cc:758-762, q_seq_len)
   bool multi_token = false;
   std::vector<int32_t> seq_of_row;  // sequence (row of block_tables) of every query token
+  // ... unless the kernel library can stack the tokens of a sequence into the q rows of its work items
+  // (one read of the context for all of them): then the plan is made from the per-sequence lengths
+  bool stacked = false;
+  std::vector<int32_t> seq_lens, q_lens;  // one entry per sequence (multi_token only)
 };
 
 // Bytes behind the plan's workspace that hold the per-token block table and its row index.
 size_t TokenTableBytes(const Prepared &p) {
-  if (!p.multi_token) return 0;
+  if (!p.multi_token || p.stacked) return 0;
   const size_t cells = static_cast<size_t>(p.batch) * static_cast<size_t>(p.desc.max_blocks_per_seq);
   return (cells * 4 + 255) / 256 * 256 + (static_cast<size_t>(p.batch) * 4 + 255) / 256 * 256;
 }
@@ -349,6 +352,8 @@ Prepared Prepare(const PaInputs &in) {
     if (in.block_tables.dim(0) != num_seqs)
       MS_VALUE_ERROR << "For PagedAttention, block_tables has " << in.block_tables.dim(0) << " rows but there are "
                      << num_seqs << " sequences.";
+    p.seq_lens = p.context_lens;
+    p.q_lens = q_lens;
     p.context_lens.swap(per_token);
     p.multi_token = true;
   }
@@ -451,12 +456,15 @@ Prepared Prepare(const PaInputs &in) {
       MS_VALUE_ERROR << "For PagedAttention, attn_mask must be float16/bfloat16/float32.";
     ds.mask_dtype = m.dtype();
   }
+  p.stacked = p.multi_token && msco_paged_attention_tma_supported(&ds) != 0;
   return p;
 }
 
-// Change detection of the host sequence lengths between consecutive calls of a thread
-// (the reference keeps them in the op's param and re-tiles on change).
-thread_local std::vector<int32_t> g_prev_context_lens;
+PlanRef GetPlan(const Prepared &p) {
+  if (p.stacked) return PlanCache::Instance().GetOrCreate(p.desc, p.seq_lens, &p.q_lens);
+  return PlanCache::Instance().GetOrCreate(p.desc, p.context_lens);
+}
+
 // Workspace bytes the last launch attempt of this thread needed (see ..._last_workspace_need).
 thread_local size_t g_last_workspace_need = 0;
 
@@ -490,7 +498,7 @@ extern "C" int ms_custom_ops_paged_attention_workspace_size(const MsPagedAttenti
   return GuardedCall(kOpName, [&] {
     const PaInputs in = Unpack(args);
     const Prepared p = Prepare(in);
-    PlanRef plan = PlanCache::Instance().GetOrCreate(p.desc, p.context_lens);
+    PlanRef plan = GetPlan(p);
     if (bytes)
       *bytes = (std::max<size_t>(msco_paged_attention_workspace_bytes(plan.get()), 256) + 255) / 256 * 256 +
                TokenTableBytes(p);
@@ -522,15 +530,14 @@ int LaunchPagedAttention(const MsPagedAttentionArgs *args, const Tensor &out, co
     CheckContiguous(lse_out, kOpName, "lse_out");
   }
   if (p.batch == 0) return MSCO_OK;
-  (void)CheckAndUpdate(p.context_lens, &g_prev_context_lens);
-  PlanRef plan = PlanCache::Instance().GetOrCreate(p.desc, p.context_lens);
+  PlanRef plan = GetPlan(p);
   const size_t plan_ws = (std::max<size_t>(msco_paged_attention_workspace_bytes(plan.get()), 256) + 255) / 256 * 256;
   g_last_workspace_need = plan_ws + TokenTableBytes(p);
   if (workspace == nullptr || workspace_bytes < g_last_workspace_need)
     MS_VALUE_ERROR << "For PagedAttention, the workspace holds " << workspace_bytes << " bytes but this launch needs "
                    << g_last_workspace_need << ".";
   const int32_t *tables = static_cast<const int32_t *>(in.block_tables.data());
-  if (p.multi_token) {
+  if (p.multi_token && !p.stacked) {
     // one block-table row per query token, built behind the plan's part of the workspace
     const size_t cells = static_cast<size_t>(p.batch) * static_cast<size_t>(p.desc.max_blocks_per_seq);
     int32_t *token_tables = reinterpret_cast<int32_t *>(static_cast<char *>(workspace) + plan_ws);

@@ -48,19 +48,23 @@ DescFields FieldsOf(const MscoPaDesc &desc) {
 }
 }  // namespace
 
-uint64_t MakeDescHash(const MscoPaDesc &desc) {
+uint64_t MakeDescHash(const MscoPaDesc &desc, bool multi_token) {
   const DescFields d = FieldsOf(desc);
-  return HashBytes(d.f, sizeof(d.f), 0x452821e638d01377ull ^ d.scale_bits);
+  return HashBytes(d.f, sizeof(d.f), (0x452821e638d01377ull ^ d.scale_bits) + (multi_token ? 1 : 0));
 }
 
-PlanKey MakePlanKey(const MscoPaDesc &desc, const std::vector<int32_t> &lens) {
+PlanKey MakePlanKey(const MscoPaDesc &desc, const std::vector<int32_t> &lens, const std::vector<int32_t> *q_lens) {
   DescFields d = FieldsOf(desc);
-  d.f[16] = static_cast<int64_t>(lens.size());
+  d.f[16] = static_cast<int64_t>(lens.size()) * 2 + (q_lens != nullptr ? 1 : 0);
   PlanKey k;
   k.h1 = HashBytes(d.f, sizeof(d.f), 0x243f6a8885a308d3ull ^ d.scale_bits);
   k.h2 = HashBytes(d.f, sizeof(d.f), 0x13198a2e03707344ull + d.scale_bits);
   k.h1 = HashBytes(lens.data(), lens.size() * sizeof(int32_t), k.h1);
   k.h2 = HashBytes(lens.data(), lens.size() * sizeof(int32_t), k.h2);
+  if (q_lens != nullptr) {
+    k.h1 = HashBytes(q_lens->data(), q_lens->size() * sizeof(int32_t), k.h1);
+    k.h2 = HashBytes(q_lens->data(), q_lens->size() * sizeof(int32_t), k.h2);
+  }
   return k;
 }
 
@@ -89,8 +93,9 @@ PlanCache::PlanCache() {
 }
 PlanCache::~PlanCache() = default;
 
-PlanRef PlanCache::GetOrCreate(const MscoPaDesc &desc, const std::vector<int32_t> &lens) {
-  const PlanKey key = MakePlanKey(desc, lens);
+PlanRef PlanCache::GetOrCreate(const MscoPaDesc &desc, const std::vector<int32_t> &lens,
+                               const std::vector<int32_t> *q_lens) {
+  const PlanKey key = MakePlanKey(desc, lens, q_lens);
   {
     std::lock_guard<std::mutex> g(mu_);
     auto it = map_.find(key);
@@ -111,7 +116,7 @@ PlanRef PlanCache::GetOrCreate(const MscoPaDesc &desc, const std::vector<int32_t
     b << "For PagedAttention, planning failed: " << msco_last_error();
     b.Throw();
   };
-  const uint64_t desc_hash = MakeDescHash(desc);
+  const uint64_t desc_hash = MakeDescHash(desc, q_lens != nullptr);
   // Recycle: take the least recently used unreferenced plan of the same descriptor out of the cache
   // and re-plan it in place for the new lengths (no allocation in the steady state).
   std::unique_ptr<Entry> reuse;
@@ -137,13 +142,18 @@ PlanRef PlanCache::GetOrCreate(const MscoPaDesc &desc, const std::vector<int32_t
   MscoPaPlan *plan = nullptr;
   if (reuse) {
     plan = reuse->plan;
-    const int rc = msco_paged_attention_replan(plan, lens.data(), static_cast<int32_t>(lens.size()));
+    const int rc = q_lens != nullptr
+                       ? msco_paged_attention_replan_tokens(plan, lens.data(), q_lens->data(), static_cast<int32_t>(lens.size()))
+                       : msco_paged_attention_replan(plan, lens.data(), static_cast<int32_t>(lens.size()));
     if (rc != MSCO_OK) {
       msco_paged_attention_plan_destroy(plan);  // its contents are undefined now
       throw_plan_error(rc);
     }
   } else {
-    const int rc = msco_paged_attention_plan(&desc, lens.data(), static_cast<int32_t>(lens.size()), &plan);
+    const int rc = q_lens != nullptr
+                       ? msco_paged_attention_plan_tokens(&desc, lens.data(), q_lens->data(),
+                                                          static_cast<int32_t>(lens.size()), &plan)
+                       : msco_paged_attention_plan(&desc, lens.data(), static_cast<int32_t>(lens.size()), &plan);
     if (rc != MSCO_OK) throw_plan_error(rc);
   }
   std::lock_guard<std::mutex> g(mu_);

@@ -42,9 +42,11 @@ struct PlanKeyHash {
   size_t operator()(const PlanKey &k) const { return static_cast<size_t>(k.h1 ^ (k.h2 * 0x9e3779b97f4a7c15ull)); }
 };
 
-PlanKey MakePlanKey(const MscoPaDesc &desc, const std::vector<int32_t> &context_lens);
-// Hash of the descriptor alone (what a re-plan must leave unchanged).
-uint64_t MakeDescHash(const MscoPaDesc &desc);
+// `q_seq_lens` (NULL for a decode batch): query tokens per sequence of a multi-token call.
+PlanKey MakePlanKey(const MscoPaDesc &desc, const std::vector<int32_t> &context_lens,
+                    const std::vector<int32_t> *q_seq_lens = nullptr);
+// Hash of the descriptor alone (what a re-plan must leave unchanged); decode and multi-token plans differ.
+uint64_t MakeDescHash(const MscoPaDesc &desc, bool multi_token = false);
 
 class PlanCache;
 
@@ -71,7 +73,8 @@ class PlanCache {
  public:
   static PlanCache &Instance();
   // Returns the cached plan for (desc, lens), building it on a miss.  Throws OpError on failure.
-  PlanRef GetOrCreate(const MscoPaDesc &desc, const std::vector<int32_t> &context_lens);
+  PlanRef GetOrCreate(const MscoPaDesc &desc, const std::vector<int32_t> &context_lens,
+                      const std::vector<int32_t> *q_seq_lens = nullptr);
   void Stats(int64_t *hits, int64_t *misses, int64_t *entries);
   // misses served by re-planning an existing plan in place / by building a new plan
   void MissStats(int64_t *recycled, int64_t *created);

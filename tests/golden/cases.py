@@ -68,6 +68,9 @@ MTP_CASES = {
     "lookahead_mixed": (9001, 32, 32, 128, 128, 64, [1, 15, 30, 6], [10, 64, 64, 64], "float16", None),
     "lookahead_block16": (9003, 32, 32, 128, 16, 256, [1, 15, 30, 6], [10, 64, 64, 64], "float16", None),
     "lookahead_gqa_bf16": (9004, 16, 4, 64, 32, 128, [3, 1, 8], [515, 40, 1300], "bfloat16", None),
+    # tests/st/test_custom_paged_attention.py:2853-2875 (contexts up to 33,331 tokens) and :2878-2900 (GQA 32 / 8)
+    "lookahead_very_long": (5005, 40, 40, 128, 128, 1234, [1, 1, 1], [13333, 23333, 33331], "float16", None),
+    "lookahead_gqa_32to8": (5006, 32, 8, 128, 128, 512, [1, 15, 30, 6], [10, 64, 64, 64], "float16", None),
 }
 
 

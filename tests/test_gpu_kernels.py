@@ -528,3 +528,21 @@ def test_pa_head_dims_64_and_256_in_the_tma_kernel(hd, bs, hq, hkv, dtype):
         assert rel_l2 < 1e-2, (kernel, rel_max, rel_l2)
         outs[kernel] = to_np(out).view(np.uint16)
     assert np.array_equal(outs[_abi.KERNEL_TMA], outs[_abi.KERNEL_AUTO])
+
+
+@pytest.mark.parametrize("n,scale", [(2, 0.12), (3, 0.3), (4, 0.05)])
+def test_in_kernel_merge_equals_the_reduce_kernel(monkeypatch, n, scale):
+    # MSCO_PA_FUSED_MERGE=1: the CTA that stores a group's last partial merges the group inside the attention
+    # kernel (same merge code, same split order): bit-identical to the reduce kernel's result
+    spec = workloads.config_spec(n, scale)
+    c = workloads.decode_case(spec)
+    args = (to_dev(c["query"]), to_dev(c["key_cache"]), to_dev(c["value_cache"]), to_dev(c["block_tables"]),
+            [int(x) for x in c["context_lens"]], c["qk_scale"], 1 if spec.kv_int8 else 0, to_dev(c["k_descale"]), None,
+            to_dev(c["v_descale"]), None)
+    monkeypatch.delenv("MSCO_PA_FUSED_MERGE", raising=False)
+    ref, info = kernels.paged_attention_raw(*args)
+    assert info.partials > 0
+    monkeypatch.setenv("MSCO_PA_FUSED_MERGE", "1")
+    for _ in range(3):
+        out, _ = kernels.paged_attention_raw(*args)
+        assert np.array_equal(to_np(out).view(np.uint16), to_np(ref).view(np.uint16))

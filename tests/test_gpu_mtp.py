@@ -62,3 +62,19 @@ def test_multi_token_queries_without_mask_and_with_empty_sequences():
                                 to_dev(v1["block_tables"]), torch.from_numpy(c1["context_lens"]), q_head_num=8,
                                 kv_head_num=2, qk_scale=c1["qk_scale"])
     assert np.array_equal(out1, to_np(plain))
+
+
+@pytest.mark.parametrize("mask", [False, True])
+@pytest.mark.parametrize("heads,kvh,dtype", [(32, 8, "bfloat16"), (16, 16, "float16"), (64, 8, "float16")])
+def test_stacked_query_tokens_over_long_contexts(heads, kvh, dtype, mask):
+    # several query tokens per sequence over contexts of several KV splits: the tokens of a sequence are
+    # stacked into the q rows of one work item (one read of the context), partials are kept per token
+    c = st_inputs.st_style_case(91, heads, kvh, 128, 128, 128, [5000, 1300, 700, 2049], dtype, None, 0, False,
+                                3 if mask else 0, None, q_seq_lens=[4, 3, 9, 1])
+    v, out = _run(c, with_mask=mask)
+    g = oracle.paged_attention_golden(v["query"], v["key_cache"], v["value_cache"], v["block_tables"],
+                                      c["context_lens"], c["qk_scale"], mask=v["mask"] if mask else None,
+                                      mask_type=3 if mask else 0, q_seq_lens=c["q_seq_lens"])
+    assert_close(out, g, tol_for(dtype, False), f"stacked {heads}/{kvh} mask={mask}")
+    rel_max, rel_l2 = oracle.scale_free_error(out, g)
+    assert rel_l2 < 1e-2, (rel_max, rel_l2)

@@ -160,9 +160,16 @@ def test_multi_token_queries_infer_and_validation():
         ops.paged_attention_infer(q6, KC, KC, BT, LENS, **dict(spec, attn_mask=T((6, 512), "float16")))
     with pytest.raises(ValueError, match="block_tables has 5 rows"):
         ops.paged_attention_infer(q6, KC, KC, T((5, 8), "int32"), LENS, **mtp)
-    # the workspace also holds one block-table row and one index per query token
+    # head_dim 128: the tokens of a sequence are stacked into the q rows of the work items, the plan of one
+    # token per sequence is the decode plan
     plain = ops.paged_attention_workspace_size(Q, KC, KC, BT, LENS, **OKW)
     one_each = ops.paged_attention_workspace_size(Q, KC, KC, BT, LENS, **dict(OKW, calc_type=1, q_seq_lens=[1] * 4))
+    assert one_each == plain
+    # a head_dim the TMA kernel does not serve: one decode row per token, and the workspace also holds one
+    # block-table row and one index per query token
+    q40, kc40 = T((4, 32, 40), "float16"), T((64, 128, 8, 40), "float16")
+    plain = ops.paged_attention_workspace_size(q40, kc40, kc40, BT, LENS, **OKW)
+    one_each = ops.paged_attention_workspace_size(q40, kc40, kc40, BT, LENS, **dict(OKW, calc_type=1, q_seq_lens=[1] * 4))
     assert one_each == (plain + 255) // 256 * 256 + 256 + 256
 
 
@@ -427,3 +434,21 @@ def test_reshape_and_cache_npd_checks():
         ops.reshape_and_cache_npd_infer(k, k, cb, cb, sm, key_value_layout="TH")  # BSND-shaped cache read as BNSD
     with pytest.raises(TypeError):
         ops.reshape_and_cache_npd_infer(k, k, c, c, T((32,), "int64"), key_value_layout="TH")
+
+
+def test_stacked_query_tokens_plan():
+    # 4 q heads per kv head: up to 4 consecutive tokens of a sequence share one work item (16 q rows)
+    def plan(ql, lens, hq=32, hkv=8, **kw):
+        desc = _plan(lens, hq=hq, hkv=hkv, **kw).desc
+        return _abi.PaPlan(desc, lens, ql)
+    one = _plan([3000, 100]).info()
+    st = plan([4, 1], [3000, 100]).info()
+    assert st.rows_per_item == 16 and st.work_items == one.work_items and st.kv_tokens == one.kv_tokens
+    st = plan([9, 0], [3000, 100]).info()            # 9 tokens -> runs of 4, 4, 1; the second sequence has no query
+    assert st.work_items == 3 * 6 * 8 and st.partials == (4 + 4 + 1) * 6
+    st = plan([2, 2], [600, 0]).info()               # an empty context: its rows are zero-filled, no items
+    assert st.work_items == 2 * 8
+    assert plan([3, 3], [100, 200], hq=64, hkv=8).info().work_items == 2 * 2 * 8   # 8 q heads per kv head: 2 tokens per item
+    assert plan([3], [100], hq=128, hkv=8).info().work_items == 3 * 8              # 16 per kv head: one token per item
+    with pytest.raises(_abi.MscoError, match="TMA kernel"):
+        plan([2], [100], d=40)
