@@ -46,10 +46,12 @@ extern "C" const char *msco_last_error(void) { return g_err; }
 // K/V per kv head at the short end, so that the per-split merge is amortised.
 extern "C" int32_t msco_paged_attention_split_tokens(int32_t context_len, int32_t kv_dtype) {
   if (context_len > 65536) return 2048;
-  if (context_len > 16384) return 1024;
-  static const int tune8 = getenv("MSCO_TUNE_INT8_SPLIT") ? atoi(getenv("MSCO_TUNE_INT8_SPLIT")) : 0;  // TUNING ONLY
-  if (tune8 > 0 && kv_dtype == MSCO_DTYPE_I8) return tune8;
-  return kv_dtype == MSCO_DTYPE_I8 ? 1024 : 512;
+  if (context_len > 16384) return kv_dtype == MSCO_DTYPE_I8 ? 2048 : 1024;
+  // an int8 token is half the bytes, and the int8 kernel's per-item cost (q rows converted, 8 warps merged
+  // through shared memory) is the larger one: contexts of up to 4096 tokens are one item, longer ones
+  // are cut every 2048 tokens
+  if (kv_dtype == MSCO_DTYPE_I8) return context_len <= 4096 ? 4096 : 2048;
+  return 512;
 }
 
 static int validate_desc(const MscoPaDesc &d) {
@@ -201,9 +203,10 @@ int fill_plan(MscoPaPlan *pl, const int32_t *host_context_lens, const int32_t *q
     // per output row (the reduce kernel's view): splits and first partial.  When the attention kernel
     // merges its partials itself the reduce kernel only zero-fills the rows of empty sequences, so every
     // other row is marked as written.
+    // (partials of a run of stacked tokens are token-major: token t, split s -> parts + t * ns + s)
     for (int t = 0; t < e.ntok; ++t) {
       b_nsplit[e.qtok0 + t] = fused ? 1 : ns;
-      b_part_base[e.qtok0 + t] = (int32_t)parts;
+      b_part_base[e.qtok0 + t] = (int32_t)(parts + (int64_t)t * ns);
     }
     items += (int64_t)ns * items_per_split;
     if (ns > 1) parts += (int64_t)ns * e.ntok;

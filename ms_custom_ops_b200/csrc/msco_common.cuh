@@ -83,7 +83,7 @@ __host__ __device__ inline PlanView make_plan_view(const int32_t *w) {
 struct WorkItem {
   int b, kvh, row0, nrows, tok0, tok1, nsplit, part;
   int grp;    // index of the (sequence, kv head, q-row block) group: one arrival counter per group
-  int part0;  // partial row of the group's first split and first token: part = part0 + split * ntok + token
+  int part0;  // partial row of the group's first token and first split: token t, split s -> part0 + t * nsplit + s
   int qtok0;  // first query token (row of query / out) of the item; the sequence index b for a decode batch
   int ntok;   // query tokens stacked into the item (1 for a decode batch): q row r is token r / group
 };
@@ -159,7 +159,7 @@ __device__ __forceinline__ WorkItem decode_item(const PlanView &pv, int t, int n
     w.ntok = __ldg(pv.qntok + s);
     if (w.ntok > 1) w.nrows = w.ntok * g;  // one row block holds the whole run (the planner sees to it)
   }
-  w.part = w.part0 + split * w.ntok;
+  w.part = w.part0 + split;  // of the item's first token
   return w;
 }
 

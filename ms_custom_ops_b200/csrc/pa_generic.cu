@@ -235,9 +235,9 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p, const __grid
   }
   const int base = __ldg(pv.b_part_base + b);
   // same code as the TMA kernel's own epilogue: identical bits
-  if (D == 128) { merge_row<TQ, 128>(p, row, hq, ns, base, 1, lane); return; }
-  if (D == 64) { merge_row<TQ, 64>(p, row, hq, ns, base, 1, lane); return; }
-  if (D == 256) { merge_row<TQ, 256>(p, row, hq, ns, base, 1, lane); return; }
+  if (D == 128) { merge_row<TQ, 128>(p, row, hq, ns, base, lane); return; }
+  if (D == 64) { merge_row<TQ, 64>(p, row, hq, ns, base, lane); return; }
+  if (D == 256) { merge_row<TQ, 256>(p, row, hq, ns, base, lane); return; }
   const int64_t hq_stride = p.num_q_heads;
   // pass 1: M = max_s m_s (lanes stride over the splits)
   float M = kNeg;

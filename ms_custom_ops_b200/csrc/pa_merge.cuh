@@ -19,14 +19,12 @@ __device__ __forceinline__ float merge_warp_max(float v) {
   return v;
 }
 
-// One warp merges output row `row` (= query token * num_q_heads + hq): `ns` >= 2 splits whose partial rows are
-// base, base + stride, base + 2 stride, ... (stride 1 for a decode batch; the number of stacked query tokens
-// of the item for multi-token queries).
+// One warp merges output row `row` (= query token * num_q_heads + hq): `ns` >= 2 splits whose partial rows
+// are base, base + 1, ..., base + ns - 1.
 // D = head_dim (64, 128 or 256): a lane owns D / 32 consecutive columns.
 // All loads bypass L1 (ld.global.cg): the partials may have been written by other SMs of the same grid.
 template <typename TQ, int D>
-__device__ __forceinline__ void merge_row(const PaParams &p, int64_t row, int hq, int ns, int base, int stride,
-                                          int lane) {
+__device__ __forceinline__ void merge_row(const PaParams &p, int64_t row, int hq, int ns, int base, int lane) {
   static_assert(D == 64 || D == 128 || D == 256, "head_dim 64, 128 or 256");
   constexpr int kCols = D / 32;  // columns per lane: 2, 4 or 8
   constexpr float kNegBig = -1.0e30f;
@@ -34,7 +32,7 @@ __device__ __forceinline__ void merge_row(const PaParams &p, int64_t row, int hq
   const int64_t hq_stride = p.num_q_heads;
   // pass 1: M = max_s m_s (lanes stride over the splits)
   float M = kNegBig;
-  for (int s = lane; s < ns; s += 32) M = fmaxf(M, __ldcg(p.part_ml + ((int64_t)(base + s * stride) * hq_stride + hq) * 2));
+  for (int s = lane; s < ns; s += 32) M = fmaxf(M, __ldcg(p.part_ml + ((int64_t)(base + s) * hq_stride + hq) * 2));
   M = merge_warp_max(M);
   const int kvh = hq / p.group;
   float L = 0.f;
@@ -46,7 +44,7 @@ __device__ __forceinline__ void merge_row(const PaParams &p, int64_t row, int hq
     float f_mine = 0.f, l_mine = 0.f;
     if (s0 + lane < ns) {
       const float2 ml =
-          __ldcg(reinterpret_cast<const float2 *>(p.part_ml + ((int64_t)(base + (s0 + lane) * stride) * hq_stride + hq) * 2));
+          __ldcg(reinterpret_cast<const float2 *>(p.part_ml + ((int64_t)(base + s0 + lane) * hq_stride + hq) * 2));
       f_mine = exp2f(ml.x - M);
       l_mine = ml.y;
     }
@@ -55,7 +53,7 @@ __device__ __forceinline__ void merge_row(const PaParams &p, int64_t row, int hq
     for (int j = 0; j < cnt; ++j) {
       const float f = __shfl_sync(0xffffffffu, f_mine, j);
       const float lj = __shfl_sync(0xffffffffu, l_mine, j);
-      const float *src = p.part_o + ((int64_t)(base + (s0 + j) * stride) * hq_stride + hq) * D + lane * kCols;
+      const float *src = p.part_o + ((int64_t)(base + s0 + j) * hq_stride + hq) * D + lane * kCols;
       float v[kCols];
       if (kCols == 2) {
         const float2 t = __ldcg(reinterpret_cast<const float2 *>(src));

@@ -376,7 +376,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       const int gt = gntok > 1 ? p.group : 16;  // q rows per stacked token (a decode item is one token)
       for (int r = warp; r < gnrows; r += C::kWarps) {
         const int tq = r / gt, j = r - tq * gt;
-        merge_row<T, D>(p, (int64_t)(gq0 + tq) * p.num_q_heads + ghq0 + j, ghq0 + j, gns, gpart0 + tq, gntok, lane);
+        merge_row<T, D>(p, (int64_t)(gq0 + tq) * p.num_q_heads + ghq0 + j, ghq0 + j, gns, gpart0 + tq * gns, lane);
       }
     }
     ++n_checked;
@@ -735,7 +735,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           pk.y = pack2<T>(r2, r3);
           *reinterpret_cast<uint2 *>(static_cast<T *>(p.out) + orow * D + c4) = pk;
         } else {
-          const int64_t prow = (int64_t)(part + tq) * p.num_q_heads + hq;
+          const int64_t prow = (int64_t)(part + tq * nsplit) * p.num_q_heads + hq;
           *reinterpret_cast<float4 *>(p.part_o + prow * D + c4) = acc;
           if (c4 == 0) *reinterpret_cast<float2 *>(p.part_ml + prow * 2) = make_float2(M, L);
         }

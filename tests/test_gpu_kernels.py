@@ -387,7 +387,7 @@ def test_pa_benchmark_configs_full_size(n):
     desc = kernels.make_pa_desc(c["query"], c["key_cache"], c["block_tables"], c["qk_scale"], quant)
     plan = _abi.PaPlan(desc, [int(x) for x in lens])
     info = plan.info()
-    assert info.kernel == 2 and info.partials > 0
+    assert info.kernel == 2 and (info.partials > 0 or n == 3)  # C3: int8 contexts of up to 4096 tokens are one item
     ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device="cuda")
     out = torch.empty_like(c["query"])
     slots = workloads.slots_of_last_token(c["block_tables_host"], lens, spec.block_size)
@@ -535,6 +535,8 @@ def test_in_kernel_merge_equals_the_reduce_kernel(monkeypatch, n, scale):
     # MSCO_PA_FUSED_MERGE=1: the CTA that stores a group's last partial merges the group inside the attention
     # kernel (same merge code, same split order): bit-identical to the reduce kernel's result
     spec = workloads.config_spec(n, scale)
+    if spec.kv_int8:  # long enough for several int8 splits
+        spec.batch, spec.len_lo, spec.len_hi = 12, 3000, 9000
     c = workloads.decode_case(spec)
     args = (to_dev(c["query"]), to_dev(c["key_cache"]), to_dev(c["value_cache"]), to_dev(c["block_tables"]),
             [int(x) for x in c["context_lens"]], c["qk_scale"], 1 if spec.kv_int8 else 0, to_dev(c["k_descale"]), None,

@@ -275,7 +275,7 @@ def test_split_rule_depends_on_the_sequence_only():
     g = _abi.lib().msco_paged_attention_split_tokens
     f = lambda n: g(n, _abi.DTYPE_BF16)
     assert [f(n) for n in (1, 512, 513, 16384, 16385, 65536, 65537, 131072)] == [512] * 4 + [1024] * 2 + [2048] * 2
-    assert [g(n, _abi.DTYPE_I8) for n in (1, 1024, 16384, 16385, 65537)] == [1024] * 4 + [2048]
+    assert [g(n, _abi.DTYPE_I8) for n in (1, 4096, 4097, 16384, 16385, 65537)] == [4096] * 2 + [2048] * 4
     lens = [5000, 300, 0, 70000, 512, 513]
     info = _plan(lens).info()
     splits = [(n + f(n) - 1) // f(n) if n else 0 for n in lens]

@@ -28,6 +28,8 @@ def _p(t):
 
 def _case(spec_n, scale, seed_shift=0):
     spec = workloads.config_spec(spec_n, scale)
+    if spec.kv_int8:  # long enough for several int8 splits (contexts of up to 4096 int8 tokens are one item)
+        spec.batch, spec.len_lo, spec.len_hi = 10, 3000, 9000
     spec.seed += seed_shift
     c = workloads.decode_case(spec)
     dev = {k: to_dev(c[k]) for k in ("query", "key_cache", "value_cache", "block_tables")}
