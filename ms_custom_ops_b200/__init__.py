@@ -232,11 +232,18 @@ def _pa_args(D, query, key_cache, value_cache, block_tables, context_lens, attn_
         a = cache[attrs] = _host.MsPagedAttentionArgs()
     a.query, a.key_cache, a.value_cache, a.block_tables = D(query), D(key_cache), D(value_cache), D(block_tables)
     a.context_lens = D(context_lens, host_ok=True)
-    a.attn_mask = D(attn_mask)
-    a.batch_run_status = D(batch_run_status, host_ok=True)
-    a.k_descale, a.k_offset, a.v_descale, a.v_offset = D(k_descale), D(k_offset), D(v_descale), D(v_offset)
-    a.razor_offset, a.p_scale, a.log_n = D(razor_offset), D(p_scale), D(log_n)
-    a.q_seq_lens = D(q_seq_lens, host_ok=True)
+    # optional tensors: most are absent in most calls; a field is only touched when it is, or was, set
+    opt = (attn_mask, batch_run_status, k_descale, k_offset, v_descale, v_offset, razor_offset, p_scale, log_n,
+           q_seq_lens)
+    was = a._msco_optional_set if not fresh else ()
+    now = []
+    for name, t in zip(_PA_OPTIONAL, opt):
+        if t is not None:
+            setattr(a, name, D(t, host_ok=name in ("batch_run_status", "q_seq_lens")))
+            now.append(name)
+        elif name in was:
+            setattr(a, name, None)
+    a._msco_optional_set = now
     if not fresh:
         return a
     a.q_head_num, a.qk_scale, a.kv_head_num = int(q_head_num), float(qk_scale), int(kv_head_num)
@@ -310,15 +317,26 @@ def _paged_attention(with_lse, query, *rest):
     dev = query.device
     sh = torch.cuda.current_stream(dev).cuda_stream
     stream = C.c_void_p(sh)
+    # the output has query's shape, strides and dtype: its descriptor is a copy of query's with another address
+    od = _tls.__dict__.get("out_desc")
+    if od is None:
+        od = _tls.out_desc = _host.MsTensorDesc()
+        _tls.out_desc_ptr = C.pointer(od)
+    if query.is_contiguous() and a.query:
+        C.memmove(C.byref(od), a.query, C.sizeof(od))
+        od.data = out.data_ptr()
+        out_ptr = _tls.out_desc_ptr
+    else:
+        out_ptr = D(out)
     if with_lse:
         lse = torch.empty(query.shape[:2], dtype=torch.float32, device=dev)
 
         def launch(ws):
-            return L.ms_custom_ops_paged_attention_with_lse(C.byref(a), D(out), D(lse), C.c_void_p(ws.data_ptr()),
+            return L.ms_custom_ops_paged_attention_with_lse(C.byref(a), out_ptr, D(lse), C.c_void_p(ws.data_ptr()),
                                                             ws.numel(), stream)
     else:
         def launch(ws):
-            return L.ms_custom_ops_paged_attention(C.byref(a), D(out), C.c_void_p(ws.data_ptr()), ws.numel(), stream)
+            return L.ms_custom_ops_paged_attention(C.byref(a), out_ptr, C.c_void_p(ws.data_ptr()), ws.numel(), stream)
     # launch with the workspace at hand; if it is too small nothing was launched and the library
     # tells how much is needed (one validation + plan lookup per call in the steady state)
     ws = _workspace(dev, 0, sh)

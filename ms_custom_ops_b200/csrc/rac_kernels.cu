@@ -257,26 +257,30 @@ rac_scatter_quant_kernel(const T *__restrict__ key, const T *__restrict__ value,
 // e differs from x / d by less than |e| * 2^-24 * 1.01 < 0.0003 for |e| < 4097, and the correctly
 // rounded quotient from x / d by at most half an ulp <= 0.00025, so |t| <= 0.498 and |q| < 4096 put
 // fl(x / d) strictly within 0.5 of q: rint(fl(x / d)) = q.  Otherwise -- ties, huge quotients, zero,
-// denormal or non-finite scales, NaN -- the IEEE division is done.  The result is clamped to
-// [-128, 127] as a float (NaN -> 0 first) and M is added once more: the low byte of the sum's bit
-// pattern is the two's-complement int8.  No conversion instruction on the path; four results are
-// packed with three byte permutes.  Bit-identical to the division everywhere.
+// denormal or non-finite scales, NaN -- the IEEE division is done (quant_exact).
+// z - offset is still an integer in M's binade, so the saturation to [-128, 127] is a clamp of that
+// float to [M - 128, M + 127], and the low byte of the clamped float's bit pattern is the
+// two's-complement int8.  No conversion instruction on the path; the eight elements of a 16-byte load
+// share ONE branch (taken when any of them needs the division); four results are packed with three
+// byte permutes.  Bit-identical to the division everywhere.
+constexpr float kQMagic = 12582912.f;
 template <bool HAS_OFF>
-__device__ __forceinline__ uint32_t quant_fast(float x, float r, float off, const float *dptr) {
-  const float kMagic = 12582912.f;
-  const float z = fmaf(x, r, kMagic);
-  const float q = z - kMagic;
+__device__ __forceinline__ uint32_t quant_fast(float x, float r, float off, bool &ok) {
+  const float z = fmaf(x, r, kQMagic);
+  const float q = z - kQMagic;
   const float t = fmaf(x, r, -q);
-  float v;
-  if ((fabsf(q) < 4096.f) && (fabsf(t) <= 0.498f)) {
-    v = HAS_OFF ? q - off : q;  // integral, |v| <= 8192
-  } else {
-    v = rintf(__fdiv_rn(x, __ldg(dptr)));
-    if (HAS_OFF) v = __fsub_rn(v, off);
-    if (v != v) v = 0.f;
-  }
+  ok = ok && (fabsf(q) < 4096.f) && (fabsf(t) <= 0.498f);
+  const float zz = HAS_OFF ? z - off : z;
+  return __float_as_uint(fminf(fmaxf(zz, kQMagic - 128.f), kQMagic + 127.f));  // low byte: the int8
+}
+// the same element by the IEEE division, for the groups the fast test does not cover
+template <bool HAS_OFF>
+__device__ __noinline__ uint32_t quant_exact(float x, float d, float off) {
+  float v = rintf(__fdiv_rn(x, d));
+  if (HAS_OFF) v = __fsub_rn(v, off);
+  if (v != v) v = 0.f;
   v = fminf(fmaxf(v, -128.f), 127.f);
-  return __float_as_uint(v + kMagic);  // low byte: the int8
+  return __float_as_uint(v + kQMagic);
 }
 // byte 0 of four words -> one word
 __device__ __forceinline__ uint32_t pack_low_bytes(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
@@ -368,9 +372,13 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
         if (e < elems) {
           const T *x = reinterpret_cast<const T *>(&cur[it]);
           uint32_t w[8];
+          bool ok = true;
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            w[i] = quant_fast<HAS_OFF>(to_f32<T>(x[i]), r[it][i], HAS_OFF ? o[it][i] : 0.f, ds + e + i);
+          for (int i = 0; i < 8; ++i) w[i] = quant_fast<HAS_OFF>(to_f32<T>(x[i]), r[it][i], HAS_OFF ? o[it][i] : 0.f, ok);
+          if (!ok) {  // rare: a tie, a huge quotient, an odd scale somewhere in these eight
+#pragma unroll 1
+            for (int i = 0; i < 8; ++i) w[i] = quant_exact<HAS_OFF>(to_f32<T>(x[i]), __ldg(ds + e + i), HAS_OFF ? o[it][i] : 0.f);
+          }
           const uint32_t lo = pack_low_bytes(w[0], w[1], w[2], w[3]), hi = pack_low_bytes(w[4], w[5], w[6], w[7]);
           asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(dst + it * 256), "r"(lo), "r"(hi) : "memory");
         }
