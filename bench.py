@@ -14,8 +14,9 @@ Printed JSON line (rank 0):
              host->device copies of query / new rows / slots / block tables and the device->host
              read of the attention output are inside the timed region; `value` is the serial loop
              (the host waits for every step's result), the pipelined figure is printed beside it
-  configs    the other benchmark configurations (c3 int8 KV, c4 long skewed, c5 mixed decode, and
-             the prefill-heavy scatter of c5): throughput, attention-kernel time, roofline, parity
+  configs    the other benchmark configurations (c3 int8 KV, c4 long skewed, c5 mixed decode, the
+             prefill-heavy scatter of c5, and configuration 2 at head_dim 64 / 256): throughput,
+             attention-kernel time, roofline, parity
   roofline   the attention kernel alone: algorithmic bytes / its CUDA-event duration, against the
              measured HBM copy bandwidth (MEASURED_PEAKS.json, else the stated fallback)
   cpu_baseline  the CPU restatement of the reference golden (oracle/, all host cores), timed on
@@ -56,8 +57,17 @@ L2_BYTES = 126 << 20
 
 
 def workload_spec(name):
-    n = int(name.lower().lstrip("c"))
-    return workloads.config_spec(n)
+    """c1..c5: the benchmark configurations; c2h64 / c2h256: configuration 2 with head_dim 64 / 256 (block_size
+    64 for 256: the operator requires block_size * head_dim <= 128 * 128)."""
+    name = name.lower()
+    if "h" in name:
+        base, hd = name.split("h")
+        spec = workloads.config_spec(int(base.lstrip("c")))
+        spec.head_size = int(hd)
+        spec.block_size = min(spec.block_size, 128 * 128 // spec.head_size)
+        spec.name += f"-head{hd}"
+        return spec
+    return workloads.config_spec(int(name.lstrip("c")))
 
 
 def workload_config(spec, lens, extra=None):
@@ -439,7 +449,7 @@ def measure_decode(ctx, spec, args, full):
     # summarised in profiles/pa_tma_kernel_*.md, per context token per kv head, scaled to this
     # launch (traffic grows in proportion to the tokens read; measured on one GPU holding all heads)
     if info.kernel == 2:
-        per = NCU_DRAM_BYTES_PER_TOKEN_HEAD["int8" if spec.kv_int8 else "16bit"]
+        per = NCU_DRAM_BYTES_PER_TOKEN_HEAD["int8" if spec.kv_int8 else "16bit"] * spec.head_size / 128.0
         roofline["traffic"] = per * float(loop.lens_at(first_prof + nprof // 2).sum()) * loop.hpr
         roofline["traffic_source"] = ("ncu capture of config " + ("3" if spec.kv_int8 else "2") +
                                       " on one GPU, scaled by tokens x kv heads of this rank")
@@ -650,7 +660,9 @@ def run_gpu(args):
     # ---- the other benchmark configurations, same loop, device-timed + kernel roofline + parity ----
     extras = {}
     if not args.no_extra:
-        names = ["c3", "c4", "c5"] if world == 1 else ["c4"]
+        names = ["c3", "c4", "c5", "c2h64", "c2h256"] if world == 1 else ["c4"]
+        if args.configs:
+            names = [n for n in names if n in args.configs.split(",")]
         for name in names:
             if name == args.workload.lower():
                 continue
@@ -668,7 +680,7 @@ def run_gpu(args):
                     "split_partials": r["config"]["split_partials"]}
     peak, _ = measured_hbm_peak()
     scatter = adjacent = None
-    if world == 1 and not args.no_extra:
+    if world == 1 and not args.no_extra and (not args.configs or "rac_prefill" in args.configs.split(",")):
         scatter = measure_scatter(workload_spec("c5"), dev, peak)
         if rank == 0:
             extras["rac_prefill"] = scatter
@@ -1028,6 +1040,8 @@ def main():
     ap.add_argument("--no-extra", action="store_true",
                     help="only the headline workload (skip the `configs` entries: c3, c4, c5, prefill scatter)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="time budget of one CPU baseline leg")
+    ap.add_argument("--configs", default="", help="comma-separated subset of the `configs` entries to run "
+                    "(c3,c4,c5,c2h64,c2h256,rac_prefill); default: all")
     ap.add_argument("--nccl-gather", action="store_true", help="exchange outputs with NCCL instead of peer stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity check")
     ap.add_argument("--seq-parallel", action="store_true",

@@ -49,7 +49,8 @@ __device__ __forceinline__ void merge_row(const PaParams &p, int64_t row, int hq
       l_mine = ml.y;
     }
     const int cnt = min(32, ns - s0);
-#pragma unroll 8
+    // 16 partial rows in flight per lane: the loop is a chain of L2 round trips otherwise
+#pragma unroll 16
     for (int j = 0; j < cnt; ++j) {
       const float f = __shfl_sync(0xffffffffu, f_mine, j);
       const float lj = __shfl_sync(0xffffffffu, l_mine, j);
