@@ -260,7 +260,6 @@ int new_plan(const MscoPaDesc *desc, const int32_t *lens, const int32_t *q_lens,
   if (pl == nullptr) return fail(MSCO_ERR_INTERNAL, "paged_attention_plan: out of host memory");
   pl->desc = d;
   pl->kernel = kernel;
-  if (const char *e = getenv("MSCO_PA_INT8_SUBS")) pl->int8_subs = atoi(e) == 1 ? 1 : 2;   // TUNING ONLY
   // MSCO_PA_FUSED_MERGE=1: the attention kernel merges its split partials itself (the CTA that stores a
   // group's last partial does it) instead of leaving them to the reduce kernel: one launch less per step,
   // paid for with a device-scope fence and an atomic per multi-split item

@@ -81,7 +81,6 @@ struct MscoPaPlan {
   bool fused_merge = false;     // the attention kernel merges the split partials itself
   bool fused_merge_wanted = false;
   bool multi_token = false;     // planned from (context_lens, q_seq_lens): `batch` counts query tokens
-  int int8_subs = 2;            // int8 KV, up to 8 q rows: 16-token sub-tiles per consumer warp (1 or 2)
   int num_groups = 0;           // (sequence with tokens, kv head, q-row block) triples
   size_t sync_offset = 0;       // scheduling words inside the workspace
   size_t sync_bytes = 0;

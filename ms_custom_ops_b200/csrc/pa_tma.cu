@@ -50,9 +50,9 @@ constexpr int kDescInts = 12;  // work-item descriptor handed from the producer 
 template <int D, bool KV8, int NT, int SUBS> struct Cfg {
   static_assert(D == 64 || D == 128 || D == 256, "head_dim 64, 128 or 256");
   static_assert(!KV8 || D == 128, "int8 KV: head_dim 128");
-  static_assert(SUBS == 1 || (SUBS == 2 && KV8 && NT == 1), "two sub-tiles per warp: int8 KV, up to 8 q rows");
+  static_assert((SUBS == 2) == (KV8 && NT == 1), "two sub-tiles per warp exactly for int8 KV with up to 8 q rows");
   static_assert(D != 256 || NT == 1, "head_dim 256: up to 8 q rows per item");
-  static constexpr int kWarps = D == 256 ? 4 : ((KV8 && NT == 1 && SUBS == 1) ? 16 : 8);  // consumer warps
+  static constexpr int kWarps = D == 256 ? 4 : 8;           // consumer warps
   static constexpr int kTile = kWarps * 16 * SUBS;          // tokens per tile
   static constexpr int kAux = KV8 ? 1 : 0;                  // helper warp that prepares Q (int8 KV)
   // warps: consumers, the producer, the warp that counts stored partials, (int8 KV) the Q-preparation warp
@@ -883,7 +883,6 @@ int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp
   const bool f16 = plan->desc.q_dtype == MSCO_DTYPE_F16;
   const bool masked = plan->desc.mask_type != 0;
   const int hd = plan->desc.head_dim;
-  const bool subs2 = kv8 && !g16 && plan->int8_subs == 2;
 #define MSCO_GO(T, D, A, B, S)                                                                      \
   do {                                                                                              \
     if (masked) return launch_one<T, D, A, B, true, S>(plan, p, pp, tk, tv, stream, after_kernel);  \
@@ -895,8 +894,7 @@ int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp
     if (hd == 256) MSCO_GO(T, 256, false, 1, 1);                          \
     if (kv8) {                                                            \
       if (g16) MSCO_GO(T, 128, true, 2, 1);                               \
-      if (subs2) MSCO_GO(T, 128, true, 1, 2);                             \
-      MSCO_GO(T, 128, true, 1, 1);                                        \
+      MSCO_GO(T, 128, true, 1, 2);                                        \
     }                                                                     \
     if (g16) MSCO_GO(T, 128, false, 2, 1);                                \
     MSCO_GO(T, 128, false, 1, 1);                                         \

@@ -254,10 +254,14 @@ rac_scatter_quant_kernel(const T *__restrict__ key, const T *__restrict__ value,
 // rint(x / d) without a division, exactly: with r = fl(1 / d) and e = x * r (the exact product),
 //   z = fma(x, r, M), M = 1.5 * 2^23   rounds e to the nearest integer (ties to even) for |e| < 2^22,
 //   q = z - M                          is that integer, t = fma(x, r, -q) = e - q its distance to e.
-// e differs from x / d by less than |e| * 2^-24 * 1.01 < 0.0003 for |e| < 4097, and the correctly
-// rounded quotient from x / d by at most half an ulp <= 0.00025, so |t| <= 0.498 and |q| < 4096 put
-// fl(x / d) strictly within 0.5 of q: rint(fl(x / d)) = q.  Otherwise -- ties, huge quotients, zero,
-// denormal or non-finite scales, NaN -- the IEEE division is done (quant_exact).
+// e differs from x / d by at most |e| * 2^-24 (r is correctly rounded), and the correctly rounded
+// quotient from x / d by at most half an ulp: together less than 3.1e-5 for |q| <= 258, so
+// |t| <= 0.49995 puts fl(x / d) strictly within 0.5 of q: rint(fl(x / d)) = q (the margin holds up to
+// |q| < 512).  Quotients that leave the int8 range by more than 1 after the offset (|q| - |offset| >= 258
+// covers every |q| >= 512, offsets being at most 128 on this path) saturate whichever way they round.  Otherwise -- ties, huge quotients, zero, denormal or non-finite scales, NaN --
+// the IEEE division is done (quant_exact).  The test is this tight on purpose: one lane that fails it
+// sends its whole warp through the division for that group, and with 0.01 % of the values failing
+// that happens in 2.5 % of the groups (a +-0.002 band would make it 65 %).
 // z - offset is still an integer in M's binade, so the saturation to [-128, 127] is a clamp of that
 // float to [M - 128, M + 127], and the low byte of the clamped float's bit pattern is the
 // two's-complement int8.  No conversion instruction on the path; the eight elements of a 16-byte load
@@ -269,7 +273,9 @@ __device__ __forceinline__ uint32_t quant_fast(float x, float r, float off, bool
   const float z = fmaf(x, r, kQMagic);
   const float q = z - kQMagic;
   const float t = fmaf(x, r, -q);
-  ok = ok && (fabsf(q) < 4096.f) && (fabsf(t) <= 0.498f);
+  // (a quotient whose distance to the int8 range exceeds 1 saturates whichever way it rounds)
+  const float aq = fabsf(q);
+  ok = ok && (aq < 4096.f) && (fabsf(t) <= 0.49995f || aq - (HAS_OFF ? fabsf(off) : 0.f) >= 258.f);
   const float zz = HAS_OFF ? z - off : z;
   return __float_as_uint(fminf(fmaxf(zz, kQMagic - 128.f), kQMagic + 127.f));  // low byte: the int8
 }
@@ -332,8 +338,9 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
       r[it][i] = __frcp_rn(dd[i]);
       if (HAS_OFF) {
         o[it][i] = (float)oo[i];
-        // offsets this large would make q - off inexact in the fast path: force the exact path
-        if (fabsf(o[it][i]) > 4096.f) r[it][i] = __int_as_float(0x7fc00000);
+        // the fast test is proven for |offset| <= 128 (quotients beyond 512 then saturate whichever way
+        // they round); channels with a larger offset always take the exact path
+        if (fabsf(o[it][i]) > 128.f) r[it][i] = __int_as_float(0x7fc00000);
       }
     }
   }
@@ -376,7 +383,8 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
 #pragma unroll
           for (int i = 0; i < 8; ++i) w[i] = quant_fast<HAS_OFF>(to_f32<T>(x[i]), r[it][i], HAS_OFF ? o[it][i] : 0.f, ok);
           if (!ok) {  // rare: a tie, a huge quotient, an odd scale somewhere in these eight
-#pragma unroll 1
+            // (unrolled: a run-time index would push the register arrays into local memory)
+#pragma unroll
             for (int i = 0; i < 8; ++i) w[i] = quant_exact<HAS_OFF>(to_f32<T>(x[i]), __ldg(ds + e + i), HAS_OFF ? o[it][i] : 0.f);
           }
           const uint32_t lo = pack_low_bytes(w[0], w[1], w[2], w[3]), hi = pack_low_bytes(w[4], w[5], w[6], w[7]);
