@@ -207,7 +207,8 @@ typedef struct MscoPaPlanInfo {
 /* Split rule: tokens per KV split as a function of one sequence's length and
  * the cache element type (MSCO_DTYPE_*) only -- never of the batch -- so a
  * request's result is bitwise independent of what it is batched with. */
-int32_t msco_paged_attention_split_tokens(int32_t context_len, int32_t kv_dtype);
+int32_t msco_paged_attention_split_tokens(int32_t context_len, int32_t kv_dtype); /* head_dim 128 */
+int32_t msco_paged_attention_split_tokens_for(int32_t context_len, int32_t kv_dtype, int32_t head_dim);
 
 /* 1 when the TMA + tensor-core kernel serves this descriptor (head_dim 128, or 64 / 256 with a 16-bit
  * cache; block_size 16 / 32 / 64 / 128, at most 64 for head_dim 256), 0 when the general kernel does. */

@@ -57,7 +57,7 @@ _lib = None
 # every symbol include/msco_b200.h declares
 EXPORTS = (
     "msco_version", "msco_last_error", "msco_reshape_and_cache", "msco_reshape_and_cache_quant",
-    "msco_paged_attention_split_tokens", "msco_paged_attention_plan", "msco_paged_attention_workspace_bytes",
+    "msco_paged_attention_split_tokens", "msco_paged_attention_split_tokens_for", "msco_paged_attention_plan", "msco_paged_attention_workspace_bytes",
     "msco_paged_attention_plan_info", "msco_paged_attention_plan_destroy", "msco_paged_attention_launch",
     "msco_paged_attention_status", "msco_paged_attention_profile_enable", "msco_paged_attention_profile_read",
     "msco_paged_attention_launch_static", "msco_paged_attention_status_static",
@@ -99,6 +99,8 @@ def lib():
     L.msco_fa_update_strided.argtypes = [vp, i64, vp, i64, i32, vp, i64, i32, i32, vp]
     L.msco_paged_attention_split_tokens.restype = i32
     L.msco_paged_attention_split_tokens.argtypes = [i32, i32]
+    L.msco_paged_attention_split_tokens_for.restype = i32
+    L.msco_paged_attention_split_tokens_for.argtypes = [i32, i32, i32]
     L.msco_paged_attention_plan.restype = C.c_int
     L.msco_paged_attention_plan.argtypes = [C.POINTER(MscoPaDesc), C.POINTER(i32), i32, C.POINTER(vp)]
     L.msco_paged_attention_replan.restype = C.c_int

@@ -44,14 +44,20 @@ extern "C" const char *msco_last_error(void) { return g_err; }
 // cache element type, fixed per call) only: the result for one request never
 // depends on what else is in the batch.  A split is sized to about 256 KB of
 // K/V per kv head at the short end, so that the per-split merge is amortised.
-extern "C" int32_t msco_paged_attention_split_tokens(int32_t context_len, int32_t kv_dtype) {
+static int32_t split_tokens(int32_t context_len, int32_t token_bytes) {
   if (context_len > 65536) return 2048;
-  if (context_len > 16384) return kv_dtype == MSCO_DTYPE_I8 ? 2048 : 1024;
-  // an int8 token is half the bytes, and the int8 kernel's per-item cost (q rows converted, 8 warps merged
-  // through shared memory) is the larger one: contexts of up to 4096 tokens are one item, longer ones
-  // are cut every 2048 tokens
-  if (kv_dtype == MSCO_DTYPE_I8) return context_len <= 4096 ? 4096 : 2048;
+  // token rows of 128 bytes (int8 at head_dim 128, 16-bit at head_dim 64) are half the bytes, and the
+  // per-item cost of those kernel variants is the larger one: contexts of up to 4096 tokens are one item,
+  // longer ones are cut every 2048 tokens
+  if (token_bytes <= 128) return context_len <= 4096 ? 4096 : 2048;
+  if (context_len > 16384) return 1024;
   return 512;
+}
+extern "C" int32_t msco_paged_attention_split_tokens(int32_t context_len, int32_t kv_dtype) {
+  return split_tokens(context_len, kv_dtype == MSCO_DTYPE_I8 ? 128 : 256);
+}
+extern "C" int32_t msco_paged_attention_split_tokens_for(int32_t context_len, int32_t kv_dtype, int32_t head_dim) {
+  return split_tokens(context_len, head_dim * (kv_dtype == MSCO_DTYPE_I8 ? 1 : 2));
 }
 
 static int validate_desc(const MscoPaDesc &d) {
@@ -194,7 +200,7 @@ int fill_plan(MscoPaPlan *pl, const int32_t *host_context_lens, const int32_t *q
   const bool fused = pl->kernel == kKernelTma && pl->fused_merge_wanted;
   for (int s = 0; s < nseq; ++s) {
     const Entry &e = entries[s];
-    const int c = msco_paged_attention_split_tokens(e.len, d.kv_dtype);
+    const int c = msco_paged_attention_split_tokens_for(e.len, d.kv_dtype, d.head_dim);
     const int ns = (e.len + c - 1) / c;
     item_base[s] = (int32_t)items;
     seq_idx[s] = e.b; seq_len[s] = e.len; chunk[s] = c; nsplit[s] = ns;

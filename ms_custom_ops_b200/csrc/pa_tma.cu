@@ -50,7 +50,9 @@ constexpr int kDescInts = 12;  // work-item descriptor handed from the producer 
 template <int D, bool KV8, int NT, int SUBS> struct Cfg {
   static_assert(D == 64 || D == 128 || D == 256, "head_dim 64, 128 or 256");
   static_assert(!KV8 || D == 128, "int8 KV: head_dim 128");
-  static_assert((SUBS == 2) == (KV8 && NT == 1), "two sub-tiles per warp exactly for int8 KV with up to 8 q rows");
+  // rows of 128 bytes (int8 KV at head_dim 128, 16-bit KV at head_dim 64) with up to 8 q rows: two 16-token
+  // sub-tiles per consumer warp (256-token tiles of 32 KB, two independent MMA chains per warp)
+  static_assert((SUBS == 2) == ((KV8 || D == 64) && NT == 1), "sub-tiles per warp do not match the variant");
   static_assert(D != 256 || NT == 1, "head_dim 256: up to 8 q rows per item");
   static constexpr int kWarps = D == 256 ? 4 : 8;           // consumer warps
   static constexpr int kTile = kWarps * 16 * SUBS;          // tokens per tile
@@ -61,7 +63,7 @@ template <int D, bool KV8, int NT, int SUBS> struct Cfg {
   static constexpr int kRowBytes = KV8 ? D : 2 * D;         // one token row of one head
   static constexpr int kBoxes = kRowBytes / 128;            // 128-byte TMA boxes per token row
   static constexpr int kStageBytes = kTile * kRowBytes;     // 16 / 32 KB
-  static constexpr int kStages = D == 64 ? 8 : (D == 256 ? 5 : (KV8 ? (NT == 1 ? 4 : 8) : (NT == 1 ? 5 : 4)));
+  static constexpr int kStages = D == 64 ? (NT == 1 ? 4 : 8) : (D == 256 ? 5 : (KV8 ? (NT == 1 ? 4 : 8) : (NT == 1 ? 5 : 4)));
   static constexpr int kRows = 8 * NT;
   static constexpr int kKSteps = D / 16;                    // 16-wide slices of the head dimension
   static constexpr int kMergeStride = D + 4;                // floats per merged row (bank-conflict padding)
@@ -838,7 +840,7 @@ int launch_one(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, c
 // Tokens per tile of the kernel variant that serves `d`: a tile holds whole cache blocks.
 static int tile_tokens(const MscoPaDesc &d) {
   if (d.head_dim == 256) return 64;
-  if (d.kv_dtype == MSCO_DTYPE_I8 && d.num_q_heads / d.num_kv_heads <= 8) return 256;
+  if ((d.kv_dtype == MSCO_DTYPE_I8 || d.head_dim == 64) && d.num_q_heads / d.num_kv_heads <= 8) return 256;
   return 128;
 }
 
@@ -890,7 +892,7 @@ int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp
   } while (0)
 #define MSCO_GO_T(T)                                                      \
   do {                                                                    \
-    if (hd == 64) { if (g16) MSCO_GO(T, 64, false, 2, 1); else MSCO_GO(T, 64, false, 1, 1); } \
+    if (hd == 64) { if (g16) MSCO_GO(T, 64, false, 2, 1); else MSCO_GO(T, 64, false, 1, 2); } \
     if (hd == 256) MSCO_GO(T, 256, false, 1, 1);                          \
     if (kv8) {                                                            \
       if (g16) MSCO_GO(T, 128, true, 2, 1);                               \
