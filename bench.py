@@ -684,6 +684,8 @@ def run_gpu(args):
         scatter = measure_scatter(workload_spec("c5"), dev, peak)
         if rank == 0:
             extras["rac_prefill"] = scatter
+    if world == 1 and not args.no_extra and (not args.configs or "mtp4" in args.configs.split(",")):
+        extras["mtp4"] = measure_mtp(spec, dev)
     if world == 1 and args.adjacent:
         case = workloads.decode_case_device(spec, dev, (0, spec.kv_heads))
         adjacent = measure_adjacent(case, spec, dev, peak, not args.no_cpu)
@@ -859,6 +861,52 @@ def run_gpu_seq_parallel(args):
     dist.barrier()
     xch.release()
     dist.destroy_process_group()
+
+
+def measure_mtp(spec, dev, q_len=4):
+    """Multi-token (speculative) decode on the headline workload's shapes: `q_len` query tokens per
+    sequence (calc_type = 1, q_seq_lens) against one, same caches and lengths, operator API, device
+    resident.  The tokens of a sequence are rows of ONE work item, so the context is read from HBM once:
+    the ratio of the two step times is the figure.  Without a mask every token of a sequence sees the
+    same context, so row t of the stacked result must equal a one-token decode of query t."""
+    import torch
+    import ms_custom_ops_b200 as ops
+    case = workloads.decode_case_device(spec, dev, (0, spec.kv_heads))
+    kc, vc, bt = case["key_cache"], case["value_cache"], case["block_tables"]
+    lens = torch.from_numpy(np.asarray(case["context_lens"], dtype=np.int32))
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(spec.seed + 17)
+    q = torch.randn((spec.batch * q_len, spec.num_heads, spec.head_size), generator=gen, device=dev).to(kc.dtype)
+    ql = torch.full((spec.batch,), q_len, dtype=torch.int32)
+    kw = dict(q_head_num=spec.num_heads, kv_head_num=spec.kv_heads, qk_scale=case["qk_scale"])
+    q1 = q.view(spec.batch, q_len, spec.num_heads, spec.head_size)[:, 0].contiguous()
+
+    def timed(fn, reps=20):
+        for _ in range(4):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    one = timed(lambda: ops.paged_attention(q1, kc, vc, bt, lens, **kw))
+    many = timed(lambda: ops.paged_attention(q, kc, vc, bt, lens, calc_type=1, q_seq_lens=ql, **kw))
+    stacked = ops.paged_attention(q, kc, vc, bt, lens, calc_type=1, q_seq_lens=ql, **kw)
+    stacked = stacked.view(spec.batch, q_len, spec.num_heads, spec.head_size)
+    worst = 0.0
+    for t in range(q_len):
+        qt = q.view(spec.batch, q_len, spec.num_heads, spec.head_size)[:, t].contiguous()
+        single = ops.paged_attention(qt, kc, vc, bt, lens, **kw)
+        worst = max(worst, float((single.float() - stacked[:, t].float()).abs().max()))
+    ops.paged_attention_check_status(dev)
+    return {"workload": f"{spec.name} shapes, {q_len} query tokens per sequence (calc_type 1), no mask",
+            "q_tokens_per_sequence": q_len, "ms_one_token": one, "ms_multi_token": many, "ratio": many / one,
+            "tokens_per_s": spec.batch * q_len / many * 1e3,
+            "max_abs_diff_vs_one_token_decodes": worst}
 
 
 def measure_scatter(spec, dev, peak):
@@ -1041,7 +1089,7 @@ def main():
                     help="only the headline workload (skip the `configs` entries: c3, c4, c5, prefill scatter)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="time budget of one CPU baseline leg")
     ap.add_argument("--configs", default="", help="comma-separated subset of the `configs` entries to run "
-                    "(c3,c4,c5,c2h64,c2h256,rac_prefill); default: all")
+                    "(c3,c4,c5,c2h64,c2h256,rac_prefill,mtp4); default: all")
     ap.add_argument("--nccl-gather", action="store_true", help="exchange outputs with NCCL instead of peer stores")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity check")
     ap.add_argument("--seq-parallel", action="store_true",
