@@ -267,15 +267,18 @@ class DecodeLoop:
     def lens_at(self, i):
         return self.lens0 + np.int32(i)
 
-    def step(self):
-        """One device-resident decode step (everything it reads is in HBM already)."""
+    def step(self, gather=None):
+        """One device-resident decode step (everything it reads is in HBM already).  `gather` (a
+        sharding.PeerGather): the step's finishing kernel also pushes the output rows to the peers and
+        waits for theirs (msco_decode_step_gather); returns this rank's gathered buffer then."""
         c, i = self.case, self.i
         np.add(self.lens0, np.int32(i), out=self.cur_lens)
         self.plan.replan(self.cur_lens)
-        self.kernels.decode_step(self.plan, c["key"], c["value"], c["key_cache"], c["value_cache"], self.slots_dev[i],
-                                 c["query"], c["block_tables"], self.out_local, self.ws, c["k_descale"], None,
-                                 c["v_descale"], None)
+        got = self.kernels.decode_step(self.plan, c["key"], c["value"], c["key_cache"], c["value_cache"],
+                                       self.slots_dev[i], c["query"], c["block_tables"], self.out_local, self.ws,
+                                       c["k_descale"], None, c["v_descale"], None, gather=gather)
         self.i = i + 1
+        return got
 
     def algorithmic_bytes(self, first_step, nsteps):
         """Mean algorithmic bytes per launch over steps [first_step, first_step + nsteps)."""
@@ -370,10 +373,14 @@ def measure_decode(ctx, spec, args, full):
             return peer.gather(o)
         return sharding.all_gather_outputs(o, gathered)
 
+    fused = peer is not None and not args.separate_gather
+
     def step():
+        # the exchange rides in the step's own finishing kernel (default) or is a launch of its own
+        if fused:
+            return loop.step(gather=peer)
         loop.step()
-        if world > 1:
-            exchange(loop.out_local)
+        return exchange(loop.out_local) if world > 1 else None
 
     def barrier():
         if world > 1:
@@ -430,8 +437,9 @@ def measure_decode(ctx, spec, args, full):
     if peer is not None:
         peer.check()
         # the peer-store gather must equal NCCL's all-gather of the same slices, bit for bit
-        mine = exchange(loop.out_local)
+        mine = step()
         torch.cuda.synchronize()
+        peer.check()
         sharding.all_gather_outputs(loop.out_local, gathered)
         gather_check = bool(torch.equal(mine.view(torch.int16), gathered.view(torch.int16)))
 
@@ -462,20 +470,25 @@ def measure_decode(ctx, spec, args, full):
         torch.cuda.synchronize()
         cpu, checked = loop.cpu_check(args, loop.out_local, last)
 
-    launches_per_step = 2 + (1 if min(loop.lens0) == 0 else 0) + (1 if peer is not None else 0)
+    # scatter + attention + the finishing kernel (split merge; also the exchange of a sharded step) [+ a gather
+    # launch of its own with --separate-gather]
+    finishing = 1 if (info.partials > 0 or min(loop.lens0) == 0 or fused) else 0
+    launches_per_step = 2 + finishing + (1 if peer is not None and not fused else 0)
     result.update({
         "roofline": roofline, "cpu_baseline": cpu, "parity_check": checked, "gather_check": gather_check,
         "clocks": clocks, "e2e": e2e, "kernels_per_step": launches_per_step,
         "achieved_gbs_step": alg_bytes / ms_step / 1e6, "alg_bytes": alg_bytes,
         "config": workload_config(spec, loop.lens_at(first_timed), {
             "parallelism": f"kv-head sharding x{world}" + (
-                "" if world == 1 else (" + peer-store all-gather of outputs over NVLink" if peer is not None
-                                       else " + NCCL all-gather of outputs")),
+                "" if world == 1 else (
+                    (" + peer-store all-gather of outputs over NVLink"
+                     + (" from the kernel that finishes the output rows" if fused else " (a launch of its own)"))
+                    if peer is not None else " + NCCL all-gather of outputs")),
             "l2": f"inputs larger than L2: {alg_bytes / 1e6:.0f} MB of KV per GPU per step vs {L2_BYTES >> 20} MB",
             "launch": "real decode loop: every step appends one token per sequence (context_lens + 1, slot_mapping "
                       "moves, block tables hold the blocks reserved for the growth), the plan is re-planned in place "
-                      "every step, eager launches on one stream (cache scatter + attention, split partials merged "
-                      "inside the attention kernel)",
+                      "every step, eager launches on one stream (cache scatter, attention, merge of the split "
+                      "partials; programmatic launch overlap between them)",
             "timing": f"median of {R} loops of {K} steps each",
             "work_items": info.work_items, "split_partials": info.partials, "grid": info.grid}),
     })
@@ -1091,6 +1104,9 @@ def main():
     ap.add_argument("--configs", default="", help="comma-separated subset of the `configs` entries to run "
                     "(c3,c4,c5,c2h64,c2h256,rac_prefill,mtp4); default: all")
     ap.add_argument("--nccl-gather", action="store_true", help="exchange outputs with NCCL instead of peer stores")
+    ap.add_argument("--separate-gather", action="store_true",
+                    help="N > 1: launch the peer-store all-gather as a kernel of its own behind the step instead "
+                         "of from the step's finishing kernel")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity check")
     ap.add_argument("--seq-parallel", action="store_true",
                     help="shard every context over the ranks (all heads per rank) instead of the kv heads")

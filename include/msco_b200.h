@@ -400,6 +400,20 @@ int msco_ipc_import(const unsigned char *handle, int64_t offset, void **dev_ptr)
 int msco_ipc_release(void *dev_ptr, int64_t offset);
 int msco_peer_allgather(const MscoGatherDesc *desc, const void *local_out, uint32_t step, void *stream);
 
+/* msco_decode_step for one rank of a kv-head-sharded step, with the exchange folded in: the kernel that
+ * finishes the output rows (the split merge; rows that need no merge are read back from `out`) also
+ * stores every row into slot `rank` of every rank's gathered buffer, and its last block publishes `step`
+ * and waits -- bounded, as above -- for the peers.  Same descriptor, flag protocol, `step` sequence and
+ * status word as msco_peer_allgather, which it replaces for the step (one launch and one read-back of
+ * the slice fewer); `out` still receives the local slice.  gather->slice_bytes must equal the size of
+ * the plan's output (query rows x q heads x head_dim x 2).  No reference counterpart. */
+int msco_decode_step_gather(const MscoPaPlan *plan, const void *key, const void *value, void *key_cache,
+                            void *value_cache, const int32_t *slot_mapping, int64_t num_tokens,
+                            const void *query, const int32_t *block_tables, const float *k_descale,
+                            const int32_t *k_offset, const float *v_descale, const int32_t *v_offset,
+                            const void *attn_mask, void *out, void *workspace, size_t workspace_bytes,
+                            void *stream, const MscoGatherDesc *gather, uint32_t step);
+
 /* Kernel timing for benchmarks.  After msco_paged_attention_profile_enable(plan, 1) every launch
  * of this plan records a pair of CUDA events directly around the attention kernel (not around the
  * plan upload or the reduce kernel) into a ring of 64 pairs owned by the plan.

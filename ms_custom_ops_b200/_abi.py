@@ -61,7 +61,7 @@ EXPORTS = (
     "msco_paged_attention_plan_info", "msco_paged_attention_plan_destroy", "msco_paged_attention_launch",
     "msco_paged_attention_status", "msco_paged_attention_profile_enable", "msco_paged_attention_profile_read",
     "msco_paged_attention_launch_static", "msco_paged_attention_status_static",
-    "msco_ipc_export", "msco_ipc_import", "msco_ipc_release", "msco_peer_allgather", "msco_decode_step",
+    "msco_ipc_export", "msco_ipc_import", "msco_ipc_release", "msco_peer_allgather", "msco_decode_step", "msco_decode_step_gather",
     "msco_paged_attention_launch_lse", "msco_expand_rows_i32", "msco_paged_attention_replan", "msco_plan_arena_stats",
     "msco_reshape_and_cache_bnsd", "msco_copy_device", "msco_paged_attention_plan_tokens",
     "msco_paged_attention_replan_tokens", "msco_paged_attention_tma_supported", "msco_paged_cache_load_workspace_bytes", "msco_paged_cache_load", "msco_fa_update", "msco_fa_update_strided",
@@ -133,6 +133,8 @@ def lib():
     L.msco_paged_attention_status_static.argtypes = [vp]
     L.msco_decode_step.restype = C.c_int
     L.msco_decode_step.argtypes = [vp] * 6 + [i64] + [vp] * 9 + [sz, vp]
+    L.msco_decode_step_gather.restype = C.c_int
+    L.msco_decode_step_gather.argtypes = [vp] * 6 + [i64] + [vp] * 9 + [sz, vp, C.POINTER(MscoGatherDesc), C.c_uint32]
     L.msco_ipc_export.restype = C.c_int
     L.msco_ipc_export.argtypes = [vp, C.c_char_p, C.POINTER(i64)]
     L.msco_ipc_import.restype = C.c_int

@@ -10,6 +10,7 @@
 
 #include "msco_common.cuh"
 #include "pa_params.h"
+#include "peer_gather.cuh"
 #include "plan_arena.h"
 
 namespace msco {
@@ -411,7 +412,7 @@ int pa_launch_impl(const MscoPaPlan *plan, const void *query, const void *key_ca
                    const int32_t *block_tables, const float *k_descale, const int32_t *k_offset,
                    const float *v_descale, const int32_t *v_offset, const void *attn_mask, void *out,
                    void *workspace, size_t workspace_bytes, void *stream, bool after_kernel, float *lse = nullptr,
-                   bool sync_cleared = false) {
+                   bool sync_cleared = false, const GatherArgs *gather = nullptr) {
   if (plan == nullptr) return fail(MSCO_ERR_INVALID_ARG, "paged_attention_launch: NULL plan");
   if (plan->batch == 0) return MSCO_OK;
   const MscoPaDesc &d = plan->desc;
@@ -495,7 +496,8 @@ int pa_launch_impl(const MscoPaPlan *plan, const void *query, const void *key_ca
     MSCO_CUDA_CHECK(cudaEventRecord(pe[1], st));
     ++plan->prof_count;
   }
-  if (plan->need_reduce) rc = launch_pa_reduce(plan, p, pp, st);
+  // with a gather the finishing kernel runs even when no row needs a merge: it is the exchange then
+  if (plan->need_reduce || gather != nullptr) rc = launch_pa_reduce(plan, p, pp, st, gather);
   return rc;
 }
 
@@ -565,12 +567,13 @@ extern "C" int msco_paged_attention_launch_lse(const MscoPaPlan *plan, const voi
 // One decode step in one call: scatter the new token rows, then attention.  The attention kernel
 // is launched with programmatic stream serialisation behind the scatter kernel, so its set-up
 // overlaps the scatter's tail; it waits for the scatter's writes before it reads the cache.
-extern "C" int msco_decode_step(const MscoPaPlan *plan, const void *key, const void *value, void *key_cache,
+namespace {
+int decode_step_impl(const MscoPaPlan *plan, const void *key, const void *value, void *key_cache,
                                 void *value_cache, const int32_t *slot_mapping, int64_t num_tokens,
                                 const void *query, const int32_t *block_tables, const float *k_descale,
                                 const int32_t *k_offset, const float *v_descale, const int32_t *v_offset,
                                 const void *attn_mask, void *out, void *workspace, size_t workspace_bytes,
-                                void *stream) {
+                                void *stream, const GatherArgs *gather) {
   if (plan == nullptr) return fail(MSCO_ERR_INVALID_ARG, "decode_step: NULL plan");
   const MscoPaDesc &d = plan->desc;
   const int64_t row = (int64_t)d.num_kv_heads * d.head_dim;
@@ -604,8 +607,37 @@ extern "C" int msco_decode_step(const MscoPaPlan *plan, const void *key, const v
   }
   if (rc != MSCO_OK) return rc;
   return pa_launch_impl(plan, query, key_cache, value_cache, block_tables, k_descale, k_offset, v_descale, v_offset,
-                        attn_mask, out, workspace, workspace_bytes, stream, num_tokens > 0, nullptr, cleared);
+                        attn_mask, out, workspace, workspace_bytes, stream, num_tokens > 0, nullptr, cleared, gather);
 }
+}  // namespace
+
+extern "C" int msco_decode_step(const MscoPaPlan *plan, const void *key, const void *value, void *key_cache,
+                                void *value_cache, const int32_t *slot_mapping, int64_t num_tokens,
+                                const void *query, const int32_t *block_tables, const float *k_descale,
+                                const int32_t *k_offset, const float *v_descale, const int32_t *v_offset,
+                                const void *attn_mask, void *out, void *workspace, size_t workspace_bytes,
+                                void *stream) {
+  return decode_step_impl(plan, key, value, key_cache, value_cache, slot_mapping, num_tokens, query, block_tables,
+                          k_descale, k_offset, v_descale, v_offset, attn_mask, out, workspace, workspace_bytes, stream,
+                          nullptr);
+}
+
+extern "C" int msco_decode_step_gather(const MscoPaPlan *plan, const void *key, const void *value, void *key_cache,
+                                       void *value_cache, const int32_t *slot_mapping, int64_t num_tokens,
+                                       const void *query, const int32_t *block_tables, const float *k_descale,
+                                       const int32_t *k_offset, const float *v_descale, const int32_t *v_offset,
+                                       const void *attn_mask, void *out, void *workspace, size_t workspace_bytes,
+                                       void *stream, const MscoGatherDesc *gather, uint32_t step) {
+  if (plan == nullptr) return fail(MSCO_ERR_INVALID_ARG, "decode_step_gather: NULL plan");
+  if (plan->batch == 0) return fail(MSCO_ERR_INVALID_ARG, "decode_step_gather: an empty batch has nothing to gather");
+  GatherArgs g;
+  const int rc = fill_gather_args(gather, step, "decode_step_gather", &g);
+  if (rc != MSCO_OK) return rc;
+  return decode_step_impl(plan, key, value, key_cache, value_cache, slot_mapping, num_tokens, query, block_tables,
+                          k_descale, k_offset, v_descale, v_offset, attn_mask, out, workspace, workspace_bytes, stream,
+                          &g);
+}
+
 
 extern "C" int msco_paged_attention_status(const MscoPaPlan *plan, const void *workspace) {
   // plan may be NULL: the epoch of the last launch that used this workspace is remembered

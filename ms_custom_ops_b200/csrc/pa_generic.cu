@@ -16,6 +16,7 @@
 #include "msco_common.cuh"
 #include "pa_merge.cuh"
 #include "pa_params.h"
+#include "peer_gather.cuh"
 
 namespace msco {
 namespace {
@@ -212,17 +213,7 @@ __global__ void __launch_bounds__(kGenThreads) pa_generic_kernel(PaParams p, con
 // the lanes in parallel (one split per lane, strided for more), the weights 2^(m_s - M) stay in
 // registers, and the partial rows are accumulated in split order with several loads in flight.
 template <typename TQ>
-__global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p, const __grid_constant__ PlanParam pp) {
-  // a kernel launched behind this one with programmatic stream serialisation (the peer all-gather
-  // of a sharded step) may become resident now; it waits for this grid before it reads the output
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  // launched with programmatic stream serialisation: wait here until the attention grid before us
-  // has completed and its partials are visible (a no-op for an ordinary launch)
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const PlanView pv = make_plan_view(p.plan_in_param ? pp.w : p.plan);
-  const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (row >= pv.batch * p.num_q_heads) return;
+__device__ __forceinline__ void reduce_row(const PaParams &p, const PlanView &pv, int row, int lane) {
   const int b = row / p.num_q_heads, hq = row - b * p.num_q_heads;
   const int ns = __ldg(pv.b_nsplit + b);
   if (ns == 1) return;  // written directly by the attention kernel
@@ -274,6 +265,37 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(PaParams p, const __grid
   if (lane == 0 && p.lse != nullptr) p.lse[row] = (M + log2f(L)) * kLn2;
 }
 
+// The kernel that finishes the output rows of a launch: merges the rows that were computed in
+// several splits and -- for a rank of a kv-head-sharded step (g.world > 0) -- stores every finished
+// row, merged here or written by the attention kernel, into slot `rank` of every rank's gathered
+// buffer; the block that finishes last then publishes the step's flag and waits (bounded) for the
+// peers, exactly as the stand-alone gather kernel does.
+template <typename TQ>
+__global__ void __launch_bounds__(128)
+pa_reduce_kernel(PaParams p, const __grid_constant__ PlanParam pp, const __grid_constant__ GatherArgs g) {
+  __shared__ bool is_last;
+  // a kernel launched behind this one with programmatic stream serialisation may become resident
+  // now; it waits for this grid before it reads the output
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // launched with programmatic stream serialisation: wait here until the attention grid before us
+  // has completed and its partials are visible (a no-op for an ordinary launch)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const PlanView pv = make_plan_view(p.plan_in_param ? pp.w : p.plan);
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const bool live = row < pv.batch * p.num_q_heads;
+  if (live) reduce_row<TQ>(p, pv, row, lane);
+  if (g.world == 0) return;
+  if (live) {
+    __syncwarp();  // the row was written by the lanes of this warp (or by the grid before us)
+    const int64_t row_bytes = (int64_t)p.head_dim * (int64_t)sizeof(TQ);
+    const char *src = static_cast<const char *>(p.out) + row * row_bytes;
+    for (int64_t off = lane * 16; off < row_bytes; off += 32 * 16)
+      gather_push16(g, row * row_bytes + off, __ldcg(reinterpret_cast<const uint4 *>(src + off)));
+  }
+  gather_finish(g, &is_last);
+}
+
 }  // namespace
 
 int launch_pa_generic(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream) {
@@ -289,9 +311,20 @@ int launch_pa_generic(const MscoPaPlan *plan, const PaParams &p, const PlanParam
   return MSCO_OK;
 }
 
-int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream) {
+int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream,
+                     const GatherArgs *gather) {
+  static const GatherArgs no_gather = {};
+  const GatherArgs &g = gather != nullptr ? *gather : no_gather;
   const int rows = plan->batch * plan->desc.num_q_heads;
   if (rows == 0) return MSCO_OK;
+  if (g.world > 0) {
+    const int64_t row_bytes = (int64_t)plan->desc.head_dim * 2;
+    if (row_bytes % 16 != 0 || g.slice_bytes != rows * row_bytes)
+      return fail(MSCO_ERR_INVALID_ARG, "decode_step_gather: the gather slice is %lld bytes, the output of this plan %lld",
+                  (long long)g.slice_bytes, (long long)(rows * row_bytes));
+    if (reinterpret_cast<uintptr_t>(p.out) & 15)
+      return fail(MSCO_ERR_INVALID_ARG, "decode_step_gather: the output must be 16-byte aligned");
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((rows + 3) / 4);
   cfg.blockDim = dim3(128);
@@ -302,8 +335,8 @@ int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, const PlanParam 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (plan->desc.q_dtype == MSCO_DTYPE_F16) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__half>, p, pp));
-  else MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__nv_bfloat16>, p, pp));
+  if (plan->desc.q_dtype == MSCO_DTYPE_F16) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__half>, p, pp, g));
+  else MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__nv_bfloat16>, p, pp, g));
   return MSCO_OK;
 }
 

@@ -109,7 +109,10 @@ namespace msco {
 int launch_pa_generic(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream);
 int launch_pa_tma(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream,
                   bool after_kernel);
-int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream);
+struct GatherArgs;  // peer_gather.cuh
+// `gather` != NULL: the kernel also pushes every finished row to the peers of a kv-head-sharded step
+int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, cudaStream_t stream,
+                     const GatherArgs *gather = nullptr);
 // reshape_and_cache launchers that can also zero `clear_words` 32-bit words at `clear` (the attention
 // kernel's scheduling words) on their way; *cleared tells whether the launched kernel does it
 int launch_rac(const void *key, const void *value, void *key_cache, void *value_cache, const int32_t *slot_mapping,

@@ -166,9 +166,12 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       __syncwarp();
     }
     const int32_t *ibs = ib_ok ? ib : nullptr;
-    // when launched with programmatic stream serialisation right behind the cache-scatter kernel,
-    // everything above overlapped that kernel's tail; its writes must be visible from here on
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // When launched with programmatic stream serialisation right behind the cache-scatter kernel, this
+    // grid runs beside that kernel's tail.  What the scatter kernel writes -- the caches and the
+    // scheduling words -- is touched only after griddepcontrol.wait (below, in front of the first cache
+    // tile); the plan, the q rows and the block tables are inputs of the step that were complete before
+    // the scatter kernel started, so the first item's decode, q load and table fetch overlap it too.
+    bool synced = false;
     uint32_t st = 0, ph = 0;
     const int bs = p.block_size;
     const int bpt = kTile / bs;  // cache blocks per tile (divides 32)
@@ -200,7 +203,12 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     for (int qi = 0;; ++qi) {
       // next-but-one ticket: its latency hides behind this item's loads
       int t_nn = 0;
-      if (lane == 0) t_nn = 2 * (int)gridDim.x + (int)atomicAdd(p.sync, 1u);
+      if (synced && lane == 0) t_nn = 2 * (int)gridDim.x + (int)atomicAdd(p.sync, 1u);
+      auto sync_once = [&]() {  // first item only: the scatter kernel's writes, then the first ticket
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        synced = true;
+        if (lane == 0) t_nn = 2 * (int)gridDim.x + (int)atomicAdd(p.sync, 1u);
+      };
       // item qi + 1 (or the end marker) into the other slot, once the consumers have let go of it
       const int ns = (qi + 1) & 1;
       const uint32_t nph = ((qi + 1) >> 1) & 1;
@@ -231,6 +239,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             my_id = 0;  // stay inside the cache; the result of this item is undefined
           }
         }
+        if (!synced) sync_once();
         const int nblk_batch = min(32, nblk_item - blk0);
         for (int jb = 0; jb < nblk_batch; jb += bpt, ++tile) {
           const int nv = min(kTile, ntok - tile * kTile);  // valid tokens of this tile
@@ -264,6 +273,7 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           }
         }
       }
+      if (!synced) sync_once();  // (an item without a tile: cannot happen, but the ticket must be drawn)
       if (!more) break;
       w = w_nxt;
       t_nxt = __shfl_sync(0xffffffffu, t_nn, 0);

@@ -17,34 +17,16 @@
 #include <cstring>
 
 #include "msco_common.cuh"
+#include "peer_gather.cuh"
 
 namespace msco {
 namespace {
 
 constexpr int kPushThreads = 512;
 constexpr int kPushMaxBlocks = 16;
-constexpr uint32_t kPeerWaitLimit = 1u << 22;  // polls of ~100 ns: gives up after about half a second
-
-struct GatherArgs {
-  void *gathered[MSCO_MAX_PEERS];   // rank r's gathered buffer as mapped into this process
-  uint32_t *flags[MSCO_MAX_PEERS];  // rank r's flag array (uint32[world]) as mapped into this process
-  int64_t slice_bytes;
-  int world, rank;
-  uint32_t wait_limit;
-};
-
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 
 __global__ void __launch_bounds__(kPushThreads)
-peer_gather_kernel(GatherArgs a, const uint4 *__restrict__ local, uint32_t step, unsigned int *ticket,
-                   int32_t *status) {
+peer_gather_kernel(const __grid_constant__ GatherArgs a, const uint4 *__restrict__ local) {
   __shared__ bool is_last;
   const int64_t n16 = a.slice_bytes / 16;
   // launched with programmatic stream serialisation: the kernels of this library that produce
@@ -52,34 +34,10 @@ peer_gather_kernel(GatherArgs a, const uint4 *__restrict__ local, uint32_t step,
   // writes are visible (a no-op behind anything else)
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // 1. push the local slice into slot `rank` of every rank's gathered buffer (own copy included)
-  for (int64_t i = (int64_t)blockIdx.x * kPushThreads + threadIdx.x; i < n16; i += (int64_t)gridDim.x * kPushThreads) {
-    const uint4 v = __ldcg(local + i);
-    for (int r = 0; r < a.world; ++r)
-      reinterpret_cast<uint4 *>(static_cast<char *>(a.gathered[r]) + (int64_t)a.rank * a.slice_bytes)[i] = v;
-  }
+  for (int64_t i = (int64_t)blockIdx.x * kPushThreads + threadIdx.x; i < n16; i += (int64_t)gridDim.x * kPushThreads)
+    gather_push16(a, i * 16, __ldcg(local + i));
   // 2. the block that finishes last publishes the flags and waits for the peers
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    const unsigned int t = atomicAdd(ticket, 1u);
-    is_last = (t == gridDim.x - 1);
-    if (is_last) *ticket = 0u;  // ready for the next launch on this stream
-  }
-  __syncthreads();
-  if (!is_last) return;
-  if (threadIdx.x < a.world) {
-    const int r = threadIdx.x;
-    __threadfence_system();  // every block's pushes (ordered before its ticket) precede the flag
-    st_release_sys(a.flags[r] + a.rank, step);  // "rank's slice of step `step` is in your buffer"
-    const uint32_t *mine = a.flags[a.rank] + r; // peer r's announcement in my own flag array
-    bool ok = false;
-    for (uint32_t it = 0; it < a.wait_limit; ++it) {
-      if ((int32_t)(ld_acquire_sys(mine) - step) >= 0) { ok = true; break; }
-      __nanosleep(100);
-    }
-    if (!ok) atomicExch(status, kStatusTimeout);  // a peer never arrived: report, do not hang
-  }
+  gather_finish(a, &is_last);
 }
 
 typedef CUresult (*GetAddressRangeFn)(CUdeviceptr *, size_t *, CUdeviceptr);
@@ -129,19 +87,21 @@ extern "C" int msco_ipc_release(void *dev_ptr, int64_t offset) {
   return MSCO_OK;
 }
 
-extern "C" int msco_peer_allgather(const MscoGatherDesc *desc, const void *local_out, uint32_t step,
-                                   void *stream) {
-  if (desc == nullptr || local_out == nullptr) return fail(MSCO_ERR_INVALID_ARG, "peer_allgather: NULL argument");
+int msco::fill_gather_args(const MscoGatherDesc *desc, uint32_t step, const char *what, GatherArgs *out) {
+  if (desc == nullptr) return fail(MSCO_ERR_INVALID_ARG, "%s: NULL gather descriptor", what);
   if (desc->world < 1 || desc->world > MSCO_MAX_PEERS || desc->rank < 0 || desc->rank >= desc->world)
-    return fail(MSCO_ERR_INVALID_ARG, "peer_allgather: bad rank %d of %d", desc->rank, desc->world);
-  if (desc->slice_bytes <= 0 || desc->slice_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(local_out) & 15))
-    return fail(MSCO_ERR_INVALID_ARG, "peer_allgather: slices must be 16-byte multiples and 16-byte aligned");
+    return fail(MSCO_ERR_INVALID_ARG, "%s: bad rank %d of %d", what, desc->rank, desc->world);
+  if (desc->slice_bytes <= 0 || desc->slice_bytes % 16 != 0)
+    return fail(MSCO_ERR_INVALID_ARG, "%s: slices must be multiples of 16 bytes", what);
   if (desc->ticket == nullptr || desc->status == nullptr)
-    return fail(MSCO_ERR_INVALID_ARG, "peer_allgather: ticket / status words are required");
-  GatherArgs a;
+    return fail(MSCO_ERR_INVALID_ARG, "%s: ticket / status words are required", what);
+  GatherArgs &a = *out;
+  memset(&a, 0, sizeof(a));
   for (int r = 0; r < desc->world; ++r) {
     if (desc->gathered[r] == nullptr || desc->flags[r] == nullptr)
-      return fail(MSCO_ERR_INVALID_ARG, "peer_allgather: rank %d's buffers are not mapped", r);
+      return fail(MSCO_ERR_INVALID_ARG, "%s: rank %d's buffers are not mapped", what, r);
+    if (reinterpret_cast<uintptr_t>(desc->gathered[r]) & 15)
+      return fail(MSCO_ERR_INVALID_ARG, "%s: rank %d's gathered buffer is not 16-byte aligned", what, r);
     a.gathered[r] = desc->gathered[r];
     a.flags[r] = desc->flags[r];
   }
@@ -149,6 +109,20 @@ extern "C" int msco_peer_allgather(const MscoGatherDesc *desc, const void *local
   a.world = desc->world;
   a.rank = desc->rank;
   a.wait_limit = desc->wait_polls != 0 ? desc->wait_polls : kPeerWaitLimit;
+  a.step = step;
+  a.ticket = desc->ticket;
+  a.status = desc->status;
+  return MSCO_OK;
+}
+
+extern "C" int msco_peer_allgather(const MscoGatherDesc *desc, const void *local_out, uint32_t step,
+                                   void *stream) {
+  if (desc == nullptr || local_out == nullptr) return fail(MSCO_ERR_INVALID_ARG, "peer_allgather: NULL argument");
+  if (reinterpret_cast<uintptr_t>(local_out) & 15)
+    return fail(MSCO_ERR_INVALID_ARG, "peer_allgather: the local slice must be 16-byte aligned");
+  GatherArgs a;
+  const int rc = fill_gather_args(desc, step, "peer_allgather", &a);
+  if (rc != MSCO_OK) return rc;
   const int64_t n16 = desc->slice_bytes / 16;
   int blocks = (int)((n16 + kPushThreads - 1) / kPushThreads);
   blocks = blocks < 1 ? 1 : (blocks > kPushMaxBlocks ? kPushMaxBlocks : blocks);
@@ -161,7 +135,6 @@ extern "C" int msco_peer_allgather(const MscoGatherDesc *desc, const void *local
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, peer_gather_kernel, a, static_cast<const uint4 *>(local_out), step,
-                                     desc->ticket, desc->status));
+  MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, peer_gather_kernel, a, static_cast<const uint4 *>(local_out)));
   return MSCO_OK;
 }

@@ -1,0 +1,73 @@
+// Device-side pieces of the all-gather over NVLink peer memory, shared by the stand-alone gather kernel
+// (peer_gather.cu) and by the kernel that finishes the attention output rows of a sharded decode step
+// (pa_reduce_kernel in pa_generic.cu), which pushes each row to the peers as soon as it is final.
+//
+// Protocol: a rank stores its slice into slot `rank` of every rank's gathered buffer with plain peer
+// stores, the block that finishes last publishes the step counter in every rank's flag array with a
+// system-scope release, and then waits -- with an iteration limit -- for the counters of all peers.
+// No TMA, no multicast; the kernels of different ranks run on different GPUs.
+#pragma once
+
+#include "msco_common.cuh"
+
+namespace msco {
+
+constexpr uint32_t kPeerWaitLimit = 1u << 22;  // polls of ~100 ns: gives up after about half a second
+
+struct GatherArgs {
+  void *gathered[MSCO_MAX_PEERS];   // rank r's gathered buffer as mapped into this process
+  uint32_t *flags[MSCO_MAX_PEERS];  // rank r's flag array (uint32[world]) as mapped into this process
+  int64_t slice_bytes;
+  int world, rank;                  // world == 0: no gather (the finishing kernel of an unsharded step)
+  uint32_t wait_limit;
+  uint32_t step;
+  unsigned int *ticket;             // local word: blocks of the grid that have pushed their part
+  int32_t *status;                  // local word: kStatusTimeout when a peer never arrived
+};
+
+// Checks a gather descriptor and copies it into kernel arguments; `what` names the caller in the error text.
+int fill_gather_args(const MscoGatherDesc *desc, uint32_t step, const char *what, GatherArgs *out);
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// 16 bytes at byte offset `off` of the local slice into slot `rank` of every rank's gathered buffer
+__device__ __forceinline__ void gather_push16(const GatherArgs &a, int64_t off, const uint4 &v) {
+  for (int r = 0; r < a.world; ++r)
+    *reinterpret_cast<uint4 *>(static_cast<char *>(a.gathered[r]) + (int64_t)a.rank * a.slice_bytes + off) = v;
+}
+
+// Called by every thread of every block after the block's pushes: the block that arrives last
+// publishes the flags and waits for the peers.  `is_last` is a shared-memory flag of the caller.
+__device__ __forceinline__ void gather_finish(const GatherArgs &a, bool *is_last) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int t = atomicAdd(a.ticket, 1u);
+    *is_last = (t == gridDim.x - 1);
+    if (*is_last) *a.ticket = 0u;  // ready for the next launch on this stream
+  }
+  __syncthreads();
+  if (!*is_last) return;
+  if ((int)threadIdx.x < a.world) {
+    const int r = threadIdx.x;
+    __threadfence_system();  // every block's pushes (ordered before its ticket) precede the flag
+    st_release_sys(a.flags[r] + a.rank, a.step);  // "rank's slice of step `step` is in your buffer"
+    const uint32_t *mine = a.flags[a.rank] + r;   // peer r's announcement in my own flag array
+    bool ok = false;
+    for (uint32_t it = 0; it < a.wait_limit; ++it) {
+      if ((int32_t)(ld_acquire_sys(mine) - a.step) >= 0) { ok = true; break; }
+      __nanosleep(100);
+    }
+    if (!ok) atomicExch(a.status, kStatusTimeout);  // a peer never arrived: report, do not hang
+  }
+}
+
+}  // namespace msco

@@ -36,6 +36,10 @@ rac_scatter16_kernel(const uint4 *__restrict__ key, const uint4 *__restrict__ va
                      uint4 *__restrict__ key_cache, uint4 *__restrict__ value_cache,
                      const int32_t *__restrict__ slot_mapping, int64_t num_tokens, int k16, int v16,
                      int64_t num_slots, int32_t *oob_count, uint32_t *__restrict__ clear, int clear_words) {
+  // launched with programmatic stream serialisation itself: the grid may be resident before the
+  // kernels in front of it (the previous decode step) have finished; nothing is read or written
+  // before they have (a no-op behind an ordinary launch)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // a kernel launched behind this one with programmatic stream serialisation (the attention kernel
   // of a fused decode step) may start its set-up now; it waits for this grid before reading the cache
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -254,55 +258,103 @@ rac_scatter_quant_kernel(const T *__restrict__ key, const T *__restrict__ value,
 // rint(x / d) without a division, exactly: with r = fl(1 / d) and e = x * r (the exact product),
 //   z = fma(x, r, M), M = 1.5 * 2^23   rounds e to the nearest integer (ties to even) for |e| < 2^22,
 //   q = z - M                          is that integer, t = fma(x, r, -q) = e - q its distance to e.
-// e differs from x / d by at most |e| * 2^-24 (r is correctly rounded), and the correctly rounded
-// quotient from x / d by at most half an ulp: together less than 3.1e-5 for |q| <= 258, so
-// |t| <= 0.49995 puts fl(x / d) strictly within 0.5 of q: rint(fl(x / d)) = q (the margin holds up to
-// |q| < 512).  Quotients that leave the int8 range by more than 1 after the offset (|q| - |offset| >= 258
-// covers every |q| >= 512, offsets being at most 128 on this path) saturate whichever way they round.  Otherwise -- ties, huge quotients, zero, denormal or non-finite scales, NaN --
-// the IEEE division is done (quant_exact).  The test is this tight on purpose: one lane that fails it
-// sends its whole warp through the division for that group, and with 0.01 % of the values failing
-// that happens in 2.5 % of the groups (a +-0.002 band would make it 65 %).
-// z - offset is still an integer in M's binade, so the saturation to [-128, 127] is a clamp of that
-// float to [M - 128, M + 127], and the low byte of the clamped float's bit pattern is the
-// two's-complement int8.  No conversion instruction on the path; the eight elements of a 16-byte load
-// share ONE branch (taken when any of them needs the division); four results are packed with three
-// byte permutes.  Bit-identical to the division everywhere.
+// e differs from x / d by at most |e| * 2^-24 (r is a correctly rounded normal number), and the
+// correctly rounded quotient from x / d by at most half an ulp: together less than |q| * 2^-23 * 1.01.
+// So |t| <= 0.49995 - q^2 * 2^-30 puts fl(x / d) strictly within 0.5 of q, i.e. rint(fl(x / d)) = q:
+// below |q| = 256 the constant margin (5e-5 > 3.1e-5) covers the error, from 256 on the quadratic
+// term does (q^2 * 2^-30 >= |q| * 2^-22).  The threshold turns negative at |q| = 23170, so whatever
+// passes also fits 16 bits.  Everything else -- ties, huge quotients, NaN, and through r = NaN the
+// channels whose scale is zero-like, huge or not finite or whose offset exceeds 8192 -- fails the test
+// (the comparison is false for NaN) and takes the IEEE division (quant_exact).  The test is this
+// tight on purpose: one lane that fails it sends its whole warp through the division for that group
+// of eight, and with 0.013 % of the values failing that happens in 3 % of the groups.
+// z - offset is still an integer in M's binade, so the low 16 bits of its bit pattern are the
+// two's-complement value: two of them are packed into one register, clamped to [-128, 127] with one
+// 16-bit SIMD max and one min, and the low bytes of four halves are gathered with one byte permute.
+// Per element: 5 instructions on the FMA pipe, under 4 on the ALU pipe (the unpacking of the 16-bit
+// input, one compare, 1.75 for clamp and pack); no conversion instruction; bit-identical to the
+// division everywhere.
 constexpr float kQMagic = 12582912.f;
+constexpr float kQAccept = 0.49995f;          // |t| up to here (minus the quadratic term) is no tie
+constexpr float kQQuad = 9.313225746154785e-10f;  // 2^-30
+constexpr float kQMaxOffset = 8192.f;
+// one element: the bit pattern of M + q - offset; `ok` is cleared when the element needs the division
+// (`&`, not `&&`: a compare that feeds the predicate of the next one, no branch per element)
 template <bool HAS_OFF>
 __device__ __forceinline__ uint32_t quant_fast(float x, float r, float off, bool &ok) {
   const float z = fmaf(x, r, kQMagic);
   const float q = z - kQMagic;
   const float t = fmaf(x, r, -q);
-  // (a quotient whose distance to the int8 range exceeds 1 saturates whichever way it rounds)
-  const float aq = fabsf(q);
-  ok = ok && (aq < 4096.f) && (fabsf(t) <= 0.49995f || aq - (HAS_OFF ? fabsf(off) : 0.f) >= 258.f);
-  const float zz = HAS_OFF ? z - off : z;
-  return __float_as_uint(fminf(fmaxf(zz, kQMagic - 128.f), kQMagic + 127.f));  // low byte: the int8
+  const float thr = fmaf(q * q, -kQQuad, kQAccept);
+  ok = ok & (fabsf(t) <= thr);
+  return __float_as_uint(HAS_OFF ? z - off : z);
+}
+// the eight 16-bit values of a 16-byte load as float32 (bfloat16: one shift or one mask each)
+template <typename T> __device__ __forceinline__ void unpack8(const uint4 &raw, float (&x)[8]);
+template <> __device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4 &raw, float (&x)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[2 * i] = __uint_as_float(w[i] << 16);
+    x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <> __device__ __forceinline__ void unpack8<__half>(const uint4 &raw, float (&x)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+    x[2 * i] = f.x;
+    x[2 * i + 1] = f.y;
+  }
 }
 // the same element by the IEEE division, for the groups the fast test does not cover
 template <bool HAS_OFF>
-__device__ __noinline__ uint32_t quant_exact(float x, float d, float off) {
+__device__ __forceinline__ uint32_t quant_exact(float x, float d, float off) {
   float v = rintf(__fdiv_rn(x, d));
   if (HAS_OFF) v = __fsub_rn(v, off);
   if (v != v) v = 0.f;
   v = fminf(fmaxf(v, -128.f), 127.f);
   return __float_as_uint(v + kQMagic);
 }
-// byte 0 of four words -> one word
-__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
-  uint32_t t0, t1, o;
-  asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(t0) : "r"(w0), "r"(w1));
-  asm("prmt.b32 %0, %1, %2, 0x0040;" : "=r"(t1) : "r"(w2), "r"(w3));
-  asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(o) : "r"(t0), "r"(t1));
+// low 16 bits of four words, each clamped to [-128, 127] as a signed 16-bit value -> four bytes
+__device__ __forceinline__ uint32_t clamp_pack4(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+  uint32_t h01, h23, o;
+  asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(h01) : "r"(w0), "r"(w1));
+  asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(h23) : "r"(w2), "r"(w3));
+  asm("max.s16x2 %0, %0, %1;" : "+r"(h01) : "r"(0xff80ff80u));
+  asm("min.s16x2 %0, %0, %1;" : "+r"(h01) : "r"(0x007f007fu));
+  asm("max.s16x2 %0, %0, %1;" : "+r"(h23) : "r"(0xff80ff80u));
+  asm("min.s16x2 %0, %0, %1;" : "+r"(h23) : "r"(0x007f007fu));
+  asm("prmt.b32 %0, %1, %2, 0x6420;" : "=r"(o) : "r"(h01), "r"(h23));
   return o;
+}
+// A whole group of eight by the division: ONE out-of-line call, so that the rare path costs the common
+// one a single branch and no argument set-up (scales and offsets are re-read from global memory here).
+template <typename T, bool HAS_OFF>
+__device__ __noinline__ uint2 quant_group_exact(uint4 raw, const float *__restrict__ ds, const int32_t *__restrict__ of) {
+  float x[8];
+  unpack8<T>(raw, x);
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w[i] = quant_exact<HAS_OFF>(x[i], __ldg(ds + i), HAS_OFF ? (float)__ldg(of + i) : 0.f);
+  return make_uint2(clamp_pack4(w[0], w[1], w[2], w[3]), clamp_pack4(w[4], w[5], w[6], w[7]));
+}
+// reciprocal of a channel's scale for the fast test, NaN (= always take the division) when the
+// reciprocal would not be a correctly rounded normal number or the offset is beyond the 16-bit argument
+__device__ __forceinline__ float quant_reciprocal(float d, float off) {
+  const float ad = fabsf(d);
+  const bool plain = ad >= 1.1754944e-38f && ad <= 4.2535296e37f && fabsf(off) <= kQMaxOffset;  // [2^-126, 2^125]
+  return plain ? __frcp_rn(d) : __int_as_float(0x7fc00000);
 }
 
 // One warp quantises whole K rows or whole V rows (fixed per warp), striding over the tokens with
 // the next token's slot and row already in flight while the current one is converted.  The grid
 // is sized to what is resident at once, so the per-warp set-up (reciprocal scales, offsets) is paid
 // once and the loop runs at the rate of the conversion units.
+// (with offsets the 32 extra registers per thread would spill at two blocks per SM: one block then)
 template <typename T, bool HAS_OFF>
-__global__ void __launch_bounds__(kRacThreads, 2)
+__global__ void __launch_bounds__(kRacThreads, HAS_OFF ? 1 : 2)
 rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ value,
                               int8_t *__restrict__ key_cache, int8_t *__restrict__ value_cache,
                               const int32_t *__restrict__ slot_mapping, int64_t num_tokens, int elems,
@@ -310,7 +362,8 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
                               const float *__restrict__ v_descale, const int32_t *__restrict__ v_offset,
                               int64_t num_slots, int32_t *oob_count, bool has_v,
                               uint32_t *__restrict__ clear, int clear_words) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see rac_scatter16_kernel
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // see rac_scatter16_kernel
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   for (int i = blockIdx.x * kRacThreads + threadIdx.x; i < clear_words; i += gridDim.x * kRacThreads) clear[i] = 0u;
   const int lane = threadIdx.x & 31;
   const int64_t unit = (int64_t)blockIdx.x * kRacWarps + (threadIdx.x >> 5);
@@ -335,13 +388,8 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      r[it][i] = __frcp_rn(dd[i]);
-      if (HAS_OFF) {
-        o[it][i] = (float)oo[i];
-        // the fast test is proven for |offset| <= 128 (quotients beyond 512 then saturate whichever way
-        // they round); channels with a larger offset always take the exact path
-        if (fabsf(o[it][i]) > 128.f) r[it][i] = __int_as_float(0x7fc00000);
-      }
+      if (HAS_OFF) o[it][i] = (float)oo[i];
+      r[it][i] = quant_reciprocal(dd[i], HAS_OFF ? (float)oo[i] : 0.f);
     }
   }
   const T *src_base = is_v ? value : key;
@@ -377,17 +425,23 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
       for (int it = 0; it < 4; ++it) {
         const int e = lane * 8 + it * 256;
         if (e < elems) {
-          const T *x = reinterpret_cast<const T *>(&cur[it]);
+          float x[8];
+          unpack8<T>(cur[it], x);
           uint32_t w[8];
           bool ok = true;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) w[i] = quant_fast<HAS_OFF>(to_f32<T>(x[i]), r[it][i], HAS_OFF ? o[it][i] : 0.f, ok);
-          if (!ok) {  // rare: a tie, a huge quotient, an odd scale somewhere in these eight
-            // (unrolled: a run-time index would push the register arrays into local memory)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) w[i] = quant_exact<HAS_OFF>(to_f32<T>(x[i]), __ldg(ds + e + i), HAS_OFF ? o[it][i] : 0.f);
+          for (int i = 0; i < 8; ++i) w[i] = quant_fast<HAS_OFF>(x[i], r[it][i], HAS_OFF ? o[it][i] : 0.f, ok);
+          uint32_t lo, hi;
+          // rare: a tie, a huge quotient, an odd scale somewhere in these eight (of any lane: the vote
+          // keeps the branch warp-uniform, and the division gives the same bits where the test passed)
+          if (__any_sync(__activemask(), !ok)) {
+            const uint2 ex = quant_group_exact<T, HAS_OFF>(cur[it], ds + e, HAS_OFF ? of + e : nullptr);
+            lo = ex.x;
+            hi = ex.y;
+          } else {
+            lo = clamp_pack4(w[0], w[1], w[2], w[3]);
+            hi = clamp_pack4(w[4], w[5], w[6], w[7]);
           }
-          const uint32_t lo = pack_low_bytes(w[0], w[1], w[2], w[3]), hi = pack_low_bytes(w[4], w[5], w[6], w[7]);
           asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(dst + it * 256), "r"(lo), "r"(hi) : "memory");
         }
       }
@@ -403,6 +457,23 @@ rac_scatter_quant_fast_kernel(const T *__restrict__ key, const T *__restrict__ v
 }
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Launch with programmatic stream serialisation: the grid may become resident while the kernel in
+// front of it on the stream drains (the kernel itself waits, griddepcontrol.wait, before it touches
+// memory), which hides the launch latency between two decode steps.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 }  // namespace
 }  // namespace msco
@@ -455,13 +526,13 @@ int msco::launch_rac(const void *key, const void *value, void *key_cache, void *
   if (vec) {
     const int k16 = (int)(k_row_bytes / 16), v16 = (int)(v_row_bytes / 16);
     if (k16 + v16 > 128) {
-      rac_scatter16_kernel<8, true><<<grid16, block, 0, st>>>(
+      MSCO_CUDA_CHECK(launch_overlapped(rac_scatter16_kernel<8, true>, grid16, block, st,
           (const uint4 *)key, (const uint4 *)value, (uint4 *)key_cache, (uint4 *)value_cache, slot_mapping,
-          num_tokens, k16, v16, num_slots, oob_count, clear, clear_words);
+          num_tokens, k16, v16, num_slots, oob_count, clear, clear_words));
     } else {
-      rac_scatter16_kernel<4, true><<<grid16, block, 0, st>>>(
+      MSCO_CUDA_CHECK(launch_overlapped(rac_scatter16_kernel<4, true>, grid16, block, st,
           (const uint4 *)key, (const uint4 *)value, (uint4 *)key_cache, (uint4 *)value_cache, slot_mapping,
-          num_tokens, k16, v16, num_slots, oob_count, clear, clear_words);
+          num_tokens, k16, v16, num_slots, oob_count, clear, clear_words));
     }
     *cleared = clear_words > 0;
   } else if (k_row_bytes % 2 == 0 && v_row_bytes % 2 == 0 && (((uintptr_t)key | (uintptr_t)key_cache |
@@ -577,9 +648,9 @@ int msco::launch_rac_quant(const void *key, const void *value, int8_t *key_cache
     const int64_t want = (rows + kRacWarps - 1) / kRacWarps;
     const dim3 gridf((unsigned)std::min<int64_t>(want, (int64_t)sms * 2));  // two resident CTAs per SM
 #define MSCO_QF(T, OFF)                                                                                     \
-  rac_scatter_quant_fast_kernel<T, OFF><<<gridf, block, 0, st>>>(                                           \
+  MSCO_CUDA_CHECK(launch_overlapped(rac_scatter_quant_fast_kernel<T, OFF>, gridf, block, st,                \
       (const T *)key, (const T *)value, key_cache, value_cache, slot_mapping, num_tokens, (int)k_row_elems, \
-      k_descale, k_offset, v_descale, v_offset, num_slots, oob_count, has_v, clear, clear_words)
+      k_descale, k_offset, v_descale, v_offset, num_slots, oob_count, has_v, clear, clear_words))
     if (in_dtype == MSCO_DTYPE_F16) { if (has_off) MSCO_QF(__half, true); else MSCO_QF(__half, false); }
     else { if (has_off) MSCO_QF(__nv_bfloat16, true); else MSCO_QF(__nv_bfloat16, false); }
 #undef MSCO_QF

@@ -136,13 +136,20 @@ def pa_launch(plan: _abi.PaPlan, query, key_cache, value_cache, block_tables, ou
 
 
 def decode_step(plan: _abi.PaPlan, key, value, key_cache, value_cache, slot_mapping, query, block_tables, out,
-                workspace, k_descale=None, k_offset=None, v_descale=None, v_offset=None, mask=None):
-    """msco_decode_step on the current stream: cache scatter + attention in one call."""
-    _abi.check(_abi.lib().msco_decode_step(
-        plan.handle, _ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache), _ptr(slot_mapping),
-        slot_mapping.numel(), _ptr(query), _ptr(block_tables), _ptr(k_descale), _ptr(k_offset), _ptr(v_descale),
-        _ptr(v_offset), _ptr(mask), _ptr(out), _ptr(workspace), workspace.numel() * workspace.element_size(),
-        _stream()))
+                workspace, k_descale=None, k_offset=None, v_descale=None, v_offset=None, mask=None, gather=None):
+    """msco_decode_step on the current stream: cache scatter + attention in one call.
+    `gather` (a sharding.PeerGather): msco_decode_step_gather instead -- the kernel that finishes the
+    output rows also pushes them to the peers; returns this rank's gathered buffer then."""
+    args = (plan.handle, _ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache), _ptr(slot_mapping),
+            slot_mapping.numel(), _ptr(query), _ptr(block_tables), _ptr(k_descale), _ptr(k_offset), _ptr(v_descale),
+            _ptr(v_offset), _ptr(mask), _ptr(out), _ptr(workspace), workspace.numel() * workspace.element_size(),
+            _stream())
+    if gather is None:
+        _abi.check(_abi.lib().msco_decode_step(*args))
+        return None
+    desc, step, buf = gather.next_step()
+    _abi.check(_abi.lib().msco_decode_step_gather(*args, desc, step))
+    return buf
 
 
 def pa_status(plan: _abi.PaPlan, workspace) -> int:

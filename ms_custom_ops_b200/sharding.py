@@ -266,6 +266,13 @@ class PeerGather:
             C.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return self.buffers[parity]
 
+    def next_step(self):
+        """(descriptor by reference, step counter, gathered buffer) of the next exchange, for
+        msco_decode_step_gather: the decode step's own finishing kernel does the push and the wait."""
+        self.step += 1
+        parity = self.step & 1
+        return self._C.byref(self.descs[parity]), self._C.c_uint32((self.step + 1) // 2), self.buffers[parity]
+
     def check(self):
         """After a synchronise: raises if a bounded wait for a peer expired."""
         if int(self.words[1].item()) != 0:

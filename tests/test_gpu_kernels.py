@@ -128,6 +128,44 @@ def test_rac_quant_bit_exact(dtype, offsets):
     assert np.array_equal(to_np(dvc), gv)
 
 
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("offsets", [False, True])
+def test_rac_quant_adversarial_scales_ties_and_offsets(dtype, offsets):
+    # every 16-bit input value (NaN and infinities included) against scales chosen per element to land
+    # the quotient on or next to a tie or an integer, scales that are zero, denormal, huge, infinite, NaN
+    # or negative, powers of two, and offsets up to far beyond the int8 range: bit-exact against the
+    # division of the oracle wherever the kernel's division-free test accepts and wherever it does not
+    c, tokens = 1024, 512
+    rng = np.random.default_rng(11)
+    allv = np.arange(65536, dtype=np.uint16).view(np.float16).astype(np.float32) if dtype == "float16" else \
+        (np.arange(65536, dtype=np.uint32) << 16).view(np.float32)
+    key = rng.choice(allv, (tokens, c)).astype(np.float32)
+    val = rng.choice(allv, (tokens, c)).astype(np.float32)
+    with np.errstate(all="ignore"):
+        x0 = np.abs(key[0]) + 1e-3
+        kd = np.empty(c, np.float32)
+        kd[0::4] = x0[0::4] / (rng.integers(0, 300, c // 4) + 0.5) * (1 + rng.integers(-3, 4, c // 4) * 2.0 ** -23)
+        kd[1::4] = x0[1::4] / rng.integers(1, 30000, c // 4) * (1 + rng.integers(-3, 4, c // 4) * 2.0 ** -23)
+        kd[2::4] = 2.0 ** rng.integers(-20, 8, c // 4)
+        kd[3::4] = rng.random(c // 4) * 0.04 + 0.01
+        vd = np.exp(rng.uniform(-60, 60, c)).astype(np.float32) * rng.choice([-1.0, 1.0], c).astype(np.float32)
+        odd = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1e-45, 1e-39, 3e38, 1.7e38, 1.2e-38], dtype=np.float32)
+        vd[:64] = rng.choice(odd, 64)
+    kd = np.nan_to_num(kd, nan=1.0, posinf=1.0, neginf=1.0).astype(np.float32)
+    kd[kd == 0] = 1.0
+    ko = rng.choice([0, 1, -7, 127, -128, 129, 8192, -8192, 8193, 1 << 20], c).astype(np.int32) if offsets else None
+    vo = rng.integers(-200, 200, c).astype(np.int32) if offsets else None
+    key, val = key.astype(NP[dtype]), val.astype(NP[dtype])
+    slots = rng.permutation(tokens).astype(np.int32)
+    zero = np.zeros((tokens // 128, 128, 8, 128), np.int8)
+    gk, gv = oracle.reshape_and_cache_quant_golden(key, val, zero, zero.copy(), slots, kd, vd, ko, vo)
+    dkc, dvc = to_dev(zero), to_dev(zero)
+    kernels.rac_scatter_quant(to_dev(key), to_dev(val), dkc, dvc, to_dev(slots), to_dev(kd), to_dev(vd),
+                              to_dev(ko), to_dev(vo))
+    assert np.array_equal(to_np(dkc), gk)
+    assert np.array_equal(to_np(dvc), gv)
+
+
 # ----------------------------------------------------------------------------
 # paged attention
 # ----------------------------------------------------------------------------

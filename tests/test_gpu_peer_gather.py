@@ -100,3 +100,69 @@ def test_bounded_wait_for_a_peer_runs_out_and_reports_timeout():
                                               C.c_void_p(torch.cuda.current_stream().cuda_stream)))
     torch.cuda.synchronize()
     assert int(words[1].item()) == 0
+
+
+@pytest.mark.parametrize("lens", [[700, 1500, 33, 0, 5000, 129], [40, 17, 300, 511]])
+def test_decode_step_gather_pushes_the_finished_rows(lens):
+    """msco_decode_step_gather on one GPU standing in for rank 1 of two: the flag of the absent rank 0 is
+    provided by the test, so nothing waits on another launch.  The step's output must equal the plain
+    msco_decode_step's bit for bit, and slot 1 of BOTH gathered buffers must hold it -- rows that were
+    merged from splits and rows the attention kernel wrote itself alike (the second case has no split
+    at all: the finishing kernel runs only for the exchange)."""
+    import ctypes as C
+
+    import numpy as np
+
+    from ms_custom_ops_b200 import _abi, kernels, workloads
+    dev = torch.device("cuda", 0)
+    spec = workloads.DecodeSpec("gather", len(lens), 8, kv_heads=2, seed=5, len_lo=1, len_hi=1)
+    rng = np.random.default_rng(3)
+    lens_np = np.array(lens, dtype=np.int32)
+    nb, tables, slots = workloads.layout(spec, lens_np, rng)
+    g = torch.Generator(device=dev)
+    g.manual_seed(9)
+    kc = torch.randn((nb, 128, 2, 128), generator=g, device=dev).to(torch.bfloat16)
+    vc = torch.randn((nb, 128, 2, 128), generator=g, device=dev).to(torch.bfloat16)
+    q = torch.randn((len(lens), 8, 128), generator=g, device=dev).to(torch.bfloat16)
+    key = torch.randn((len(lens), 256), generator=g, device=dev).to(torch.bfloat16)
+    val = torch.randn((len(lens), 256), generator=g, device=dev).to(torch.bfloat16)
+    bt = torch.from_numpy(tables).to(dev)
+    sl = torch.from_numpy(slots).to(dev)
+    desc = kernels.make_pa_desc(q, kc, bt, spec.qk_scale, 0)
+    plan = _abi.PaPlan(desc, [int(x) for x in lens])
+    ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device=dev)
+    want = torch.empty_like(q)
+    kernels.decode_step(plan, key, val, kc, vc, sl, q, bt, want, ws)
+    torch.cuda.synchronize()
+
+    slice_bytes = q.numel() * 2
+    gathered = [torch.zeros(2 * slice_bytes, dtype=torch.uint8, device=dev) for _ in range(2)]
+    flags = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in range(2)]
+    words = torch.zeros(2, dtype=torch.int32, device=dev)
+    d = _abi.MscoGatherDesc()
+    d.world, d.rank, d.slice_bytes = 2, 1, slice_bytes
+    d.ticket, d.status = words.data_ptr(), words.data_ptr() + 4
+    d.wait_polls = 20000
+    for r in range(2):
+        d.gathered[r], d.flags[r] = gathered[r].data_ptr(), flags[r].data_ptr()
+    flags[1][0] = 1  # "rank 0 has pushed step 1": written by the test, rank 0 does not exist
+
+    class OneStep:
+        def next_step(self):
+            return C.byref(d), C.c_uint32(1), None
+    got = torch.empty_like(q)
+    kernels.decode_step(plan, key, val, kc, vc, sl, q, bt, got, ws, gather=OneStep())
+    torch.cuda.synchronize()
+    kernels.pa_status(plan, ws)
+    assert int(words[1].item()) == 0 and int(words[0].item()) == 0  # no timeout, ticket back at zero
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    mine = got.view(torch.uint8).reshape(-1)
+    for r in range(2):
+        assert torch.equal(gathered[r][slice_bytes:], mine), f"slot 1 of rank {r}'s buffer"
+        assert int(gathered[r][:slice_bytes].max().item()) == 0
+        assert int(flags[r][1].item()) == 1
+    # a slice of the wrong size is refused before anything is launched
+    d.slice_bytes = slice_bytes + 16
+    with pytest.raises(_abi.MscoError):
+        kernels.decode_step(plan, key, val, kc, vc, sl, q, bt, got, ws, gather=OneStep())
+    plan.close()
