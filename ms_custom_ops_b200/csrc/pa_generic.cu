@@ -270,9 +270,9 @@ __device__ __forceinline__ void reduce_row(const PaParams &p, const PlanView &pv
 // row, merged here or written by the attention kernel, into slot `rank` of every rank's gathered
 // buffer; the block that finishes last then publishes the step's flag and waits (bounded) for the
 // peers, exactly as the stand-alone gather kernel does.
-template <typename TQ>
+template <typename TQ, int PW>
 __global__ void __launch_bounds__(128)
-pa_reduce_kernel(PaParams p, const __grid_constant__ PlanParam pp, const __grid_constant__ GatherArgs g) {
+pa_reduce_kernel(PaParams p, const __grid_constant__ PlanParamT<PW> pp, const __grid_constant__ GatherArgs g) {
   __shared__ bool is_last;
   // a kernel launched behind this one with programmatic stream serialisation may become resident
   // now; it waits for this grid before it reads the output
@@ -335,8 +335,15 @@ int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, const PlanParam 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (plan->desc.q_dtype == MSCO_DTYPE_F16) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__half>, p, pp, g));
-  else MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__nv_bfloat16>, p, pp, g));
+  const bool f16 = plan->desc.q_dtype == MSCO_DTYPE_F16;
+  if (p.plan_in_param && plan->plan_words <= (size_t)kPlanParamWordsSmall) {  // see PlanParamSmall
+    const PlanParamSmall &ps = *reinterpret_cast<const PlanParamSmall *>(&pp);
+    if (f16) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__half, kPlanParamWordsSmall>, p, ps, g));
+    else MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__nv_bfloat16, kPlanParamWordsSmall>, p, ps, g));
+    return MSCO_OK;
+  }
+  if (f16) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__half, kPlanParamWords>, p, pp, g));
+  else MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__nv_bfloat16, kPlanParamWords>, p, pp, g));
   return MSCO_OK;
 }
 

@@ -47,10 +47,16 @@ struct PaParams {
 
 // Plans of up to kPlanParamWords words travel as a kernel parameter (no upload, no stream
 // operation in front of the attention kernel); larger ones are copied into the workspace.
+// Two parameter sizes: a launch with 9 KB of parameters starts about a microsecond later than one with
+// 2.5 KB, so plans of up to kPlanParamWordsSmall words (about 70 sequences) use the small form.
 constexpr int kPlanParamWords = 2304;
-struct PlanParam {
-  int32_t w[kPlanParamWords];
+constexpr int kPlanParamWordsSmall = 640;
+template <int W>
+struct PlanParamT {
+  int32_t w[W];
 };
+using PlanParam = PlanParamT<kPlanParamWords>;
+using PlanParamSmall = PlanParamT<kPlanParamWordsSmall>;  // a prefix of PlanParam
 constexpr size_t kPlanRegionOffset = 256;  // workspace: [status block | plan words | scheduling words | partials]
 constexpr int kSyncHeaderWords = 4;        // scheduling words: [ticket, 3 unused, one counter per group]
 

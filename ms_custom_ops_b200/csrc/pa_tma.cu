@@ -108,10 +108,10 @@ __device__ __forceinline__ float load_mask_elem(const void *mask, int dtype, int
   return __ldg(static_cast<const float *>(mask) + idx);
 }
 
-template <typename T, int D, bool KV8, int NT, bool MASK, int SUBS>
+template <typename T, int D, bool KV8, int NT, bool MASK, int SUBS, int PW>
 __global__ void __launch_bounds__(Cfg<D, KV8, NT, SUBS>::kThreads, 1)
 pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, PaParams p,
-              const __grid_constant__ PlanParam pp) {
+              const __grid_constant__ PlanParamT<PW> pp) {
   using C = Cfg<D, KV8, NT, SUBS>;
   // fp16 arithmetic for int8 KV (integers up to 1279 are exact in fp16, not in bf16)
   using MT = typename std::conditional<KV8, __half, T>::type;
@@ -409,6 +409,23 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const int tok0 = dsc[4], tok1 = dsc[5], nsplit = dsc[6], part = dsc[7];
     const int grp = dsc[8], part0 = dsc[9], qtok0 = dsc[10], ntok = dsc[11];
     const int gt = ntok > 1 ? p.group : 16;  // q rows per stacked query token: row r belongs to token r / gt
+    // additive mask: element offset of context token tok0 in the mask row of each of this lane's q rows
+    // (rows 8nt + 2q4 + j), once per item; -1 for rows the item does not have
+    int64_t mrow[MASK ? NT : 1][2];
+    if (MASK) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int r = 8 * nt + 2 * q4 + j;
+          mrow[nt][j] = -1;
+          if (r < nrows) {
+            const int tq = r / gt;
+            mrow[nt][j] = (int64_t)(qtok0 + tq) * p.mask_batch_stride +
+                          (int64_t)(kvh * p.group + row0 + r - tq * gt) * p.mask_head_stride + tok0;
+          }
+        }
+    }
     float *mbuf = reinterpret_cast<float *>(smem + C::kOffMerge + (C::kMergeBufs == 2 ? (qi & 1) * C::kMergeBytes : 0));
     float2 *mlbuf = reinterpret_cast<float2 *>(smem + C::kOffMl + (C::kMergeBufs == 2 ? (qi & 1) * C::kMlBytes : 0));
 
@@ -485,14 +502,11 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             mk[sb][nt][0] = mk[sb][nt][1] = mk[sb][nt][2] = mk[sb][nt][3] = 0.f;
             if (active) {
               const int tw = t0 + 16 * sb + gid;  // token inside the tile
-              const int tk = tok0 + ti * kTile + tw;
+              const int tk = ti * kTile + tw;     // ... and inside the item
 #pragma unroll
               for (int j = 0; j < 2; ++j) {
-                const int r = 8 * nt + 2 * q4 + j;
-                if (r < nrows) {
-                  const int tq = r / gt;
-                  const int64_t base = (int64_t)(qtok0 + tq) * p.mask_batch_stride +
-                                       (int64_t)(kvh * p.group + row0 + r - tq * gt) * p.mask_head_stride;
+                const int64_t base = mrow[MASK ? nt : 0][j];
+                if (base >= 0) {
                   if (tw < nv) mk[sb][nt][j] = load_mask_elem(p.mask, p.mask_dtype, base + tk);
                   if (tw + 8 < nv) mk[sb][nt][2 + j] = load_mask_elem(p.mask, p.mask_dtype, base + tk + 8);
                 }
@@ -818,12 +832,12 @@ int make_cache_tmap(CUtensorMap *tm, const void *cache, const MscoPaDesc &d) {
   return MSCO_OK;
 }
 
-template <typename T, int D, bool KV8, int NT, bool MASK, int SUBS>
-int launch_one(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, const CUtensorMap &tk,
-               const CUtensorMap &tv, cudaStream_t stream, bool after_kernel) {
+template <typename T, int D, bool KV8, int NT, bool MASK, int SUBS, int PW>
+int launch_sized(const MscoPaPlan *plan, const PaParams &p, const PlanParamT<PW> &pp, const CUtensorMap &tk,
+                 const CUtensorMap &tv, cudaStream_t stream, bool after_kernel) {
   using C = Cfg<D, KV8, NT, SUBS>;
   static_assert(C::kDynSmem <= 232448, "shared memory budget of one SM exceeded");
-  auto kfn = pa_tma_kernel<T, D, KV8, NT, MASK, SUBS>;
+  auto kfn = pa_tma_kernel<T, D, KV8, NT, MASK, SUBS, PW>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [&] {
@@ -843,6 +857,16 @@ int launch_one(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, c
   cfg.numAttrs = after_kernel ? 1 : 0;
   MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kfn, tk, tv, p, pp));
   return MSCO_OK;
+}
+
+// Small plans of the unmasked variants (the decode hot path) take the small parameter form.
+template <typename T, int D, bool KV8, int NT, bool MASK, int SUBS>
+int launch_one(const MscoPaPlan *plan, const PaParams &p, const PlanParam &pp, const CUtensorMap &tk,
+               const CUtensorMap &tv, cudaStream_t stream, bool after_kernel) {
+  if (!MASK && p.plan_in_param && plan->plan_words <= (size_t)kPlanParamWordsSmall)
+    return launch_sized<T, D, KV8, NT, false, SUBS, kPlanParamWordsSmall>(
+        plan, p, *reinterpret_cast<const PlanParamSmall *>(&pp), tk, tv, stream, after_kernel);
+  return launch_sized<T, D, KV8, NT, MASK, SUBS, kPlanParamWords>(plan, p, pp, tk, tv, stream, after_kernel);
 }
 
 }  // namespace
