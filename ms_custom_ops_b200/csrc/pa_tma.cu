@@ -178,9 +178,10 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     // Work items are handed out by a ticket (the list is longest-first): the first two items of a CTA
     // are fixed (its own index, and that plus the grid size), every further one comes from an atomic
     // counter in the workspace that is zero when the kernel starts.  Which CTA computes an item has no
-    // influence on the item's bits.  The descriptor and the q rows of item i + 1 are published BEFORE
-    // the tiles of item i are issued, so they are in shared memory (and, for an int8 cache, converted
-    // by the helper warp) a whole item ahead of their use.
+    // influence on the item's bits.  The descriptor and the q rows of item i + 1 are published as soon as
+    // the last tile of item i has been issued -- the consumers still have the tiles in the ring in
+    // front of them -- so they are in shared memory (and, for an int8 cache, converted by the helper
+    // warp) before the consumers ask for them.
     auto publish = [&](const WorkItem &w, int qs) {  // lane 0: descriptor + q rows into slot qs
       int *d = desc + qs * kDescInts;
       d[0] = w.b; d[1] = w.kvh; d[2] = w.row0; d[3] = w.nrows;
@@ -197,34 +198,19 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         bulk_load(smem + C::kOffQ + qs * C::kQSlotBytes + tq * run, qsrc, run, &qfull[qs]);
       }
     };
-    int t_nxt = (int)blockIdx.x + (int)gridDim.x;
+    int t_nxt = (int)blockIdx.x + (int)gridDim.x;  // the second item of a CTA is fixed too
     WorkItem w = decode_item(pv, blockIdx.x, p.num_kv_heads, p.group, C::kRows, ibs);  // grid <= items
     if (lane == 0) publish(w, 0);  // slot 0 is free at the start
     for (int qi = 0;; ++qi) {
-      // next-but-one ticket: its latency hides behind this item's loads
-      int t_nn = 0;
-      if (synced && lane == 0) t_nn = 2 * (int)gridDim.x + (int)atomicAdd(p.sync, 1u);
-      auto sync_once = [&]() {  // first item only: the scatter kernel's writes, then the first ticket
+      // the ticket of item qi + 1 is drawn here and used once this item's tiles are out: its latency
+      // hides behind them, and a CTA never holds more than the item it loads (a ticket drawn any
+      // earlier would pin one more item to this CTA and lengthen the tail of the grid by that item)
+      int t_draw = 0;
+      if (qi >= 1 && lane == 0) t_draw = 2 * (int)gridDim.x + (int)atomicAdd(p.sync, 1u);
+      auto sync_once = [&]() {  // first item only: from here on the scatter kernel's writes are visible
         asm volatile("griddepcontrol.wait;" ::: "memory");
         synced = true;
-        if (lane == 0) t_nn = 2 * (int)gridDim.x + (int)atomicAdd(p.sync, 1u);
       };
-      // item qi + 1 (or the end marker) into the other slot, once the consumers have let go of it
-      const int ns = (qi + 1) & 1;
-      const uint32_t nph = ((qi + 1) >> 1) & 1;
-      if (!mbar_wait(&qempty[ns], nph ^ 1, kWaitLimit)) {
-        report_status(p.status, p.epoch, kStatusTimeout);
-        return;
-      }
-      const bool more = t_nxt < total;
-      WorkItem w_nxt = w;
-      if (more) {
-        w_nxt = decode_item(pv, t_nxt, p.num_kv_heads, p.group, C::kRows, ibs);
-        if (lane == 0) publish(w_nxt, ns);
-      } else if (lane == 0) {  // no work left: tell the consumers
-        desc[ns * kDescInts] = -1;
-        mbar_arrive(&qfull[ns]);
-      }
       const int ntok = w.tok1 - w.tok0;
       const int nblk_item = (ntok + bs - 1) / bs;
       const int32_t *trow = p.block_tables + (int64_t)w.b * p.max_blocks_per_seq + w.tok0 / bs;
@@ -273,10 +259,24 @@ pa_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           }
         }
       }
-      if (!synced) sync_once();  // (an item without a tile: cannot happen, but the ticket must be drawn)
-      if (!more) break;
-      w = w_nxt;
-      t_nxt = __shfl_sync(0xffffffffu, t_nn, 0);
+      if (!synced) sync_once();  // (an item without a tile cannot happen; the scheduling words need the wait)
+      // item qi + 1 (or the end marker) into the other slot, once the consumers have let go of it
+      if (qi >= 1) t_nxt = __shfl_sync(0xffffffffu, t_draw, 0);
+      const int ns = (qi + 1) & 1;
+      const uint32_t nph = ((qi + 1) >> 1) & 1;
+      if (!mbar_wait(&qempty[ns], nph ^ 1, kWaitLimit)) {
+        report_status(p.status, p.epoch, kStatusTimeout);
+        return;
+      }
+      if (t_nxt >= total) {  // no work left: tell the consumers
+        if (lane == 0) {
+          desc[ns * kDescInts] = -1;
+          mbar_arrive(&qfull[ns]);
+        }
+        break;
+      }
+      w = decode_item(pv, t_nxt, p.num_kv_heads, p.group, C::kRows, ibs);
+      if (lane == 0) publish(w, ns);
     }
     return;
   }

@@ -12,7 +12,7 @@
 
 namespace msco {
 
-constexpr uint32_t kPeerWaitLimit = 1u << 22;  // polls of ~100 ns: gives up after about half a second
+constexpr uint32_t kPeerWaitLimit = 1u << 22;  // polls of ~0.1 us: gives up after about half a second
 
 struct GatherArgs {
   void *gathered[MSCO_MAX_PEERS];   // rank r's gathered buffer as mapped into this process
@@ -43,29 +43,42 @@ __device__ __forceinline__ void gather_push16(const GatherArgs &a, int64_t off, 
     *reinterpret_cast<uint4 *>(static_cast<char *>(a.gathered[r]) + (int64_t)a.rank * a.slice_bytes + off) = v;
 }
 
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // Called by every thread of every block after the block's pushes: the block that arrives last
 // publishes the flags and waits for the peers.  `is_last` is a shared-memory flag of the caller.
+// System-scope fences are what this exchange costs (each waits for the acknowledgement of the peer
+// stores in flight, a round trip over NVLink), so there is exactly one per block on the way in -- by one
+// thread, after the block barrier, which makes it cover the whole block's stores -- and the flag itself
+// is a release store; the spin reads relaxed and fences once when the flag has arrived.  (One fence per
+// thread plus an acquiring load per poll cost 20 us per exchange on two GPUs, twice a library all-gather.)
 __device__ __forceinline__ void gather_finish(const GatherArgs &a, bool *is_last) {
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
+    __threadfence_system();  // the block's pushes (ordered before the barrier) precede its ticket
     const unsigned int t = atomicAdd(a.ticket, 1u);
     *is_last = (t == gridDim.x - 1);
-    if (*is_last) *a.ticket = 0u;  // ready for the next launch on this stream
+    if (*is_last) {
+      *a.ticket = 0u;        // ready for the next launch on this stream
+      __threadfence_system();  // the tickets of the other blocks (and with them their pushes) precede the flags
+    }
   }
   __syncthreads();
   if (!*is_last) return;
   if ((int)threadIdx.x < a.world) {
     const int r = threadIdx.x;
-    __threadfence_system();  // every block's pushes (ordered before its ticket) precede the flag
     st_release_sys(a.flags[r] + a.rank, a.step);  // "rank's slice of step `step` is in your buffer"
     const uint32_t *mine = a.flags[a.rank] + r;   // peer r's announcement in my own flag array
     bool ok = false;
     for (uint32_t it = 0; it < a.wait_limit; ++it) {
-      if ((int32_t)(ld_acquire_sys(mine) - a.step) >= 0) { ok = true; break; }
-      __nanosleep(100);
+      if ((int32_t)(ld_relaxed_sys(mine) - a.step) >= 0) { ok = true; break; }
+      __nanosleep(40);
     }
+    __threadfence_system();  // acquire side: the peer's slice (written before its flag) is visible from here on
     if (!ok) atomicExch(a.status, kStatusTimeout);  // a peer never arrived: report, do not hang
   }
 }
