@@ -452,3 +452,36 @@ def test_stacked_query_tokens_plan():
     assert plan([3], [100], hq=128, hkv=8).info().work_items == 3 * 8              # 16 per kv head: one token per item
     with pytest.raises(_abi.MscoError, match="TMA kernel"):
         plan([2], [100], d=40)
+
+
+def test_decode_step_gather_validates_before_anything_is_launched():
+    # the fused decode step with the exchange folded in: a NULL plan, an empty batch and a malformed
+    # gather descriptor are refused on the host, before any CUDA call
+    import ctypes as C
+    L = _abi.lib()
+    nul = C.c_void_p(None)
+
+    def call(plan, desc):
+        return L.msco_decode_step_gather(plan, *([nul] * 5), 0, *([nul] * 9), 0, nul, desc, C.c_uint32(1))
+
+    def last_error():
+        return L.msco_last_error().decode()
+
+    d = _abi.MscoGatherDesc()
+    assert call(nul, C.byref(d)) == _abi.ERR_INVALID_ARG
+    empty = _plan([])
+    assert call(empty.handle, C.byref(d)) == _abi.ERR_INVALID_ARG
+    assert "nothing to gather" in last_error()
+    plan = _plan([100, 2000])
+    assert call(plan.handle, None) == _abi.ERR_INVALID_ARG
+    assert "NULL gather descriptor" in last_error()
+    d.world, d.rank, d.slice_bytes = 2, 2, 4096           # rank out of range
+    assert call(plan.handle, C.byref(d)) == _abi.ERR_INVALID_ARG
+    assert "bad rank" in last_error()
+    d.rank, d.slice_bytes = 1, 4090                        # not a multiple of 16
+    assert call(plan.handle, C.byref(d)) == _abi.ERR_INVALID_ARG
+    d.slice_bytes = 4096                                   # ticket / status words missing
+    assert call(plan.handle, C.byref(d)) == _abi.ERR_INVALID_ARG
+    assert "ticket / status" in last_error()
+    for p in (empty, plan):
+        p.close()
