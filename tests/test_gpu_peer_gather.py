@@ -166,3 +166,72 @@ def test_decode_step_gather_pushes_the_finished_rows(lens):
     with pytest.raises(_abi.MscoError):
         kernels.decode_step(plan, key, val, kc, vc, sl, q, bt, got, ws, gather=OneStep())
     plan.close()
+
+
+def _step_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import numpy as np
+
+        from ms_custom_ops_b200 import _abi, kernels, sharding, workloads
+        lens = [700, 1500, 33, 5000, 129, 2048]
+        hq, hkv = 8, 2                      # per rank
+        spec = workloads.DecodeSpec("gather2", len(lens), hq, kv_heads=hkv, seed=5, len_lo=1, len_hi=1)
+        rng = np.random.default_rng(3)      # same tables on every rank
+        nb, tables, slots = workloads.layout(spec, np.array(lens, dtype=np.int32), rng)
+        g = torch.Generator(device=dev)
+        g.manual_seed(100 + rank)           # every rank its own heads
+        kc = torch.randn((nb, 128, hkv, 128), generator=g, device=dev).to(torch.bfloat16)
+        vc = torch.randn((nb, 128, hkv, 128), generator=g, device=dev).to(torch.bfloat16)
+        q = torch.randn((len(lens), hq, 128), generator=g, device=dev).to(torch.bfloat16)
+        key = torch.randn((len(lens), hkv * 128), generator=g, device=dev).to(torch.bfloat16)
+        val = torch.randn((len(lens), hkv * 128), generator=g, device=dev).to(torch.bfloat16)
+        bt, sl = torch.from_numpy(tables).to(dev), torch.from_numpy(slots).to(dev)
+        desc = kernels.make_pa_desc(q, kc, bt, spec.qk_scale, 0)
+        plan = _abi.PaPlan(desc, lens)
+        ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device=dev)
+        pg = sharding.PeerGather(q.shape, q.dtype, dev)
+        out = torch.empty_like(q)
+        ok = True
+        for step in range(4):  # both gathered buffers, twice
+            got = kernels.decode_step(plan, key, val, kc, vc, sl, q, bt, out, ws, gather=pg)
+            torch.cuda.synchronize()
+            pg.check()
+            kernels.pa_status(plan, ws)
+            want = sharding.all_gather_outputs(out)
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(got.view(torch.int16), want.view(torch.int16))
+            q = (q.float() * 0.5 + 0.1).to(torch.bfloat16)  # another query next step
+        ret[rank] = ok
+        dist.barrier()
+        plan.close()
+        pg.release()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_decode_step_gather_on_two_gpus_matches_nccl():
+    """The decode step whose finishing kernel pushes the rows to the peer, on two real ranks: the gathered
+    buffer of every rank equals NCCL's all-gather of the two local outputs, bit for bit, step after step."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_step_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+        assert p.exitcode == 0, "a rank failed or timed out"
+    assert dict(ret) == {0: True, 1: True}
