@@ -576,15 +576,28 @@ def measure_e2e(ctx, loop, args, exchange, barrier, max_over_ranks):
                  "pinned_slabs_added": a1["slabs"] - a0["slabs"], "arena_blocks_taken": a1["block_allocs"] - a0["block_allocs"]}
         return max_over_ranks(e0.elapsed_time(e1)) / K, stats
 
-    # (1) serial
+    # (1) serial.  What step i + 1 needs from step i's result is the CONTENT of its inputs; its lengths
+    # (one more token per sequence) and slots are known beforehand, so -- as a serving loop would --
+    # the host prepares them, and has the next step's launch plan made (a planning-only operator call
+    # that leaves the plan in the cache), while the GPU runs step i.  The staging sets alternate so
+    # that the pinned buffer being filled is never the one an upload may still be reading.
+    def plan_ahead(slot_i):
+        d_q, _, _, _, d_bt = d_views[slot_i]
+        ops.paged_attention_workspace_size(d_q, kc, vc, d_bt, h_lens, **pa_kw)
+
+    set_step(loop.i, loop.i & 1)
+
     def serial_step():
-        set_step(loop.i, 0)
-        d_stage[0].copy_(h_stage[0], non_blocking=True)
-        o = operators(0)
+        si = loop.i & 1
+        d_stage[si].copy_(h_stage[si], non_blocking=True)
+        o = operators(si)
         h_out[0].copy_(o, non_blocking=True)
+        set_step(loop.i + 1, si ^ 1)               # host work of the next step, under this step's GPU time
+        plan_ahead(si ^ 1)
         torch.cuda.current_stream().synchronize()  # the step's result is read on the host
         loop.i += 1
     serial_ms, serial_stats = time_loop(serial_step)
+    set_step(loop.i, 0)                            # the loops below start from the lengths of step loop.i
 
     # (2) pipelined
     comp = torch.cuda.current_stream()
@@ -643,7 +656,9 @@ def measure_e2e(ctx, loop, args, exchange, barrier, max_over_ranks):
     return {"value": b / serial_ms * 1e3, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "ms_per_step": serial_ms,
             "mode": "serial: upload -> reshape_and_cache + paged_attention (operator API) -> download -> host waits; "
-                    "lengths grow every step, every step re-plans",
+                    "lengths grow every step, every step needs a new launch plan (a plan-cache miss, re-planned in "
+                    "place), which the host has made by a planning-only operator call while the GPU ran the step "
+                    "before -- the lengths of a decode step are known ahead, its inputs are not",
             "plan_cache": serial_stats,
             "pipelined_value": b / pipe_ms * 1e3, "pipelined_ms_per_step": pipe_ms,
             "pipelined_mode": "two independent batches in flight: copy streams move step i+1's inputs and step i-1's "
