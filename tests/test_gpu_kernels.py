@@ -386,6 +386,49 @@ def test_fused_decode_step_equals_separate_calls(n, scale):
     plan.close()
 
 
+@pytest.mark.parametrize("n,scale", [(2, 0.1), (3, 0.3)])
+def test_decode_step_captured_in_a_cuda_graph_replays_bit_identically(n, scale):
+    # a decode step whose lengths do not change (a frozen step) can be captured once and replayed: the
+    # three launches -- with their programmatic launch overlap -- become graph nodes, the plan rides in
+    # the kernel parameters; the replays must reproduce the eager step's cache and output bit for bit
+    spec = workloads.config_spec(n, scale)
+    c = workloads.decode_case(spec)
+    dev = {k: to_dev(c[k]) for k in ("query", "key", "value", "block_tables", "slot_mapping")}
+    kd, vd = to_dev(c["k_descale"]), to_dev(c["v_descale"])
+    desc = kernels.make_pa_desc(dev["query"], to_dev(c["key_cache"]), dev["block_tables"], c["qk_scale"],
+                                1 if spec.kv_int8 else 0)
+    plan = _abi.PaPlan(desc, [int(x) for x in c["context_lens"]])
+    ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device="cuda")
+
+    def step(kc, vc, out):
+        kernels.decode_step(plan, dev["key"], dev["value"], kc, vc, dev["slot_mapping"], dev["query"],
+                            dev["block_tables"], out, ws, kd, None, vd, None)
+    kc0, vc0 = to_dev(c["key_cache"]), to_dev(c["value_cache"])
+    want = torch.empty_like(dev["query"])
+    step(kc0, vc0, want)            # eager: also sets the kernels' attributes before any capture
+    torch.cuda.synchronize()
+    kernels.pa_status(plan, ws)
+
+    kc1, vc1 = to_dev(c["key_cache"]), to_dev(c["value_cache"])
+    got = torch.empty_like(dev["query"])
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            step(kc1, vc1, got)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        got.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        kernels.pa_status(plan, ws)
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert torch.equal(kc1.view(torch.uint8), kc0.view(torch.uint8))
+    assert torch.equal(vc1.view(torch.uint8), vc0.view(torch.uint8))
+    plan.close()
+
+
 def test_pa_out_of_range_block_id_is_reported_not_faulted():
     case = _st_case("gqa_32to8_alibi", mask_free=True)
     v = st_inputs.operator_view(case)
