@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(kGenThreads) pa_generic_kernel(PaParams p, con
 // One warp per (sequence, q head) output row.  The (m, l) pairs of up to 32 splits are loaded by
 // the lanes in parallel (one split per lane, strided for more), the weights 2^(m_s - M) stay in
 // registers, and the partial rows are accumulated in split order with several loads in flight.
-template <typename TQ>
+template <typename TQ, int PF>
 __device__ __forceinline__ void reduce_row(const PaParams &p, const PlanView &pv, int row, int lane) {
   const int b = row / p.num_q_heads, hq = row - b * p.num_q_heads;
   const int ns = __ldg(pv.b_nsplit + b);
@@ -226,9 +226,9 @@ __device__ __forceinline__ void reduce_row(const PaParams &p, const PlanView &pv
   }
   const int base = __ldg(pv.b_part_base + b);
   // same code as the TMA kernel's own epilogue: identical bits
-  if (D == 128) { merge_row<TQ, 128>(p, row, hq, ns, base, lane); return; }
-  if (D == 64) { merge_row<TQ, 64>(p, row, hq, ns, base, lane); return; }
-  if (D == 256) { merge_row<TQ, 256>(p, row, hq, ns, base, lane); return; }
+  if (D == 128) { merge_row<TQ, 128, PF>(p, row, hq, ns, base, lane); return; }
+  if (D == 64) { merge_row<TQ, 64, PF>(p, row, hq, ns, base, lane); return; }
+  if (D == 256) { merge_row<TQ, 256>(p, row, hq, ns, base, lane); return; }  // (8 columns per lane: no batches, the registers of every launch would pay for them)
   const int64_t hq_stride = p.num_q_heads;
   // pass 1: M = max_s m_s (lanes stride over the splits)
   float M = kNeg;
@@ -270,7 +270,11 @@ __device__ __forceinline__ void reduce_row(const PaParams &p, const PlanView &pv
 // row, merged here or written by the attention kernel, into slot `rank` of every rank's gathered
 // buffer; the block that finishes last then publishes the step's flag and waits (bounded) for the
 // peers, exactly as the stand-alone gather kernel does.
-template <typename TQ, int PW>
+// PF: how many partial rows a lane requests at a time (see merge_row).  32 for launches with rows of more
+// than 16 splits (long contexts; 190 registers), 16 when the grid still fits the SMs in one wave at the
+// 110 registers that costs, 0 (56 registers, loads inside the loop) for grids of thousands of rows, where
+// occupancy hides the latency better than prefetching does.
+template <typename TQ, int PW, int PF>
 __global__ void __launch_bounds__(128)
 pa_reduce_kernel(PaParams p, const __grid_constant__ PlanParamT<PW> pp, const __grid_constant__ GatherArgs g) {
   __shared__ bool is_last;
@@ -284,7 +288,7 @@ pa_reduce_kernel(PaParams p, const __grid_constant__ PlanParamT<PW> pp, const __
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   const bool live = row < pv.batch * p.num_q_heads;
-  if (live) reduce_row<TQ>(p, pv, row, lane);
+  if (live) reduce_row<TQ, PF>(p, pv, row, lane);
   if (g.world == 0) return;
   if (live) {
     __syncwarp();  // the row was written by the lanes of this warp (or by the grid before us)
@@ -336,14 +340,21 @@ int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, const PlanParam 
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const bool f16 = plan->desc.q_dtype == MSCO_DTYPE_F16;
+  const int blocks = (rows + 3) / 4;
+  const int pf = plan->max_splits > 16 ? 32 : (blocks <= 4 * plan->num_sms ? 16 : 0);
+#define MSCO_RK(T, PW, PP)                                                                                 \
+  do {                                                                                                    \
+    if (pf == 32) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<T, PW, 32>, p, PP, g));       \
+    else if (pf == 16) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<T, PW, 16>, p, PP, g));  \
+    else MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<T, PW, 0>, p, PP, g));                 \
+  } while (0)
   if (p.plan_in_param && plan->plan_words <= (size_t)kPlanParamWordsSmall) {  // see PlanParamSmall
     const PlanParamSmall &ps = *reinterpret_cast<const PlanParamSmall *>(&pp);
-    if (f16) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__half, kPlanParamWordsSmall>, p, ps, g));
-    else MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__nv_bfloat16, kPlanParamWordsSmall>, p, ps, g));
-    return MSCO_OK;
+    if (f16) MSCO_RK(__half, kPlanParamWordsSmall, ps); else MSCO_RK(__nv_bfloat16, kPlanParamWordsSmall, ps);
+  } else {
+    if (f16) MSCO_RK(__half, kPlanParamWords, pp); else MSCO_RK(__nv_bfloat16, kPlanParamWords, pp);
   }
-  if (f16) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__half, kPlanParamWords>, p, pp, g));
-  else MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<__nv_bfloat16, kPlanParamWords>, p, pp, g));
+#undef MSCO_RK
   return MSCO_OK;
 }
 

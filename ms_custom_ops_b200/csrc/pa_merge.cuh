@@ -23,13 +23,41 @@ __device__ __forceinline__ float merge_warp_max(float v) {
 // are base, base + 1, ..., base + ns - 1.
 // D = head_dim (64, 128 or 256): a lane owns D / 32 consecutive columns.
 // All loads bypass L1 (ld.global.cg): the partials may have been written by other SMs of the same grid.
-template <typename TQ, int D>
+// PREFETCH = 0: the partial rows are loaded inside the accumulation loop (16-fold unrolled): the form for
+// the attention kernel's own epilogue, where registers are short.  PREFETCH = 16 or 32 (the merge kernel):
+// the rows are requested in batches of that many before the first is used, and the first batch goes out
+// before anything else -- it does not depend on the maxima of pass 1 -- so a row of up to PREFETCH splits
+// costs two dependent round trips (maxima, then nothing: the rows are already on their way) instead of
+// three or more.  Same accumulation order in every form: the same bits.
+template <typename TQ, int D, int PREFETCH = 0>
 __device__ __forceinline__ void merge_row(const PaParams &p, int64_t row, int hq, int ns, int base, int lane) {
   static_assert(D == 64 || D == 128 || D == 256, "head_dim 64, 128 or 256");
+  static_assert(PREFETCH == 0 || PREFETCH == 16 || PREFETCH == 32, "batches of 16 or 32 rows");
   constexpr int kCols = D / 32;  // columns per lane: 2, 4 or 8
+  constexpr int kBatch = PREFETCH > 0 ? PREFETCH : 1;
   constexpr float kNegBig = -1.0e30f;
   constexpr float kLn2f = 0.6931471805599453f;
   const int64_t hq_stride = p.num_q_heads;
+  [[maybe_unused]] float vb[kBatch][kCols];
+  [[maybe_unused]] auto load_batch = [&](int s_first, int cnt) {  // partial rows s_first .. s_first + cnt - 1
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      if (u < cnt) {
+        const float *src = p.part_o + ((int64_t)(base + s_first + u) * hq_stride + hq) * D + lane * kCols;
+        if (kCols == 2) {
+          const float2 t = __ldcg(reinterpret_cast<const float2 *>(src));
+          vb[u][0] = t.x; vb[u][1] = t.y;
+        } else {
+#pragma unroll
+          for (int c = 0; c < kCols; c += 4) {
+            const float4 t = __ldcg(reinterpret_cast<const float4 *>(src + c));
+            vb[u][c] = t.x; vb[u][c + 1] = t.y; vb[u][c + 2] = t.z; vb[u][c + 3] = t.w;
+          }
+        }
+      }
+    }
+  };
+  if constexpr (PREFETCH > 0) load_batch(0, min(PREFETCH, ns));
   // pass 1: M = max_s m_s (lanes stride over the splits)
   float M = kNegBig;
   for (int s = lane; s < ns; s += 32) M = fmaxf(M, __ldcg(p.part_ml + ((int64_t)(base + s) * hq_stride + hq) * 2));
@@ -49,26 +77,43 @@ __device__ __forceinline__ void merge_row(const PaParams &p, int64_t row, int hq
       l_mine = ml.y;
     }
     const int cnt = min(32, ns - s0);
-    // 16 partial rows in flight per lane: the loop is a chain of L2 round trips otherwise
-#pragma unroll 16
-    for (int j = 0; j < cnt; ++j) {
-      const float f = __shfl_sync(0xffffffffu, f_mine, j);
-      const float lj = __shfl_sync(0xffffffffu, l_mine, j);
-      const float *src = p.part_o + ((int64_t)(base + s0 + j) * hq_stride + hq) * D + lane * kCols;
-      float v[kCols];
-      if (kCols == 2) {
-        const float2 t = __ldcg(reinterpret_cast<const float2 *>(src));
-        v[0] = t.x; v[1] = t.y;
-      } else {
+    if constexpr (PREFETCH > 0) {
+      for (int j0 = 0; j0 < cnt; j0 += PREFETCH) {
+        const int n = min(PREFETCH, cnt - j0);
+        if (s0 + j0 > 0) load_batch(s0 + j0, n);  // (the first batch is on its way since the start)
 #pragma unroll
-        for (int c = 0; c < kCols; c += 4) {
-          const float4 t = __ldcg(reinterpret_cast<const float4 *>(src + c));
-          v[c] = t.x; v[c + 1] = t.y; v[c + 2] = t.z; v[c + 3] = t.w;
+        for (int u = 0; u < kBatch; ++u) {
+          if (u < n) {  // warp-uniform
+            const float f = __shfl_sync(0xffffffffu, f_mine, j0 + u);
+            const float lj = __shfl_sync(0xffffffffu, l_mine, j0 + u);
+            L = fmaf(lj, f, L);
+#pragma unroll
+            for (int c = 0; c < kCols; ++c) acc[c] = fmaf(vb[u][c], f, acc[c]);
+          }
         }
       }
-      L = fmaf(lj, f, L);
+    } else {
+      // 16 partial rows in flight per lane: the loop is a chain of L2 round trips otherwise
+#pragma unroll 16
+      for (int j = 0; j < cnt; ++j) {
+        const float f = __shfl_sync(0xffffffffu, f_mine, j);
+        const float lj = __shfl_sync(0xffffffffu, l_mine, j);
+        const float *src = p.part_o + ((int64_t)(base + s0 + j) * hq_stride + hq) * D + lane * kCols;
+        float v[kCols];
+        if (kCols == 2) {
+          const float2 t = __ldcg(reinterpret_cast<const float2 *>(src));
+          v[0] = t.x; v[1] = t.y;
+        } else {
 #pragma unroll
-      for (int c = 0; c < kCols; ++c) acc[c] = fmaf(v[c], f, acc[c]);
+          for (int c = 0; c < kCols; c += 4) {
+            const float4 t = __ldcg(reinterpret_cast<const float4 *>(src + c));
+            v[c] = t.x; v[c + 1] = t.y; v[c + 2] = t.z; v[c + 3] = t.w;
+          }
+        }
+        L = fmaf(lj, f, L);
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) acc[c] = fmaf(v[c], f, acc[c]);
+      }
     }
   }
   const float inv = 1.f / L;
