@@ -50,33 +50,16 @@ rac_scatter16_kernel(const uint4 *__restrict__ key, const uint4 *__restrict__ va
   const int total = k16 + v16;  // K chunks then V chunks, one flat index space
   for (int64_t tok = (int64_t)blockIdx.x * kRacWarps + (threadIdx.x >> 5); tok < num_tokens; tok += nwarps) {
     const int64_t slot = __ldg(slot_mapping + tok);
-    const uint4 *ks = key + tok * k16;
-    const uint4 *vs = value + tok * v16;
-    // the first UNROLL chunks of the row are requested together with the slot, not behind it: for a
-    // decode step (a few dozen tokens) this kernel is two dependent round trips instead of three.
-    // Rows of padding tokens are readable memory; what was read for them is dropped.
-    uint4 r0[UNROLL];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int c = lane + 32 * u;
-      if (c < total) r0[u] = (c < k16) ? ld_stream16(ks + c) : ld_stream16(vs + (c - k16));
-    }
     if (slot < 0) continue;  // padding token: nothing is written
     if (slot >= num_slots) {
       if (lane == 0 && oob_count != nullptr) atomicAdd(oob_count, 1);
       continue;
     }
+    const uint4 *ks = key + tok * k16;
     uint4 *kd = key_cache + slot * k16;
+    const uint4 *vs = value + tok * v16;
     uint4 *vd = value_cache + slot * v16;
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int c = lane + 32 * u;
-      if (c < total) {
-        uint4 *dst = (c < k16) ? kd + c : vd + (c - k16);
-        if (CS) st_stream16(dst, r0[u]); else *dst = r0[u];
-      }
-    }
-    for (int c0 = lane + 32 * UNROLL; c0 < total; c0 += 32 * UNROLL) {
+    for (int c0 = lane; c0 < total; c0 += 32 * UNROLL) {
       uint4 r[UNROLL];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
