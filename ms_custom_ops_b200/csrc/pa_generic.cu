@@ -270,10 +270,10 @@ __device__ __forceinline__ void reduce_row(const PaParams &p, const PlanView &pv
 // row, merged here or written by the attention kernel, into slot `rank` of every rank's gathered
 // buffer; the block that finishes last then publishes the step's flag and waits (bounded) for the
 // peers, exactly as the stand-alone gather kernel does.
-// PF: how many partial rows a lane requests at a time (see merge_row).  32 for launches with rows of more
-// than 16 splits (long contexts; 190 registers), 16 when the grid still fits the SMs in one wave at the
-// 110 registers that costs, 0 (56 registers, loads inside the loop) for grids of thousands of rows, where
-// occupancy hides the latency better than prefetching does.
+// PF: how many partial rows a lane requests at a time (see merge_row).  0 (56 registers, loads inside the
+// loop) for grids of more than eight blocks per SM, where occupancy hides the latency better than
+// prefetching does; otherwise 32 for launches with rows of more than 16 splits (long contexts; 190
+// registers), and 16 when the grid fits the SMs in one wave at the 110 registers that costs.
 template <typename TQ, int PW, int PF>
 __global__ void __launch_bounds__(128)
 pa_reduce_kernel(PaParams p, const __grid_constant__ PlanParamT<PW> pp, const __grid_constant__ GatherArgs g) {
@@ -341,7 +341,7 @@ int launch_pa_reduce(const MscoPaPlan *plan, const PaParams &p, const PlanParam 
   cfg.numAttrs = 1;
   const bool f16 = plan->desc.q_dtype == MSCO_DTYPE_F16;
   const int blocks = (rows + 3) / 4;
-  const int pf = plan->max_splits > 16 ? 32 : (blocks <= 4 * plan->num_sms ? 16 : 0);
+  const int pf = blocks > 8 * plan->num_sms ? 0 : (plan->max_splits > 16 ? 32 : (blocks <= 4 * plan->num_sms ? 16 : 0));
 #define MSCO_RK(T, PW, PP)                                                                                 \
   do {                                                                                                    \
     if (pf == 32) MSCO_CUDA_CHECK(cudaLaunchKernelEx(&cfg, pa_reduce_kernel<T, PW, 32>, p, PP, g));       \
