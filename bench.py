@@ -52,7 +52,7 @@ UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 # (dram__bytes_read.sum + dram__bytes_write.sum) / (context tokens * kv heads) from the ncu captures
 # in profiles/: config 2 (16-bit KV, 512 algorithmic bytes) and config 3 (int8 KV, 256 algorithmic)
-NCU_DRAM_BYTES_PER_TOKEN_HEAD = {"16bit": 524.5, "int8": 265.4}
+NCU_DRAM_BYTES_PER_TOKEN_HEAD = {"16bit": 525.6, "int8": 266.0}
 L2_BYTES = 126 << 20
 
 
