@@ -360,7 +360,7 @@ def measure_decode(ctx, spec, args, full):
     peer = None
     if world > 1 and not args.nccl_gather:
         try:
-            peer = sharding.PeerGather(q.shape, q.dtype, dev)
+            peer = sharding.PeerGather(q.shape, q.dtype, dev, packets=not args.flag_exchange)
         except Exception as e:  # mapping a peer's memory may be refused: say so and fall back to NCCL
             print(f"peer all-gather unavailable ({e}); using NCCL", file=sys.stderr)
         ok = torch.tensor([1 if peer is not None else 0], device=dev)
@@ -482,7 +482,9 @@ def measure_decode(ctx, spec, args, full):
             "parallelism": f"kv-head sharding x{world}" + (
                 "" if world == 1 else (
                     (" + peer-store all-gather of outputs over NVLink"
-                     + (" from the kernel that finishes the output rows" if fused else " (a launch of its own)"))
+                     + ((" from the kernel that finishes the output rows, as 8-byte packets that carry their step number"
+                        if not args.flag_exchange else " from the kernel that finishes the output rows, fences + flags")
+                       if fused else " (a launch of its own)"))
                     if peer is not None else " + NCCL all-gather of outputs")),
             "l2": f"inputs larger than L2: {alg_bytes / 1e6:.0f} MB of KV per GPU per step vs {L2_BYTES >> 20} MB",
             "launch": "real decode loop: every step appends one token per sequence (context_lens + 1, slot_mapping "
@@ -1119,6 +1121,9 @@ def main():
     ap.add_argument("--configs", default="", help="comma-separated subset of the `configs` entries to run "
                     "(c3,c4,c5,c2h64,c2h256,rac_prefill,mtp4); default: all")
     ap.add_argument("--nccl-gather", action="store_true", help="exchange outputs with NCCL instead of peer stores")
+    ap.add_argument("--flag-exchange", action="store_true",
+                    help="N > 1: the step's own exchange uses fences and one flag per rank instead of 8-byte "
+                         "packets that carry their step number")
     ap.add_argument("--separate-gather", action="store_true",
                     help="N > 1: launch the peer-store all-gather as a kernel of its own behind the step instead "
                          "of from the step's finishing kernel")

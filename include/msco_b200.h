@@ -394,6 +394,13 @@ typedef struct MscoGatherDesc {
   uint32_t wait_polls;                /* polls (about 0.1 us apart) before the wait for a peer gives up and
                                          sets *status = MSCO_ERR_TIMEOUT; 0 = the default, 2^22 (about half a second) */
   uint32_t reserved;
+  void *packets[MSCO_MAX_PEERS];      /* optional (all NULL: not used).  packets[r]: rank r's packet buffer as
+                                         mapped in this process, 2 * world * slice_bytes bytes, zero before the first
+                                         step.  With it msco_decode_step_gather exchanges the rows as 8-byte packets
+                                         {4 data bytes, step}: the receiver sees a packet's data when it sees its step,
+                                         so the exchange needs no fence, no flag and no last block -- one NVLink
+                                         crossing instead of three; every thread copies the packets it waits for into
+                                         its own plain gathered buffer.  flags[] are not used then. */
 } MscoGatherDesc;
 int msco_ipc_export(const void *dev_ptr, unsigned char *handle /* [64] */, int64_t *offset);
 int msco_ipc_import(const unsigned char *handle, int64_t offset, void **dev_ptr);

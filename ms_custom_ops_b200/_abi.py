@@ -42,7 +42,8 @@ IPC_HANDLE_BYTES = 64
 class MscoGatherDesc(C.Structure):
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("gathered", C.c_void_p * MAX_PEERS),
                 ("flags", C.c_void_p * MAX_PEERS), ("slice_bytes", C.c_int64), ("ticket", C.c_void_p),
-                ("status", C.c_void_p), ("wait_polls", C.c_uint32), ("reserved", C.c_uint32)]
+                ("status", C.c_void_p), ("wait_polls", C.c_uint32), ("reserved", C.c_uint32),
+                ("packets", C.c_void_p * MAX_PEERS)]
 
 
 class MscoError(RuntimeError):

@@ -290,10 +290,28 @@ pa_reduce_kernel(PaParams p, const __grid_constant__ PlanParamT<PW> pp, const __
   const bool live = row < pv.batch * p.num_q_heads;
   if (live) reduce_row<TQ, PF>(p, pv, row, lane);
   if (g.world == 0) return;
+  const int64_t row_bytes = (int64_t)p.head_dim * (int64_t)sizeof(TQ);
+  const char *src = static_cast<const char *>(p.out) + row * row_bytes;
+  if (g.packets[0] != nullptr) {
+    // packet form: every lane sends its 16 bytes of the row to the peers (and stores them into its own
+    // gathered buffer), then waits for the same 16 bytes of every peer's row and copies them in.  No
+    // fence, no flag, no last block: a lane depends on nothing but the packets it waits for.
+    if (live) {
+      __syncwarp();  // the row was written by the lanes of this warp (or by the grid before us)
+      for (int64_t off = lane * 16; off < row_bytes; off += 32 * 16) {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(src + off));
+        *reinterpret_cast<uint4 *>(static_cast<char *>(g.gathered[g.rank]) + (int64_t)g.rank * g.slice_bytes +
+                                   row * row_bytes + off) = v;
+        packets_push16(g, row * row_bytes + off, v);
+      }
+      bool ok = true;
+      for (int64_t off = lane * 16; off < row_bytes; off += 32 * 16) ok = packets_pull16(g, row * row_bytes + off) && ok;
+      if (!ok) atomicExch(g.status, kStatusTimeout);  // a peer never sent: report, do not hang
+    }
+    return;
+  }
   if (live) {
     __syncwarp();  // the row was written by the lanes of this warp (or by the grid before us)
-    const int64_t row_bytes = (int64_t)p.head_dim * (int64_t)sizeof(TQ);
-    const char *src = static_cast<const char *>(p.out) + row * row_bytes;
     for (int64_t off = lane * 16; off < row_bytes; off += 32 * 16)
       gather_push16(g, row * row_bytes + off, __ldcg(reinterpret_cast<const uint4 *>(src + off)));
   }

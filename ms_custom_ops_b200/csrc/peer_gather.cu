@@ -105,6 +105,18 @@ int msco::fill_gather_args(const MscoGatherDesc *desc, uint32_t step, const char
     a.gathered[r] = desc->gathered[r];
     a.flags[r] = desc->flags[r];
   }
+  // the packet buffers: all of them or none
+  int with_packets = 0;
+  for (int r = 0; r < desc->world; ++r) with_packets += desc->packets[r] != nullptr ? 1 : 0;
+  if (with_packets != 0 && with_packets != desc->world)
+    return fail(MSCO_ERR_INVALID_ARG, "%s: packet buffers must be given for every rank or for none", what);
+  for (int r = 0; r < desc->world; ++r) {
+    if (reinterpret_cast<uintptr_t>(desc->packets[r]) & 15)
+      return fail(MSCO_ERR_INVALID_ARG, "%s: rank %d's packet buffer is not 16-byte aligned", what, r);
+    a.packets[r] = desc->packets[r];
+  }
+  if (with_packets != 0 && step == 0)
+    return fail(MSCO_ERR_INVALID_ARG, "%s: steps count from 1 (0 marks an empty packet)", what);
   a.slice_bytes = desc->slice_bytes;
   a.world = desc->world;
   a.rank = desc->rank;

@@ -23,6 +23,7 @@ struct GatherArgs {
   uint32_t step;
   unsigned int *ticket;             // local word: blocks of the grid that have pushed their part
   int32_t *status;                  // local word: kStatusTimeout when a peer never arrived
+  void *packets[MSCO_MAX_PEERS];    // rank r's packet buffer (2 x world x slice_bytes), or all NULL
 };
 
 // Checks a gather descriptor and copies it into kernel arguments; `what` names the caller in the error text.
@@ -41,6 +42,44 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
 __device__ __forceinline__ void gather_push16(const GatherArgs &a, int64_t off, const uint4 &v) {
   for (int r = 0; r < a.world; ++r)
     *reinterpret_cast<uint4 *>(static_cast<char *>(a.gathered[r]) + (int64_t)a.rank * a.slice_bytes + off) = v;
+}
+
+// ---- packet form of the exchange (GatherArgs::packets set) ----
+// 16 data bytes travel as four 8-byte packets {data word, step}, written with two 16-byte stores.  A
+// packet is valid when its step word equals the step waited for: data and validity arrive together, so the
+// sender needs no fence and publishes no flag.  (Stores of 8 aligned bytes are not torn; the two packets
+// of a 16-byte store may arrive apart, which is harmless.)
+__device__ __forceinline__ void packets_push16(const GatherArgs &a, int64_t off, const uint4 &v) {
+  const uint4 p0 = make_uint4(v.x, a.step, v.y, a.step), p1 = make_uint4(v.z, a.step, v.w, a.step);
+  for (int r = 0; r < a.world; ++r) {
+    if (r == a.rank) continue;
+    uint4 *dst = reinterpret_cast<uint4 *>(static_cast<char *>(a.packets[r]) + ((int64_t)a.rank * a.slice_bytes + off) * 2);
+    asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(p0.x), "r"(p0.y), "r"(p0.z), "r"(p0.w) : "memory");
+    asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst + 1), "r"(p1.x), "r"(p1.y), "r"(p1.z), "r"(p1.w) : "memory");
+  }
+}
+// Waits (bounded) for the 16 data bytes at byte offset `off` of every peer's slice in this rank's packet
+// buffer and copies them into this rank's plain gathered buffer.  Returns false when a peer never sent.
+__device__ __forceinline__ bool packets_pull16(const GatherArgs &a, int64_t off) {
+  bool all = true;
+  for (int r = 0; r < a.world; ++r) {
+    if (r == a.rank) continue;
+    const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const char *>(a.packets[a.rank]) +
+                                                       ((int64_t)r * a.slice_bytes + off) * 2);
+    uint4 p0, p1;
+    bool ok = false;
+    for (uint32_t it = 0; it < a.wait_limit; ++it) {
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(p0.x), "=r"(p0.y), "=r"(p0.z), "=r"(p0.w) : "l"(src) : "memory");
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(p1.x), "=r"(p1.y), "=r"(p1.z), "=r"(p1.w) : "l"(src + 1) : "memory");
+      if (p0.y == a.step && p0.w == a.step && p1.y == a.step && p1.w == a.step) { ok = true; break; }
+      __nanosleep(40);
+    }
+    if (ok)
+      *reinterpret_cast<uint4 *>(static_cast<char *>(a.gathered[a.rank]) + (int64_t)r * a.slice_bytes + off) =
+          make_uint4(p0.x, p0.z, p1.x, p1.z);
+    all = all && ok;
+  }
+  return all;
 }
 
 __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t *p) {

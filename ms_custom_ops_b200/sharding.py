@@ -200,7 +200,9 @@ class PeerGather:
         gathered = pg.gather(out_local)                                # [world, *out_local.shape]
     """
 
-    def __init__(self, slice_shape, dtype, device, group=None):
+    def __init__(self, slice_shape, dtype, device, group=None, packets=True):
+        """`packets=False`: msco_decode_step_gather then uses the flag protocol of msco_peer_allgather
+        (fences and a flag per rank) instead of the packet form."""
         import ctypes as C
 
         import torch
@@ -217,11 +219,14 @@ class PeerGather:
         if self.slice_bytes % 16:
             raise ValueError("slice size must be a multiple of 16 bytes")
         L = _abi.lib()
-        # one arena per rank, exported once: [gathered 0 | gathered 1 | flags 0 | flags 1], 256-byte aligned parts
+        # one arena per rank, exported once: [gathered 0 | gathered 1 | flags 0 | flags 1 | packets 0 | packets 1],
+        # 256-byte aligned parts; the packet buffers (twice the gathered size: every 4 data bytes travel with
+        # their step number) serve the decode step that does the exchange itself (msco_decode_step_gather)
         gbytes = self.world * self.slice_bytes
         goff = [0, (gbytes + 255) // 256 * 256]
         foff = [goff[1] * 2, goff[1] * 2 + 256]
-        self.arena = torch.zeros(foff[1] + 256, dtype=torch.uint8, device=device)
+        poff = [foff[1] + 256, foff[1] + 256 + 2 * goff[1]]
+        self.arena = torch.zeros(poff[1] + 2 * goff[1], dtype=torch.uint8, device=device)
         self.buffers = [self.arena[o:o + gbytes].view(dtype).view((self.world,) + self.slice_shape) for o in goff]
         self.words = torch.zeros(4, dtype=torch.int32, device=device)  # [ticket, status, -, -]
         torch.cuda.synchronize(device)
@@ -250,6 +255,8 @@ class PeerGather:
             for r in range(self.world):
                 d.gathered[r] = bases[r] + goff[parity]
                 d.flags[r] = bases[r] + foff[parity]
+                if packets:
+                    d.packets[r] = bases[r] + poff[parity]
             self.descs.append(d)
         self.step = 0
         dist.barrier(group=group)  # every rank has mapped every buffer before the first push

@@ -235,3 +235,86 @@ def test_decode_step_gather_on_two_gpus_matches_nccl():
             p.kill()
         assert p.exitcode == 0, "a rank failed or timed out"
     assert dict(ret) == {0: True, 1: True}
+
+
+def _packets_of(data_u8, step):
+    """Packet image of a byte tensor: every 4 data bytes followed by the step number (uint32)."""
+    words = data_u8.view(torch.int32).reshape(-1, 1)
+    return torch.cat([words, torch.full_like(words, step)], dim=1).reshape(-1).view(torch.uint8)
+
+
+@pytest.mark.parametrize("peer_sends", [True, False])
+def test_decode_step_gather_packet_form(peer_sends):
+    """The packet form of the exchange on one GPU standing in for rank 1 of two.  The absent rank 0's
+    packets are written by the test (or not at all: then the bounded wait must run out, the status word
+    must read MSCO_ERR_TIMEOUT and the context must stay usable).  What rank 1 sends must be the packet
+    image of its output in slot 1 of rank 0's packet buffer; its own gathered buffer must hold rank 0's
+    slice in slot 0 and its own output in slot 1."""
+    import ctypes as C
+
+    import numpy as np
+
+    from ms_custom_ops_b200 import _abi, kernels, workloads
+    dev = torch.device("cuda", 0)
+    lens = [700, 1500, 33, 0, 5000, 129]
+    spec = workloads.DecodeSpec("packets", len(lens), 8, kv_heads=2, seed=5, len_lo=1, len_hi=1)
+    rng = np.random.default_rng(3)
+    nb, tables, slots = workloads.layout(spec, np.array(lens, dtype=np.int32), rng)
+    g = torch.Generator(device=dev)
+    g.manual_seed(9)
+    kc = torch.randn((nb, 128, 2, 128), generator=g, device=dev).to(torch.bfloat16)
+    vc = torch.randn((nb, 128, 2, 128), generator=g, device=dev).to(torch.bfloat16)
+    q = torch.randn((len(lens), 8, 128), generator=g, device=dev).to(torch.bfloat16)
+    key = torch.randn((len(lens), 256), generator=g, device=dev).to(torch.bfloat16)
+    val = torch.randn((len(lens), 256), generator=g, device=dev).to(torch.bfloat16)
+    bt, sl = torch.from_numpy(tables).to(dev), torch.from_numpy(slots).to(dev)
+    desc = kernels.make_pa_desc(q, kc, bt, spec.qk_scale, 0)
+    plan = _abi.PaPlan(desc, [int(x) for x in lens])
+    ws = torch.empty(max(plan.workspace_bytes, 256), dtype=torch.uint8, device=dev)
+    want = torch.empty_like(q)
+    kernels.decode_step(plan, key, val, kc, vc, sl, q, bt, want, ws)
+    torch.cuda.synchronize()
+
+    slice_bytes = q.numel() * 2
+    gathered = [torch.zeros(2 * slice_bytes, dtype=torch.uint8, device=dev) for _ in range(2)]
+    flags = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in range(2)]
+    packets = [torch.zeros(4 * slice_bytes, dtype=torch.uint8, device=dev) for _ in range(2)]
+    words = torch.zeros(2, dtype=torch.int32, device=dev)
+    d = _abi.MscoGatherDesc()
+    d.world, d.rank, d.slice_bytes = 2, 1, slice_bytes
+    d.ticket, d.status = words.data_ptr(), words.data_ptr() + 4
+    d.wait_polls = 2000
+    for r in range(2):
+        d.gathered[r], d.flags[r], d.packets[r] = gathered[r].data_ptr(), flags[r].data_ptr(), packets[r].data_ptr()
+    step = 3
+    theirs = torch.randint(0, 256, (slice_bytes,), dtype=torch.uint8, device=dev, generator=g)
+    if peer_sends:
+        packets[1][:2 * slice_bytes] = _packets_of(theirs, step)   # rank 0's slice, slot 0 of MY packet buffer
+
+    class OneStep:
+        def next_step(self):
+            return C.byref(d), C.c_uint32(step), None
+    got = torch.empty_like(q)
+    kernels.decode_step(plan, key, val, kc, vc, sl, q, bt, got, ws, gather=OneStep())
+    torch.cuda.synchronize()
+    kernels.pa_status(plan, ws)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    mine = got.view(torch.uint8).reshape(-1)
+    # what was sent: slot 1 of rank 0's packet buffer is the packet image of my output
+    assert torch.equal(packets[0][2 * slice_bytes:], _packets_of(mine, step))
+    assert int(packets[0][:2 * slice_bytes].max().item()) == 0
+    assert torch.equal(gathered[1][slice_bytes:], mine)          # my own slot, stored directly
+    assert int(flags[0].abs().max().item()) == 0 and int(flags[1].abs().max().item()) == 0  # no flags in this form
+    if peer_sends:
+        assert int(words[1].item()) == 0
+        assert torch.equal(gathered[1][:slice_bytes], theirs)
+    else:
+        assert int(words[1].item()) == _abi.ERR_TIMEOUT          # nobody sent: reported, not hung
+        words.zero_()
+        packets[1][:2 * slice_bytes] = _packets_of(theirs, step + 1)
+        step += 1                                                # the context is alive: the next step completes
+        kernels.decode_step(plan, key, val, kc, vc, sl, q, bt, got, ws, gather=OneStep())
+        torch.cuda.synchronize()
+        assert int(words[1].item()) == 0
+        assert torch.equal(gathered[1][:slice_bytes], theirs)
+    plan.close()
