@@ -96,6 +96,8 @@ def test_multi_token_oracle_matches_reference_golden(name):
     np.testing.assert_allclose(out, g, rtol=0, atol=5e-4 if c["q_dtype"] == "float16" else 1e-6)
     # the mask is causal inside the window of new tokens: the last token of a sequence sees everything,
     # so it equals plain decode attention over the same context
+    if int(np.sum(c["context_lens"])) > 40000:
+        return  # (the long fixtures: the numpy golden above is a minute of CPU time already)
     last = np.cumsum(c["q_seq_lens"]) - 1
     plain = oracle.paged_attention_golden(c["query"][last], c["key_cache"], c["value_cache"], c["block_tables"],
                                           c["context_lens"], c["qk_scale"])
