@@ -397,6 +397,30 @@ def measure_decode(ctx, spec, args, full):
     for _ in range(W):
         step()
     loop.kernels.pa_status(loop.plan, loop.ws)
+    packet_form = fused and not args.flag_exchange
+    if packet_form:
+        # the packet form of the exchange is checked against NCCL before anything is timed; should it
+        # disagree or time out on some rank, every rank goes over to the flag form together
+        ok = 1
+        try:
+            mine = step()
+            torch.cuda.synchronize()
+            peer.check()
+            sharding.all_gather_outputs(loop.out_local, gathered)
+            torch.cuda.synchronize()
+            ok = int(torch.equal(mine.view(torch.int16), gathered.view(torch.int16)))
+        except Exception as e:  # noqa: BLE001 -- reported below, the run goes on with the other form
+            print(f"packet exchange failed its check on rank {rank}: {e}", file=sys.stderr)
+            ok = 0
+        t_ok = torch.tensor([ok], device=dev)
+        dist.all_reduce(t_ok, op=dist.ReduceOp.MIN)
+        if int(t_ok.item()) == 0:
+            if rank == 0:
+                print("packet exchange did not pass its check: using fences + flags", file=sys.stderr)
+            peer.release()
+            peer = sharding.PeerGather(q.shape, q.dtype, dev, packets=False)
+            packet_form = False
+            step()
     # clocks are sampled from the start of the device-timed region to the end of the end-to-end region
     sampler = None
     if rank == 0 and full:
@@ -483,7 +507,7 @@ def measure_decode(ctx, spec, args, full):
                 "" if world == 1 else (
                     (" + peer-store all-gather of outputs over NVLink"
                      + ((" from the kernel that finishes the output rows, as 8-byte packets that carry their step number"
-                        if not args.flag_exchange else " from the kernel that finishes the output rows, fences + flags")
+                        if packet_form else " from the kernel that finishes the output rows, fences + flags")
                        if fused else " (a launch of its own)"))
                     if peer is not None else " + NCCL all-gather of outputs")),
             "l2": f"inputs larger than L2: {alg_bytes / 1e6:.0f} MB of KV per GPU per step vs {L2_BYTES >> 20} MB",
